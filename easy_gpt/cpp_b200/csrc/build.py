@@ -1,0 +1,115 @@
+"""Builds the CUDA kernels into one shared library, in the tree, at first use.
+
+Each ``.cu`` file is compiled by nvcc for sm_100a into ``_build/<name>.o`` and
+the objects are linked into ``libeasygpt_kernels.so`` beside this file.  A stamp
+records the hash of the sources and the flags, so a stale library is rebuilt
+and a current one is loaded as it is.  If the tree is not writable, the build
+goes to a per-user folder under the system's temporary directory.  A line is
+printed to stderr for every file, so that a first call does not look hung.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_NAME = "libeasygpt_kernels.so"
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _sources():
+    return sorted(HERE.glob("*.cu"))
+
+
+def _fingerprint() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list(HERE.glob("*.cu")) + list(HERE.glob("*.cuh"))):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise BuildError("nvcc was not found (set NVCC or put it on PATH); the CUDA kernels cannot be built")
+
+
+def _writable(folder: Path) -> bool:
+    try:
+        folder.mkdir(parents=True, exist_ok=True)
+        probe = folder / f".probe_{os.getpid()}"
+        probe.write_text("")
+        probe.unlink()
+        return True
+    except OSError:
+        return False
+
+
+def _current(lib: Path, stamp: Path, fp: str) -> bool:
+    try:
+        return lib.is_file() and json.loads(stamp.read_text()).get("fingerprint") == fp
+    except (OSError, ValueError):
+        return False
+
+
+def library_path(verbose: bool = True) -> Path:
+    """Path of an up-to-date kernel library, building it if need be."""
+    fp = _fingerprint()
+    in_tree = (HERE / LIB_NAME, HERE / "_build" / "stamp.json")
+    if _current(*in_tree, fp):
+        return in_tree[0]
+    if _writable(HERE / "_build") and _writable(HERE):
+        out_dir, build_dir = HERE, HERE / "_build"
+    else:
+        base = Path(tempfile.gettempdir()) / f"easy_gpt_b200_build_{os.getuid()}"
+        out_dir, build_dir = base, base / "_build"
+        build_dir.mkdir(parents=True, exist_ok=True)
+        if _current(out_dir / LIB_NAME, build_dir / "stamp.json", fp):
+            return out_dir / LIB_NAME
+    nvcc = _nvcc()
+    sources = _sources()
+
+    def say(msg):
+        if verbose:
+            print(f"[easy_gpt.cpp_b200] {msg}", file=sys.stderr, flush=True)
+
+    say(f"building {len(sources)} CUDA files for sm_100a into {out_dir} (first call only)")
+
+    def compile_one(src: Path) -> str:
+        obj = build_dir / (src.stem + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise BuildError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")
+        say(f"compiled {src.name}")
+        return str(obj)
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        objects = list(pool.map(compile_one, sources))
+    tmp_lib = out_dir / (LIB_NAME + f".{os.getpid()}.tmp")
+    r = subprocess.run([nvcc, "-shared", "-o", str(tmp_lib), *objects, "-lcuda"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp_lib, out_dir / LIB_NAME)
+    (build_dir / "stamp.json").write_text(json.dumps({"fingerprint": fp}))
+    say(f"built {out_dir / LIB_NAME}")
+    return out_dir / LIB_NAME
+
+
+if __name__ == "__main__":
+    print(library_path())

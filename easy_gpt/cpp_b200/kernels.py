@@ -1,0 +1,213 @@
+"""Python face of the hand-written CUDA kernels (``csrc/*.cu``).
+
+The kernels are plain ``extern "C"`` launchers in one shared library built by
+``csrc/build.py``; they are called through ctypes with raw device pointers and
+the current torch stream, so they are captured by CUDA graphs like any other
+launch.  There is no other implementation behind these functions: if the
+library cannot be built or loaded, importing it raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc.build import library_path
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BITS = {1: "a token id lies outside the vocabulary",
+               2: "a block table entry needed by attention is not a valid page",
+               4: "a cache write position lies outside the pool",
+               8: "a bounded wait inside a kernel gave up"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+_lib = None
+launch_count = 0     # number of kernel launches issued through this module (for the bench's gpu_launches)
+
+
+def library() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = library_path()
+        try:
+            _lib = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
+        for name in dir(_Signatures):
+            if name.startswith("eg_"):
+                fn = getattr(_lib, name)
+                fn.argtypes = getattr(_Signatures, name)
+                fn.restype = c_int
+    return _lib
+
+
+class _Signatures:
+    eg_embedding_gather = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    eg_add_rmsnorm = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float]
+    eg_gemm_f32_nt = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int]
+    eg_rope_cache = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
+    eg_attention_generic = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
+                            c_float, c_void_p]
+    eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
+    eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}" + (" (a size this kernel does not take)" if code == 1 else ""))
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+def embedding_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, status: torch.Tensor) -> None:
+    """residual[t] = float32(table[ids[t]]); a bad id sets a status bit."""
+    _cuda(ids, table, residual, status)
+    _need(ids.dtype == torch.int32 and residual.dtype == torch.float32, "ids int32, residual float32")
+    _need(table.is_contiguous() and residual.is_contiguous(), "contiguous table and residual")
+    T, (V, H) = ids.numel(), table.shape
+    _need(residual.shape[-1] == H and residual.numel() >= T * H, "residual too small")
+    _check(library().eg_embedding_gather(_stream(), dtype_code(table.dtype), _ptr(ids), _ptr(table), _ptr(residual),
+                                         T, H, V, _ptr(status)), "embedding_gather")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """residual += delta (if given, and rows is None); out = rmsnorm(residual) * gain.
+    With rows: out[r] is computed from row rows[r] and the residual is not written."""
+    _cuda(residual, delta, gain, out, rows)
+    H = residual.shape[-1]
+    _need(residual.dtype == torch.float32 and gain.dtype == torch.float32, "residual and gain are float32")
+    _need(residual.is_contiguous() and out.is_contiguous() and (delta is None or delta.is_contiguous()), "contiguous rows")
+    _need(gain.numel() == H and out.shape[-1] == H and (delta is None or delta.shape[-1] == H), "width mismatch")
+    n = rows.numel() if rows is not None else residual.numel() // H
+    _need(out.numel() >= n * H, "out too small")
+    if rows is not None:
+        _need(rows.dtype == torch.int32, "rows int32")
+    dd = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    _check(library().eg_add_rmsnorm(_stream(), dd, dtype_code(out.dtype), _ptr(residual), _ptr(delta), _ptr(rows),
+                                    _ptr(gain), _ptr(out), n, H, float(eps)), "add_rmsnorm")
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T + bias, all float32, true 32-bit arithmetic."""
+    _cuda(a, w, bias, out)
+    _need(a.dtype == w.dtype == out.dtype == torch.float32, "float32 only")
+    _need(a.dim() == 2 and w.dim() == 2 and out.dim() == 2, "matrices")
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape[0] == M and out.shape[1] == N, "shape mismatch")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "unit inner strides")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N, "bias float32 [N]")
+    _check(library().eg_gemm_f32_nt(_stream(), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                    out.stride(0), M, N, K), "gemm_f32_nt")
+
+
+def rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+               slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+               inv_freq: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+               page_size: int, status: torch.Tensor) -> None:
+    """Rotates q and k of qkv [T, (NH+2NKV)*HD] (q in place) and stores k, v at
+    slot_map[t] of caches shaped [pages, NKV, page_size, HD] (slices of one pool)."""
+    _cuda(qkv, bias, positions, slot_map, k_cache, v_cache, inv_freq, status)
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qkv row layout")
+    _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float32, "positions int32, inv_freq float32")
+    _need(inv_freq.numel() * 2 == rotary_dim, "inv_freq has rotary_dim/2 entries")
+    page_stride = head_stride = pool_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None and slot_map.dtype == torch.int32, "cache and int32 slot map")
+        _need(k_cache.dtype == qkv.dtype == v_cache.dtype, "cache dtype equals activation dtype")
+        _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.shape == v_cache.shape,
+              "cache shape [pages, NKV, page_size, HD]")
+        _need(k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim and k_cache.stride() == v_cache.stride(),
+              "cache strides")
+        page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
+        pool_slots = k_cache.shape[0] * page_size
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == qkv.shape[1], "bias float32 over the whole row")
+    _check(library().eg_rope_cache(_stream(), dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(positions),
+                                   _ptr(slot_map), _ptr(k_cache), _ptr(v_cache), _ptr(inv_freq), T, num_heads,
+                                   num_kv_heads, head_dim, rotary_dim, page_size, page_stride, head_stride, pool_slots,
+                                   _ptr(status)), "rope_cache")
+
+
+def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
+                      status: torch.Tensor) -> None:
+    """q: [T, >=NH*HD] rows (a view into the qkv buffer is fine); out [T, NH*HD]."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status)
+    T = q.shape[0]
+    _need(head_dim <= 256, f"attention_generic takes head sizes up to 256, not {head_dim}")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype, "q/out/cache layout")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1, "block table")
+    _need(token_seq.dtype == torch.int32 and positions.dtype == torch.int32, "int32 metadata")
+    page_size = k_cache.shape[2]
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.stride() == v_cache.stride()
+          and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim, "cache shape [pages, NKV, page_size, HD]")
+    _check(library().eg_attention_generic(
+        _stream(), dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+        block_table.stride(0), _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads, num_kv_heads,
+        head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
+        _ptr(status)), "attention_generic")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = up * silu(gate) for rows laid out [gate (I) | up (I)]."""
+    _cuda(gate_up, out)
+    T, two_i = gate_up.shape
+    inter = two_i // 2
+    _need(two_i == 2 * inter and out.shape == (T, inter) and gate_up.dtype == out.dtype, "swiglu shapes")
+    _need(gate_up.stride(1) == 1 and out.stride(1) == 1, "unit inner strides")
+    _check(library().eg_swiglu(_stream(), dtype_code(out.dtype), _ptr(gate_up), gate_up.stride(0), _ptr(out),
+                               out.stride(0), T, inter), "swiglu")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = lowest index of the maximum of logits[r, :] (float32 rows)."""
+    _cuda(logits, out)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "float32 rows")
+    _need(out.dtype == torch.int32 and out.numel() >= logits.shape[0], "int32 out")
+    _check(library().eg_argmax(_stream(), _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out)),
+           "argmax")
+
+
+def describe_status(word: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "ok"

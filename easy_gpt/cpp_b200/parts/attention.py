@@ -1,0 +1,94 @@
+"""Grouped-query attention over the paged cache.
+
+Per token: q, k, v = x Wq^T + bq, ... (src/models/self_attn.cpp:225-227) as ONE
+product with the three weights stacked; q and k are rotated and k, v stored in
+the cache by one kernel; every query head h attends the keys of KV head
+h / (NH/NKV) of its own request up to its own position (optionally only the last
+``window`` of them); the heads are concatenated head-major and projected by Wo
+(src/models/self_attn.cpp:255-258).  Scale 1/sqrt(head_dim) (:253).
+
+Parameters: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, out_bias,
+window (None = all keys).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..registry import register_part
+from ..weights.loader import TensorRequest
+from .base import CacheView, Mixer, PagedKVNeed, StepContext
+from .linear import Linear
+
+
+class Attention(Mixer):
+    def __init__(self, params, prefix, position=None):
+        super().__init__(params, prefix, position)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.out_bias = bool(p.get("out_bias", False))
+        self.window = p.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.window is not None and self.window <= 0:
+            raise ValueError("window must be positive")
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        self.qkv = self.out = None
+
+    # -- weights ----------------------------------------------------------
+    def tensor_requests(self):
+        q_out, kv_out = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        reqs = [TensorRequest.matrix(f"{self.prefix}.q_proj.weight", q_out, self.hidden),
+                TensorRequest.matrix(f"{self.prefix}.k_proj.weight", kv_out, self.hidden),
+                TensorRequest.matrix(f"{self.prefix}.v_proj.weight", kv_out, self.hidden),
+                TensorRequest.matrix(f"{self.prefix}.o_proj.weight", self.hidden, q_out)]
+        if self.qkv_bias:
+            reqs += [TensorRequest.vector(f"{self.prefix}.q_proj.bias", q_out),
+                     TensorRequest.vector(f"{self.prefix}.k_proj.bias", kv_out),
+                     TensorRequest.vector(f"{self.prefix}.v_proj.bias", kv_out)]
+        if self.out_bias:
+            reqs.append(TensorRequest.vector(f"{self.prefix}.o_proj.bias", self.hidden))
+        return reqs
+
+    def load(self, tensors, device, dtype):
+        names = [f"{self.prefix}.{n}_proj" for n in "qkv"]
+        w = torch.cat([tensors[n + ".weight"].float() for n in names], dim=0)
+        b = torch.cat([tensors[n + ".bias"].float().reshape(-1) for n in names]) if self.qkv_bias else None
+        self.qkv = Linear(w, b, device, dtype)
+        self.out = Linear(tensors[f"{self.prefix}.o_proj.weight"],
+                          tensors.get(f"{self.prefix}.o_proj.bias") if self.out_bias else None, device, dtype)
+        if self.position is not None:
+            self.position.load(tensors, device, dtype)
+
+    def weight_bytes(self):
+        return self.qkv.weight_bytes() + self.out.weight_bytes()
+
+    # -- cache ------------------------------------------------------------
+    def cache_need(self):
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    # -- forward ----------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        T = x.shape[0]
+        tables = ctx.groups[cache.group]
+        qkv = self.qkv(x)
+        rot = self.position
+        if rot is None:
+            raise NotImplementedError("attention without a rotary encoding is not built")
+        kernels.rope_cache(qkv, None, ctx.positions, tables.slot_map if cache.writes else None,
+                           cache.k if cache.writes else None, cache.v if cache.writes else None,
+                           rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
+                           tables.page_size, ctx.status)
+        attn = torch.empty((T, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
+        kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
+                                  self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status)
+        return self.out(attn)
+
+
+register_part("mixer", "attention", Attention)

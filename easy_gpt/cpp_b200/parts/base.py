@@ -1,0 +1,142 @@
+"""Interfaces of the parts a layer is put together from.
+
+A *mixer* moves information between the tokens of a request (attention here);
+a *feed-forward* works on each token alone; a *norm* normalises the residual
+stream; a *position encoding* is handed to the mixer that wants one.  Every part
+is built from ``PartSpec.params`` (its sizes and constants) and ``prefix`` (where
+its tensors live) and never learns which model it sits in.
+
+The residual stream is float32 in both precisions.  A block hands each part the
+normalised input in the compute dtype and gets back a *delta* in the compute
+dtype; the next norm adds the delta to the residual in float32 while it
+normalises (one fused kernel).
+
+To add a part: subclass the matching base, implement ``tensor_requests``,
+``load`` and ``forward`` (and ``cache_need`` for a mixer that keeps something per
+request), and ``register_part(role, kind, cls)``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..weights.loader import TensorRequest
+
+
+# ---------------------------------------------------------------------------
+# what a mixer needs the cache manager to keep for it
+# ---------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values of every token (or of the last ``window`` tokens) in pages."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A tensor of fixed shape per live request (float32), zeroed when a request starts."""
+    shape: Tuple[int, ...]
+
+
+# ---------------------------------------------------------------------------
+# what a step hands to the parts
+# ---------------------------------------------------------------------------
+
+@dataclass
+class GroupTables:
+    """Cache addressing of one cache group for this step."""
+    page_size: int
+    block_table: torch.Tensor      # int32 [num_seqs, max_pages]: page id per logical page, -1 where none
+    slot_map: torch.Tensor         # int32 [T]: page * page_size + offset where the token's key/value is stored
+
+
+@dataclass
+class StepContext:
+    """Everything about one step's batch that a part may need.  All tensors are on
+    the device; the ``host_*`` twins are Python lists for parts (and tests) that
+    plan their launches on the host."""
+    dtype: torch.dtype
+    device: torch.device
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor        # int32 [T]
+    positions: torch.Tensor        # int32 [T] absolute position of each token in its request
+    token_seq: torch.Tensor        # int32 [T] which entry of the batch the token belongs to
+    seq_starts: torch.Tensor       # int32 [num_seqs + 1] prefix sums of the entries' token counts
+    seq_context: torch.Tensor      # int32 [num_seqs] tokens of the request already cached before this step
+    seq_slots: torch.Tensor        # int32 [num_seqs] state slot of each entry's request
+    status: torch.Tensor           # int32 [1] device status word the kernels OR their complaints into
+    groups: Dict[int, GroupTables] = field(default_factory=dict)
+    host_seq_starts: List[int] = field(default_factory=list)
+    host_seq_context: List[int] = field(default_factory=list)
+    host_seq_slots: List[int] = field(default_factory=list)
+    max_query_len: int = 0
+    max_context_len: int = 0       # longest context + query of the batch
+    all_decode: bool = False       # every entry brings exactly one token
+
+
+@dataclass
+class CacheView:
+    """What the cache manager gives a mixer for one run entry."""
+    group: int = -1                           # key into StepContext.groups (paged) ...
+    k: Optional[torch.Tensor] = None          # [pages, NKV, page_size, HD] slice of the pool for this cache
+    v: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None      # [max_slots, *StateNeed.shape] for a mixer with fixed-size state
+    writes: bool = True                       # False: read another entry's cache, store nothing
+
+
+# ---------------------------------------------------------------------------
+# the parts
+# ---------------------------------------------------------------------------
+
+class Part:
+    def __init__(self, params: Mapping, prefix: str):
+        self.params = dict(params)
+        self.prefix = prefix
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return []
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device: torch.device, dtype: torch.dtype) -> None:
+        """Take this part's tensors (host, stored precision) to the device in the form its kernels want."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one forward reads (for roofline arithmetic)."""
+        return 0
+
+
+class PositionEncoding(Part):
+    """Built once per layer; the mixer calls whatever its kind offers."""
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual += delta (float32, in place, unless rows is given); returns the
+        normalised rows in ``out`` (compute dtype).  With ``rows`` only those rows
+        are normalised, into out[:len(rows)], and the residual is left as it is."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def __init__(self, params: Mapping, prefix: str, position: Optional[PositionEncoding] = None):
+        super().__init__(params, prefix)
+        self.position = position
+
+    def cache_need(self):
+        """PagedKVNeed, StateNeed or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        """x [T, hidden] normalised input -> delta [T, hidden], both in ctx.dtype."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError

@@ -1,0 +1,65 @@
+"""Token embedding and the output head.
+
+Embedding: residual[t] = E[id[t]] (src/models/embedding.cpp:54-76).  Head:
+logits = x E^T when tied (the reference always is, src/models/gpt_model.cpp:324-328,
+src/models/embedding.cpp:78-81) or x W_head^T with ``lm_head.weight`` when not.
+Logits are float32 in both precisions.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..registry import register_part
+from ..weights.loader import TensorRequest
+from .base import Part
+from .linear import Linear
+
+
+class TokenEmbedding(Part):
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.table = None
+
+    def tensor_requests(self):
+        return [TensorRequest.matrix(self.prefix + ".weight", self.vocab, self.hidden)]
+
+    def load(self, tensors, device, dtype):
+        self.table = tensors[self.prefix + ".weight"].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, token_ids, residual, status):
+        kernels.embedding_gather(token_ids, self.table, residual, status)
+
+
+class LMHead(Part):
+    """params: vocab_size, hidden_size, tied_to (prefix of the embedding, or None)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.tied_to = params.get("tied_to")
+        self.linear = None
+
+    def tensor_requests(self):
+        if self.tied_to:
+            return []
+        return [TensorRequest.matrix(self.prefix + ".weight", self.vocab, self.hidden)]
+
+    def load(self, tensors, device, dtype, tied_table=None):
+        if self.tied_to:
+            self.linear = Linear.sharing(tied_table)
+        else:
+            self.linear = Linear(tensors[self.prefix + ".weight"], None, device, dtype)
+
+    def weight_bytes(self):
+        return self.linear.weight_bytes()
+
+    def forward(self, x):
+        return self.linear(x, out_dtype=torch.float32)
+
+
+register_part("head", "embedding", TokenEmbedding)
+register_part("head", "lm_head", LMHead)

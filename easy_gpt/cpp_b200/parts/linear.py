@@ -1,0 +1,53 @@
+"""y = x W^T + b with W stored [out, in] (src/models/linear.cpp:42-44).
+
+In bfloat16 the product goes to the library GEMM (cuBLAS through torch), where
+the reference's engine calls cublasGemmEx too (src/cuda/ops/matmul.cu:194-204),
+unless a hand-written kernel takes the shape.  In float32 it is always the
+package's own FFMA kernel: true 32-bit arithmetic whose sums do not depend on
+the batch.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], device, dtype: torch.dtype):
+        self.weight = weight.to(device=device, dtype=dtype).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        self.dtype = dtype
+        # the bias is added in float32 by our kernels; the library GEMM wants it in its own dtype
+        self.bias_f32 = None if bias is None else bias.to(device=device, dtype=torch.float32).reshape(-1).contiguous()
+        self.bias = None if bias is None else self.bias_f32.to(dtype)
+
+    @classmethod
+    def sharing(cls, weight: torch.Tensor) -> "Linear":
+        """A bias-free product with a weight that another part owns (a tied head
+        multiplies by the embedding table itself, not by a copy)."""
+        self = cls.__new__(cls)
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+        self.dtype = weight.dtype
+        self.bias = self.bias_f32 = None
+        return self
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        M = x.shape[0]
+        out_dtype = out_dtype or self.dtype
+        if self.dtype == torch.float32:
+            out = torch.empty((M, self.out_features), device=x.device, dtype=torch.float32)
+            kernels.gemm_f32_nt(x, self.weight, self.bias_f32, out)
+            return out
+        if out_dtype == torch.float32:
+            out = torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+            if self.bias_f32 is not None:
+                out += self.bias_f32
+            return out
+        return torch.nn.functional.linear(x, self.weight, self.bias)

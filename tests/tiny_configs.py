@@ -1,0 +1,52 @@
+"""Two tiny configurations of the architecture that differ in every size and
+option, and helpers that write them as model folders with random weights."""
+import json
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+# A: 2 layers, 4 heads in 2 groups, head size 16, tied head, eps 1e-6, theta 1e4, all keys everywhere
+CONFIG_A = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "intermediate_size": 160, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 1024, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_A = dict(seed=0, std=0.08, bias_std=0.08, gain_std=0.0)
+
+# B: 3 layers, 6 heads in 2 groups of 3, head size 32 given by its own key (6*32 != 80), width and
+# vocabulary that are no powers of two, untied head, eps 1e-5, theta 1e6, a window of 24 from layer 1 on
+CONFIG_B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 80, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32,
+    "intermediate_size": 208, "vocab_size": 391, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 2048, "bos_token_id": -1, "eos_token_id": 7,
+    "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 1,
+}
+RANDOM_B = dict(seed=3, std=0.07, bias_std=0.1, gain_std=0.1)
+
+# C: one KV head, head size 64, no biases at all, window on every layer
+CONFIG_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 112, "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 64,
+    "intermediate_size": 144, "vocab_size": 203, "rope_theta": 50000.0, "rms_norm_eps": 3e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 4096, "attention_bias": False,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 0,
+}
+RANDOM_C = dict(seed=5, std=0.06, bias_std=0.0, gain_std=0.05)
+
+CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C)}
+
+
+def write_tiny(name: str, folder=None, store_dtype="float32") -> Path:
+    from easy_gpt.cpp_b200.weights.random_init import write_random_model
+
+    cfg, rnd = CONFIGS[name]
+    folder = Path(folder or tempfile.mkdtemp(prefix=f"tiny_{name}_"))
+    return write_random_model(folder, cfg, store_dtype=store_dtype, **rnd)
+
+
+def random_tokens(vocab: int, n: int, seed: int):
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
