@@ -1,0 +1,105 @@
+"""GptEngine: the Python entry point.  Token ids in, token ids out.
+
+It mirrors the reference's ``GptEngine::run`` (src/gpt_engine.cpp:33-43): add the
+inputs, run the model until every request has ended, hand back the outputs — but
+through the scheduler and the one step function, on the device.
+"""
+from __future__ import annotations
+
+import json
+import tempfile
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .model import Model
+from .scheduler import Request, Scheduler, SchedulerOptions
+from .step import StepEntry, StepRunner
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def max_new_tokens_from_max_steps(max_steps: int, prompt_len: int) -> int:
+    """--max-steps caps prompt + generated tokens; at least one token is generated
+    (src/continuous_batch_server.cpp:313)."""
+    return max(1, max_steps - prompt_len + 1)
+
+
+class GptEngine:
+    def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                 cache_tokens: Optional[int] = None, max_active: int = 16, prefill_batch: int = 4,
+                 max_batch_tokens: int = 2048, chunk_size: int = 512, max_tokens_per_request: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("GptEngine needs a CUDA device; there is no CPU path")
+        torch_dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
+        self.model = Model.from_dir(model_dir, device=device, dtype=torch_dtype)
+        spec = self.model.spec
+        if cache_tokens is None:
+            cache_tokens = max_active * min(spec.max_positions, 4096)
+        num_pages = -(-cache_tokens // page_size)
+        self.runner = StepRunner(self.model, page_size, num_pages, max_slots=max_active,
+                                 max_tokens_per_request=max_tokens_per_request or min(spec.max_positions, num_pages * page_size))
+        self.scheduler = Scheduler(self.runner.cache, SchedulerOptions(
+            max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, max_active=max_active, prefill_batch=prefill_batch,
+            eos_token_id=spec.eos_token_id, max_positions=spec.max_positions))
+        self.sampler = Sampler(self.model.device, max_rows=max_active)
+
+    # -- requests -------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    max_new_tokens: Optional[int] = None, max_steps: Optional[int] = None) -> Request:
+        params = params or SamplingParams()
+        if max_new_tokens is None:
+            max_new_tokens = max_new_tokens_from_max_steps(max_steps if max_steps is not None else 100, len(prompt))
+        vocab = self.model.spec.vocab_size
+        for t in prompt:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        return self.scheduler.add(prompt, params, max_new_tokens)
+
+    def step(self) -> List[Request]:
+        """One scheduler round and one model step.  Returns the requests that finished."""
+        batch = self.scheduler.schedule()
+        if not batch:
+            return []
+        entries = [StepEntry(s.request.id, s.request.tokens[s.start:s.start + s.count],
+                             [s.count - 1] if s.samples else []) for s in batch]
+        logits = self.runner.run(entries, check=False, commit=False)
+        sampling = [s for s in batch if s.samples]
+        tokens: List[int] = []
+        if sampling:
+            dev = self.sampler.sample(logits, [s.request.params for s in sampling], [s.request.id for s in sampling],
+                                      [len(s.request.output) for s in sampling])
+            tokens = self.sampler.to_host(dev)
+        return self.scheduler.update(batch, tokens)
+
+    def run_to_completion(self) -> None:
+        while self.scheduler.has_work():
+            before = self.scheduler.stats.steps
+            self.step()
+            if self.scheduler.stats.steps == before and self.scheduler.has_work():
+                raise RuntimeError("the scheduler made no progress although requests are waiting")
+        self.runner.check_status()
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None,
+                 max_steps: Optional[int] = None, temperature: float = 0.8, top_p: float = 0.95, top_k: int = 20,
+                 seed: int = 42, greedy: bool = False) -> List[List[int]]:
+        """Generates for every prompt (lists of token ids) and returns the new tokens of each."""
+        params = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, seed=seed, greedy=greedy)
+        requests = [self.add_request(p, params, max_new_tokens, max_steps) for p in prompts]
+        self.run_to_completion()
+        for r in requests:
+            if r.error:
+                raise RuntimeError(f"request {r.id}: {r.error}")
+        return [list(r.output) for r in requests]
+
+
+def engine_with_random_weights(config: dict, seed: int, folder=None, store_dtype="bfloat16", **engine_options) -> GptEngine:
+    """Writes a model folder with random weights for ``config`` and opens an engine on it."""
+    from ..weights.random_init import write_random_model
+
+    folder = Path(folder or tempfile.mkdtemp(prefix="easy_gpt_random_"))
+    write_random_model(folder, config, seed, store_dtype=store_dtype)
+    return GptEngine(folder, **engine_options)

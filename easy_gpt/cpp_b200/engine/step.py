@@ -180,14 +180,17 @@ class StepRunner:
         )
         return ctx, (view("logit_rows") if R else None)
 
-    def run(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
+    def run(self, entries: Sequence[StepEntry], check: bool = True, commit: bool = True) -> Optional[torch.Tensor]:
         """Logits [wanted, vocab] float32 on the device (None if nothing is wanted).
         With ``check`` the device status word is read back (a synchronisation) and
-        a complaint of a kernel becomes an exception."""
+        a complaint of a kernel becomes an exception.  With ``commit`` the requests'
+        cached lengths advance here; a scheduler that keeps its own count passes False
+        and calls ``cache.commit`` itself."""
         ctx, rows = self.build_context(entries)
         logits = self.model.forward(ctx, self.cache, rows)
-        for e in entries:
-            self.cache.commit(e.request, len(e.tokens))
+        if commit:
+            for e in entries:
+                self.cache.commit(e.request, len(e.tokens))
         self.steps_run += 1
         if check:
             self.check_status()

@@ -67,6 +67,7 @@ class _Signatures:
                             c_float, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]
+    eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
 
 
 def _stream() -> int:
@@ -207,6 +208,20 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _need(out.dtype == torch.int32 and out.numel() >= logits.shape[0], "int32 out")
     _check(library().eg_argmax(_stream(), _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out)),
            "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor) -> None:
+    """Per row: temperature <= 0 -> greedy; else softmax(logits / T) cut by top_k
+    (0 = off) and top_p (1 = off), drawn by inverse CDF in index order with uniform[r]."""
+    _cuda(logits, temperature, top_k, top_p, uniform, out)
+    rows = logits.shape[0]
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "float32 rows")
+    _need(temperature.dtype == top_p.dtype == uniform.dtype == torch.float32 and top_k.dtype == torch.int32
+          and out.dtype == torch.int32, "float32 temperature/top_p/uniform, int32 top_k/out")
+    _need(min(temperature.numel(), top_k.numel(), top_p.numel(), uniform.numel(), out.numel()) >= rows, "one value per row")
+    _check(library().eg_sample(_stream(), _ptr(logits), logits.stride(0), rows, logits.shape[1], _ptr(temperature),
+                               _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out)), "sample")
 
 
 def describe_status(word: int) -> str:

@@ -1,0 +1,56 @@
+"""Sampling of next tokens from float32 logits on the device: one kernel launch
+for the whole batch, greedy rows and sampled rows together."""
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import SamplingParams
+from .rng import uniform
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int = 256):
+        self.device = torch.device(device)
+        self._cap = 0
+        self._grow(max_rows)
+
+    def _grow(self, rows: int) -> None:
+        if rows <= self._cap:
+            return
+        self._cap = max(rows, 2 * self._cap)
+        # one pinned float32 block [4, cap]: temperature, top_p, uniform, top_k (as int bits)
+        self._host = torch.empty((4, self._cap), dtype=torch.float32).pin_memory()
+        self._dev = torch.empty((4, self._cap), dtype=torch.float32, device=self.device)
+        self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+        self._out_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], request_ids: Sequence[int],
+               token_indices: Sequence[int]) -> torch.Tensor:
+        """Returns int32 tokens [rows] on the device.  Row r is sampled with
+        params[r]; its uniform number is keyed by (seed, request_ids[r], token_indices[r])."""
+        rows = logits.shape[0]
+        assert len(params) == len(request_ids) == len(token_indices) == rows
+        self._grow(rows)
+        if all(p.is_greedy for p in params):
+            kernels.argmax(logits, self._out)
+            return self._out[:rows]
+        h = self._host.numpy()
+        for r, p in enumerate(params):
+            h[0, r] = 0.0 if p.is_greedy else p.temperature
+            h[1, r] = p.top_p
+            h[2, r] = 0.0 if p.is_greedy else uniform(p.seed, int(request_ids[r]), int(token_indices[r]))
+        h[3, :rows].view(np.int32)[:] = [p.top_k for p in params]
+        self._dev[:, :rows].copy_(self._host[:, :rows], non_blocking=True)
+        kernels.sample(logits, self._dev[0], self._dev[3].view(torch.int32), self._dev[1], self._dev[2], self._out)
+        return self._out[:rows]
+
+    def to_host(self, tokens: torch.Tensor) -> list:
+        """Device tokens -> Python ints (synchronises the stream)."""
+        n = tokens.numel()
+        self._out_host[:n].copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:n].tolist()
