@@ -1,0 +1,343 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of the Qwen2.5-0.5B configuration (24
+layers, hidden 896, 14 query heads, 2 KV heads, head size 64, intermediate
+4864, vocabulary 151936, tied head) with random bfloat16 weights, a batch of 8
+requests and contexts that end at 4096 tokens.  A "step" is one decode step of
+the whole batch.  One JSON line is printed:
+
+  value      decoded tokens per second, timed on the device with CUDA events
+             around exactly K steps (token ids fed back on the device)
+  e2e        the same through GptEngine.step(): host token ids in, host token
+             ids out, every step
+  prefill    one prompt of 2,048 tokens in one step
+  roofline   bytes the decode step has to read (every weight once, the cache of
+             the live requests) / its time, against the measured copy bandwidth
+  points     decode at batch 1 and 64
+
+Inputs of a step (about 1.3 GB of weights and cache) are larger than the L2, so
+no flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIG_05B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 24, "hidden_size": 896, "num_attention_heads": 14, "num_key_value_heads": 2,
+    "intermediate_size": 4864, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 32768, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (read-only queries)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = sorted(int(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def model_folder(config, seed=0):
+    import hashlib
+
+    from easy_gpt.cpp_b200.weights.random_init import write_random_model
+
+    tag = hashlib.sha256(json.dumps(config, sort_keys=True).encode()).hexdigest()[:12]
+    folder = Path(tempfile.gettempdir()) / f"easy_gpt_bench_{os.getuid()}_{tag}_{seed}"
+    if not (folder / "model.safetensors").is_file() or not (folder / "done").is_file():
+        t0 = time.time()
+        write_random_model(folder, config, seed, std=0.02, store_dtype="bfloat16")
+        (folder / "done").write_text("ok")
+        print(f"[bench] wrote random weights to {folder} in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+    return folder
+
+
+def prompts_for(batch, length, vocab, seed):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, size=length).tolist() for _ in range(batch)]
+
+
+def prepare_decode(engine, batch, start_context, new_tokens, vocab, seed):
+    """Adds `batch` requests and runs steps until every one of them is decoding."""
+    from easy_gpt.cpp_b200.sampling import GREEDY
+
+    reqs = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts_for(batch, start_context, vocab, seed)]
+    while any(r.known - r.computed != 1 or r.state != "running" for r in reqs):
+        engine.step()
+    return reqs
+
+
+def time_decode_device(engine, reqs, steps, warmup):
+    """K decode steps with the sampled tokens fed back on the device: no host round
+    trip inside the timed region.  Returns (seconds, launches of our kernels, bytes read per step)."""
+    import torch
+
+    from easy_gpt.cpp_b200 import kernels
+
+    runner, cache, sampler = engine.runner, engine.runner.cache, engine.sampler
+    rids = [r.id for r in reqs]
+    n = len(rids)
+    graph = runner.decode_graph(n)
+    tokens = [r.tokens[-1] for r in reqs]
+    bytes_per_step = []
+
+    def one_step(first):
+        for rid in rids:
+            cache.reserve(rid, 1)
+        logits = graph.replay(rids, tokens, tokens_on_device=not first)
+        kernels.argmax(logits[:n], sampler._out)
+        graph.set_tokens_from_device(sampler._out[:n])
+        for rid in rids:
+            cache.commit(rid, 1)
+
+    one_step(True)
+    for _ in range(warmup - 1):
+        one_step(False)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kv_per_token = cache.kv_bytes_per_token()
+    weights = engine.model.weight_bytes_per_step()
+    before = kernels.launch_count
+    start.record()
+    for _ in range(steps):
+        bytes_per_step.append(weights + kv_per_token * sum(cache.length_of(r) + 1 for r in rids))
+        one_step(False)
+    stop.record()
+    torch.cuda.synchronize()
+    launches = (kernels.launch_count - before) + steps * graph.launches
+    # keep the scheduler's view in step with what was decoded here
+    final = sampler.to_host(sampler._out[:n])
+    for r, t in zip(reqs, final):
+        extra = cache.length_of(r.id) - r.computed
+        r.output += [0] * (extra - 1) + [t]
+        r.computed += extra
+    return start.elapsed_time(stop) / 1e3, launches, sum(bytes_per_step) / len(bytes_per_step)
+
+
+def time_decode_e2e(engine, reqs, steps, warmup):
+    """K steps through GptEngine.step(): host token ids in (pinned staging, one copy
+    per step), sampled token ids read back to the host every step."""
+    import torch
+
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        engine.step()
+    stop.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    return max(start.elapsed_time(stop) / 1e3, wall)
+
+
+def measure_decode(folder, config, batch, steps, warmup, want_e2e):
+    import torch
+
+    from easy_gpt.cpp_b200.engine import GptEngine
+
+    total_steps = warmup + steps + (warmup + steps if want_e2e else 0) + 4
+    start_context = CONTEXT - (2 * (warmup + steps) + 4 if want_e2e else warmup + steps + 4)
+    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (CONTEXT + 64), max_active=batch,
+                       prefill_batch=batch, max_batch_tokens=4096, chunk_size=2048, max_tokens_per_request=CONTEXT + 64)
+    reqs = prepare_decode(engine, batch, start_context, total_steps + 64, config["vocab_size"], seed=batch)
+    out = {}
+    with ClockSampler() as clocks:
+        seconds, launches, step_bytes = time_decode_device(engine, reqs, steps, warmup)
+    out["clocks"] = clocks.summary()
+    out["seconds"], out["launches"], out["step_bytes"] = seconds, launches, step_bytes
+    out["tok_s"] = batch * steps / seconds
+    out["context_end"] = max(engine.runner.cache.length_of(r.id) for r in reqs)
+    if want_e2e:
+        e2e_seconds = time_decode_e2e(engine, reqs, steps, warmup)
+        out["e2e_tok_s"] = batch * steps / e2e_seconds
+        # per step: the packed metadata of the batch goes up, the sampled tokens come back
+        graph = engine.runner.decode_graph(batch)
+        out["h2d"] = graph.size * 4
+        out["d2h"] = batch * 4
+    engine.runner.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def prefill_flops(config, tokens):
+    H, I, V = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
+    NH, NKV = config["num_attention_heads"], config["num_key_value_heads"]
+    HD = config.get("head_dim") or H // NH
+    L = config["num_hidden_layers"]
+    per_token = 2 * (H * (NH + 2 * NKV) * HD + NH * HD * H + 3 * H * I)
+    gemm = L * per_token * tokens + 2 * H * V                      # logits at the last position only
+    attention = L * 4 * NH * HD * (tokens * (tokens + 1) // 2)      # QK^T and PV over the causal half
+    return gemm + attention
+
+
+def measure_prefill(folder, config, repeats=5):
+    import torch
+
+    from easy_gpt.cpp_b200.engine import Model, StepEntry, StepRunner
+
+    model = Model.from_dir(folder, device="cuda:0", dtype=torch.bfloat16)
+    runner = StepRunner(model, page_size=64, num_pages=2 * PREFILL_TOKENS // 64, max_slots=2)
+    prompt = prompts_for(1, PREFILL_TOKENS, config["vocab_size"], seed=99)[0]
+    times = []
+    for i in range(repeats + 2):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.run([StepEntry("p", prompt, [PREFILL_TOKENS - 1])], check=False)
+        stop.record()
+        torch.cuda.synchronize()
+        runner.end("p")
+        if i >= 2:
+            times.append(start.elapsed_time(stop) / 1e3)
+    runner.check_status()
+    times.sort()
+    del runner, model
+    torch.cuda.empty_cache()
+    return times[len(times) // 2]
+
+
+def run_ours(args):
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device; this engine has no CPU path"}))
+        return 1
+    config = dict(CONFIG_05B)
+    layers_full = config["num_hidden_layers"]
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    pk = peaks()
+    folder = model_folder(config)
+    main = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=True)
+    points = {}
+    for b in (1, 64):
+        r = measure_decode(folder, config, b, args.steps, args.warmup, want_e2e=False)
+        points[f"decode_b{b}"] = round(r["tok_s"], 1)
+    prefill_s = measure_prefill(folder, config)
+    flops = prefill_flops(config, PREFILL_TOKENS)
+    achieved = main["step_bytes"] / (main["seconds"] / args.steps) / 1e9
+    line = {
+        "metric": "decode tok/s", "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * main["seconds"] / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "qwen2.5-0.5b-sizes-random-weights", "global_batch": args.batch, "seq_len": CONTEXT,
+            "parallelism": "single-gpu", "layers": config["num_hidden_layers"], "layers_full": layers_full,
+            "hidden": config["hidden_size"], "heads": config["num_attention_heads"],
+            "kv_heads": config["num_key_value_heads"], "head_dim": config["hidden_size"] // config["num_attention_heads"],
+            "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "tied_head": True,
+            "context_end": main["context_end"], "page_size": 64, "prefill_tokens": PREFILL_TOKENS,
+            "l2": "inputs of a step exceed L2", "sampling": "greedy",
+        },
+        "clocks": main["clocks"],
+        "e2e": {"value": round(main["e2e_tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
+                "d2h_bytes_per_step": main["d2h"]},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_s, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_s * 1e3, 3),
+                    "frac": round(flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C++/CMake program without setup.py or pyproject.toml: pip cannot install it, "
+                          "and its CUDA backend names only sm_120"}))
+        return 0
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -59,6 +59,7 @@ class CacheGroup:
         # host block tables by slot; -1 where no page is held
         self.tables = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
         self.kv: Optional[torch.Tensor] = None
+        self.scratch_page = -1
 
     @property
     def window(self) -> Optional[int]:
@@ -109,7 +110,9 @@ class CacheManager:
         self._requests: Dict[object, _Request] = {}
         if device is not None:
             for g in self.groups:
-                g.kv = torch.zeros((len(g.cache_ids), g.pool.num_pages, 2, g.need.num_kv_heads, page_size, g.need.head_dim),
+                # one page beyond the pool (id num_pages): rows that pad a captured batch write there
+                g.scratch_page = g.pool.num_pages
+                g.kv = torch.zeros((len(g.cache_ids), g.pool.num_pages + 1, 2, g.need.num_kv_heads, page_size, g.need.head_dim),
                                    device=device, dtype=dtype)
             for cache_id, need in self._state_needs.items():
                 self.state[cache_id] = torch.zeros((max_slots, *need.shape), device=device, dtype=torch.float32)

@@ -42,7 +42,7 @@ def _pad4(n: int) -> int:
 
 class StepRunner:
     def __init__(self, model: Model, page_size: int, num_pages: int, max_slots: int,
-                 max_tokens_per_request: Optional[int] = None):
+                 max_tokens_per_request: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.device = model.device
         max_tokens_per_request = max_tokens_per_request or min(model.spec.max_positions, num_pages * page_size)
@@ -56,6 +56,9 @@ class StepRunner:
         self._ring_next = 0
         self._dev: Optional[torch.Tensor] = None
         self.steps_run = 0
+        self.use_graphs = use_graphs
+        self._graphs: Dict[int, object] = {}
+        self.graph_replays = 0
 
     # -- request lifetime -------------------------------------------------------
     def end(self, request) -> None:
@@ -186,8 +189,10 @@ class StepRunner:
         a complaint of a kernel becomes an exception.  With ``commit`` the requests'
         cached lengths advance here; a scheduler that keeps its own count passes False
         and calls ``cache.commit`` itself."""
-        ctx, rows = self.build_context(entries)
-        logits = self.model.forward(ctx, self.cache, rows)
+        logits = self._run_captured(entries) if self.use_graphs else None
+        if logits is None:
+            ctx, rows = self.build_context(entries)
+            logits = self.model.forward(ctx, self.cache, rows)
         if commit:
             for e in entries:
                 self.cache.commit(e.request, len(e.tokens))
@@ -195,6 +200,41 @@ class StepRunner:
         if check:
             self.check_status()
         return logits
+
+    def decode_graph(self, n: int):
+        """The captured step for n single-token entries (None if n is beyond the buckets)."""
+        from .decode_graph import DecodeGraph, bucket_for
+
+        b = bucket_for(n)
+        if b < 0 or b > self.cache.max_slots:
+            b = self.cache.max_slots if n <= self.cache.max_slots else -1
+        if b < 0:
+            return None
+        if b not in self._graphs:
+            self._graphs[b] = DecodeGraph(self, b)
+        return self._graphs[b]
+
+    def _run_captured(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Steps in which every live entry brings one token and wants its logits go
+        through a captured graph; anything else returns None (the general path)."""
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        if len({e.request for e in entries}) != len(entries) or not all(self.cache.has_request(e.request) for e in entries):
+            return None
+        graph = self.decode_graph(len(entries))
+        if graph is None:
+            return None
+        need: Dict[int, int] = {g.index: 0 for g in self.cache.groups}
+        for e in entries:
+            for gi, k in self.cache.pages_needed(e.request, 1).items():
+                need[gi] += k
+        if any(need[g.index] > g.pool.free_count for g in self.cache.groups):
+            return None                      # the general path raises the proper error
+        for e in entries:
+            self.cache.reserve(e.request, 1)
+        logits = graph.replay([e.request for e in entries], [e.tokens[0] for e in entries])
+        self.graph_replays += 1
+        return logits[:len(entries)]
 
     def check_status(self) -> None:
         word = int(self.status.item())
