@@ -1,0 +1,325 @@
+// Paged grouped-query attention on the warp-level tensor cores (bfloat16), for
+// every token of a step: decoded tokens and, until a tiled prefill kernel takes
+// them, the tokens of prompt portions too.
+//
+// One CTA works on (token, KV head, split): the G = NH/NKV query heads that share
+// the KV head are the rows of the MMA (padded to 16), so a key tile is read once
+// for all of them.  The token's visible keys [first, pos] are cut into tiles of
+// 64 keys (aligned to 64, so a tile's 16-key quarters never straddle a page of
+// 16, 32, 64, ... tokens); the tiles are dealt to `splits` CTAs in contiguous
+// runs, each CTA streams its run through a cp.async pipeline, its four warps take
+// a quarter of every tile each, and keep a running softmax (m, l, acc) in
+// float32 (src/cuda/ops/self_attn_detail.cuh:325-382).  The warps' states are
+// merged in shared memory; with one split the result is written at once, else a
+// partial (m, l, acc) goes to scratch memory and `attention_merge_kernel` merges
+// the splits.
+//
+// score = (q . k) * scale in float32, exp by expf, P is rounded to bfloat16 for the
+// P V product (as V is bfloat16 anyway); sums and the accumulator stay float32.
+#include "mma_utils.cuh"
+
+namespace {
+
+constexpr int TILE_KEYS = 64;
+constexpr int THREADS = 128;
+
+template <int HD>
+struct Layout {
+    static constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per key row
+    static constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+    static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;          // K or V
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int STAGES = (3 * STAGE_BYTES <= 160 * 1024) ? 3 : 2;
+    static constexpr int MERGE_BYTES = 4 * 16 * (HD + 2) * 4;
+    static constexpr int SMEM = (STAGES * STAGE_BYTES > MERGE_BYTES) ? STAGES * STAGE_BYTES : MERGE_BYTES;
+    __device__ static __forceinline__ int offset(int row, int chunk) {      // bytes inside a K or V tile
+        return (row * CHUNKS + (chunk ^ (row & SWZ))) * 16;
+    }
+};
+
+struct Params {
+    const bf16* q;
+    int ldq;
+    const bf16* k_cache;
+    const bf16* v_cache;
+    long long page_stride, head_stride;
+    const int* block_table;
+    int table_stride;
+    const int* token_seq;
+    const int* positions;
+    bf16* out;
+    int ldo;
+    float* partial_acc;       // [T, NH, splits, HD]
+    float* partial_ml;        // [T, NH, splits, 2]
+    int num_heads, num_kv_heads, page_size, num_pages, window, splits;
+    float scale;
+    int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p) {
+    using L = Layout<HD>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int t = blockIdx.x;
+    const int G = p.num_heads / p.num_kv_heads;
+    const int gblocks = (G + 15) / 16;
+    const int kvh = blockIdx.y / gblocks;
+    const int g0 = (blockIdx.y % gblocks) * 16;                   // first query head of the group handled here
+    const int split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+
+    const int pos = p.positions[t];
+    const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int* table = p.block_table + (size_t)p.token_seq[t] * p.table_stride;
+    const int tile_lo = first / TILE_KEYS, tile_hi = pos / TILE_KEYS;           // inclusive
+    const int per = (tile_hi - tile_lo + 1 + p.splits - 1) / p.splits;
+    const int my_lo = tile_lo + split * per;
+    const int my_hi = min(tile_hi, my_lo + per - 1);
+    const int ntiles = my_hi - my_lo + 1;                                       // may be <= 0
+
+    // ---- query rows as A fragments: row r <-> head kvh*G + g0 + r
+    uint32_t qf[HD / 16][4];
+    {
+        const int r0 = g0 + gid, r1 = g0 + gid + 8;
+        const bf16* q0 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r0) * HD;
+        const bf16* q1 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r1) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            const int d = ks * 16 + 2 * tig;
+            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+            qf[ks][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+            qf[ks][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+        }
+    }
+
+    auto load_tile = [&](int tile, int stage) {
+        unsigned char* ks = smem + stage * L::STAGE_BYTES;
+        unsigned char* vs = ks + L::TILE_BYTES;
+        for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
+            const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
+            const int kpos = tile * TILE_KEYS + row;
+            bool valid = kpos >= first && kpos <= pos;
+            long long off = 0;
+            if (valid) {
+                const int page = table[kpos / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                    valid = false;
+                } else {
+                    off = (long long)page * p.page_stride + (long long)kvh * p.head_stride +
+                          (long long)(kpos % p.page_size) * HD + chunk * 8;
+                }
+            }
+            cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
+            cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
+        }
+    };
+
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;                 // rows gid and gid + 8
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+#pragma unroll
+    for (int s = 0; s < L::STAGES - 1; ++s) {
+        if (s < ntiles) load_tile(my_lo + s, s);
+        cp_async_commit();
+    }
+    for (int it = 0; it < ntiles; ++it) {
+        cp_async_wait<L::STAGES - 2>();
+        __syncthreads();
+        {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
+            const int nxt = it + L::STAGES - 1;
+            if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES);
+            cp_async_commit();
+        }
+        const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES;
+        const unsigned char* vs = ks + L::TILE_BYTES;
+        const int key_base = (my_lo + it) * TILE_KEYS + warp * 16;               // this warp's 16 keys
+        if (key_base > pos || key_base + 15 < first) continue;                    // nothing visible in this quarter
+
+        // S = Q K^T for 16 rows x 16 keys
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t b[4];
+            const int mi = lane >> 3, r = lane & 7;
+            ldmatrix_x4(b, ks + L::offset(warp * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+            mma_bf16_16816(s[0], qf[kk], b[0], b[1]);
+            mma_bf16_16816(s[1], qf[kk], b[2], b[3]);
+        }
+        // scale, mask, running softmax
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
+                const bool ok = kpos >= first && kpos <= pos;
+                s[j][e] = ok ? s[j][e] * p.scale : -INFINITY;
+                if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
+            }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);               // finite: a key of this quarter is visible
+        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pf[4];
+        float ps0 = 0.f, ps1 = 0.f;
+        {
+            float e00 = expf(s[0][0] - mn0), e01 = expf(s[0][1] - mn0), e02 = expf(s[0][2] - mn1), e03 = expf(s[0][3] - mn1);
+            float e10 = expf(s[1][0] - mn0), e11 = expf(s[1][1] - mn0), e12 = expf(s[1][2] - mn1), e13 = expf(s[1][3] - mn1);
+            ps0 = e00 + e01 + e10 + e11;
+            ps1 = e02 + e03 + e12 + e13;
+            pf[0] = pack_bf16(e00, e01);
+            pf[1] = pack_bf16(e02, e03);
+            pf[2] = pack_bf16(e10, e11);
+            pf[3] = pack_bf16(e12, e13);
+        }
+        l0 = l0 * c0 + ps0;
+        l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            acc[i][0] *= c0;
+            acc[i][1] *= c0;
+            acc[i][2] *= c1;
+            acc[i][3] *= c1;
+        }
+        // acc += P V
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt += 2) {
+            uint32_t b[4];
+            const int mi = lane >> 3, r = lane & 7;
+            ldmatrix_x4_trans(b, vs + L::offset(warp * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
+            mma_bf16_16816(acc[nt], pf, b[0], b[1]);
+            mma_bf16_16816(acc[nt + 1], pf, b[2], b[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                                              // the pipeline's memory is free now
+
+    // ---- merge the four warps: rows r = gid, gid + 8
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* wm = reinterpret_cast<float*>(smem);                                   // [4][16]
+    float* wl = wm + 64;                                                          // [4][16]
+    float* wacc = wl + 64;                                                        // [4][16][HD]
+    if (tig == 0) {
+        wm[warp * 16 + gid] = m0;
+        wm[warp * 16 + gid + 8] = m1;
+        wl[warp * 16 + gid] = l0;
+        wl[warp * 16 + gid + 8] = l1;
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * tig;
+        float* a0 = wacc + ((warp * 16 + gid) * HD + d);
+        float* a1 = wacc + ((warp * 16 + gid + 8) * HD + d);
+        a0[0] = acc[i][0];
+        a0[1] = acc[i][1];
+        a1[0] = acc[i][2];
+        a1[1] = acc[i][3];
+    }
+    __syncthreads();
+    const int rows = min(16, G - g0);
+    for (int e = threadIdx.x; e < rows * HD; e += THREADS) {
+        const int r = e / HD, d = e % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, wm[w * 16 + r]);
+        float l = 0.f, a = 0.f;
+        if (m > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = expf(wm[w * 16 + r] - m);                          // -inf -> 0
+                l += wl[w * 16 + r] * f;
+                a += wacc[(w * 16 + r) * HD + d] * f;
+            }
+        }
+        const int h = kvh * G + g0 + r;
+        if (p.splits == 1) {
+            p.out[(size_t)t * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+        } else {
+            const size_t slot = ((size_t)t * p.num_heads + h) * p.splits + split;
+            p.partial_acc[slot * HD + d] = a;
+            if (d == 0) {
+                p.partial_ml[slot * 2] = m;
+                p.partial_ml[slot * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}
+__global__ void attention_merge_kernel(const float* __restrict__ partial_acc, const float* __restrict__ partial_ml,
+                                       bf16* __restrict__ out, int ldo, int num_heads, int head_dim, int splits) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t base = ((size_t)t * num_heads + h) * splits;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[(base + s) * 2]);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float l = 0.f, a = 0.f;
+        if (m > -INFINITY) {
+            for (int s = 0; s < splits; ++s) {
+                const float f = expf(partial_ml[(base + s) * 2] - m);
+                l += partial_ml[(base + s) * 2 + 1] * f;
+                a += partial_acc[(base + s) * head_dim + d] * f;
+            }
+        }
+        out[(size_t)t * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+    }
+}
+
+template <int HD>
+int launch(cudaStream_t stream, const Params& p, int tokens) {
+    using L = Layout<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int G = p.num_heads / p.num_kv_heads;
+    dim3 grid(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
+    attention_paged_kernel<HD><<<grid, THREADS, L::SMEM, stream>>>(p);
+    int rc = eg_launch_status();
+    if (rc == 0 && p.splits > 1) {
+        dim3 mg(tokens, p.num_heads);
+        attention_merge_kernel<<<mg, HD < 128 ? 64 : 128, 0, stream>>>(p.partial_acc, p.partial_ml, p.out, p.ldo, p.num_heads, HD, p.splits);
+        rc = eg_launch_status();
+    }
+    return rc;
+}
+
+}  // namespace
+
+// Head sizes 32, 64, 128, 256 and page sizes that are multiples of 16; anything else
+// returns cudaErrorInvalidValue and the caller uses the generic kernel.
+// partial_acc / partial_ml: scratch of tokens*heads*splits*(head_dim + 2) floats, needed when splits > 1.
+EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                              const int* block_table, int table_stride, const int* token_seq, const int* positions,
+                              void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
+                              int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
+                              int num_pages, int window, float scale, int splits, int* status) {
+    if (tokens <= 0) return 0;
+    if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
+        splits > 65535 || (splits > 1 && (!partial_acc || !partial_ml)))
+        return (int)cudaErrorInvalidValue;
+    Params p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
+             table_stride, token_seq, positions, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
+             page_size, num_pages, window, splits, scale, status};
+    switch (head_dim) {
+        case 32: return launch<32>(stream, p, tokens);
+        case 64: return launch<64>(stream, p, tokens);
+        case 128: return launch<128>(stream, p, tokens);
+        case 256: return launch<256>(stream, p, tokens);
+        default: return (int)cudaErrorInvalidValue;
+    }
+}

@@ -65,6 +65,9 @@ class _Signatures:
     eg_attention_generic = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
                             c_float, c_void_p]
+    eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
+                          c_int, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -188,6 +191,55 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         block_table.stride(0), _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads, num_kv_heads,
         head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         _ptr(status)), "attention_generic")
+
+
+PAGED_ATTENTION_HEAD_DIMS = (32, 64, 128, 256)
+SM_COUNT = 148
+
+
+def attention_paged_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Sizes the tensor-core kernel takes; the rest goes to ``attention_generic``."""
+    return dtype == torch.bfloat16 and head_dim in PAGED_ATTENTION_HEAD_DIMS and page_size % 16 == 0
+
+
+def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
+    """How many CTAs share one (token, KV head): enough to fill the GPU about four
+    times over, at most one per tile of 64 keys."""
+    base = tokens * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
+    tiles = max(1, -(-max_context // 64))
+    return max(1, min(tiles, (4 * SM_COUNT) // max(1, base)))
+
+
+def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                    token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, num_heads: int,
+                    num_kv_heads: int, head_dim: int, window: Optional[int], scale: float, splits: int,
+                    status: torch.Tensor) -> None:
+    """bfloat16 attention over the paged cache on the tensor cores; same contract as
+    ``attention_generic``.  With splits > 1 it uses scratch memory for the partial results."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status)
+    T = q.shape[0]
+    page_size = k_cache.shape[2]
+    _need(attention_paged_takes(q.dtype, head_dim, page_size),
+          f"attention_paged takes bfloat16, head sizes {PAGED_ATTENTION_HEAD_DIMS} and pages of a multiple of 16 tokens")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == k_cache.dtype == torch.bfloat16, "q/out/cache layout")
+    _need(q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0, "q rows must be 4-byte aligned")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1, "block table")
+    _need(token_seq.dtype == torch.int32 and positions.dtype == torch.int32, "int32 metadata")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.stride() == v_cache.stride()
+          and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim and k_cache.data_ptr() % 16 == 0
+          and k_cache.stride(0) % 8 == 0 and k_cache.stride(1) % 8 == 0, "cache shape [pages, NKV, page_size, HD], 16-byte rows")
+    acc = ml = None
+    if splits > 1:
+        acc = torch.empty(T * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
+        ml = torch.empty(T * num_heads * splits * 2, dtype=torch.float32, device=q.device)
+    _check(library().eg_attention_paged(
+        _stream(), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
+        _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml), T, num_heads, num_kv_heads,
+        head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
+        int(splits), _ptr(status)), "attention_paged")
+    if splits > 1:
+        global launch_count
+        launch_count += 1                      # the merge kernel
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

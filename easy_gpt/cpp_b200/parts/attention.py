@@ -86,8 +86,16 @@ class Attention(Mixer):
                            rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
                            tables.page_size, ctx.status)
         attn = torch.empty((T, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
-        kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
-                                  self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status)
+        if kernels.attention_paged_takes(x.dtype, self.head_dim, tables.page_size):
+            longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
+            splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
+            kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
+                                    self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, splits,
+                                    ctx.status)
+        else:
+            kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
+                                      self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                                      ctx.status)
         return self.out(attn)
 
 

@@ -1,0 +1,298 @@
+"""Each kernel alone against its plain float32 reference, at sizes other than the
+engine's tiny models (GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+# -- embedding ---------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_gather_and_bad_ids(dtype):
+    from easy_gpt.cpp_b200 import kernels
+
+    table = torch.randn(301, 70, generator=gen(0)).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.full((5, 70), 7.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.embedding_gather(ids.to(DEV), table.to(DEV), out, status)
+    assert torch.equal(out.cpu(), plain_model.embed(table.float(), ids.tolist()))
+    assert status.item() == 0
+    bad = torch.tensor([3, 301, -1], dtype=torch.int32, device=DEV)
+    kernels.embedding_gather(bad, table.to(DEV), out[:3], status)
+    assert status.item() == 1 and float(out[1].abs().sum()) == 0.0 and float(out[2].abs().sum()) == 0.0
+    with pytest.raises(kernels.KernelError, match="no CPU path"):
+        kernels.embedding_gather(ids, table, out.cpu(), status)
+
+
+# -- norm ----------------------------------------------------------------------
+
+@pytest.mark.parametrize("hidden, eps", [(70, 1e-6), (896, 1e-5), (3584, 1e-6), (5000, 3e-4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, eps, dtype):
+    from easy_gpt.cpp_b200 import kernels
+
+    rows = 9
+    resid = torch.randn(rows, hidden, generator=gen(1)) * 3
+    delta = (torch.randn(rows, hidden, generator=gen(2))).to(dtype)
+    gain = 1 + 0.2 * torch.randn(hidden, generator=gen(3))
+    want_resid = resid + delta.float()
+    want = plain_model.rms_norm(want_resid, gain, eps)
+    r = resid.to(DEV)
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(r, delta.to(DEV), gain.to(DEV), out, eps)
+    assert torch.equal(r.cpu(), want_resid)                        # the float32 sum is exact to the bit
+    tol = 2e-6 * float(want.abs().max()) if dtype == torch.float32 else 8e-3 * float(want.abs().max())
+    assert float((out.float().cpu() - want).abs().max()) <= tol
+    # without delta; and only some rows (the final norm), residual untouched
+    out2 = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    rows_idx = torch.tensor([7, 0, 4], dtype=torch.int32, device=DEV)
+    before = r.clone()
+    kernels.add_rmsnorm(r, delta.to(DEV), gain.to(DEV), out2, eps, rows=rows_idx)
+    assert torch.equal(r, before)
+    want2 = plain_model.rms_norm(want_resid[[7, 0, 4]] + delta.float()[[7, 0, 4]], gain, eps)
+    assert float((out2.float().cpu() - want2).abs().max()) <= tol * 2
+    kernels.add_rmsnorm(r, None, gain.to(DEV), out, eps)
+    assert float((out.float().cpu() - want).abs().max()) <= tol
+
+
+# -- float32 matrix product ---------------------------------------------------------
+
+@pytest.mark.parametrize("M, N, K", [(1, 70, 33), (5, 1152, 896), (67, 129, 250), (130, 64, 17)])
+def test_gemm_f32_is_true_32_bit_and_batch_invariant(M, N, K):
+    from easy_gpt.cpp_b200 import kernels
+
+    a = torch.randn(M, K, generator=gen(4))
+    w = torch.randn(N, K, generator=gen(5))
+    b = torch.randn(N, generator=gen(6))
+    out = torch.empty(M, N, device=DEV)
+    kernels.gemm_f32_nt(a.to(DEV), w.to(DEV), b.to(DEV), out)
+    want = (a.double() @ w.double().t() + b.double())
+    # float32 accumulation error of a K-term sum, far below TF32's 1e-3
+    assert float((out.cpu().double() - want).abs().max()) <= 2e-6 * math.sqrt(K) * float(want.abs().max())
+    # a row's result does not depend on the other rows of the batch
+    one = torch.empty(1, N, device=DEV)
+    kernels.gemm_f32_nt(a[M // 2:M // 2 + 1].to(DEV), w.to(DEV), b.to(DEV), one)
+    assert torch.equal(one[0], out[M // 2])
+    # strided input (a slice of a wider buffer)
+    wide = torch.randn(M, K + 40, generator=gen(7)).to(DEV)
+    kernels.gemm_f32_nt(wide[:, 8:8 + K], w.to(DEV), None, out)
+    want = wide[:, 8:8 + K].cpu().double() @ w.double().t()
+    assert float((out.cpu().double() - want).abs().max()) <= 2e-6 * math.sqrt(K) * float(want.abs().max())
+
+
+# -- rotary encoding + cache write -----------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("NH, NKV, HD, rot, theta", [(4, 2, 16, 16, 1e4), (14, 2, 64, 64, 1e6), (3, 1, 48, 32, 5e4)])
+def test_rope_cache(dtype, NH, NKV, HD, rot, theta):
+    from easy_gpt.cpp_b200 import kernels
+    from easy_gpt.cpp_b200.parts.rope import RotaryEncoding
+
+    T, ps, pages = 11, 8, 6
+    width = (NH + 2 * NKV) * HD
+    qkv = torch.randn(T, width, generator=gen(8)).to(dtype)
+    bias = torch.randn(width, generator=gen(9)) * 0.5
+    positions = torch.tensor([0, 1, 2, 3, 4000, 4001, 7, 131071, 9, 10, 11], dtype=torch.int32)
+    slots = torch.tensor([0, 1, 2, 3, 40, 41, 15, 16, 47, 8, 9], dtype=torch.int32)
+    kc = torch.zeros(pages, NKV, ps, HD, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    inv = RotaryEncoding.inverse_frequencies(rot, theta)
+    assert torch.equal(inv, plain_model.rope_inverse_frequencies(rot, theta))
+    x = qkv.to(DEV).clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.rope_cache(x, bias.to(DEV), positions.to(DEV), slots.to(DEV), kc, vc, inv.to(DEV), NH, NKV, HD, rot, ps, status)
+    assert status.item() == 0
+    full = qkv.float() + bias
+    q = full[:, :NH * HD].reshape(T, NH, HD)
+    k = full[:, NH * HD:(NH + NKV) * HD].reshape(T, NKV, HD)
+    v = full[:, (NH + NKV) * HD:].reshape(T, NKV, HD)
+
+    def rotate(t):
+        return torch.cat([plain_model.rope(t[..., :rot], positions.long(), theta), t[..., rot:]], dim=-1)
+
+    tol = 3e-6 * float(full.abs().max()) if dtype == torch.float32 else 8e-3 * float(full.abs().max())
+    assert float((x[:, :NH * HD].float().cpu().reshape(T, NH, HD) - rotate(q)).abs().max()) <= tol
+    kr = rotate(k)
+    for t in range(T):
+        page, off = int(slots[t]) // ps, int(slots[t]) % ps
+        assert float((kc[page, :, off].float().cpu() - kr[t]).abs().max()) <= tol
+        assert float((vc[page, :, off].float().cpu() - v[t]).abs().max()) <= tol
+    used = {(int(s) // ps, int(s) % ps) for s in slots}
+    for page in range(pages):
+        for off in range(ps):
+            if (page, off) not in used:
+                assert float(kc[page, :, off].abs().sum()) == 0.0       # nothing else was touched
+    # a layer that reads another's cache: q rotated, nothing stored; and a bad slot is flagged
+    kc.zero_()
+    y = qkv.to(DEV).clone()
+    kernels.rope_cache(y, bias.to(DEV), positions.to(DEV), None, None, None, inv.to(DEV), NH, NKV, HD, rot, ps, status)
+    assert torch.equal(y[:, :NH * HD], x[:, :NH * HD]) and float(kc.abs().sum()) == 0.0
+    kernels.rope_cache(y, None, positions.to(DEV), torch.full((T,), pages * ps, dtype=torch.int32, device=DEV), kc, vc,
+                       inv.to(DEV), NH, NKV, HD, rot, ps, status)
+    assert status.item() == 4
+
+
+# -- attention over the paged cache ----------------------------------------------------------
+
+def paged_case(seed, NH, NKV, HD, ps, contexts, queries, dtype, window=None, spike=None):
+    """Builds a cache holding `contexts[i] + queries[i]` keys for each sequence in
+    shuffled pages, and the query tokens (the last queries[i] positions of each)."""
+    g = gen(seed)
+    nseq = len(contexts)
+    totals = [c + q for c, q in zip(contexts, queries)]
+    pages_per = [-(-t // ps) for t in totals]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.full((nseq, width), -1, dtype=torch.int32)
+    kc = torch.randn(num_pages, NKV, ps, HD, generator=g)          # unused slots hold garbage on purpose
+    vc = torch.randn(num_pages, NKV, ps, HD, generator=g)
+    K, V = [], []
+    it = iter(perm)
+    for s in range(nseq):
+        k = torch.randn(totals[s], NKV, HD, generator=g)
+        v = torch.randn(totals[s], NKV, HD, generator=g)
+        if spike is not None and totals[s] > spike[0]:
+            k[spike[0]] *= spike[1]                                   # one far key that must not be missed
+        for lp in range(pages_per[s]):
+            page = next(it)
+            table[s, lp] = page
+            n = min(ps, totals[s] - lp * ps)
+            kc[page, :, :n] = k[lp * ps:lp * ps + n].transpose(0, 1)
+            vc[page, :, :n] = v[lp * ps:lp * ps + n].transpose(0, 1)
+        K.append(k)
+        V.append(v)
+    T = sum(queries)
+    q = torch.randn(T, NH, HD, generator=g)
+    token_seq = torch.tensor([s for s in range(nseq) for _ in range(queries[s])], dtype=torch.int32)
+    positions = torch.tensor([contexts[s] + i for s in range(nseq) for i in range(queries[s])], dtype=torch.int32)
+    if dtype == torch.bfloat16:
+        q, kc, vc = q.bfloat16(), kc.bfloat16(), vc.bfloat16()
+        K = [k.bfloat16().float() for k in K]
+        V = [v.bfloat16().float() for v in V]
+    # plain reference: whole-sequence attention, rows of the query tokens picked out
+    want = torch.empty(T, NH * HD)
+    row = 0
+    for s in range(nseq):
+        n = totals[s]
+        qs = torch.zeros(n, NH, HD)
+        qs[contexts[s]:] = q[row:row + queries[s]].float()
+        full = plain_model.attention_core(qs, K[s], V[s], torch.arange(n), window)
+        want[row:row + queries[s]] = full[contexts[s]:]
+        row += queries[s]
+    return dict(q=q.reshape(T, NH * HD), kc=kc, vc=vc, table=table, token_seq=token_seq, positions=positions, want=want)
+
+
+ATTENTION_CASES = [
+    # NH, NKV, HD, page, contexts, queries, window
+    (4, 2, 16, 4, [0, 9, 30], [5, 1, 7], None),
+    (6, 2, 32, 16, [100, 0, 63, 64], [1, 33, 1, 2], None),
+    (14, 2, 64, 16, [700, 15, 16, 17], [1, 1, 1, 1], None),
+    (14, 2, 64, 64, [300, 0], [40, 130], None),
+    (12, 2, 128, 32, [257, 1000], [3, 1], None),
+    (3, 1, 64, 16, [200, 90], [1, 20], 40),
+    (8, 8, 32, 16, [77], [5], 17),
+    (40, 2, 32, 16, [50], [2], None),            # 20 query heads per KV head: two row blocks
+    (2, 1, 80, 16, [45], [4], None),             # a head size only the generic kernel takes
+    (4, 2, 256, 16, [130], [2], None),
+]
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_kernels(case, dtype):
+    from easy_gpt.cpp_b200 import kernels
+
+    NH, NKV, HD, ps, contexts, queries, window = case
+    c = paged_case(11, NH, NKV, HD, ps, contexts, queries, dtype, window)
+    scale = 1.0 / math.sqrt(HD)
+    T = c["q"].shape[0]
+    args = [c[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tol = 2e-5 if dtype == torch.float32 else 2.5e-2
+    out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+    kernels.attention_generic(*args, out, NH, NKV, HD, window, scale, status)
+    assert status.item() == 0
+    err = float((out.float().cpu() - c["want"]).abs().max())
+    assert err <= tol, f"generic: {err}"
+    if kernels.attention_paged_takes(dtype, HD, ps):
+        for splits in (1, 2, 5, 64):
+            out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+            kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, splits, status)
+            assert status.item() == 0
+            err = float((out.float().cpu() - c["want"]).abs().max())
+            assert err <= tol, f"paged splits={splits}: {err}"
+    else:
+        assert dtype == torch.float32 or HD == 80 or ps % 16
+        if dtype == torch.bfloat16:
+            with pytest.raises(kernels.KernelError, match="attention_paged takes"):
+                kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, 1, status)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_and_a_windows_edge(dtype):
+    """One key among hundreds carries nearly all the weight; it sits at a page's
+    edge, at a tile's edge, and right at / just outside a window's edge."""
+    from easy_gpt.cpp_b200 import kernels
+
+    NH, NKV, HD, ps = 4, 2, 64, 16
+    scale = 1.0 / math.sqrt(HD)
+    for far, window in ((0, None), (63, None), (64, None), (511, None), (600 - 100 + 1, 100), (600 - 100, 100)):
+        c = paged_case(far + 1, NH, NKV, HD, ps, [600], [1], dtype, window, spike=(far, 6.0))
+        # point the query at the spiked key: score of the far key dominates unless it is masked
+        args = {k: v.clone() for k, v in c.items()}
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        dev = [args[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
+        tol = 3e-5 if dtype == torch.float32 else 3e-2
+        for name in ("generic", "paged"):
+            out = torch.zeros(1, NH * HD, dtype=dtype, device=DEV)
+            if name == "generic":
+                kernels.attention_generic(*dev, out, NH, NKV, HD, window, scale, status)
+            elif dtype == torch.bfloat16:
+                kernels.attention_paged(*dev, out, NH, NKV, HD, window, scale, 3, status)
+            else:
+                continue
+            err = float((out.float().cpu() - c["want"]).abs().max())
+            assert err <= tol and status.item() == 0, (name, far, window, err)
+
+
+def test_attention_flags_a_missing_page():
+    from easy_gpt.cpp_b200 import kernels
+
+    c = paged_case(3, 4, 2, 64, 16, [40], [1], torch.bfloat16)
+    c["table"][0, 1] = -1
+    dev = [c[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
+    for fn, extra in ((kernels.attention_generic, ()), (kernels.attention_paged, (2,))):
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.zeros(1, 4 * 64, dtype=torch.bfloat16, device=DEV)
+        fn(*dev, out, 4, 2, 64, None, 0.125, *extra, status)
+        assert status.item() == 2
+        assert torch.isfinite(out.float()).all()
+
+
+# -- SwiGLU ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T, I", [(1, 208), (7, 4864), (300, 37)])
+def test_swiglu(dtype, T, I):
+    from easy_gpt.cpp_b200 import kernels
+
+    gu = (torch.randn(T, 2 * I, generator=gen(12)) * 3).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    kernels.swiglu(gu.to(DEV), out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    want = u * (g * (1.0 / (1.0 + torch.exp(-g))))
+    tol = 1e-6 * float(want.abs().max()) if dtype == torch.float32 else 8e-3 * float(want.abs().max())
+    assert float((out.float().cpu() - want).abs().max()) <= tol
