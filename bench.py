@@ -281,6 +281,17 @@ def run_ours(args):
         config["num_hidden_layers"] = args.layers
     pk = peaks()
     folder = model_folder(config)
+    if args.only == "decode":
+        r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": config["num_hidden_layers"], "context": CONTEXT,
+                          "tok_s": round(r["tok_s"], 1), "ms_per_step": round(1e3 * r["seconds"] / args.steps, 4),
+                          "gb_s": round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9, 1)}))
+        return 0
+    if args.only == "prefill":
+        s = measure_prefill(folder, config)
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": config["num_hidden_layers"],
+                          "ms": round(s * 1e3, 3), "tflops": round(prefill_flops(config, PREFILL_TOKENS) / s / 1e12, 1)}))
+        return 0
     main = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=True)
     points = {}
     for b in (1, 64):
@@ -318,6 +329,7 @@ def run_ours(args):
 
 
 def main():
+    global CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -325,12 +337,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    CONTEXT = args.context
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a C++/CMake program without setup.py or pyproject.toml: pip cannot install it, "

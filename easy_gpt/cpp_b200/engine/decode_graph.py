@@ -70,14 +70,14 @@ class DecodeGraph:
         stream = torch.cuda.Stream(device=dev)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
-            runner.model.forward(self.ctx, cache, self.rows)
+            runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         from .. import kernels
         before = kernels.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.logits = runner.model.forward(self.ctx, cache, self.rows)
+            self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
         self.launches = kernels.launch_count - before      # our own kernels inside one replay
 
     def _fill_padding(self, hv: np.ndarray, start_row: int) -> None:

@@ -14,7 +14,8 @@ import torch
 from .. import architectures, parts  # noqa: F401  (registers what the framework ships)
 from ..cache.manager import CacheManager
 from ..config.spec import LayerSpec, ModelSpec
-from ..parts.base import StepContext
+from .. import kernels
+from ..parts.base import PendingNorm, StepContext
 from ..registry import model_spec_from_config, part_class
 from ..weights.loader import load_checked
 
@@ -37,11 +38,18 @@ class Block:
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
 
-    def forward(self, residual, delta, ctx: StepContext, cache, work):
-        x = self.mixer_norm.forward(residual, delta, work)
-        delta = self.mixer.forward(x, ctx, cache)
-        x = self.ff_norm.forward(residual, delta, work)
-        return self.feed_forward.forward(x, ctx)
+    def forward(self, residual, spare, delta, ctx: StepContext, cache, work):
+        """Returns (residual, spare, delta): the buffer that now holds the residual
+        stream, the other one, and the feed-forward's output still to be added."""
+        fused_rows = kernels.SKINNY_MAX_TOKENS
+        pending = PendingNorm(self.mixer_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
+        delta = self.mixer.forward(pending if self.mixer.accepts_pending_norm else pending.materialize(), ctx, cache)
+        assert pending.consumed, "a mixer that accepts a pending norm must use it"
+        residual, spare = pending.residual_after, pending.spare_after
+        pending = PendingNorm(self.ff_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
+        delta = self.feed_forward.forward(pending if self.feed_forward.accepts_pending_norm else pending.materialize(), ctx)
+        assert pending.consumed, "a feed-forward that accepts a pending norm must use it"
+        return pending.residual_after, pending.spare_after, delta
 
 
 class Model:
@@ -109,17 +117,22 @@ class Model:
         return total + self.final_norm.weight_bytes() + self.lm_head.weight_bytes()
 
     # -- forward ------------------------------------------------------------------
-    def forward(self, ctx: StepContext, cache: CacheManager, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    def forward(self, ctx: StepContext, cache: CacheManager, logit_rows: Optional[torch.Tensor],
+                all_rows: bool = False) -> Optional[torch.Tensor]:
         """Runs the batch through every run entry; returns float32 logits at
-        ``logit_rows`` (token indices into the batch), or None when none is wanted."""
+        ``logit_rows`` (token indices into the batch), or None when none is wanted.
+        ``all_rows``: logit_rows is 0..T-1 in order (a decode step), no gather needed."""
         T, H = ctx.num_tokens, self.spec.hidden_size
         residual = torch.empty((T, H), device=self.device, dtype=torch.float32)
+        spare = torch.empty((T, H), device=self.device, dtype=torch.float32)
         work = torch.empty((T, H), device=self.device, dtype=self.dtype)
         self.embedding.forward(ctx.token_ids, residual, ctx.status)
         delta = None
         for e in self.spec.run_order:
-            delta = self.blocks[e.layer].forward(residual, delta, ctx, cache.view(e.cache, e.writes_cache), work)
+            residual, spare, delta = self.blocks[e.layer].forward(residual, spare, delta, ctx,
+                                                                  cache.view(e.cache, e.writes_cache), work)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        x = self.final_norm.forward(residual, delta, work, rows=logit_rows)
-        return self.lm_head.forward(x)
+        pending = PendingNorm(self.final_norm, residual, delta, spare, work, rows=None if all_rows else logit_rows,
+                              max_fused_rows=kernels.SKINNY_MAX_TOKENS)
+        return self.lm_head.forward(pending if self.lm_head.accepts_pending_norm else pending.materialize())

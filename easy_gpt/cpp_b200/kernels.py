@@ -9,6 +9,7 @@ library cannot be built or loaded, importing it raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -68,6 +69,9 @@ class _Signatures:
     eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
                           c_int, c_void_p]
+    eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -242,8 +246,77 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         launch_count += 1                      # the merge kernel
 
 
+SKINNY_MAX_TOKENS = 64
+EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE = 0, 1, 2, 3
+# programmatic dependent launch between the decode kernels (EASY_GPT_PDL=0 switches it off)
+USE_PDL = os.environ.get("EASY_GPT_PDL", "1") != "0"
+
+
+def skinny_row_blocks(n_rows: int) -> int:
+    """16-row blocks per CTA: the largest of 8, 4, 2, 1 that still gives every SM a CTA."""
+    for rb in (8, 4, 2):
+        if -(-n_rows // (rb * 16)) >= SM_COUNT:
+            return rb
+    return 1
+
+
+def gemm_skinny_takes(dtype: torch.dtype, tokens: int, in_features: int) -> bool:
+    return dtype == torch.bfloat16 and 0 < tokens <= SKINNY_MAX_TOKENS and in_features % 8 == 0
+
+
+def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int, *,
+                x: Optional[torch.Tensor] = None, resid_in: Optional[torch.Tensor] = None,
+                resid_out: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
+                gain: Optional[torch.Tensor] = None, eps: float = 0.0, tokens: Optional[int] = None,
+                row_blocks: Optional[int] = None, rope: Optional[dict] = None) -> None:
+    """Decode-step product out = f(x W^T + bias) for up to 64 tokens, bfloat16 weights
+    streamed once.  Either ``x`` (bfloat16 [M, K]) or the norm prologue (``resid_in``,
+    optional ``delta`` and ``resid_out``, ``gain``, ``eps``) gives the input.  Epilogues:
+    EPI_STORE (bfloat16), EPI_F32, EPI_SWIGLU (interleaved gate/up rows), EPI_QKV_ROPE
+    (``rope``: num_heads, num_kv_heads, head_dim, positions, slot_map, k_cache, v_cache,
+    inv_freq, status)."""
+    _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain)
+    N, K = weight.shape
+    norm = x is None
+    if norm:
+        _need(resid_in is not None and gain is not None and resid_in.dtype == gain.dtype == torch.float32
+              and resid_in.is_contiguous() and resid_in.shape[-1] == K, "norm prologue: float32 residual [M, K] and gain")
+        _need(delta is None or (delta.dtype == torch.bfloat16 and delta.is_contiguous() and delta.shape[-1] == K), "delta bfloat16 [M, K]")
+        _need(resid_out is None or (resid_out.dtype == torch.float32 and resid_out.is_contiguous()
+                                    and resid_out.data_ptr() != resid_in.data_ptr()), "resid_out: another float32 buffer")
+        M = tokens if tokens is not None else resid_in.shape[0]
+    else:
+        _need(x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == K and x.stride(1) == 1
+              and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "x: bfloat16 [M, K], 16-byte aligned rows")
+        M = x.shape[0]
+    _need(weight.dtype == torch.bfloat16 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
+          and weight.data_ptr() % 16 == 0, "weight: bfloat16 [N, K], 16-byte aligned rows")
+    _need(gemm_skinny_takes(weight.dtype, M, K), f"gemm_skinny takes 1..{SKINNY_MAX_TOKENS} tokens and K % 8 == 0")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
+    rb = row_blocks or skinny_row_blocks(N)
+    r = rope or {}
+    if epilogue == EPI_QKV_ROPE:
+        kc, vc = r["k_cache"], r["v_cache"]
+        _need(out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape[1] == r["num_heads"] * r["head_dim"], "q out")
+        _need(r["inv_freq"].numel() * 2 == r["head_dim"], "the fused rotation covers the whole head")
+        _need(kc.dtype == torch.bfloat16 and kc.stride(3) == 1 and kc.stride(2) == r["head_dim"] and kc.stride() == vc.stride(), "cache layout")
+        rb = r["head_dim"] // 16
+        extra = (r["num_heads"], r["num_kv_heads"], r["head_dim"], _ptr(r["positions"]), _ptr(r["slot_map"]), _ptr(kc),
+                 _ptr(vc), _ptr(r["inv_freq"]), kc.shape[2], kc.stride(0), kc.stride(1), kc.shape[0] * kc.shape[2],
+                 _ptr(r["status"]))
+    else:
+        want = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
+        cols = N // 2 if epilogue == EPI_SWIGLU else N
+        _need(out.dtype == want and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == cols, "out shape")
+        extra = (0, 0, 0, None, None, None, None, None, 0, 0, 0, 0, None)
+    _check(library().eg_gemm_skinny(
+        _stream(), epilogue, int(norm), int(USE_PDL), _ptr(weight), weight.stride(0), _ptr(bias), M, N, K,
+        _ptr(x), 0 if norm else x.stride(0), _ptr(resid_in), _ptr(resid_out), _ptr(delta), _ptr(gain), float(eps),
+        _ptr(out), out.stride(0), rb, *extra), "gemm_skinny")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = up * silu(gate) for rows laid out [gate (I) | up (I)]."""
+    """out[t, i] = up * silu(gate) for rows laid out [gate_0, up_0, gate_1, up_1, ...]."""
     _cuda(gate_up, out)
     T, two_i = gate_up.shape
     inter = two_i // 2

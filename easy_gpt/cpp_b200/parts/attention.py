@@ -19,7 +19,7 @@ import torch
 from .. import kernels
 from ..registry import register_part
 from ..weights.loader import TensorRequest
-from .base import CacheView, Mixer, PagedKVNeed, StepContext
+from .base import CacheView, Mixer, PagedKVNeed, PendingNorm, StepContext
 from .linear import Linear
 
 
@@ -74,19 +74,37 @@ class Attention(Mixer):
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
 
     # -- forward ----------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
-        T = x.shape[0]
+    accepts_pending_norm = True
+
+    def forward(self, x, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        """x: the normalised input [T, hidden], or a PendingNorm that stands for it."""
+        T = ctx.num_tokens
         tables = ctx.groups[cache.group]
-        qkv = self.qkv(x)
         rot = self.position
         if rot is None:
             raise NotImplementedError("attention without a rotary encoding is not built")
-        kernels.rope_cache(qkv, None, ctx.positions, tables.slot_map if cache.writes else None,
-                           cache.k if cache.writes else None, cache.v if cache.writes else None,
-                           rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
-                           tables.page_size, ctx.status)
-        attn = torch.empty((T, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
-        if kernels.attention_paged_takes(x.dtype, self.head_dim, tables.page_size):
+        pending = x if isinstance(x, PendingNorm) else None
+        dtype, device = ctx.dtype, ctx.device
+        if (pending is not None and pending.fusable and cache.writes and rot.rotary_dim == self.head_dim
+                and self.head_dim in (16, 32, 64, 128)):
+            # decode: add + norm + QKV product + bias + rotation + cache write in one kernel
+            q = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
+            kernels.gemm_skinny(self.qkv.weight, self.qkv.bias_f32, q, kernels.EPI_QKV_ROPE, tokens=T,
+                                **pending.fused_args(),
+                                rope=dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                                          positions=ctx.positions, slot_map=tables.slot_map, k_cache=cache.k,
+                                          v_cache=cache.v, inv_freq=rot.inv_freq, status=ctx.status))
+            qkv = q
+        else:
+            if pending is not None:
+                x = pending.materialize()
+            qkv = self.qkv(x)
+            kernels.rope_cache(qkv, None, ctx.positions, tables.slot_map if cache.writes else None,
+                               cache.k if cache.writes else None, cache.v if cache.writes else None,
+                               rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
+                               tables.page_size, ctx.status)
+        attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
+        if kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
             longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,

@@ -115,6 +115,11 @@ class PositionEncoding(Part):
 
 
 class Norm(Part):
+    def rms_parameters(self):
+        """(gain float32 [size], eps) if this norm is a plain RMSNorm that a consumer's
+        kernel may fold in; None otherwise."""
+        return None
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """residual += delta (float32, in place, unless rows is given); returns the
@@ -123,7 +128,48 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class PendingNorm:
+    """x = norm(residual + delta), not computed yet.
+
+    A block hands this to a part that sets ``accepts_pending_norm``.  Such a part
+    either folds the add and the norm into its own first kernel (``fused_args``,
+    possible when ``fusable``) or calls ``materialize`` and works on the tensor.
+    Either way the sum residual + delta ends up in ``residual_after``: in place
+    when materialised, in the spare buffer when fused (other CTAs of the fused
+    kernel still read the old residual while one of them writes the new one).
+    """
+
+    def __init__(self, norm: "Norm", residual: torch.Tensor, delta: Optional[torch.Tensor], spare: torch.Tensor,
+                 work: torch.Tensor, rows: Optional[torch.Tensor] = None, max_fused_rows: int = 0):
+        self.norm, self.residual, self.delta, self.spare, self.work, self.rows = norm, residual, delta, spare, work, rows
+        self.residual_after = residual
+        self.spare_after = spare
+        self.consumed = False
+        rms = norm.rms_parameters()
+        self.fusable = (rms is not None and rows is None and work.dtype == torch.bfloat16
+                        and 0 < residual.shape[0] <= max_fused_rows
+                        and (delta is None or delta.dtype == torch.bfloat16))
+        self._rms = rms
+
+    def materialize(self) -> torch.Tensor:
+        assert not self.consumed
+        self.consumed = True
+        return self.norm.forward(self.residual, self.delta, self.work, self.rows)
+
+    def fused_args(self) -> dict:
+        """Keyword arguments of ``kernels.gemm_skinny``'s norm prologue."""
+        assert not self.consumed and self.fusable
+        self.consumed = True
+        gain, eps = self._rms
+        if self.delta is not None:
+            self.residual_after, self.spare_after = self.spare, self.residual
+        return dict(resid_in=self.residual, resid_out=self.spare if self.delta is not None else None,
+                    delta=self.delta, gain=gain, eps=eps)
+
+
 class Mixer(Part):
+    accepts_pending_norm = False       # True: forward() takes a PendingNorm instead of a tensor
+
     def __init__(self, params: Mapping, prefix: str, position: Optional[PositionEncoding] = None):
         super().__init__(params, prefix)
         self.position = position
@@ -138,5 +184,7 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_pending_norm = False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -12,7 +12,7 @@ import torch
 from .. import kernels
 from ..registry import register_part
 from ..weights.loader import TensorRequest
-from .base import Part
+from .base import Part, PendingNorm
 from .linear import Linear
 
 
@@ -57,7 +57,16 @@ class LMHead(Part):
     def weight_bytes(self):
         return self.linear.weight_bytes()
 
+    accepts_pending_norm = True
+
     def forward(self, x):
+        """x: normalised rows [R, hidden] or a PendingNorm; returns float32 logits [R, vocab]."""
+        if isinstance(x, PendingNorm):
+            if x.fusable:
+                out = torch.empty((x.residual.shape[0], self.vocab), device=x.residual.device, dtype=torch.float32)
+                kernels.gemm_skinny(self.linear.weight, None, out, kernels.EPI_F32, **x.fused_args())
+                return out
+            x = x.materialize()
         return self.linear(x, out_dtype=torch.float32)
 
 

@@ -1,8 +1,9 @@
 """y = x W^T + b with W stored [out, in] (src/models/linear.cpp:42-44).
 
-In bfloat16 the product goes to the library GEMM (cuBLAS through torch), where
-the reference's engine calls cublasGemmEx too (src/cuda/ops/matmul.cu:194-204),
-unless a hand-written kernel takes the shape.  In float32 it is always the
+In bfloat16, steps of up to 64 tokens (decoding) go to the package's own
+weight-streaming kernel (``csrc/gemm_skinny.cu``); larger ones go to the library
+GEMM (cuBLAS through torch), where the reference's engine calls cublasGemmEx too
+(src/cuda/ops/matmul.cu:194-204).  In float32 it is always the
 package's own FFMA kernel: true 32-bit arithmetic whose sums do not depend on
 the batch.
 """
@@ -44,6 +45,11 @@ class Linear:
         if self.dtype == torch.float32:
             out = torch.empty((M, self.out_features), device=x.device, dtype=torch.float32)
             kernels.gemm_f32_nt(x, self.weight, self.bias_f32, out)
+            return out
+        if kernels.gemm_skinny_takes(self.dtype, M, self.in_features) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+            out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype)
+            kernels.gemm_skinny(self.weight, self.bias_f32, out,
+                                kernels.EPI_F32 if out_dtype == torch.float32 else kernels.EPI_STORE, x=x)
             return out
         if out_dtype == torch.float32:
             out = torch.mm(x, self.weight.t(), out_dtype=torch.float32)

@@ -1,6 +1,8 @@
 """SwiGLU feed-forward: down( up(x) * silu(gate(x)) ) (src/models/mlp.cpp:41-49).
-gate and up are stacked into one product; parameters: hidden_size,
-intermediate_size, bias."""
+gate and up become one product whose weight rows are interleaved (gate_0, up_0,
+gate_1, up_1, ...), so that every tile of the product holds both halves of the
+outputs it covers and the activation can run in the product's epilogue.
+Parameters: hidden_size, intermediate_size, bias."""
 from __future__ import annotations
 
 import torch
@@ -8,7 +10,7 @@ import torch
 from .. import kernels
 from ..registry import register_part
 from ..weights.loader import TensorRequest
-from .base import FeedForward
+from .base import FeedForward, PendingNorm
 from .linear import Linear
 
 
@@ -32,9 +34,10 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors, device, dtype):
         p = self.prefix
-        w = torch.cat([tensors[f"{p}.gate_proj.weight"].float(), tensors[f"{p}.up_proj.weight"].float()], dim=0)
-        b = torch.cat([tensors[f"{p}.gate_proj.bias"].float().reshape(-1),
-                       tensors[f"{p}.up_proj.bias"].float().reshape(-1)]) if self.bias else None
+        w = torch.stack([tensors[f"{p}.gate_proj.weight"].float(), tensors[f"{p}.up_proj.weight"].float()], dim=1)
+        w = w.reshape(2 * self.inter, self.hidden)
+        b = torch.stack([tensors[f"{p}.gate_proj.bias"].float().reshape(-1),
+                         tensors[f"{p}.up_proj.bias"].float().reshape(-1)], dim=1).reshape(-1) if self.bias else None
         self.gate_up = Linear(w, b, device, dtype)
         self.down = Linear(tensors[f"{p}.down_proj.weight"], tensors.get(f"{p}.down_proj.bias") if self.bias else None,
                            device, dtype)
@@ -42,10 +45,23 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
+    accepts_pending_norm = True
+
     def forward(self, x, ctx):
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.inter), device=x.device, dtype=x.dtype)
-        kernels.swiglu(gu, act)
+        """x: the normalised input [T, hidden], or a PendingNorm that stands for it."""
+        T = ctx.num_tokens
+        act = torch.empty((T, self.inter), device=ctx.device, dtype=ctx.dtype)
+        if isinstance(x, PendingNorm) and x.fusable:
+            # decode: add + norm + gate/up product + SwiGLU in one kernel
+            kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, tokens=T,
+                                **x.fused_args())
+        else:
+            if isinstance(x, PendingNorm):
+                x = x.materialize()
+            if kernels.gemm_skinny_takes(ctx.dtype, T, self.hidden):
+                kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, x=x)
+            else:
+                kernels.swiglu(self.gate_up(x), act)
         return self.down(act)
 
 

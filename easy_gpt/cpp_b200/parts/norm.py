@@ -30,6 +30,9 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.gain.numel() * 4
 
+    def rms_parameters(self):
+        return self.gain, self.eps
+
     def forward(self, residual, delta, out, rows: Optional[torch.Tensor] = None):
         kernels.add_rmsnorm(residual, delta, self.gain, out, self.eps, rows)
         n = rows.numel() if rows is not None else residual.shape[0]

@@ -292,7 +292,117 @@ def test_swiglu(dtype, T, I):
     gu = (torch.randn(T, 2 * I, generator=gen(12)) * 3).to(dtype)
     out = torch.empty(T, I, dtype=dtype, device=DEV)
     kernels.swiglu(gu.to(DEV), out)
-    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    g, u = gu.float()[:, 0::2], gu.float()[:, 1::2]                 # interleaved rows: gate_0, up_0, gate_1, ...
     want = u * (g * (1.0 / (1.0 + torch.exp(-g))))
     tol = 1e-6 * float(want.abs().max()) if dtype == torch.float32 else 8e-3 * float(want.abs().max())
     assert float((out.float().cpu() - want).abs().max()) <= tol
+
+
+# -- the decode-step product with its prologues and epilogues -------------------------------
+
+def bf(t):
+    return t.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 32, 64])
+@pytest.mark.parametrize("N, K, rb", [(48, 40, 1), (1152, 896, 4), (200, 4864, 1), (391, 80, 8), (896, 896, 2)])
+def test_gemm_skinny_plain(M, N, K, rb):
+    from easy_gpt.cpp_b200 import kernels
+
+    x = bf(torch.randn(M, K, generator=gen(20)))
+    w = bf(torch.randn(N, K, generator=gen(21)) * 0.1)
+    b = torch.randn(N, generator=gen(22))
+    want = x.float() @ w.float().t() + b
+    scale = float(want.abs().max())
+    out32 = torch.empty(M, N, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), b.to(DEV), out32, kernels.EPI_F32, x=x.to(DEV), row_blocks=rb)
+    assert float((out32.cpu() - want).abs().max()) <= 1e-5 * scale * math.sqrt(K)          # float32 accumulation
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), None, out16, kernels.EPI_STORE, x=x.to(DEV))
+    assert float((out16.float().cpu() - (want - b)).abs().max()) <= 8e-3 * scale
+    # a token's result does not depend on the other tokens of the step
+    one = torch.empty(1, N, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), b.to(DEV), one, kernels.EPI_F32, x=x[M - 1:M].to(DEV).clone(), row_blocks=rb)
+    assert float((one[0] - out32[M - 1]).abs().max()) <= 1e-6 * scale
+
+
+@pytest.mark.parametrize("M", [2, 8, 40])
+def test_gemm_skinny_norm_prologue_and_swiglu(M):
+    from easy_gpt.cpp_b200 import kernels
+
+    K, I = 896, 304
+    resid = torch.randn(M, K, generator=gen(23)) * 2
+    delta = bf(torch.randn(M, K, generator=gen(24)))
+    gain = 1 + 0.1 * torch.randn(K, generator=gen(25))
+    gate, up = torch.randn(I, K, generator=gen(26)) * 0.05, torch.randn(I, K, generator=gen(27)) * 0.05
+    w = bf(torch.stack([gate, up], dim=1).reshape(2 * I, K))
+    eps = 1e-5
+    summed = resid + delta.float()
+    xn = bf(plain_model.rms_norm(summed, gain, eps)).float()                     # the kernel rounds x to bfloat16 too
+    g = xn @ bf(gate).float().t()
+    u = xn @ bf(up).float().t()
+    want = u * (g / (1 + torch.exp(-g)))
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    r_in, r_out = resid.to(DEV), torch.zeros(M, K, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), None, out, kernels.EPI_SWIGLU, resid_in=r_in, resid_out=r_out, delta=delta.to(DEV),
+                        gain=gain.to(DEV), eps=eps)
+    assert torch.equal(r_out.cpu(), summed) and torch.equal(r_in.cpu(), resid)
+    assert float((out.float().cpu() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    # without delta: nothing is written to a residual
+    out2 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), None, out2, kernels.EPI_SWIGLU, resid_in=r_out, gain=gain.to(DEV), eps=eps)
+    assert float((out2.float() - out.float()).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("NH, NKV, HD", [(14, 2, 64), (6, 2, 32), (3, 1, 128), (4, 4, 16)])
+def test_gemm_skinny_qkv_rope_cache(NH, NKV, HD):
+    """The fused kernel against the unfused chain: norm, product, rope_cache."""
+    from easy_gpt.cpp_b200 import kernels
+    from easy_gpt.cpp_b200.parts.rope import RotaryEncoding
+
+    M, K, ps, pages = 5, 80 if HD == 16 else 896, 16, 9
+    N = (NH + 2 * NKV) * HD
+    resid = torch.randn(M, K, generator=gen(30))
+    delta = bf(torch.randn(M, K, generator=gen(31)) * 0.5)
+    gain = 1 + 0.1 * torch.randn(K, generator=gen(32))
+    w = bf(torch.randn(N, K, generator=gen(33)) * 0.05)
+    bias = torch.randn(N, generator=gen(34)) * 0.3
+    positions = torch.tensor([0, 5, 77, 4000, 130], dtype=torch.int32)
+    slots = torch.tensor([3, 20, 143, 64, 17], dtype=torch.int32)
+    inv = RotaryEncoding.inverse_frequencies(HD, 1e6)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(pages, NKV, ps, HD, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(M, NH * HD, dtype=torch.bfloat16, device=DEV)
+    r_out = torch.empty(M, K, device=DEV)
+    kernels.gemm_skinny(w.to(DEV), bias.to(DEV), q, kernels.EPI_QKV_ROPE, resid_in=resid.to(DEV), resid_out=r_out,
+                        delta=delta.to(DEV), gain=gain.to(DEV), eps=1e-6,
+                        rope=dict(num_heads=NH, num_kv_heads=NKV, head_dim=HD, positions=positions.to(DEV),
+                                  slot_map=slots.to(DEV), k_cache=kc, v_cache=vc, inv_freq=inv.to(DEV), status=status))
+    assert status.item() == 0
+    # plain chain in float32 on the same bfloat16-rounded inputs
+    xn = bf(plain_model.rms_norm(resid + delta.float(), gain, 1e-6)).float()
+    full = xn @ w.float().t() + bias
+    qw = plain_model.rope(full[:, :NH * HD].reshape(M, NH, HD), positions.long(), 1e6).reshape(M, -1)
+    kw = plain_model.rope(full[:, NH * HD:(NH + NKV) * HD].reshape(M, NKV, HD), positions.long(), 1e6)
+    vw = full[:, (NH + NKV) * HD:].reshape(M, NKV, HD)
+    tol = 1e-2 * float(full.abs().max())
+    assert float((q.float().cpu() - qw).abs().max()) <= tol
+    for m in range(M):
+        page, off = int(slots[m]) // ps, int(slots[m]) % ps
+        assert float((kc[page, :, off].float().cpu() - kw[m]).abs().max()) <= tol
+        assert float((vc[page, :, off].float().cpu() - vw[m]).abs().max()) <= tol
+    assert int((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == M                  # only the five slots were written
+
+
+def test_gemm_skinny_refuses_what_it_does_not_take():
+    from easy_gpt.cpp_b200 import kernels
+
+    w = bf(torch.randn(32, 40)).to(DEV)
+    with pytest.raises(kernels.KernelError, match="takes 1..64 tokens"):
+        kernels.gemm_skinny(w, None, torch.empty(65, 32, dtype=torch.bfloat16, device=DEV), kernels.EPI_STORE,
+                            x=bf(torch.randn(65, 40)).to(DEV))
+    w2 = bf(torch.randn(32, 36)).to(DEV)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_skinny(w2, None, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV), kernels.EPI_STORE,
+                            x=bf(torch.randn(2, 36)).to(DEV))
