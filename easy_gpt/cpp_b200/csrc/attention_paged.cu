@@ -11,8 +11,8 @@
 // a quarter of every tile each, and keep a running softmax (m, l, acc) in
 // float32 (src/cuda/ops/self_attn_detail.cuh:325-382).  The warps' states are
 // merged in shared memory; with one split the result is written at once, else a
-// partial (m, l, acc) goes to scratch memory and `attention_merge_kernel` merges
-// the splits.
+// partial (m, l, acc) goes to scratch memory and the CTA of that (token, KV head)
+// that finishes last (a ticket counter; nobody waits) merges the splits in order.
 //
 // score = (q . k) * scale in float32, exp by expf, P is rounded to bfloat16 for the
 // P V product (as V is bfloat16 anyway); sums and the accumulator stay float32.
@@ -29,7 +29,8 @@ struct Layout {
     static constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
     static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;          // K or V
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int STAGES = (3 * STAGE_BYTES <= 160 * 1024) ? 3 : 2;
+    // up to five tiles in flight per CTA, within about 96 KB of shared memory (two stages at least)
+    static constexpr int STAGES = (96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((96 * 1024 / STAGE_BYTES) >= 2 ? (96 * 1024 / STAGE_BYTES) : 2);
     static constexpr int MERGE_BYTES = 4 * 16 * (HD + 2) * 4;
     static constexpr int SMEM = (STAGES * STAGE_BYTES > MERGE_BYTES) ? STAGES * STAGE_BYTES : MERGE_BYTES;
     __device__ static __forceinline__ int offset(int row, int chunk) {      // bytes inside a K or V tile
@@ -54,12 +55,19 @@ struct Params {
     int num_heads, num_kv_heads, page_size, num_pages, window, splits;
     float scale;
     int* status;
+    const void* prefetch;         // weights of a kernel that runs soon: pulled into L2 meanwhile
+    long long prefetch_bytes;
+    int* counters;                // [tokens * gridDim.y] tickets, zero before and after every launch
+    int use_pdl;
+    unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
 };
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p) {
     using L = Layout<HD>;
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int is_last;
+    TraceScope trace_scope(p.trace);
     const int t = blockIdx.x;
     const int G = p.num_heads / p.num_kv_heads;
     const int gblocks = (G + 15) / 16;
@@ -69,6 +77,20 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
 
+    if (p.prefetch) {
+        constexpr long long PIECE = 4096;
+        const long long pieces = (p.prefetch_bytes + PIECE - 1) / PIECE;
+        const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+        for (long long i = cta * THREADS + threadIdx.x; i < pieces; i += ctas * THREADS) {
+            const long long off = i * PIECE;
+            const long long n = p.prefetch_bytes - off < PIECE ? p.prefetch_bytes - off : PIECE;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(static_cast<const char*>(p.prefetch) + off),
+                         "r"((unsigned)(n & ~15LL)) : "memory");
+        }
+    }
+    if (p.use_pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");     // q and the new keys come from the kernel before
+    trace_scope.mark(0);
     const int pos = p.positions[t];
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
     const int* table = p.block_table + (size_t)p.token_seq[t] * p.table_stride;
@@ -127,9 +149,11 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         if (s < ntiles) load_tile(my_lo + s, s);
         cp_async_commit();
     }
+    trace_scope.mark(1);
     for (int it = 0; it < ntiles; ++it) {
         cp_async_wait<L::STAGES - 2>();
         __syncthreads();
+        if (it == 0) trace_scope.mark(2);
         {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
             const int nxt = it + L::STAGES - 1;
             if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES);
@@ -201,6 +225,8 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         }
     }
     cp_async_wait<0>();
+    trace_scope.mark(3);
+    if (p.use_pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     __syncthreads();                                                              // the pipeline's memory is free now
 
     // ---- merge the four warps: rows r = gid, gid + 8
@@ -255,25 +281,55 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
             }
         }
     }
-}
+    trace_scope.mark(4);
+    if (p.splits == 1) return;
 
-// out[t, h, :] = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}
-__global__ void attention_merge_kernel(const float* __restrict__ partial_acc, const float* __restrict__ partial_ml,
-                                       bf16* __restrict__ out, int ldo, int num_heads, int head_dim, int splits) {
-    const int t = blockIdx.x, h = blockIdx.y;
-    const size_t base = ((size_t)t * num_heads + h) * splits;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[(base + s) * 2]);
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float l = 0.f, a = 0.f;
-        if (m > -INFINITY) {
-            for (int s = 0; s < splits; ++s) {
-                const float f = expf(partial_ml[(base + s) * 2] - m);
-                l += partial_ml[(base + s) * 2 + 1] * f;
-                a += partial_acc[(base + s) * head_dim + d] * f;
-            }
+    // ---- the last CTA of this (token, KV head) to get here merges the splits, in order:
+    // out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = p.counters + (size_t)t * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        is_last = ticket == p.splits - 1;
+        if (is_last) *counter = 0;                                                // all have arrived: ready for the next launch
+    }
+    __syncthreads();
+    trace_scope.mark(5);
+    if (!is_last) return;
+    __threadfence();
+    // 1. every row's maximum and per-split factor e^{m_s - m}; the loads of all splits are in flight together
+    float* fac = reinterpret_cast<float*>(smem);                                  // [rows][splits]
+    float* inv_l = fac + 16 * p.splits;                                            // [rows]
+    for (int e = threadIdx.x; e < rows * p.splits; e += THREADS) {
+        const int r = e / p.splits, s2 = e % p.splits;
+        const size_t slot = ((size_t)t * p.num_heads + kvh * G + g0 + r) * p.splits + s2;
+        fac[r * p.splits + s2] = __ldcg(p.partial_ml + slot * 2);                  // m_s for now
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) {
+        const int r = threadIdx.x;
+        float m = -INFINITY;
+        for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, fac[r * p.splits + s2]);
+        const size_t base = ((size_t)t * p.num_heads + kvh * G + g0 + r) * p.splits;
+        float l = 0.f;
+        for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float f = m > -INFINITY ? expf(fac[r * p.splits + s2] - m) : 0.f;
+            fac[r * p.splits + s2] = f;
+            l += __ldcg(p.partial_ml + (base + s2) * 2 + 1) * f;
         }
-        out[(size_t)t * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+        inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
+    }
+    __syncthreads();
+    // 2. the weighted sum of the splits' accumulators
+    for (int e = threadIdx.x; e < rows * HD; e += THREADS) {
+        const int r = e / HD, d = e % HD;
+        const int h = kvh * G + g0 + r;
+        const float* src = p.partial_acc + ((size_t)t * p.num_heads + h) * p.splits * HD + d;
+        float a = 0.f;
+#pragma unroll 8
+        for (int s2 = 0; s2 < p.splits; ++s2) a += __ldcg(src + (size_t)s2 * HD) * fac[r * p.splits + s2];
+        p.out[(size_t)t * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(a * inv_l[r]);
     }
 }
 
@@ -287,34 +343,39 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
         configured = true;
     }
     const int G = p.num_heads / p.num_kv_heads;
-    dim3 grid(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
-    attention_paged_kernel<HD><<<grid, THREADS, L::SMEM, stream>>>(p);
-    int rc = eg_launch_status();
-    if (rc == 0 && p.splits > 1) {
-        dim3 mg(tokens, p.num_heads);
-        attention_merge_kernel<<<mg, HD < 128 ? 64 : 128, 0, stream>>>(p.partial_acc, p.partial_ml, p.out, p.ldo, p.num_heads, HD, p.splits);
-        rc = eg_launch_status();
-    }
-    return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = L::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.use_pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD>, p);
 }
 
 }  // namespace
 
 // Head sizes 32, 64, 128, 256 and page sizes that are multiples of 16; anything else
 // returns cudaErrorInvalidValue and the caller uses the generic kernel.
-// partial_acc / partial_ml: scratch of tokens*heads*splits*(head_dim + 2) floats, needed when splits > 1.
+// partial_acc / partial_ml: scratch of tokens*heads*splits*(head_dim + 2) floats, and counters: one zeroed int
+// per (token, KV head block) (left zero), needed when splits > 1.
 EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
                               const int* block_table, int table_stride, const int* token_seq, const int* positions,
                               void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
                               int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
-                              int num_pages, int window, float scale, int splits, int* status) {
+                              int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
+                              long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace) {
     if (tokens <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
-        splits > 65535 || (splits > 1 && (!partial_acc || !partial_ml)))
+        splits > 128 || (splits > 1 && (!partial_acc || !partial_ml || !counters)))
         return (int)cudaErrorInvalidValue;
     Params p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
              table_stride, token_seq, positions, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
-             page_size, num_pages, window, splits, scale, status};
+             page_size, num_pages, window, splits, scale, status, prefetch_bytes >= 16 ? prefetch : nullptr, prefetch_bytes,
+             counters, use_pdl, trace};
     switch (head_dim) {
         case 32: return launch<32>(stream, p, tokens);
         case 64: return launch<64>(stream, p, tokens);

@@ -56,4 +56,26 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return r;
 }
 
+// Optional timeline of a launch: the earliest CTA start and the latest CTA end on the GPU's
+// nanosecond clock, kept in trace[0] / trace[1] (the host presets them to ~0 / 0), and phase
+// stamps of the first CTA in trace[2..15].  A null pointer costs one predicated branch.
+struct TraceScope {
+    unsigned long long* slot;
+    __device__ __forceinline__ static unsigned long long now() {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        return t;
+    }
+    __device__ __forceinline__ explicit TraceScope(unsigned long long* s) : slot(s) {
+        if (slot && threadIdx.x == 0) atomicMin(slot, now());
+    }
+    __device__ __forceinline__ ~TraceScope() {
+        if (slot && threadIdx.x == 0) atomicMax(slot + 1, now());
+    }
+    // Phase stamps of the launch's first CTA: slot[2 + i], i < 14.
+    __device__ __forceinline__ void mark(int i) const {
+        if (slot && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) slot[2 + i] = now();
+    }
+};
+
 static inline int eg_launch_status() { return (int)cudaGetLastError(); }

@@ -4,19 +4,24 @@
 // kernel is built around that stream.  The roles of the MMA are swapped: 16 weight
 // rows are the M side of mma.m16n8k16 and 8 tokens are its N side, so no tensor
 // core work is wasted on padding tokens up to a tile.  Every thread fetches its
-// piece of the weight fragment with one 16-byte load straight from global memory
-// (8 consecutive k of one row; the k order inside a 32-wide chunk is permuted the
-// same way for both operands, which a sum does not notice), several chunks ahead,
-// and nothing of W passes through shared memory.  A CTA has 8 warps arranged as
-// RB row blocks x KS slices of K; the slices are summed through shared memory in a
-// fixed order.
+// piece of the weight fragment with one 32-byte load straight from global memory
+// (16 consecutive k of one row, so that a warp's load covers whole 128-byte lines;
+// the k order inside a 64-wide chunk is permuted the same way for both operands,
+// which a sum does not notice), several chunks ahead, and nothing of W passes
+// through shared memory.  A CTA's warps are arranged as RB row blocks x KS slices
+// of K, and K may be cut further across gridDim.y CTAs.  Slices are summed in a
+// fixed order: inside a CTA through shared memory, across CTAs through scratch
+// memory by the CTA that arrives last (a ticket counter; nobody waits for anybody).
 //
 // Prologues (what x is):
 //   plain      x is a bfloat16 matrix in global memory
-//   norm       x = gain * rmsnorm(residual_in + delta) computed by every CTA into
-//              shared memory (float32 sums, src/models/norm.cpp:46-60); CTA 0 also
-//              writes residual_in + delta to residual_out (another buffer, so that
-//              no CTA reads what CTA 0 has already updated)
+//   norm       x = gain * rmsnorm(residual_in + delta), computed by every CTA in one
+//              pass: v = residual_in + delta, the row's sum of squares in float32
+//              (src/models/norm.cpp:46-60) and bfloat16(gain * v) into shared memory;
+//              the row's factor 1/sqrt(mean + eps) multiplies the product's result
+//              instead of every x (the product is linear in x).  CTA 0 also writes v to
+//              residual_out (another buffer, so that no CTA reads what CTA 0 has
+//              already updated).  Meant for a few tokens: every CTA repeats it.
 // Epilogues (what happens to y):
 //   store      + bias -> bfloat16 [M, N]
 //   f32        + bias -> float32 [M, N] (logits)
@@ -26,12 +31,15 @@
 //
 // Every kernel starts streaming its weights before it waits for the kernel in front
 // of it (programmatic dependent launch), so the pipeline of small kernels overlaps.
+// A kernel can also be told which weights a later kernel will stream; when its own
+// stream has been issued it asks the L2 (126 MB) to fetch them.
 #include "mma_utils.cuh"
 
 namespace {
 
-constexpr int THREADS = 256;
-constexpr int UNROLL = 4;            // 32-wide k chunks in flight per warp
+constexpr int MAX_THREADS = 512;
+constexpr int UNROLL = 4;            // 64-wide k chunks in flight per warp (256 bytes per thread)
+constexpr int CHUNK = 64;
 
 enum { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3 };
 
@@ -61,20 +69,51 @@ struct Params {
     int* status;
     int RB, KS;
     int use_pdl;
+    const void* prefetch;        // weights of a kernel that runs soon: pulled into L2 meanwhile
+    long long prefetch_bytes;
+    float* scratch;              // [gridDim.y][gridDim.x][RB*16][tokens] partial sums when K is cut across CTAs
+    int* counters;               // [gridDim.x] tickets, zero before and after every launch
+    unsigned long long* trace;   // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
 };
 
-__device__ __forceinline__ uint4 ldg128(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+struct W32 {                      // 16 consecutive bfloat16 of one weight row
+    uint32_t r[8];
+};
+
+__device__ __forceinline__ W32 ldg256(const void* p) {
+    W32 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
+                 : "l"(p));
     return v;
+}
+
+// Asks the L2 to fetch [ptr, ptr + bytes) (16-byte aligned, a multiple of 16 bytes); nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* ptr, unsigned bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
+}
+
+// Every CTA asks for its share of a later kernel's weights, in pieces of 4 KB.
+__device__ __forceinline__ void prefetch_next_weights(const void* base, long long bytes) {
+    constexpr long long PIECE = 4096;
+    const long long pieces = (bytes + PIECE - 1) / PIECE;
+    const long long cta = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+    const long long ctas = (long long)gridDim.x * gridDim.y;
+    for (long long i = cta * blockDim.x + threadIdx.x; i < pieces; i += ctas * blockDim.x) {
+        const long long off = i * PIECE;
+        const long long n = bytes - off < PIECE ? bytes - off : PIECE;
+        prefetch_l2(static_cast<const char*>(base) + off, (unsigned)(n & ~15LL));
+    }
 }
 
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
 template <int NT, int EPI, bool NORM>
-__global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
+    extern __shared__ __align__(32) unsigned char smem[];
+    __shared__ int is_last;
+    TraceScope trace_scope(p.trace);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int rb = warp % p.RB, ks = warp / p.RB;
@@ -84,115 +123,193 @@ __global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
     const bool ok_a = row_a < p.N, ok_b = row_b < p.N;
     const bf16* wa = p.W + (size_t)(ok_a ? row_a : 0) * p.ldw;
     const bf16* wb = p.W + (size_t)(ok_b ? row_b : 0) * p.ldw;
-    const int chunks = (p.K + 31) / 32;
-    const int per = (chunks + p.KS - 1) / p.KS;
-    const int c_lo = ks * per, c_hi = min(chunks, c_lo + per);
+    const int chunks = (p.K + CHUNK - 1) / CHUNK;
+    const int slices = p.KS * gridDim.y;
+    const int per = (chunks + slices - 1) / slices;
+    const int c_lo = (blockIdx.y * p.KS + ks) * per, c_hi = min(chunks, c_lo + per);
+    constexpr int MT = NT * 8;
 
     // ---- start the weight stream: UNROLL chunks per row in registers
-    uint4 wra[UNROLL], wrb[UNROLL];
-    auto fetch = [&](int c, uint4& ra, uint4& rb_) {
-        const int k = c * 32 + tig * 8;
-        const bool in = c < c_hi && k < p.K;                      // K is a multiple of 8
-        ra = (in && ok_a) ? ldg128(wa + k) : make_uint4(0, 0, 0, 0);
-        rb_ = (in && ok_b) ? ldg128(wb + k) : make_uint4(0, 0, 0, 0);
+    W32 wra[UNROLL], wrb[UNROLL];
+    auto fetch = [&](int c, W32& ra, W32& rb_) {
+        const int k = c * CHUNK + tig * 16;
+        const bool in = c < c_hi && k < p.K;                      // K is a multiple of 16
+        if (in && ok_a) ra = ldg256(wa + k);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ra.r[i] = 0u;
+        if (in && ok_b) rb_ = ldg256(wb + k);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rb_.r[i] = 0u;
     };
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) fetch(c_lo + u, wra[u], wrb[u]);
+    if (p.prefetch) prefetch_next_weights(p.prefetch, p.prefetch_bytes);
 
+    trace_scope.mark(0);
     if (p.use_pdl) grid_dependency_wait();                        // from here on the previous kernel's results are read
+    trace_scope.mark(1);
 
-    // ---- x: normalised into shared memory, or read from global memory
+    // ---- x: staged into shared memory by the norm prologue, or read from global memory
     const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;     // bytes; rows 16 banks apart
     unsigned char* xs = smem;
+    float* row_factor = reinterpret_cast<float*>(smem + (size_t)MT * xs_stride);      // [MT]
+    const int nwarps = blockDim.x >> 5;
     if (NORM) {
-        for (int m = warp; m < NT * 8; m += THREADS / 32) {
-            bf16* dst = reinterpret_cast<bf16*>(xs + (size_t)m * xs_stride);
+        const int quads = p.K / 4;
+        for (int m = warp; m < MT; m += nwarps) {
+            uint2* dst = reinterpret_cast<uint2*>(xs + (size_t)m * xs_stride);
             if (m >= p.M) {
-                for (int k = lane; k < p.K; k += 32) dst[k] = __float2bfloat16_rn(0.f);
+                for (int i = lane; i < quads; i += 32) dst[i] = make_uint2(0u, 0u);
+                if (lane == 0) row_factor[m] = 0.f;
                 continue;
             }
-            const float* r = p.resid_in + (size_t)m * p.K;
-            const bf16* d = p.delta ? p.delta + (size_t)m * p.K : nullptr;
-            float* ro = (blockIdx.x == 0 && p.resid_out) ? p.resid_out + (size_t)m * p.K : nullptr;
+            const float4* r = reinterpret_cast<const float4*>(p.resid_in + (size_t)m * p.K);
+            const uint2* d = p.delta ? reinterpret_cast<const uint2*>(p.delta + (size_t)m * p.K) : nullptr;
+            const float4* g = reinterpret_cast<const float4*>(p.gain);
+            float4* ro = (blockIdx.x == 0 && blockIdx.y == 0 && p.resid_out)
+                             ? reinterpret_cast<float4*>(p.resid_out + (size_t)m * p.K) : nullptr;
             float ss = 0.f;
-            for (int k = lane; k < p.K; k += 32) {
-                float v = r[k];
-                if (d) v += __bfloat162float(d[k]);
-                if (ro) ro[k] = v;
-                ss += v * v;
+            // four quads per lane at a time: all loads of a batch are issued before anything is
+            // stored, so that they overlap (a store to the residual could alias them otherwise)
+            constexpr int BATCH = 4;
+            for (int i0 = lane; i0 < quads; i0 += 32 * BATCH) {
+                float4 rv[BATCH], gv[BATCH];
+                uint2 dv[BATCH];
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const int i = i0 + 32 * b;
+                    if (i < quads) {
+                        rv[b] = r[i];
+                        gv[b] = g[i];
+                        dv[b] = d ? d[i] : make_uint2(0u, 0u);
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < BATCH; ++b) {
+                    const int i = i0 + 32 * b;
+                    if (i < quads) {
+                        float4 v = rv[b];
+                        const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&dv[b].x);
+                        const __nv_bfloat162 d23 = *reinterpret_cast<const __nv_bfloat162*>(&dv[b].y);
+                        v.x += __low2float(d01); v.y += __high2float(d01); v.z += __low2float(d23); v.w += __high2float(d23);
+                        if (ro) ro[i] = v;
+                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                        dst[i] = make_uint2(pack_bf16(gv[b].x * v.x, gv[b].y * v.y), pack_bf16(gv[b].z * v.z, gv[b].w * v.w));
+                    }
+                }
             }
             ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
-            for (int k = lane; k < p.K; k += 32) {
-                float v = r[k];
-                if (d) v += __bfloat162float(d[k]);
-                dst[k] = __float2bfloat16_rn(p.gain[k] * (v * inv));
-            }
+            if (lane == 0) row_factor[m] = 1.0f / sqrtf(ss / (float)p.K + p.eps);
         }
         __syncthreads();
     }
 
+    trace_scope.mark(2);
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     for (int c = c_lo; c < c_hi; c += UNROLL) {
-        uint4 ca[UNROLL], cb[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            ca[u] = wra[u];
-            cb[u] = wrb[u];
-        }
+            const int k = (c + u) * CHUNK + tig * 16;
+            if (c + u < c_hi) {                                   // the same for the whole warp
+                // Lanes whose k lies beyond K feed zeros but still take part: mma.sync is
+                // a warp-wide instruction and must not be skipped by some lanes.
+                const bool k_in = k < p.K;
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) fetch(c + UNROLL + u, wra[u], wrb[u]);
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int m = nt * 8 + gid;
+                    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+                    if (NORM) {
+                        if (k_in) {
+                            const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)m * xs_stride + (size_t)k * 2);
+                            x0 = src[0];
+                            x1 = src[1];
+                        }
+                    } else if (k_in && m < p.M) {
+                        const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + k);
+                        x0 = src[0];
+                        x1 = src[1];
+                    }
+                    // four k-steps of 16: step s takes this thread's elements 4s .. 4s+3 of both operands
+                    const uint32_t xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k = (c + u) * 32 + tig * 8;
-            if (c + u >= c_hi) continue;                          // the same for the whole warp
-            // Lanes whose k lies beyond K feed zeros but still take part: mma.sync is
-            // a warp-wide instruction and must not be skipped by some lanes.
-            const bool k_in = k < p.K;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int m = nt * 8 + gid;
-                uint4 xv = make_uint4(0, 0, 0, 0);
-                if (NORM) {
-                    if (k_in) xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * xs_stride + (size_t)k * 2);
-                } else {
-                    if (k_in && m < p.M) xv = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + k);
+                    for (int s = 0; s < 4; ++s) {
+                        const uint32_t a[4] = {wra[u].r[2 * s], wrb[u].r[2 * s], wra[u].r[2 * s + 1], wrb[u].r[2 * s + 1]};
+                        mma_bf16_16816(acc[nt], a, xr[2 * s], xr[2 * s + 1]);
+                    }
                 }
-                const uint32_t a0[4] = {ca[u].x, cb[u].x, ca[u].y, cb[u].y};
-                const uint32_t a1[4] = {ca[u].z, cb[u].z, ca[u].w, cb[u].w};
-                mma_bf16_16816(acc[nt], a0, xv.x, xv.y);
-                mma_bf16_16816(acc[nt], a1, xv.z, xv.w);
             }
+            fetch(c + UNROLL + u, wra[u], wrb[u]);                // this register set's next chunk, UNROLL chunks ahead
         }
     }
+    trace_scope.mark(3);
     if (p.use_pdl) grid_dependents_launch();                      // the next kernel may start its own weight stream
 
-    // ---- sum the K slices: red[ks][row in CTA][token]
+    // ---- sum the K slices of this CTA: red[warp][row][token] -> tile[row in CTA][token]
+    float my_factor = 1.f;
+    if (NORM && threadIdx.x < MT) my_factor = row_factor[threadIdx.x];
     __syncthreads();                                              // xs is dead; reuse the memory
-    float* red = reinterpret_cast<float*>(smem);
-    const int MT = NT * 8;
+    float* red = reinterpret_cast<float*>(smem);                  // [nwarps][16][MT]
+    float* tile = red + (size_t)nwarps * 16 * MT;                 // [rows_per_cta][MT]
+    float* factor = tile + (size_t)rows_per_cta * MT;             // [MT]
+    if (threadIdx.x < MT) factor[threadIdx.x] = my_factor;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        float* base = red + ((size_t)ks * rows_per_cta + rb * 16) * MT + nt * 8 + 2 * tig;
+        float* base = red + (size_t)warp * 16 * MT + nt * 8 + 2 * tig;
         base[(size_t)gid * MT] = acc[nt][0];
         base[(size_t)gid * MT + 1] = acc[nt][1];
         base[(size_t)(gid + 8) * MT] = acc[nt][2];
         base[(size_t)(gid + 8) * MT + 1] = acc[nt][3];
     }
     __syncthreads();
-    auto value = [&](int r, int m) -> float {                     // r: row inside the CTA
+    const int tile_elems = rows_per_cta * MT;
+    for (int e = threadIdx.x; e < tile_elems; e += blockDim.x) {
+        const int r = e / MT, m = e % MT;
         float v = 0.f;
-        for (int s = 0; s < p.KS; ++s) v += red[((size_t)s * rows_per_cta + r) * MT + m];
+        for (int s = 0; s < p.KS; ++s) v += red[((size_t)(s * p.RB + r / 16) * 16 + (r % 16)) * MT + m];
+        tile[e] = v;
+    }
+    __syncthreads();
+
+    trace_scope.mark(4);
+    // ---- K cut across CTAs: the last CTA of this row group to arrive sums all parts, in order
+    if (gridDim.y > 1) {
+        float* mine = p.scratch + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * tile_elems;
+        for (int e = threadIdx.x; e < tile_elems; e += blockDim.x) mine[e] = tile[e];
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int ticket = atomicAdd(&p.counters[blockIdx.x], 1);
+            is_last = ticket == (int)gridDim.y - 1;
+            if (is_last) p.counters[blockIdx.x] = 0;              // everyone has arrived: ready for the next launch
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        for (int e = threadIdx.x; e < tile_elems; e += blockDim.x) {
+            float v = 0.f;
+            for (int y = 0; y < (int)gridDim.y; ++y)
+                v += __ldcg(p.scratch + ((size_t)y * gridDim.x + blockIdx.x) * tile_elems + e);
+            tile[e] = v;
+        }
+        __syncthreads();
+    }
+
+    trace_scope.mark(5);
+    auto value = [&](int r, int m) -> float {                     // r: row inside the CTA
+        float v = tile[r * MT + m];
+        if (NORM) v *= factor[m];
         const int n = n0 + r;
         if (p.bias && n < p.N) v += p.bias[n];
         return v;
     };
 
     if (EPI == EPI_STORE || EPI == EPI_F32) {
-        for (int e = threadIdx.x; e < rows_per_cta * p.M; e += THREADS) {
+        for (int e = threadIdx.x; e < rows_per_cta * p.M; e += blockDim.x) {
             const int m = e / rows_per_cta, r = e % rows_per_cta;
             const int n = n0 + r;
             if (n >= p.N) continue;
@@ -202,7 +319,7 @@ __global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
         }
     } else if (EPI == EPI_SWIGLU) {
         const int half = rows_per_cta / 2;
-        for (int e = threadIdx.x; e < half * p.M; e += THREADS) {
+        for (int e = threadIdx.x; e < half * p.M; e += blockDim.x) {
             const int m = e / half, i = e % half;
             const int n = n0 + 2 * i;
             if (n + 1 >= p.N) continue;
@@ -215,7 +332,7 @@ __global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
         const int head = blockIdx.x;
         const bool is_q = head < p.num_heads, is_k = !is_q && head < p.num_heads + p.num_kv_heads;
         if (is_q || is_k) {
-            for (int e = threadIdx.x; e < half * p.M; e += THREADS) {
+            for (int e = threadIdx.x; e < half * p.M; e += blockDim.x) {
                 const int m = e / half, j = e % half;
                 const float x0 = value(j, m), x1 = value(j + half, m);
                 const float a = (float)p.positions[m] * p.inv_freq[j];
@@ -238,7 +355,7 @@ __global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
                 }
             }
         } else {
-            for (int e = threadIdx.x; e < HD * p.M; e += THREADS) {
+            for (int e = threadIdx.x; e < HD * p.M; e += blockDim.x) {
                 const int m = e / HD, j = e % HD;
                 const long long slot = p.slot_map[m];
                 if (slot < 0 || slot >= p.pool_slots) {
@@ -254,10 +371,11 @@ __global__ void __launch_bounds__(THREADS) skinny_kernel(const Params p) {
 }
 
 template <int NT, int EPI, bool NORM>
-int launch_one(cudaStream_t stream, const Params& p, int ctas) {
-    const int MT = NT * 8;
-    const size_t red_bytes = (size_t)8 * 16 * MT * sizeof(float);                 // RB*KS = 8 warps x 16 rows
-    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) : 0;
+int launch_one(cudaStream_t stream, const Params& p, int ctas, int k_split) {
+    constexpr int MT = NT * 8;
+    const int nwarps = p.RB * p.KS;
+    const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
+    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) : 0;
     const size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
     if (smem_bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = skinny_kernel<NT, EPI, NORM>;
@@ -268,8 +386,8 @@ int launch_one(cudaStream_t stream, const Params& p, int ctas) {
         configured = smem_bytes;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(THREADS);
+    cfg.gridDim = dim3(ctas, k_split);
+    cfg.blockDim = dim3(nwarps * 32);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -281,11 +399,11 @@ int launch_one(cudaStream_t stream, const Params& p, int ctas) {
 }
 
 template <int EPI, bool NORM>
-int launch_nt(cudaStream_t stream, const Params& p, int ctas) {
-    if (p.M <= 8) return launch_one<1, EPI, NORM>(stream, p, ctas);
-    if (p.M <= 16) return launch_one<2, EPI, NORM>(stream, p, ctas);
-    if (p.M <= 32) return launch_one<4, EPI, NORM>(stream, p, ctas);
-    if (p.M <= 64) return launch_one<8, EPI, NORM>(stream, p, ctas);
+int launch_nt(cudaStream_t stream, const Params& p, int ctas, int k_split) {
+    if (p.M <= 8) return launch_one<1, EPI, NORM>(stream, p, ctas, k_split);
+    if (p.M <= 16) return launch_one<2, EPI, NORM>(stream, p, ctas, k_split);
+    if (p.M <= 32) return launch_one<4, EPI, NORM>(stream, p, ctas, k_split);
+    if (p.M <= 64) return launch_one<8, EPI, NORM>(stream, p, ctas, k_split);
     return (int)cudaErrorInvalidValue;
 }
 
@@ -293,16 +411,21 @@ int launch_nt(cudaStream_t stream, const Params& p, int ctas) {
 
 // epilogue: 0 store bf16, 1 store f32, 2 swiglu (interleaved rows), 3 qkv + rope + cache (one CTA per head).
 // norm != 0: x = gain * rmsnorm(resid_in + delta) (delta may be null), resid_out (may be null) receives the sum.
-// row_blocks: 16-row blocks per CTA (1, 2, 4 or 8); the 8 warps of a CTA cover row_blocks x (8 / row_blocks) K slices.
-// Takes M <= 64, K % 8 == 0, 16-byte aligned rows of W and x.  Anything else: cudaErrorInvalidValue.
+// row_blocks x k_slices warps per CTA (their product 1..16); k_split CTAs share the K range of a row group and
+// then need `scratch` (k_split * ceil(N / (row_blocks*16)) * row_blocks*16 * padded tokens floats) and `counters`
+// (one zeroed int per row group; left zero).  Takes M <= 64, K % 16 == 0, 32-byte aligned rows of W, 16-byte
+// aligned rows of x.  Anything else: cudaErrorInvalidValue.
 EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw,
                           const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in,
                           float* resid_out, const void* delta, const float* gain, float eps, void* out, long long ldo,
-                          int row_blocks, int num_heads, int num_kv_heads, int head_dim, const int* positions,
-                          const int* slot_map, void* k_cache, void* v_cache, const float* inv_freq, int page_size,
-                          long long page_stride, long long head_stride, long long pool_slots, int* status) {
+                          int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int num_heads,
+                          int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache,
+                          void* v_cache, const float* inv_freq, int page_size, long long page_stride,
+                          long long head_stride, long long pool_slots, int* status, const void* prefetch,
+                          long long prefetch_bytes, unsigned long long* trace) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64 || K % 8 || ldw % 8 || (!norm && ldx % 8) || (row_blocks != 1 && row_blocks != 2 && row_blocks != 4 && row_blocks != 8))
+    if (M > 64 || K % 16 || ldw % 16 || (!norm && ldx % 8) || row_blocks < 1 || k_slices < 1 ||
+        row_blocks * k_slices > MAX_THREADS / 32 || k_split < 1 || k_split > 64 || (k_split > 1 && (!scratch || !counters)))
         return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_QKV_ROPE && (row_blocks * 16 != head_dim || N != (num_heads + 2 * num_kv_heads) * head_dim))
         return (int)cudaErrorInvalidValue;
@@ -314,10 +437,12 @@ EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_p
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.positions = positions;
     p.slot_map = slot_map; p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.inv_freq = inv_freq;
     p.page_size = page_size; p.page_stride = page_stride; p.head_stride = head_stride; p.pool_slots = pool_slots;
-    p.status = status; p.RB = row_blocks; p.KS = 8 / row_blocks; p.use_pdl = use_pdl;
+    p.status = status; p.RB = row_blocks; p.KS = k_slices; p.use_pdl = use_pdl;
+    p.prefetch = prefetch_bytes >= 16 ? prefetch : nullptr; p.prefetch_bytes = prefetch_bytes;
+    p.scratch = scratch; p.counters = counters; p.trace = trace;
     const int ctas = (N + row_blocks * 16 - 1) / (row_blocks * 16);
 #define EG_SKINNY(E)                                                                             \
-    case E: return norm ? launch_nt<E, true>(stream, p, ctas) : launch_nt<E, false>(stream, p, ctas);
+    case E: return norm ? launch_nt<E, true>(stream, p, ctas, k_split) : launch_nt<E, false>(stream, p, ctas, k_split);
     switch (epilogue) {
         EG_SKINNY(EPI_STORE)
         EG_SKINNY(EPI_F32)

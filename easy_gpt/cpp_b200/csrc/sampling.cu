@@ -47,14 +47,22 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
     return r;
 }
 
+// Several blocks share a row (one block cannot pull 600 KB of logits fast enough to
+// matter beside a decode step); each writes its best (value, index) to scratch and the
+// block that finishes last (a ticket counter; nobody waits) picks the row's winner.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
+              float* __restrict__ part_val, int* __restrict__ part_idx, int* __restrict__ counters) {
     __shared__ ArgMax scratch[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
+    __shared__ int is_last;
+    const int r = blockIdx.x, nb = gridDim.y;
+    const float* row = logits + (size_t)r * ld;
+    const int per = (vocab + nb - 1) / nb;
+    const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
     ArgMax best;
     best.v = -INFINITY;
     best.i = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         ArgMax c;
         c.v = row[i];
         c.i = i;
@@ -62,12 +70,40 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
         if (c.v == c.v) best = argmax_better(best, c);
     }
     best = block_argmax(best, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+    if (nb == 1) {
+        if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+        return;
+    }
+    if (threadIdx.x == 0) {
+        part_val[(size_t)r * nb + blockIdx.y] = best.v;
+        part_idx[(size_t)r * nb + blockIdx.y] = best.i;
+        __threadfence();
+        const int ticket = atomicAdd(&counters[r], 1);
+        is_last = ticket == nb - 1;
+        if (is_last) counters[r] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    ArgMax a;
+    a.v = -INFINITY;
+    a.i = 0x7fffffff;
+    if ((int)threadIdx.x < nb) {
+        a.v = __ldcg(part_val + (size_t)r * nb + threadIdx.x);
+        a.i = __ldcg(part_idx + (size_t)r * nb + threadIdx.x);
+        if (a.i == 0x7fffffff) a.v = -INFINITY;
+    }
+    a = block_argmax(a, scratch);
+    if (threadIdx.x == 0) out[r] = a.i == 0x7fffffff ? 0 : a.i;
 }
 
-EG_API int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, int* out) {
+// blocks_per_row > 1 needs part_val / part_idx (rows * blocks_per_row each) and counters (rows, zeroed; left zero).
+EG_API int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, int* out,
+                     int blocks_per_row, float* part_val, int* part_idx, int* counters) {
     if (rows <= 0) return 0;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
+    if (blocks_per_row < 1 || blocks_per_row > SAMPLE_THREADS || (blocks_per_row > 1 && (!part_val || !part_idx || !counters)))
+        return (int)cudaErrorInvalidValue;
+    argmax_kernel<<<dim3(rows, blocks_per_row), SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out, part_val, part_idx, counters);
     return eg_launch_status();
 }
 

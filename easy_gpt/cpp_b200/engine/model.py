@@ -41,7 +41,7 @@ class Block:
     def forward(self, residual, spare, delta, ctx: StepContext, cache, work):
         """Returns (residual, spare, delta): the buffer that now holds the residual
         stream, the other one, and the feed-forward's output still to be added."""
-        fused_rows = kernels.SKINNY_MAX_TOKENS
+        fused_rows = kernels.FUSED_NORM_MAX_TOKENS
         pending = PendingNorm(self.mixer_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
         delta = self.mixer.forward(pending if self.mixer.accepts_pending_norm else pending.materialize(), ctx, cache)
         assert pending.consumed, "a mixer that accepts a pending norm must use it"
@@ -85,6 +85,18 @@ class Model:
                 p.load(tensors, self.device, self.dtype)
         self.final_norm.load(tensors, self.device, self.dtype)
         self.lm_head.load(tensors, self.device, self.dtype, tied_table=self.embedding.table)
+        self._wire_prefetch_hints()
+
+    def _wire_prefetch_hints(self) -> None:
+        """Tells every part which weights are streamed right after it (by the run order)."""
+        order = []
+        for e in self.spec.run_order:
+            b = self.blocks[e.layer]
+            order += [b.mixer, b.feed_forward]
+        order.append(self.lm_head)
+        for part, nxt in zip(order, order[1:]):
+            if not part.prefetch_hints:
+                part.prefetch_hints = tuple(nxt.streamed_weights())
 
     @staticmethod
     def from_dir(model_dir, device="cuda:0", dtype=torch.bfloat16) -> "Model":
@@ -134,5 +146,5 @@ class Model:
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         pending = PendingNorm(self.final_norm, residual, delta, spare, work, rows=None if all_rows else logit_rows,
-                              max_fused_rows=kernels.SKINNY_MAX_TOKENS)
+                              max_fused_rows=kernels.FUSED_NORM_MAX_TOKENS)
         return self.lm_head.forward(pending if self.lm_head.accepts_pending_norm else pending.materialize())

@@ -68,13 +68,47 @@ class _Signatures:
                             c_float, c_void_p]
     eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
-                          c_int, c_void_p]
+                          c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
-                      c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
+                      c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
+                      c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
+                      c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
-    eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]
+    eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+
+
+class Timeline:
+    """Optional device-side timeline of the decode kernels: every launch while ``active`` gets a
+    slot where its CTAs record their earliest start and latest end (GPU nanosecond clock).  Inside
+    a CUDA graph the slots are rewritten by every replay.  For profiling; costs nothing when off."""
+    active = False
+    buffer: Optional[torch.Tensor] = None
+    names: list = []
+
+    @classmethod
+    def start(cls, device="cuda", capacity=4096):
+        cls.buffer = torch.zeros((capacity, 16), dtype=torch.int64, device=device)
+        cls.names = []
+        cls.active = True
+        cls.reset()
+
+    @classmethod
+    def reset(cls):
+        cls.buffer[:, 0] = (1 << 62)
+        cls.buffer[:, 1:] = 0
+
+    @classmethod
+    def slot(cls, name: str):
+        if not cls.active or len(cls.names) >= cls.buffer.shape[0]:
+            return None
+        cls.names.append(name)
+        return cls.buffer.data_ptr() + 128 * (len(cls.names) - 1)
+
+    @classmethod
+    def read(cls):
+        rows = cls.buffer[:len(cls.names)].cpu().tolist()
+        return [(n, r[0], r[1], r[2:]) for n, r in zip(cls.names, rows)]
 
 
 def _stream() -> int:
@@ -207,17 +241,32 @@ def attention_paged_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> 
 
 
 def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
-    """How many CTAs share one (token, KV head): enough to fill the GPU about four
-    times over, at most one per tile of 64 keys."""
+    """How many CTAs share one (token, KV head): enough to give every SM about two
+    CTAs, at most one per tile of 64 keys and at most 128."""
     base = tokens * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
     tiles = max(1, -(-max_context // 64))
-    return max(1, min(tiles, (4 * SM_COUNT) // max(1, base)))
+    return max(1, min(tiles, 128, (2 * SM_COUNT) // max(1, base)))
+
+
+_attention_tickets = {}
+
+
+def _attention_counters(device, n: int) -> torch.Tensor:
+    """Zeroed ticket counters for the split merge (the kernel leaves them zero)."""
+    key = str(device)
+    have = _attention_tickets.get(key)
+    if have is None or have.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("attention counters must exist before a CUDA graph is captured (run the step once eagerly first)")
+        have = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _attention_tickets[key] = have
+    return have
 
 
 def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                     token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, num_heads: int,
                     num_kv_heads: int, head_dim: int, window: Optional[int], scale: float, splits: int,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, prefetch: Optional[torch.Tensor] = None) -> None:
     """bfloat16 attention over the paged cache on the tensor cores; same contract as
     ``attention_generic``.  With splits > 1 it uses scratch memory for the partial results."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status)
@@ -232,50 +281,85 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.stride() == v_cache.stride()
           and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim and k_cache.data_ptr() % 16 == 0
           and k_cache.stride(0) % 8 == 0 and k_cache.stride(1) % 8 == 0, "cache shape [pages, NKV, page_size, HD], 16-byte rows")
-    acc = ml = None
+    acc = ml = counters = None
     if splits > 1:
         acc = torch.empty(T * num_heads * splits * head_dim, dtype=torch.float32, device=q.device)
         ml = torch.empty(T * num_heads * splits * 2, dtype=torch.float32, device=q.device)
+        counters = _attention_counters(q.device, T * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16)))
     _check(library().eg_attention_paged(
         _stream(), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
         _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml), T, num_heads, num_kv_heads,
         head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
-        int(splits), _ptr(status)), "attention_paged")
-    if splits > 1:
-        global launch_count
-        launch_count += 1                      # the merge kernel
+        int(splits), _ptr(status), _ptr(prefetch) if PREFETCH_WEIGHTS else None,
+        prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
+        _ptr(counters), int(USE_PDL), Timeline.slot(f"attention s={splits}")), "attention_paged")
 
 
 SKINNY_MAX_TOKENS = 64
+PREFETCH_WEIGHTS = os.environ.get("EASY_GPT_PREFETCH", "0") != "0"
+FUSED_NORM_MAX_TOKENS = 16     # every CTA repeats the norm prologue: worth it only for a few tokens
 EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE = 0, 1, 2, 3
 # programmatic dependent launch between the decode kernels (EASY_GPT_PDL=0 switches it off)
 USE_PDL = os.environ.get("EASY_GPT_PDL", "1") != "0"
 
 
-def skinny_row_blocks(n_rows: int) -> int:
-    """16-row blocks per CTA: the largest of 8, 4, 2, 1 that still gives every SM a CTA."""
-    for rb in (8, 4, 2):
-        if -(-n_rows // (rb * 16)) >= SM_COUNT:
-            return rb
-    return 1
+def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
+    """(row_blocks, k_slices, k_split): how the warps of a CTA and the CTAs of the grid share a
+    [n_rows, in_features] weight matrix.  Every warp should have about four 64-wide chunks of K to
+    stream (all in flight at once); big matrices put two 16-row blocks in a CTA, small ones cut K
+    across CTAs so that most SMs take part."""
+    chunks = -(-in_features // 64)
+    if head_dim:                                   # fused QKV: one CTA per head
+        rb = head_dim // 16
+        ks = 1
+        while ks * 2 * rb <= 16 and chunks > 4 * ks:
+            ks *= 2
+        return rb, ks, 1
+    if n_rows >= 64 * SM_COUNT:                    # wide matrices (gate/up, the head): 64 rows per CTA
+        return 4, 2, 1
+    rb, ks = 1, 8
+    split = max(1, min(8, round(chunks / (ks * 2.5))))
+    if -(-n_rows // 16) * split > 4 * SM_COUNT:
+        split = 1
+    return rb, ks, split
 
 
 def gemm_skinny_takes(dtype: torch.dtype, tokens: int, in_features: int) -> bool:
-    return dtype == torch.bfloat16 and 0 < tokens <= SKINNY_MAX_TOKENS and in_features % 8 == 0
+    return dtype == torch.bfloat16 and 0 < tokens <= SKINNY_MAX_TOKENS and in_features % 16 == 0
+
+
+_skinny_scratch = {}
+
+
+def _scratch_for(device, floats: int, row_groups: int):
+    """Per-device scratch for products whose K range is cut across CTAs: partial sums and
+    ticket counters (zero between launches).  Allocated once, outside any graph capture."""
+    key = str(device)
+    have = _skinny_scratch.get(key)
+    if have is None or have[0].numel() < floats or have[1].numel() < row_groups:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the decode scratch must be allocated before a CUDA graph is captured "
+                              "(run the step once eagerly first)")
+        have = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+                torch.zeros(max(row_groups, 1 << 14), dtype=torch.int32, device=device))
+        _skinny_scratch[key] = have
+    return have
 
 
 def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int, *,
                 x: Optional[torch.Tensor] = None, resid_in: Optional[torch.Tensor] = None,
                 resid_out: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, tokens: Optional[int] = None,
-                row_blocks: Optional[int] = None, rope: Optional[dict] = None) -> None:
+                plan=None, rope: Optional[dict] = None, prefetch: Optional[torch.Tensor] = None) -> None:
     """Decode-step product out = f(x W^T + bias) for up to 64 tokens, bfloat16 weights
     streamed once.  Either ``x`` (bfloat16 [M, K]) or the norm prologue (``resid_in``,
     optional ``delta`` and ``resid_out``, ``gain``, ``eps``) gives the input.  Epilogues:
     EPI_STORE (bfloat16), EPI_F32, EPI_SWIGLU (interleaved gate/up rows), EPI_QKV_ROPE
     (``rope``: num_heads, num_kv_heads, head_dim, positions, slot_map, k_cache, v_cache,
-    inv_freq, status)."""
-    _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain)
+    inv_freq, status).  ``plan``: (row_blocks, k_slices, k_split), by default ``skinny_plan``.
+    ``prefetch``: a contiguous tensor (weights of a kernel that runs soon) that this kernel
+    asks the L2 to fetch while it works."""
+    _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain, prefetch)
     N, K = weight.shape
     norm = x is None
     if norm:
@@ -289,18 +373,17 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         _need(x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == K and x.stride(1) == 1
               and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "x: bfloat16 [M, K], 16-byte aligned rows")
         M = x.shape[0]
-    _need(weight.dtype == torch.bfloat16 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
-          and weight.data_ptr() % 16 == 0, "weight: bfloat16 [N, K], 16-byte aligned rows")
-    _need(gemm_skinny_takes(weight.dtype, M, K), f"gemm_skinny takes 1..{SKINNY_MAX_TOKENS} tokens and K % 8 == 0")
+    _need(weight.dtype == torch.bfloat16 and weight.stride(1) == 1 and weight.stride(0) % 16 == 0
+          and weight.data_ptr() % 32 == 0, "weight: bfloat16 [N, K], 32-byte aligned rows")
+    _need(gemm_skinny_takes(weight.dtype, M, K), f"gemm_skinny takes 1..{SKINNY_MAX_TOKENS} tokens and K % 16 == 0")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
-    rb = row_blocks or skinny_row_blocks(N)
     r = rope or {}
     if epilogue == EPI_QKV_ROPE:
         kc, vc = r["k_cache"], r["v_cache"]
         _need(out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape[1] == r["num_heads"] * r["head_dim"], "q out")
         _need(r["inv_freq"].numel() * 2 == r["head_dim"], "the fused rotation covers the whole head")
         _need(kc.dtype == torch.bfloat16 and kc.stride(3) == 1 and kc.stride(2) == r["head_dim"] and kc.stride() == vc.stride(), "cache layout")
-        rb = r["head_dim"] // 16
+        rb, ks, split = plan or skinny_plan(N, K, r["head_dim"])
         extra = (r["num_heads"], r["num_kv_heads"], r["head_dim"], _ptr(r["positions"]), _ptr(r["slot_map"]), _ptr(kc),
                  _ptr(vc), _ptr(r["inv_freq"]), kc.shape[2], kc.stride(0), kc.stride(1), kc.shape[0] * kc.shape[2],
                  _ptr(r["status"]))
@@ -308,11 +391,20 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         want = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
         cols = N // 2 if epilogue == EPI_SWIGLU else N
         _need(out.dtype == want and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == cols, "out shape")
+        rb, ks, split = plan or skinny_plan(N, K)
         extra = (0, 0, 0, None, None, None, None, None, 0, 0, 0, 0, None)
+    scratch = counters = None
+    if split > 1:
+        groups = -(-N // (rb * 16))
+        padded = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+        scratch, counters = _scratch_for(weight.device, split * groups * rb * 16 * padded, groups)
     _check(library().eg_gemm_skinny(
         _stream(), epilogue, int(norm), int(USE_PDL), _ptr(weight), weight.stride(0), _ptr(bias), M, N, K,
         _ptr(x), 0 if norm else x.stride(0), _ptr(resid_in), _ptr(resid_out), _ptr(delta), _ptr(gain), float(eps),
-        _ptr(out), out.stride(0), rb, *extra), "gemm_skinny")
+        _ptr(out), out.stride(0), rb, ks, split, _ptr(scratch), _ptr(counters), *extra,
+        _ptr(prefetch) if PREFETCH_WEIGHTS else None,
+        prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
+        Timeline.slot(f"skinny e={epilogue} n={int(norm)} {N}x{K} plan={rb},{ks},{split}")), "gemm_skinny")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -326,13 +418,32 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                out.stride(0), T, inter), "swiglu")
 
 
+_argmax_scratch = {}
+ARGMAX_BLOCKS = 32
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = lowest index of the maximum of logits[r, :] (float32 rows)."""
     _cuda(logits, out)
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "float32 rows")
     _need(out.dtype == torch.int32 and out.numel() >= logits.shape[0], "int32 out")
-    _check(library().eg_argmax(_stream(), _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out)),
-           "argmax")
+    rows, vocab = logits.shape
+    blocks = max(1, min(ARGMAX_BLOCKS, vocab // 4096))
+    vals = idxs = counters = None
+    if blocks > 1:
+        key = str(logits.device)
+        have = _argmax_scratch.get(key)
+        if have is None or have[2].numel() < rows:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("argmax scratch must exist before a CUDA graph is captured")
+            cap = max(rows, 1024)
+            have = (torch.empty(cap * ARGMAX_BLOCKS, dtype=torch.float32, device=logits.device),
+                    torch.empty(cap * ARGMAX_BLOCKS, dtype=torch.int32, device=logits.device),
+                    torch.zeros(cap, dtype=torch.int32, device=logits.device))
+            _argmax_scratch[key] = have
+        vals, idxs, counters = have
+    _check(library().eg_argmax(_stream(), _ptr(logits), logits.stride(0), rows, vocab, _ptr(out), blocks, _ptr(vals),
+                               _ptr(idxs), _ptr(counters)), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

@@ -69,6 +69,9 @@ class Attention(Mixer):
     def weight_bytes(self):
         return self.qkv.weight_bytes() + self.out.weight_bytes()
 
+    def streamed_weights(self):
+        return [self.qkv.weight, self.out.weight]
+
     # -- cache ------------------------------------------------------------
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
@@ -109,12 +112,12 @@ class Attention(Mixer):
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                     self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, splits,
-                                    ctx.status)
+                                    ctx.status, prefetch=self._hint(0) if T <= kernels.SKINNY_MAX_TOKENS else None)
         else:
             kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                       self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
                                       ctx.status)
-        return self.out(attn)
+        return self.out(attn, prefetch=self._hint(1))
 
 
 register_part("mixer", "attention", Attention)

@@ -109,6 +109,17 @@ class Part:
         """Bytes of weights one forward reads (for roofline arithmetic)."""
         return 0
 
+    def streamed_weights(self) -> List[torch.Tensor]:
+        """The large weights this part's kernels stream, in the order they are used."""
+        return []
+
+    # Set by the model after loading: ``streamed_weights()`` of the part that runs next.
+    # A part's decode kernels may ask the L2 to fetch these while they work (a hint only).
+    prefetch_hints: Sequence[torch.Tensor] = ()
+
+    def _hint(self, i: int) -> Optional[torch.Tensor]:
+        return self.prefetch_hints[i] if i < len(self.prefetch_hints) else None
+
 
 class PositionEncoding(Part):
     """Built once per layer; the mixer calls whatever its kind offers."""

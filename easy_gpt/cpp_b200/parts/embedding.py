@@ -57,6 +57,11 @@ class LMHead(Part):
     def weight_bytes(self):
         return self.linear.weight_bytes()
 
+    def streamed_weights(self):
+        # the head is far larger than the L2; only its first rows are worth asking for ahead of time
+        rows = min(self.vocab, (24 << 20) // (self.hidden * self.linear.weight.element_size()))
+        return [self.linear.weight[:rows]]
+
     accepts_pending_norm = True
 
     def forward(self, x):

@@ -39,7 +39,8 @@ class Linear:
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                 prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
         M = x.shape[0]
         out_dtype = out_dtype or self.dtype
         if self.dtype == torch.float32:
@@ -49,7 +50,7 @@ class Linear:
         if kernels.gemm_skinny_takes(self.dtype, M, self.in_features) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
             out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype)
             kernels.gemm_skinny(self.weight, self.bias_f32, out,
-                                kernels.EPI_F32 if out_dtype == torch.float32 else kernels.EPI_STORE, x=x)
+                                kernels.EPI_F32 if out_dtype == torch.float32 else kernels.EPI_STORE, x=x, prefetch=prefetch)
             return out
         if out_dtype == torch.float32:
             out = torch.mm(x, self.weight.t(), out_dtype=torch.float32)

@@ -45,6 +45,9 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
+    def streamed_weights(self):
+        return [self.gate_up.weight, self.down.weight]
+
     accepts_pending_norm = True
 
     def forward(self, x, ctx):
@@ -54,15 +57,16 @@ class SwiGLU(FeedForward):
         if isinstance(x, PendingNorm) and x.fusable:
             # decode: add + norm + gate/up product + SwiGLU in one kernel
             kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, tokens=T,
-                                **x.fused_args())
+                                prefetch=self._hint(0), **x.fused_args())
         else:
             if isinstance(x, PendingNorm):
                 x = x.materialize()
             if kernels.gemm_skinny_takes(ctx.dtype, T, self.hidden):
-                kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, x=x)
+                kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, x=x,
+                                    prefetch=self._hint(0))
             else:
                 kernels.swiglu(self.gate_up(x), act)
-        return self.down(act)
+        return self.down(act, prefetch=self._hint(1))
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -305,8 +305,9 @@ def bf(t):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 13, 32, 64])
-@pytest.mark.parametrize("N, K, rb", [(48, 40, 1), (1152, 896, 4), (200, 4864, 1), (391, 80, 8), (896, 896, 2)])
-def test_gemm_skinny_plain(M, N, K, rb):
+@pytest.mark.parametrize("N, K, plan", [(48, 48, (1, 1, 1)), (1152, 896, (4, 2, 1)), (200, 4864, (1, 8, 3)), (391, 80, (8, 2, 1)),
+                                        (896, 896, (2, 4, 2)), (896, 4864, None), (4000, 208, None)])
+def test_gemm_skinny_plain(M, N, K, plan):
     from easy_gpt.cpp_b200 import kernels
 
     x = bf(torch.randn(M, K, generator=gen(20)))
@@ -315,14 +316,14 @@ def test_gemm_skinny_plain(M, N, K, rb):
     want = x.float() @ w.float().t() + b
     scale = float(want.abs().max())
     out32 = torch.empty(M, N, device=DEV)
-    kernels.gemm_skinny(w.to(DEV), b.to(DEV), out32, kernels.EPI_F32, x=x.to(DEV), row_blocks=rb)
+    kernels.gemm_skinny(w.to(DEV), b.to(DEV), out32, kernels.EPI_F32, x=x.to(DEV), plan=plan)
     assert float((out32.cpu() - want).abs().max()) <= 1e-5 * scale * math.sqrt(K)          # float32 accumulation
     out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_skinny(w.to(DEV), None, out16, kernels.EPI_STORE, x=x.to(DEV))
     assert float((out16.float().cpu() - (want - b)).abs().max()) <= 8e-3 * scale
     # a token's result does not depend on the other tokens of the step
     one = torch.empty(1, N, device=DEV)
-    kernels.gemm_skinny(w.to(DEV), b.to(DEV), one, kernels.EPI_F32, x=x[M - 1:M].to(DEV).clone(), row_blocks=rb)
+    kernels.gemm_skinny(w.to(DEV), b.to(DEV), one, kernels.EPI_F32, x=x[M - 1:M].to(DEV).clone(), plan=plan)
     assert float((one[0] - out32[M - 1]).abs().max()) <= 1e-6 * scale
 
 
@@ -360,7 +361,7 @@ def test_gemm_skinny_qkv_rope_cache(NH, NKV, HD):
     from easy_gpt.cpp_b200 import kernels
     from easy_gpt.cpp_b200.parts.rope import RotaryEncoding
 
-    M, K, ps, pages = 5, 80 if HD == 16 else 896, 16, 9
+    M, K, ps, pages = 5, 80 if HD == 16 else 896, 16, 9      # K = 80: a width that is no multiple of 64
     N = (NH + 2 * NKV) * HD
     resid = torch.randn(M, K, generator=gen(30))
     delta = bf(torch.randn(M, K, generator=gen(31)) * 0.5)
@@ -398,11 +399,11 @@ def test_gemm_skinny_qkv_rope_cache(NH, NKV, HD):
 def test_gemm_skinny_refuses_what_it_does_not_take():
     from easy_gpt.cpp_b200 import kernels
 
-    w = bf(torch.randn(32, 40)).to(DEV)
+    w = bf(torch.randn(32, 48)).to(DEV)
     with pytest.raises(kernels.KernelError, match="takes 1..64 tokens"):
         kernels.gemm_skinny(w, None, torch.empty(65, 32, dtype=torch.bfloat16, device=DEV), kernels.EPI_STORE,
-                            x=bf(torch.randn(65, 40)).to(DEV))
-    w2 = bf(torch.randn(32, 36)).to(DEV)
+                            x=bf(torch.randn(65, 48)).to(DEV))
+    w2 = bf(torch.randn(32, 40)).to(DEV)
     with pytest.raises(kernels.KernelError):
         kernels.gemm_skinny(w2, None, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV), kernels.EPI_STORE,
-                            x=bf(torch.randn(2, 36)).to(DEV))
+                            x=bf(torch.randn(2, 40)).to(DEV))
