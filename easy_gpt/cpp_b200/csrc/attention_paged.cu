@@ -356,6 +356,226 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD>, p);
 }
 
+
+// ---------------------------------------------------------------------------
+// Prompt portions: a tile of 64 consecutive query tokens of one request and one
+// query head per CTA (four warps of 16 rows), against key tiles of 64 from the
+// paged cache — the portion's own keys were stored there just before.  The K/V
+// tiles of a KV head are read by the CTAs of its G query heads at about the same
+// time and come from the L2 after the first.  Causal and window limits are
+// applied per element; the running softmax is the same as above.
+// ---------------------------------------------------------------------------
+
+struct PrefillParams {
+    const bf16* q;
+    int ldq;
+    const bf16* k_cache;
+    const bf16* v_cache;
+    long long page_stride, head_stride;
+    const int* block_table;
+    int table_stride;
+    const int* positions;      // [T]
+    const int* tiles;          // [num_tiles][3]: sequence (row of the block table), first token, tokens in the tile
+    bf16* out;
+    int ldo;
+    int num_heads, num_kv_heads, page_size, num_pages, window;
+    float scale;
+    int* status;
+};
+
+template <int HD>
+struct PrefillLayout {
+    static constexpr int CHUNKS = HD / 8;
+    static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int STAGES = 3;
+    static constexpr int SMEM = STAGES * STAGE_BYTES;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const PrefillParams p) {
+    using L = Layout<HD>;
+    using PL = PrefillLayout<HD>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    // later tiles of a request see more keys: start them first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y;
+    const int kvh = h / (p.num_heads / p.num_kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
+    const int* table = p.block_table + (size_t)seq * p.table_stride;
+    const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;           // positions in a tile are consecutive
+    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+    const int tile_lo = first / TILE_KEYS, ntiles = pos_hi / TILE_KEYS - tile_lo + 1;
+
+    // rows of this warp: r0 = warp*16 + gid, r1 = r0 + 8
+    const int r0 = warp * 16 + gid, r1 = r0 + 8;
+    const bool v0 = r0 < count, v1 = r1 < count;
+    const int qp0 = pos_lo + r0, qp1 = pos_lo + r1;
+    uint32_t qf[HD / 16][4];
+    {
+        const bf16* q0 = p.q + (size_t)(t0 + (v0 ? r0 : 0)) * p.ldq + (size_t)h * HD;
+        const bf16* q1 = p.q + (size_t)(t0 + (v1 ? r1 : 0)) * p.ldq + (size_t)h * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            const int d = ks * 16 + 2 * tig;
+            qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+            qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+            qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+            qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+        }
+    }
+
+    auto load_tile = [&](int kt, int stage) {
+        unsigned char* ks = smem + stage * PL::STAGE_BYTES;
+        unsigned char* vs = ks + PL::TILE_BYTES;
+        for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
+            const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
+            const int kpos = kt * TILE_KEYS + row;
+            bool valid = kpos >= first && kpos <= pos_hi;
+            long long off = 0;
+            if (valid) {
+                const int page = table[kpos / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                    valid = false;
+                } else {
+                    off = (long long)page * p.page_stride + (long long)kvh * p.head_stride +
+                          (long long)(kpos % p.page_size) * HD + chunk * 8;
+                }
+            }
+            cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
+            cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
+        }
+    };
+
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < PL::STAGES - 1; ++s) {
+        if (s < ntiles) load_tile(tile_lo + s, s);
+        cp_async_commit();
+    }
+    for (int it = 0; it < ntiles; ++it) {
+        cp_async_wait<PL::STAGES - 2>();
+        __syncthreads();
+        {
+            const int nxt = it + PL::STAGES - 1;
+            if (nxt < ntiles) load_tile(tile_lo + nxt, nxt % PL::STAGES);
+            cp_async_commit();
+        }
+        const unsigned char* ks = smem + (it % PL::STAGES) * PL::STAGE_BYTES;
+        const unsigned char* vs = ks + PL::TILE_BYTES;
+        const int key_base = (tile_lo + it) * TILE_KEYS;
+        // this warp's rows see keys up to qp1 (or qp0): skip a key tile that lies wholly behind or before them
+        const int warp_hi = pos_lo + min(count - 1, warp * 16 + 15), warp_lo = pos_lo + warp * 16;
+        const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
+        if (warp * 16 >= count || key_base > warp_hi || key_base + TILE_KEYS - 1 < warp_first) continue;
+
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {                                    // 16 keys each
+                uint32_t b[4];
+                const int mi = lane >> 3, r = lane & 7;
+                ldmatrix_x4(b, ks + L::offset(kb * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+                mma_bf16_16816(s[2 * kb], qf[kk], b[0], b[1]);
+                mma_bf16_16816(s[2 * kb + 1], qf[kk], b[2], b[3]);
+            }
+        }
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
+                const int qp = e < 2 ? qp0 : qp1;
+                const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+                s[j][e] = ok ? s[j][e] * p.scale : -INFINITY;
+                if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
+            }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
+        // a row that sees nothing yet keeps m = -inf: use 0 as the reference so that exp(-inf - 0) = 0
+        const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = expf(m0 - ref0), c1 = expf(m1 - ref1);
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pf[4][4];
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+            const float e00 = expf(s[2 * kb][0] - ref0), e01 = expf(s[2 * kb][1] - ref0);
+            const float e02 = expf(s[2 * kb][2] - ref1), e03 = expf(s[2 * kb][3] - ref1);
+            const float e10 = expf(s[2 * kb + 1][0] - ref0), e11 = expf(s[2 * kb + 1][1] - ref0);
+            const float e12 = expf(s[2 * kb + 1][2] - ref1), e13 = expf(s[2 * kb + 1][3] - ref1);
+            ps0 += e00 + e01 + e10 + e11;
+            ps1 += e02 + e03 + e12 + e13;
+            pf[kb][0] = pack_bf16(e00, e01);
+            pf[kb][1] = pack_bf16(e02, e03);
+            pf[kb][2] = pack_bf16(e10, e11);
+            pf[kb][3] = pack_bf16(e12, e13);
+        }
+        l0 = l0 * c0 + ps0;
+        l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            acc[i][0] *= c0;
+            acc[i][1] *= c0;
+            acc[i][2] *= c1;
+            acc[i][3] *= c1;
+        }
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                uint32_t b[4];
+                const int mi = lane >> 3, r = lane & 7;
+                ldmatrix_x4_trans(b, vs + L::offset(kb * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
+                mma_bf16_16816(acc[nt], pf[kb], b[0], b[1]);
+                mma_bf16_16816(acc[nt + 1], pf[kb], b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * tig;
+        if (v0) *reinterpret_cast<uint32_t*>(p.out + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = pack_bf16(acc[i][0] * i0, acc[i][1] * i0);
+        if (v1) *reinterpret_cast<uint32_t*>(p.out + (size_t)(t0 + r1) * p.ldo + (size_t)h * HD + d) = pack_bf16(acc[i][2] * i1, acc[i][3] * i1);
+    }
+}
+
+template <int HD>
+int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
+    using PL = PrefillLayout<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, PL::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(num_tiles, p.num_heads);
+    attention_prefill_kernel<HD><<<grid, THREADS, PL::SMEM, stream>>>(p);
+    return eg_launch_status();
+}
+
 }  // namespace
 
 // Head sizes 32, 64, 128, 256 and page sizes that are multiples of 16; anything else
@@ -381,6 +601,26 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
         case 64: return launch<64>(stream, p, tokens);
         case 128: return launch<128>(stream, p, tokens);
         case 256: return launch<256>(stream, p, tokens);
+        default: return (int)cudaErrorInvalidValue;
+    }
+}
+
+// Prompt portions in tiles of 64 query tokens: tiles[num_tiles][3] = (block table row, first token, count <= 64);
+// the tokens of a tile are consecutive positions of one request.  Head sizes 32, 64, 128; pages of a multiple of 16.
+EG_API int eg_attention_prefill(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* block_table, int table_stride, const int* positions, const int* tiles,
+                                int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                int page_size, long long page_stride, long long head_stride, int num_pages, int window,
+                                float scale, int* status) {
+    if (num_tiles <= 0) return 0;
+    if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return (int)cudaErrorInvalidValue;
+    PrefillParams p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
+                    table_stride, positions, tiles, (bf16*)out, ldo, num_heads, num_kv_heads, page_size, num_pages, window,
+                    scale, status};
+    switch (head_dim) {
+        case 32: return launch_prefill<32>(stream, p, num_tiles);
+        case 64: return launch_prefill<64>(stream, p, num_tiles);
+        case 128: return launch_prefill<128>(stream, p, num_tiles);
         default: return (int)cudaErrorInvalidValue;
     }
 }

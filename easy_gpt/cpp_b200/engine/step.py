@@ -133,8 +133,10 @@ class StepRunner:
         total_len = context.astype(np.int64) + counts
         width = {g.index: int(-(-int(total_len.max()) // g.page_size)) for g in cache.groups}
 
+        tile = kernels.QUERY_TILE
+        tiles = [(i, int(starts[i]) + o, min(tile, int(counts[i]) - o)) for i in range(n) for o in range(0, int(counts[i]), tile)]
         layout = [("token_ids", T), ("positions", T), ("token_seq", T), ("seq_starts", n + 1), ("seq_context", n),
-                  ("seq_slots", n), ("logit_rows", R)]
+                  ("seq_slots", n), ("logit_rows", R), ("query_tiles", 3 * len(tiles))]
         for g in cache.groups:
             layout += [(f"slot_map{g.index}", T), (f"table{g.index}", n * width[g.index])]
         offsets, off = {}, 0
@@ -155,6 +157,7 @@ class StepRunner:
         put("seq_context", context)
         put("seq_slots", slots)
         put("logit_rows", np.asarray(rows, dtype=np.int32))
+        put("query_tiles", np.asarray(tiles, dtype=np.int32).reshape(-1))
         rids = [e.request for e in entries]
         for g in cache.groups:
             sm = np.concatenate([cache.slot_positions(g.index, e.request, int(context[i]), int(counts[i]))
@@ -180,6 +183,7 @@ class StepRunner:
             host_seq_starts=starts.tolist(), host_seq_context=context.tolist(), host_seq_slots=slots.tolist(),
             max_query_len=int(counts.max()), max_context_len=int(total_len.max()),
             all_decode=bool((counts == 1).all()),
+            query_tiles=view("query_tiles").view(len(tiles), 3),
         )
         return ctx, (view("logit_rows") if R else None)
 

@@ -69,6 +69,8 @@ class _Signatures:
     eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
                           c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p]
+    eg_attention_prefill = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -295,7 +297,41 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _ptr(counters), int(USE_PDL), Timeline.slot(f"attention s={splits}")), "attention_paged")
 
 
-SKINNY_MAX_TOKENS = 64
+PREFILL_ATTENTION_HEAD_DIMS = (32, 64, 128)
+QUERY_TILE = 64
+
+
+def attention_prefill_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in PREFILL_ATTENTION_HEAD_DIMS and page_size % 16 == 0
+
+
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      positions: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
+                      status: torch.Tensor) -> None:
+    """bfloat16 attention for prompt portions: ``tiles`` [n, 3] int32 lists (block table row,
+    first token, count <= 64) for runs of consecutive tokens of one request."""
+    _cuda(q, k_cache, v_cache, block_table, positions, tiles, out, status)
+    page_size = k_cache.shape[2]
+    _need(attention_prefill_takes(q.dtype, head_dim, page_size),
+          f"attention_prefill takes bfloat16, head sizes {PREFILL_ATTENTION_HEAD_DIMS} and pages of a multiple of 16 tokens")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == k_cache.dtype == torch.bfloat16, "q/out/cache layout")
+    _need(q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0, "4-byte aligned rows")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1, "block table")
+    _need(positions.dtype == torch.int32 and tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 3
+          and tiles.is_contiguous(), "int32 positions and tiles [n, 3]")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.stride() == v_cache.stride()
+          and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim and k_cache.data_ptr() % 16 == 0
+          and k_cache.stride(0) % 8 == 0 and k_cache.stride(1) % 8 == 0, "cache shape [pages, NKV, page_size, HD], 16-byte rows")
+    _check(library().eg_attention_prefill(
+        _stream(), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
+        _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
+        page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
+        _ptr(status)), "attention_prefill")
+
+
+SKINNY_KERNEL_TOKENS = 64      # what the kernel takes
+SKINNY_MAX_TOKENS = 16         # up to where it beats the library product (the policy of ``gemm_skinny_takes``)
 PREFETCH_WEIGHTS = os.environ.get("EASY_GPT_PREFETCH", "0") != "0"
 FUSED_NORM_MAX_TOKENS = 16     # every CTA repeats the norm prologue: worth it only for a few tokens
 EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE = 0, 1, 2, 3
@@ -375,7 +411,7 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         M = x.shape[0]
     _need(weight.dtype == torch.bfloat16 and weight.stride(1) == 1 and weight.stride(0) % 16 == 0
           and weight.data_ptr() % 32 == 0, "weight: bfloat16 [N, K], 32-byte aligned rows")
-    _need(gemm_skinny_takes(weight.dtype, M, K), f"gemm_skinny takes 1..{SKINNY_MAX_TOKENS} tokens and K % 16 == 0")
+    _need(0 < M <= SKINNY_KERNEL_TOKENS and K % 16 == 0, f"gemm_skinny takes 1..{SKINNY_KERNEL_TOKENS} tokens and K % 16 == 0")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
     r = rope or {}
     if epilogue == EPI_QKV_ROPE:

@@ -107,7 +107,13 @@ class Attention(Mixer):
                                rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
                                tables.page_size, ctx.status)
         attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
-        if kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
+        if (ctx.query_tiles is not None and ctx.max_query_len > 4
+                and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size)):
+            # prompt portions: tiles of 64 query tokens against the cache
+            kernels.attention_prefill(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
+                                      self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                                      ctx.status)
+        elif kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
             longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,

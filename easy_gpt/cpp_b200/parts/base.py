@@ -78,6 +78,8 @@ class StepContext:
     max_query_len: int = 0
     max_context_len: int = 0       # longest context + query of the batch
     all_decode: bool = False       # every entry brings exactly one token
+    # runs of up to 64 consecutive tokens of one entry: int32 [n, 3] = (entry, first token, count); None in captured steps
+    query_tiles: Optional[torch.Tensor] = None
 
 
 @dataclass

@@ -207,6 +207,9 @@ ATTENTION_CASES = [
     (40, 2, 32, 16, [50], [2], None),            # 20 query heads per KV head: two row blocks
     (2, 1, 80, 16, [45], [4], None),             # a head size only the generic kernel takes
     (4, 2, 256, 16, [130], [2], None),
+    (14, 2, 64, 16, [0, 100, 5], [200, 77, 64], None),        # prompt portions over several query tiles
+    (6, 3, 128, 32, [31], [150], 50),
+    (4, 1, 32, 16, [0], [129], 33),
 ]
 
 
@@ -239,6 +242,17 @@ def test_attention_kernels(case, dtype):
         if dtype == torch.bfloat16:
             with pytest.raises(kernels.KernelError, match="attention_paged takes"):
                 kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, 1, status)
+    if kernels.attention_prefill_takes(dtype, HD, ps):
+        tiles, t0 = [], 0
+        for s_idx, n in enumerate(queries):
+            tiles += [(s_idx, t0 + o, min(64, n - o)) for o in range(0, n, 64)]
+            t0 += n
+        out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+        kernels.attention_prefill(args[0], args[1], args[2], args[3], args[5], torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                                  out, NH, NKV, HD, window, scale, status)
+        assert status.item() == 0
+        err = float((out.float().cpu() - c["want"]).abs().max())
+        assert err <= tol, f"prefill: {err}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
