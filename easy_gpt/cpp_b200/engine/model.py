@@ -71,6 +71,12 @@ class Model:
             out += b.parts()
         return out + [self.final_norm, self.lm_head]
 
+    @property
+    def capturable(self) -> bool:
+        """Whether decode steps of this model may be captured in a CUDA graph: every part says so."""
+        parts = self.all_parts() + [b.mixer.position for b in self.blocks if b.mixer.position is not None]
+        return all(p.capturable for p in parts)
+
     def tensor_requests(self):
         reqs = []
         for p in self.all_parts():

@@ -56,7 +56,7 @@ class StepRunner:
         self._ring_next = 0
         self._dev: Optional[torch.Tensor] = None
         self.steps_run = 0
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and model.capturable
         self._graphs: Dict[int, object] = {}
         self.graph_replays = 0
 

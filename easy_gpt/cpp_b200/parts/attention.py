@@ -24,6 +24,8 @@ from .linear import Linear
 
 
 class Attention(Mixer):
+    capturable = True
+
     def __init__(self, params, prefix, position=None):
         super().__init__(params, prefix, position)
         p = params

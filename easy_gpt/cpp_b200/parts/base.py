@@ -97,6 +97,12 @@ class CacheView:
 # ---------------------------------------------------------------------------
 
 class Part:
+    # True if forward() only launches device work whose shape depends on the batch's size alone
+    # (no host reads of the batch's contents, no .item()): then decode steps may be captured in a
+    # CUDA graph.  A part that plans on the host (ctx.host_*) leaves this False and every step of
+    # a model that contains it runs eagerly.
+    capturable = False
+
     def __init__(self, params: Mapping, prefix: str):
         self.params = dict(params)
         self.prefix = prefix

@@ -17,6 +17,8 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
+    capturable = True
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.vocab = int(params["vocab_size"])
@@ -35,6 +37,8 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     """params: vocab_size, hidden_size, tied_to (prefix of the embedding, or None)."""
+
+    capturable = True
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    capturable = True
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.hidden = int(params["hidden_size"])

@@ -14,6 +14,8 @@ from .base import Norm
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.size = int(params["size"])

@@ -13,6 +13,8 @@ from .base import PositionEncoding
 
 
 class RotaryEncoding(PositionEncoding):
+    capturable = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.head_dim = int(params["head_dim"])

@@ -77,3 +77,26 @@ def test_trace_run_program(tiny, dtype, tmp_path):
     steps = H.trace_mixed(tiny["requests"])
     got = H.run_program(tiny["folder"], dtype, steps, tmp_path / "out")
     H.compare(got, tiny["refs"][dtype], tolerance(tiny, dtype), f"trace_run {tiny['name']} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tiny, dtype):
+    """Requests of one, two and three tokens: whole, and token by token from an empty cache
+    (position 0 has one key, itself; nothing earlier may leak in from a page used before)."""
+    vocab = tiny["cfg"]["vocab_size"]
+    requests = {f"s{n}": tiny_configs.random_tokens(vocab, n, 50 + n) for n in (1, 2, 3)}
+    c, w = plain_model.read_model_dir(tiny["folder"], round_to_bf16=(dtype == "bfloat16"))
+    refs = {rid: plain_model.forward_logits(c, w, toks).numpy() for rid, toks in requests.items()}
+    tol = 1e-4 if dtype == "float32" else tolerance(tiny, dtype)
+    # first fill the only pages with another request, so that the short ones get used pages
+    warm = {"warm": tiny_configs.random_tokens(vocab, 48, 7)}
+    one_by_one = []
+    for rid, toks in requests.items():
+        for i, t in enumerate(toks):
+            one_by_one.append({"step": len(one_by_one), "entries": [{"id": rid, "tokens": [t], "want": [0]}],
+                               "end": [rid] if i == len(toks) - 1 else []})
+    for steps in (H.trace_whole(requests), one_by_one):
+        runner = make_runner(tiny["folder"], dtype, H.trace_whole(warm), 16)
+        H.run_in_process(runner, H.trace_whole(warm))
+        got = H.run_in_process(runner, steps)
+        H.compare(got, refs, tol, f"first tokens {tiny['name']} {dtype}")
