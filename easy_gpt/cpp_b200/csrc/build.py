@@ -35,7 +35,7 @@ def _sources():
 
 def _fingerprint() -> str:
     h = hashlib.sha256()
-    for p in sorted(list(HERE.glob("*.cu")) + list(HERE.glob("*.cuh"))):
+    for p in sorted(list(HERE.glob("*.cu")) + list(HERE.glob("*.cuh")) + list(HERE.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
