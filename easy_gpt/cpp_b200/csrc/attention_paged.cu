@@ -14,7 +14,8 @@
 // partial (m, l, acc) goes to scratch memory and the CTA of that (token, KV head)
 // that finishes last (a ticket counter; nobody waits) merges the splits in order.
 //
-// score = (q . k) * scale in float32, exp by expf, P is rounded to bfloat16 for the
+// score = (q . k) * scale in float32; the running softmax works in base 2 (scores times
+// log2 e, exp2f: one hardware instruction, 2 ulp); P is rounded to bfloat16 for the
 // P V product (as V is bfloat16 anyway); sums and the accumulator stay float32.
 #include "mma_utils.cuh"
 
@@ -74,6 +75,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     const int kvh = blockIdx.y / gblocks;
     const int g0 = (blockIdx.y % gblocks) * 16;                   // first query head of the group handled here
     const int split = blockIdx.z;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
 
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
             for (int e = 0; e < 4; ++e) {
                 const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
                 const bool ok = kpos >= first && kpos <= pos;
-                s[j][e] = ok ? s[j][e] * p.scale : -INFINITY;
+                s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
                 if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
             }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
@@ -190,14 +192,14 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
         const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);               // finite: a key of this quarter is visible
-        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+        const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
         m0 = mn0;
         m1 = mn1;
         uint32_t pf[4];
         float ps0 = 0.f, ps1 = 0.f;
         {
-            float e00 = expf(s[0][0] - mn0), e01 = expf(s[0][1] - mn0), e02 = expf(s[0][2] - mn1), e03 = expf(s[0][3] - mn1);
-            float e10 = expf(s[1][0] - mn0), e11 = expf(s[1][1] - mn0), e12 = expf(s[1][2] - mn1), e13 = expf(s[1][3] - mn1);
+            float e00 = exp2f(s[0][0] - mn0), e01 = exp2f(s[0][1] - mn0), e02 = exp2f(s[0][2] - mn1), e03 = exp2f(s[0][3] - mn1);
+            float e10 = exp2f(s[1][0] - mn0), e11 = exp2f(s[1][1] - mn0), e12 = exp2f(s[1][2] - mn1), e13 = exp2f(s[1][3] - mn1);
             ps0 = e00 + e01 + e10 + e11;
             ps1 = e02 + e03 + e12 + e13;
             pf[0] = pack_bf16(e00, e01);
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         if (m > -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = expf(wm[w * 16 + r] - m);                          // -inf -> 0
+                const float f = exp2f(wm[w * 16 + r] - m);                          // -inf -> 0
                 l += wl[w * 16 + r] * f;
                 a += wacc[(w * 16 + r) * HD + d] * f;
             }
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         const size_t base = ((size_t)t * p.num_heads + kvh * G + g0 + r) * p.splits;
         float l = 0.f;
         for (int s2 = 0; s2 < p.splits; ++s2) {
-            const float f = m > -INFINITY ? expf(fac[r * p.splits + s2] - m) : 0.f;
+            const float f = m > -INFINITY ? exp2f(fac[r * p.splits + s2] - m) : 0.f;
             fac[r * p.splits + s2] = f;
             l += __ldcg(p.partial_ml + (base + s2) * 2 + 1) * f;
         }
@@ -401,6 +403,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
     const int tile = gridDim.x - 1 - blockIdx.x;
     const int h = blockIdx.y;
     const int kvh = h / (p.num_heads / p.num_kv_heads);
+    const float scale_log2 = p.scale * 1.4426950408889634f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
@@ -498,7 +501,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
                 const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
                 const int qp = e < 2 ? qp0 : qp1;
                 const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
-                s[j][e] = ok ? s[j][e] * p.scale : -INFINITY;
+                s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
                 if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
             }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
@@ -508,17 +511,17 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
         const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
         // a row that sees nothing yet keeps m = -inf: use 0 as the reference so that exp(-inf - 0) = 0
         const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float c0 = expf(m0 - ref0), c1 = expf(m1 - ref1);
+        const float c0 = exp2f(m0 - ref0), c1 = exp2f(m1 - ref1);
         m0 = mn0;
         m1 = mn1;
         uint32_t pf[4][4];
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
-            const float e00 = expf(s[2 * kb][0] - ref0), e01 = expf(s[2 * kb][1] - ref0);
-            const float e02 = expf(s[2 * kb][2] - ref1), e03 = expf(s[2 * kb][3] - ref1);
-            const float e10 = expf(s[2 * kb + 1][0] - ref0), e11 = expf(s[2 * kb + 1][1] - ref0);
-            const float e12 = expf(s[2 * kb + 1][2] - ref1), e13 = expf(s[2 * kb + 1][3] - ref1);
+            const float e00 = exp2f(s[2 * kb][0] - ref0), e01 = exp2f(s[2 * kb][1] - ref0);
+            const float e02 = exp2f(s[2 * kb][2] - ref1), e03 = exp2f(s[2 * kb][3] - ref1);
+            const float e10 = exp2f(s[2 * kb + 1][0] - ref0), e11 = exp2f(s[2 * kb + 1][1] - ref0);
+            const float e12 = exp2f(s[2 * kb + 1][2] - ref1), e13 = exp2f(s[2 * kb + 1][3] - ref1);
             ps0 += e00 + e01 + e10 + e11;
             ps1 += e02 + e03 + e12 + e13;
             pf[kb][0] = pack_bf16(e00, e01);

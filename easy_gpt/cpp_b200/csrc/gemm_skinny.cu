@@ -146,18 +146,26 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) fetch(c_lo + u, wra[u], wrb[u]);
     if (p.prefetch) prefetch_next_weights(p.prefetch, p.prefetch_bytes);
+    // The norm's gain is a weight too: it goes to shared memory (behind x and the row factors)
+    // before the wait, so that its trip from HBM is off the critical path.
+    const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;     // bytes; rows 16 banks apart
+    float* gain_s = reinterpret_cast<float*>(smem + (size_t)MT * xs_stride + MT * sizeof(float));
+    if (NORM) {
+        const float4* g = reinterpret_cast<const float4*>(p.gain);
+        for (int i = threadIdx.x; i < p.K / 4; i += blockDim.x) reinterpret_cast<float4*>(gain_s)[i] = g[i];
+    }
 
     trace_scope.mark(0);
     if (p.use_pdl) grid_dependency_wait();                        // from here on the previous kernel's results are read
     trace_scope.mark(1);
 
     // ---- x: staged into shared memory by the norm prologue, or read from global memory
-    const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;     // bytes; rows 16 banks apart
     unsigned char* xs = smem;
     float* row_factor = reinterpret_cast<float*>(smem + (size_t)MT * xs_stride);      // [MT]
     const int nwarps = blockDim.x >> 5;
     if (NORM) {
         const int quads = p.K / 4;
+        __syncthreads();                                          // gain_s is complete
         for (int m = warp; m < MT; m += nwarps) {
             uint2* dst = reinterpret_cast<uint2*>(xs + (size_t)m * xs_stride);
             if (m >= p.M) {
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             }
             const float4* r = reinterpret_cast<const float4*>(p.resid_in + (size_t)m * p.K);
             const uint2* d = p.delta ? reinterpret_cast<const uint2*>(p.delta + (size_t)m * p.K) : nullptr;
-            const float4* g = reinterpret_cast<const float4*>(p.gain);
+            const float4* g = reinterpret_cast<const float4*>(gain_s);
             float4* ro = (blockIdx.x == 0 && blockIdx.y == 0 && p.resid_out)
                              ? reinterpret_cast<float4*>(p.resid_out + (size_t)m * p.K) : nullptr;
             float ss = 0.f;
@@ -375,7 +383,7 @@ int launch_one(cudaStream_t stream, const Params& p, int ctas, int k_split) {
     constexpr int MT = NT * 8;
     const int nwarps = p.RB * p.KS;
     const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
-    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) : 0;
+    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) : 0;
     const size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
     if (smem_bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = skinny_kernel<NT, EPI, NORM>;

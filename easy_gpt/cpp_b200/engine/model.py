@@ -141,6 +141,7 @@ class Model:
         ``logit_rows`` (token indices into the batch), or None when none is wanted.
         ``all_rows``: logit_rows is 0..T-1 in order (a decode step), no gather needed."""
         T, H = ctx.num_tokens, self.spec.hidden_size
+        ctx.scratch.clear()
         residual = torch.empty((T, H), device=self.device, dtype=torch.float32)
         spare = torch.empty((T, H), device=self.device, dtype=torch.float32)
         work = torch.empty((T, H), device=self.device, dtype=self.dtype)

@@ -63,6 +63,9 @@ class _Signatures:
     eg_gemm_f32_nt = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int]
     eg_rope_cache = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
+    eg_rope_table = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
+    eg_rope_cache_vec = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                         c_longlong, c_longlong, c_longlong, c_void_p]
     eg_attention_generic = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
                             c_float, c_void_p]
@@ -210,6 +213,38 @@ def rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch
                                    _ptr(slot_map), _ptr(k_cache), _ptr(v_cache), _ptr(inv_freq), T, num_heads,
                                    num_kv_heads, head_dim, rotary_dim, page_size, page_stride, head_stride, pool_slots,
                                    _ptr(status)), "rope_cache")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """float32 [T, rotary_dim/2, 2]: (cos, sin) of float32(position) * inv_freq, by the accurate cosf/sinf."""
+    _cuda(positions, inv_freq)
+    _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float32, "positions int32, inv_freq float32")
+    T, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    _check(library().eg_rope_table(_stream(), _ptr(positions), _ptr(inv_freq), _ptr(table), T, half), "rope_table")
+    return table
+
+
+def rope_cache_table(qkv: torch.Tensor, table: torch.Tensor, slot_map: Optional[torch.Tensor],
+                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                     head_dim: int, page_size: int, status: torch.Tensor) -> None:
+    """``rope_cache`` for the whole head rotated, with cos/sin from ``rope_table`` (shared by the
+    layers of a step) and wide accesses.  head_dim % 8 == 0."""
+    _cuda(qkv, table, slot_map, k_cache, v_cache, status)
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim and head_dim % 8 == 0, "qkv row layout")
+    _need(table.dtype == torch.float32 and table.is_contiguous() and tuple(table.shape) == (T, head_dim // 2, 2), "table [T, HD/2, 2]")
+    page_stride = head_stride = pool_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None and slot_map.dtype == torch.int32, "cache and int32 slot map")
+        _need(k_cache.dtype == qkv.dtype == v_cache.dtype, "cache dtype equals activation dtype")
+        _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.shape == v_cache.shape
+              and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim and k_cache.stride() == v_cache.stride(), "cache layout")
+        page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
+        pool_slots = k_cache.shape[0] * page_size
+    _check(library().eg_rope_cache_vec(_stream(), dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(table), _ptr(slot_map),
+                                       _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim, page_size,
+                                       page_stride, head_stride, pool_slots, _ptr(status)), "rope_cache_table")
 
 
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,

@@ -104,10 +104,13 @@ class Attention(Mixer):
             if pending is not None:
                 x = pending.materialize()
             qkv = self.qkv(x)
-            kernels.rope_cache(qkv, None, ctx.positions, tables.slot_map if cache.writes else None,
-                               cache.k if cache.writes else None, cache.v if cache.writes else None,
-                               rot.inv_freq, self.num_heads, self.num_kv_heads, self.head_dim, rot.rotary_dim,
-                               tables.page_size, ctx.status)
+            store = (tables.slot_map, cache.k, cache.v) if cache.writes else (None, None, None)
+            if rot.rotary_dim == self.head_dim and self.head_dim % 8 == 0:
+                kernels.rope_cache_table(qkv, rot.table(ctx), *store, self.num_heads, self.num_kv_heads, self.head_dim,
+                                         tables.page_size, ctx.status)
+            else:
+                kernels.rope_cache(qkv, None, ctx.positions, *store, rot.inv_freq, self.num_heads, self.num_kv_heads,
+                                   self.head_dim, rot.rotary_dim, tables.page_size, ctx.status)
         attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
         if (ctx.query_tiles is not None and ctx.max_query_len > 4
                 and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size)):

@@ -80,6 +80,8 @@ class StepContext:
     all_decode: bool = False       # every entry brings exactly one token
     # runs of up to 64 consecutive tokens of one entry: int32 [n, 3] = (entry, first token, count); None in captured steps
     query_tiles: Optional[torch.Tensor] = None
+    # per-step data that parts share between layers (cleared at the start of every forward)
+    scratch: Dict = field(default_factory=dict)
 
 
 @dataclass

@@ -8,6 +8,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from .. import kernels
 from ..registry import register_part
 from .base import PositionEncoding
 
@@ -33,6 +34,14 @@ class RotaryEncoding(PositionEncoding):
 
     def load(self, tensors, device, dtype):
         self.inv_freq = self.inverse_frequencies(self.rotary_dim, self.theta).to(device)
+
+    def table(self, ctx) -> torch.Tensor:
+        """cos/sin [T, rotary_dim/2, 2] of this step's positions: computed by the first layer that
+        asks and shared by every layer with the same parameters."""
+        key = ("rope", self.theta, self.rotary_dim)
+        if key not in ctx.scratch:
+            ctx.scratch[key] = kernels.rope_table(ctx.positions, self.inv_freq)
+        return ctx.scratch[key]
 
 
 register_part("position", "rope", RotaryEncoding)

@@ -421,3 +421,31 @@ def test_gemm_skinny_refuses_what_it_does_not_take():
     with pytest.raises(kernels.KernelError):
         kernels.gemm_skinny(w2, None, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV), kernels.EPI_STORE,
                             x=bf(torch.randn(2, 40)).to(DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_cache_with_table_equals_rope_cache(dtype):
+    from easy_gpt.cpp_b200 import kernels
+    from easy_gpt.cpp_b200.parts.rope import RotaryEncoding
+
+    T, NH, NKV, HD, ps, pages = 37, 5, 1, 24, 8, 7
+    width = (NH + 2 * NKV) * HD
+    qkv = torch.randn(T, width, generator=gen(40)).to(dtype).to(DEV)
+    positions = torch.randint(0, 70000, (T,), generator=gen(41), dtype=torch.int32).to(DEV)
+    slots = torch.randperm(pages * ps, generator=gen(42))[:T].to(torch.int32).to(DEV)
+    inv = RotaryEncoding.inverse_frequencies(HD, 1e6).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a, b = qkv.clone(), qkv.clone()
+    ka, va = (torch.zeros(pages, NKV, ps, HD, dtype=dtype, device=DEV) for _ in range(2))
+    kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
+    kernels.rope_cache(a, None, positions, slots, ka, va, inv, NH, NKV, HD, HD, ps, status)
+    table = kernels.rope_table(positions, inv)
+    ang = positions.float()[:, None] * inv[None, :]
+    assert torch.equal(table[..., 0], torch.cos(ang)) or float((table[..., 0] - torch.cos(ang)).abs().max()) <= 2e-7
+    kernels.rope_cache_table(b, table, slots, kb, vb, NH, NKV, HD, ps, status)
+    # the same cos/sin and the same formula; in float32 the compiler may fuse the multiply-adds of the two
+    # kernels differently, which is worth one rounding of the result
+    ulp = 0.0 if dtype == torch.bfloat16 else 2.5e-7 * float(a.float().abs().max())
+    for x, y in ((a, b), (ka, kb), (va, vb)):
+        assert float((x.float() - y.float()).abs().max()) <= ulp
+    assert status.item() == 0
