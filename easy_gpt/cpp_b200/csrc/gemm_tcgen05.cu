@@ -1,0 +1,263 @@
+// Prefill matrix product on the 5th-generation tensor cores:
+//   C[M, N] = A[M, K] * W[N, K]^T (+ bias), bfloat16 in, float32 accumulation in TMEM.
+//
+// One CTA computes one 128 x 128 tile of C.  Its warps have fixed roles:
+//   warp 0   one thread issues the TMA loads (cp.async.bulk.tensor) of the A and W tiles
+//            [128 x 64] into a ring of shared-memory stages, 128-byte swizzled
+//   warp 1   allocates 128 TMEM columns; one thread issues tcgen05.mma (M 128, N 128, K 16,
+//            four per stage) straight from shared-memory descriptors and hands each stage
+//            back with tcgen05.commit; the last commit announces the accumulator
+//   warps 2-5  read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp at a time),
+//            apply the epilogue and store bfloat16:
+//              store    C = acc + bias
+//              swiglu   columns interleaved (2i = gate_i, 2i+1 = up_i): out[m, i] = up * silu(gate)
+// Stages are handed over with mbarriers (full: TMA bytes landed; empty: the MMAs that read the
+// stage are done).  Two CTAs fit an SM (3 stages x 32 KB each, 2 x 128 TMEM columns), so one
+// tile's epilogue overlaps the other's main loop.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread raises the CTA's
+// abort flag and EG_STATUS_WAIT_TIMEOUT in the status word; all roles then leave their loops,
+// meet at the final barrier, and the TMEM is freed as usual.  Nothing spins for ever.
+//
+// Takes N % 128 == 0, K % 64 == 0, 16-byte aligned rows; any M (rows beyond M are zero-filled by
+// the TMA and not stored).  Anything else: cudaErrorInvalidValue, and the caller uses the library product.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int STAGES = 3;
+constexpr int TILE_A_BYTES = BM * BK * 2, TILE_B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;          // + slack to align the ring to 1024 bytes
+constexpr int THREADS = 192;                                     // 6 warps
+constexpr int TMEM_COLS = 128;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(status, EG_STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_addr(smem_dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16), 128-byte swizzled:
+// groups of 8 rows are 1024 bytes apart (stride byte offset); the leading byte offset is unused for this layout.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_address) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_address & 0x3FFFF) >> 4);              // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                      // leading byte offset (ignored), 16-byte units
+    d |= (uint64_t)(1024 >> 4) << 32;                            // stride byte offset
+    d |= (uint64_t)1 << 46;                                      // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                                      // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor for kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
+__device__ __forceinline__ uint32_t umma_idesc() {
+    uint32_t d = 0;
+    d |= 1u << 4;                                                // D format: F32
+    d |= 1u << 7;                                                // A format: BF16
+    d |= 1u << 10;                                               // B format: BF16
+    d |= (uint32_t)(BN >> 3) << 17;                              // N / 8
+    d |= (uint32_t)(BM >> 4) << 24;                              // M / 16
+    return d;
+}
+
+struct Params {
+    bf16* out;
+    long long ldo;
+    const float* bias;
+    int M, N, K;
+    int epilogue;
+    int* status;
+};
+
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int k_blocks = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {                                             // TMEM: 128 columns of 128 lanes x 32 bits
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                         // ---- TMA producer
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1, &abort_flag, p.status)) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                unsigned char* a = ring + s * STAGE_BYTES;
+                tma_load_2d(a, &map_a, &full_bar[s], kb * BK, m0);
+                tma_load_2d(a + TILE_A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                         // ---- MMA issuer
+            const uint32_t idesc = umma_idesc();
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t a_addr = smem_addr(ring + s * STAGE_BYTES), b_addr = a_addr + TILE_A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    // 16 elements of K = 32 bytes further inside the swizzled row
+                    const uint64_t adesc = umma_desc(a_addr + k * 32), bdesc = umma_desc(b_addr + k * 32);
+                    const uint32_t accumulate = (kb | k) ? 1u : 0u;
+                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                                 ::"r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                }
+                // hands the stage back once the MMAs above have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&empty_bar[s])) : "memory");
+            }
+            if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&acc_bar)) : "memory");
+        }
+    } else {                                                     // ---- epilogue warps 2..5
+        const bool ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (ok) {
+            const int quad = warp & 3;                           // a warp may touch TMEM lanes 32*(warp % 4) ..
+            const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < p.M) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __uint_as_float(r[j]);
+                        if (p.bias) v[j] += p.bias[n0 + c0 + j];
+                    }
+                    if (p.epilogue == EPI_SWIGLU) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
+                            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+                            __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldo + (n0 + c0) / 2);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldo + n0 + c0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), cut into boxes of [box_rows x 64], 128-byte swizzled.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// epilogue: 0 store (out [M, N]), 2 swiglu on interleaved columns (out [M, N/2]).
+EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
+                           const float* bias, void* out, long long ldo, int M, int N, int K, int* status) {
+    if (M <= 0 || N <= 0) return 0;
+    if (N % BN || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 ||
+        (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) || !status)
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_w;
+    if (make_map(&map_a, A, M, K, lda, BM) || make_map(&map_w, W, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    Params p{(bf16*)out, ldo, bias, M, N, K, epilogue, status};
+    dim3 grid(N / BN, (M + BM - 1) / BM);
+    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
+    return eg_launch_status();
+}

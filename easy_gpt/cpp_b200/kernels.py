@@ -78,6 +78,8 @@ class _Signatures:
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
                       c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p]
+    eg_gemm_tcgen05 = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                       c_int, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -476,6 +478,34 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         _ptr(prefetch) if PREFETCH_WEIGHTS else None,
         prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
         Timeline.slot(f"skinny e={epilogue} n={int(norm)} {N}x{K} plan={rb},{ks},{split}")), "gemm_skinny")
+
+
+USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "1") != "0"
+
+
+def gemm_tcgen05_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
+    """Shapes the tcgen05/TMA product takes: bfloat16, N a multiple of 128, K a multiple of 64."""
+    return (USE_TCGEN05 and dtype == torch.bfloat16 and tokens > SKINNY_MAX_TOKENS and out_features % 128 == 0
+            and in_features % 64 == 0)
+
+
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 status: torch.Tensor, swiglu_epilogue: bool = False) -> None:
+    """out = x @ weight^T + bias on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).  With
+    ``swiglu_epilogue`` the weight's rows are interleaved gate/up and out is [M, N/2]."""
+    _cuda(x, weight, bias, out, status)
+    M, K = x.shape
+    N = weight.shape[0]
+    _need(x.dtype == weight.dtype == out.dtype == torch.bfloat16, "bfloat16 only")
+    _need(weight.shape[1] == K and N % 128 == 0 and K % 64 == 0, "gemm_tcgen05 takes N % 128 == 0 and K % 64 == 0")
+    _need(x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1, "unit inner strides")
+    _need(x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+          and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0, "16-byte aligned rows")
+    _need(tuple(out.shape) == (M, N // 2 if swiglu_epilogue else N), "out shape")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
+    _check(library().eg_gemm_tcgen05(_stream(), EPI_SWIGLU if swiglu_epilogue else EPI_STORE, _ptr(x), x.stride(0),
+                                     _ptr(weight), weight.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
+                                     _ptr(status)), "gemm_tcgen05")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

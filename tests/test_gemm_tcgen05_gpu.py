@@ -1,0 +1,64 @@
+"""The tcgen05/TMA matrix product against a float32 reference (GPU)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(t):
+    return t.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M, N, K", [(128, 128, 64), (128, 128, 256), (200, 256, 128), (17, 128, 64), (2048, 1152, 896),
+                                      (333, 896, 4864), (1000, 9728, 896)])
+def test_store_epilogue(M, N, K):
+    from easy_gpt.cpp_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + N + K)
+    x = bf(torch.randn(M, K, generator=g)).to(DEV)
+    w = bf(torch.randn(N, K, generator=g) * 0.1).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.gemm_tcgen05(x, w, b, out, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    want = x.float() @ w.float().t() + b
+    err = float((out.float() - want).abs().max())
+    assert err <= 8e-3 * float(want.abs().max()), err
+    # no bias, strided input (a slice of a wider buffer)
+    wide = bf(torch.randn(M, K + 64, generator=g)).to(DEV)
+    kernels.gemm_tcgen05(wide[:, 8:8 + K], w, None, out, status)
+    want = wide[:, 8:8 + K].float() @ w.float().t()
+    assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max())
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("M, I, K", [(130, 64, 64), (2048, 4864, 896)])
+def test_swiglu_epilogue(M, I, K):
+    from easy_gpt.cpp_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + I)
+    x = bf(torch.randn(M, K, generator=g)).to(DEV)
+    gate, up = bf(torch.randn(I, K, generator=g) * 0.05), bf(torch.randn(I, K, generator=g) * 0.05)
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).to(DEV)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.gemm_tcgen05(x, w, None, out, status, swiglu_epilogue=True)
+    gv, uv = x.float() @ gate.float().to(DEV).t(), x.float() @ up.float().to(DEV).t()
+    want = uv * (gv / (1 + torch.exp(-gv)))
+    assert status.item() == 0
+    assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
+def test_refuses_other_shapes():
+    from easy_gpt.cpp_b200 import kernels
+
+    x = bf(torch.randn(64, 80)).to(DEV)
+    w = bf(torch.randn(100, 80)).to(DEV)
+    with pytest.raises(kernels.KernelError, match="N % 128"):
+        kernels.gemm_tcgen05(x, w, None, torch.empty(64, 100, dtype=torch.bfloat16, device=DEV),
+                             torch.zeros(1, dtype=torch.int32, device=DEV))
