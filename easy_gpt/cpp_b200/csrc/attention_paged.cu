@@ -49,6 +49,7 @@ struct Params {
     int table_stride;
     const int* token_seq;
     const int* positions;
+    const int* seq_context;   // [sequences] keys cached before this step (those from it on are written by the kernel in front); may be null
     bf16* out;
     int ldo;
     float* partial_acc;       // [T, NH, splits, HD]
@@ -91,9 +92,11 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
                          "r"((unsigned)(n & ~15LL)) : "memory");
         }
     }
-    if (p.use_pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");     // q and the new keys come from the kernel before
-    trace_scope.mark(0);
+    // Positions and block tables were uploaded before the step and the cached keys were written by earlier
+    // steps, so everything up to the first fresh key can be fetched before the kernel in front has finished.
+    if (p.use_pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int pos = p.positions[t];
+    const int fresh_from = p.seq_context ? p.seq_context[p.token_seq[t]] : 0;
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
     const int* table = p.block_table + (size_t)p.token_seq[t] * p.table_stride;
     const int tile_lo = first / TILE_KEYS, tile_hi = pos / TILE_KEYS;           // inclusive
@@ -102,29 +105,16 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     const int my_hi = min(tile_hi, my_lo + per - 1);
     const int ntiles = my_hi - my_lo + 1;                                       // may be <= 0
 
-    // ---- query rows as A fragments: row r <-> head kvh*G + g0 + r
-    uint32_t qf[HD / 16][4];
-    {
-        const int r0 = g0 + gid, r1 = g0 + gid + 8;
-        const bf16* q0 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r0) * HD;
-        const bf16* q1 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r1) * HD;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            const int d = ks * 16 + 2 * tig;
-            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
-            qf[ks][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
-            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
-            qf[ks][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
-        }
-    }
-
-    auto load_tile = [&](int tile, int stage) {
+    // mode 0: every row; 1 (before the wait): all but the fresh keys; 2 (after it): the fresh keys only
+    auto load_tile = [&](int tile, int stage, int mode) {
         unsigned char* ks = smem + stage * L::STAGE_BYTES;
         unsigned char* vs = ks + L::TILE_BYTES;
         for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = tile * TILE_KEYS + row;
             bool valid = kpos >= first && kpos <= pos;
+            const bool fresh = valid && kpos >= fresh_from;
+            if ((mode == 1 && fresh) || (mode == 2 && !fresh)) continue;
             long long off = 0;
             if (valid) {
                 const int page = table[kpos / p.page_size];
@@ -148,17 +138,42 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
 
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s) {
-        if (s < ntiles) load_tile(my_lo + s, s);
+        if (s < ntiles) load_tile(my_lo + s, s, 1);
         cp_async_commit();
     }
+    trace_scope.mark(0);
+    if (p.use_pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");     // q and the fresh keys come from the kernel in front
     trace_scope.mark(1);
+#pragma unroll
+    for (int s = 0; s < L::STAGES - 1; ++s)
+        if (s < ntiles && (my_lo + s + 1) * TILE_KEYS > fresh_from) load_tile(my_lo + s, s, 2);
+    cp_async_commit();
+
+    // ---- query rows as A fragments: row r <-> head kvh*G + g0 + r
+    uint32_t qf[HD / 16][4];
+    {
+        const int r0 = g0 + gid, r1 = g0 + gid + 8;
+        const bf16* q0 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r0) * HD;
+        const bf16* q1 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r1) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            const int d = ks * 16 + 2 * tig;
+            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+            qf[ks][1] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+            qf[ks][3] = r1 < G ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+        }
+    }
+
+
     for (int it = 0; it < ntiles; ++it) {
-        cp_async_wait<L::STAGES - 2>();
+        if (it == 0) cp_async_wait<0>();                                          // the first tiles and their fresh rows
+        else cp_async_wait<L::STAGES - 2>();
         __syncthreads();
         if (it == 0) trace_scope.mark(2);
         {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
             const int nxt = it + L::STAGES - 1;
-            if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES);
+            if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES, 0);
             cp_async_commit();
         }
         const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES;
@@ -228,7 +243,6 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
     cp_async_wait<0>();
     trace_scope.mark(3);
-    if (p.use_pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     __syncthreads();                                                              // the pipeline's memory is free now
 
     // ---- merge the four warps: rows r = gid, gid + 8
@@ -584,10 +598,11 @@ int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
 // Head sizes 32, 64, 128, 256 and page sizes that are multiples of 16; anything else
 // returns cudaErrorInvalidValue and the caller uses the generic kernel.
 // partial_acc / partial_ml: scratch of tokens*heads*splits*(head_dim + 2) floats, and counters: one zeroed int
-// per (token, KV head block) (left zero), needed when splits > 1.
+// per (token, KV head block) (left zero), needed when splits > 1.  seq_context (may be null): per block-table row, the
+// number of keys that were in the cache before this step; those may be fetched before the kernel in front has finished.
 EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
                               const int* block_table, int table_stride, const int* token_seq, const int* positions,
-                              void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
+                              const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
                               int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
                               int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
                               long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace) {
@@ -596,7 +611,7 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
         splits > 128 || (splits > 1 && (!partial_acc || !partial_ml || !counters)))
         return (int)cudaErrorInvalidValue;
     Params p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
-             table_stride, token_seq, positions, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
+             table_stride, token_seq, positions, seq_context, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
              page_size, num_pages, window, splits, scale, status, prefetch_bytes >= 16 ? prefetch : nullptr, prefetch_bytes,
              counters, use_pdl, trace};
     switch (head_dim) {

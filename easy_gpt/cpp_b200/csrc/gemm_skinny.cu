@@ -129,6 +129,10 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     const int c_lo = (blockIdx.y * p.KS + ks) * per, c_hi = min(chunks, c_lo + per);
     constexpr int MT = NT * 8;
 
+    // The next kernel may start at once: what it does before its own wait (weights, cached keys) does not
+    // depend on this kernel, and its wait still covers this kernel's completion.
+    if (p.use_pdl) grid_dependents_launch();
+
     // ---- start the weight stream: UNROLL chunks per row in registers
     W32 wra[UNROLL], wrb[UNROLL];
     auto fetch = [&](int c, W32& ra, W32& rb_) {
@@ -255,7 +259,6 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         }
     }
     trace_scope.mark(3);
-    if (p.use_pdl) grid_dependents_launch();                      // the next kernel may start its own weight stream
 
     // ---- sum the K slices of this CTA: red[warp][row][token] -> tile[row in CTA][token]
     float my_factor = 1.f;

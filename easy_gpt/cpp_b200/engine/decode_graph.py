@@ -13,6 +13,7 @@ scratch page, so they read and write nothing that belongs to a request.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Sequence
 
 import numpy as np
@@ -76,8 +77,17 @@ class DecodeGraph:
         from .. import kernels
         before = kernels.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
+        # No garbage collection while the stream is capturing: freeing an older engine's graphs or
+        # tensors there is a CUDA call that is not allowed during a capture and would invalidate it.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.launches = kernels.launch_count - before      # our own kernels inside one replay
 
     def _fill_padding(self, hv: np.ndarray, start_row: int) -> None:

@@ -69,7 +69,7 @@ class _Signatures:
     eg_attention_generic = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
                             c_float, c_void_p]
-    eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+    eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
                           c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p]
     eg_attention_prefill = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
@@ -305,9 +305,12 @@ def _attention_counters(device, n: int) -> torch.Tensor:
 def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                     token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, num_heads: int,
                     num_kv_heads: int, head_dim: int, window: Optional[int], scale: float, splits: int,
-                    status: torch.Tensor, prefetch: Optional[torch.Tensor] = None) -> None:
+                    status: torch.Tensor, prefetch: Optional[torch.Tensor] = None,
+                    seq_context: Optional[torch.Tensor] = None) -> None:
     """bfloat16 attention over the paged cache on the tensor cores; same contract as
-    ``attention_generic``.  With splits > 1 it uses scratch memory for the partial results."""
+    ``attention_generic``.  With splits > 1 it uses scratch memory for the partial results.
+    ``seq_context`` (int32 per block-table row): keys cached before this step; given it, the kernel
+    fetches those while the kernel in front of it (which writes the new keys) is still running."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status)
     T = q.shape[0]
     page_size = k_cache.shape[2]
@@ -327,7 +330,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         counters = _attention_counters(q.device, T * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16)))
     _check(library().eg_attention_paged(
         _stream(), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
-        _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml), T, num_heads, num_kv_heads,
+        _ptr(token_seq), _ptr(positions), _ptr(seq_context), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml), T, num_heads, num_kv_heads,
         head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         int(splits), _ptr(status), _ptr(prefetch) if PREFETCH_WEIGHTS else None,
         prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,

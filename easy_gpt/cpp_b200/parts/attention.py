@@ -123,7 +123,8 @@ class Attention(Mixer):
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                     self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, splits,
-                                    ctx.status, prefetch=self._hint(0) if T <= kernels.SKINNY_MAX_TOKENS else None)
+                                    ctx.status, prefetch=self._hint(0) if T <= kernels.SKINNY_MAX_TOKENS else None,
+                                    seq_context=ctx.seq_context)
         else:
             kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                       self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,

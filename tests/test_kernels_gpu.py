@@ -237,6 +237,12 @@ def test_attention_kernels(case, dtype):
             assert status.item() == 0
             err = float((out.float().cpu() - c["want"]).abs().max())
             assert err <= tol, f"paged splits={splits}: {err}"
+        # told how many keys were cached before the step, it fetches those ahead of its dependency wait
+        out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+        kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, 3, status,
+                                seq_context=torch.tensor(contexts, dtype=torch.int32, device=DEV))
+        err = float((out.float().cpu() - c["want"]).abs().max())
+        assert err <= tol and status.item() == 0, f"paged with seq_context: {err}"
     else:
         assert dtype == torch.float32 or HD == 80 or ps % 16
         if dtype == torch.bfloat16:
