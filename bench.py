@@ -269,6 +269,94 @@ def measure_prefill(folder, config, repeats=5):
     return times[len(times) // 2]
 
 
+def print_timeline(folder, config, batch):
+    """Device-side timeline of one captured decode step: for every kind of kernel its launches, the
+    mean time from its first CTA's start to its last CTA's end (this includes waiting for the kernel
+    in front, since kernels are launched ahead of their dependencies), and how long before the end of
+    the kernel in front it started.  Uses the kernels' optional %globaltimer trace."""
+    import collections
+
+    import torch
+
+    from easy_gpt.cpp_b200 import kernels
+    from easy_gpt.cpp_b200.engine import GptEngine
+
+    kernels.Timeline.start()
+    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (CONTEXT + 64), max_active=batch,
+                       prefill_batch=batch, max_batch_tokens=4096, chunk_size=2048, max_tokens_per_request=CONTEXT + 64)
+    kernels.Timeline.names = []
+    prepare_decode(engine, batch, CONTEXT - 40, 100, config["vocab_size"], seed=1)
+    for _ in range(5):
+        engine.step()
+    torch.cuda.synchronize()
+    kernels.Timeline.reset()
+    engine.step()
+    torch.cuda.synchronize()
+    rows = sorted((r for r in kernels.Timeline.read() if r[2] > 0), key=lambda r: r[1])
+    t0, t1 = rows[0][1], max(r[2] for r in rows)
+    print(f"decode step, batch {batch}, context {CONTEXT}: {len(rows)} traced kernels, {(t1 - t0) / 1e3:.1f} us from first start to last end")
+    agg = collections.OrderedDict()
+    prev_end = t0
+    for name, start, end, _ in rows:
+        a = agg.setdefault(name, [0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += (end - start) / 1e3
+        a[2] += (prev_end - start) / 1e3
+        prev_end = end
+    print(f"{'kernel':58s} {'n':>4s} {'first start..last end us':>25s} {'started before previous end us':>31s}")
+    for name, (n, dur, early) in agg.items():
+        print(f"{name:58s} {n:4d} {dur / n:25.2f} {early / n:31.2f}")
+    return 0
+
+
+def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
+    """The package's tcgen05/TMA product against the library product at the prefill shapes: each
+    timed as a CUDA graph of eight launches on distinct weights with the L2 flushed before."""
+    import torch
+
+    from easy_gpt.cpp_b200 import kernels
+
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    H, I = config["hidden_size"], config["intermediate_size"]
+    qkv = (config["num_attention_heads"] + 2 * config["num_key_value_heads"]) * (H // config["num_attention_heads"])
+
+    def graph_us(fns):
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for f in fns:
+                f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        times = []
+        for i in range(12):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(a.elapsed_time(b) * 1e3 / len(fns))
+        return sorted(times)[len(times) // 2]
+
+    print(f"{tokens} tokens; microseconds per product and TFLOP/s")
+    for name, N, K in (("qkv", qkv, H), ("o", H, H), ("gate_up", 2 * I, H), ("down", H, I)):
+        x = torch.randn(tokens, K, device=dev).bfloat16()
+        ws = [(torch.randn(N, K, device=dev) * 0.05).bfloat16() for _ in range(8)]
+        out = torch.empty(tokens, N, device=dev, dtype=torch.bfloat16)
+        ours = graph_us([(lambda w=w: kernels.gemm_tcgen05(x, w, None, out, status)) for w in ws])
+        lib = graph_us([(lambda w=w: torch.nn.functional.linear(x, w)) for w in ws])
+        flops = 2 * tokens * N * K
+        print(f"  {name:8s} [{N} x {K}]  tcgen05 {ours:7.2f} us {flops / ours / 1e6:7.1f}   library {lib:7.2f} us {flops / lib / 1e6:7.1f}")
+    assert status.item() == 0
+    return 0
+
+
 def run_ours(args):
     import torch
 
@@ -287,6 +375,10 @@ def run_ours(args):
                           "tok_s": round(r["tok_s"], 1), "ms_per_step": round(1e3 * r["seconds"] / args.steps, 4),
                           "gb_s": round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9, 1)}))
         return 0
+    if args.only == "timeline":
+        return print_timeline(folder, config, args.batch)
+    if args.only == "gemm":
+        return print_gemm_comparison(config)
     if args.only == "prefill":
         s = measure_prefill(folder, config)
         print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": config["num_hidden_layers"],
@@ -338,7 +430,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:
