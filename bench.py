@@ -133,6 +133,7 @@ def prepare_decode(engine, batch, start_context, new_tokens, vocab, seed):
     reqs = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts_for(batch, start_context, vocab, seed)]
     while any(r.known - r.computed != 1 or r.state != "running" for r in reqs):
         engine.step()
+    engine.sync()                       # no token left in flight
     return reqs
 
 
@@ -196,6 +197,7 @@ def time_decode_e2e(engine, reqs, steps, warmup):
     start.record()
     for _ in range(steps):
         engine.step()
+    engine.sync()                       # the last step's tokens have reached the host
     stop.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0

@@ -123,6 +123,8 @@ class DecodeGraph:
 
         if not tokens_on_device:
             put("token_ids", np.asarray(tokens, dtype=np.int32))
+        # (with tokens_on_device the ids were put there by set_tokens_from_device; the rows that pad the
+        # bucket keep whatever id they had: any valid id will do for them)
         put("positions", lengths)
         put("seq_context", lengths)
         put("seq_slots", slots)

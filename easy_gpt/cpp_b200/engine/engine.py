@@ -46,6 +46,7 @@ class GptEngine:
             max_batch_tokens=max_batch_tokens, chunk_size=chunk_size, max_active=max_active, prefill_batch=prefill_batch,
             eos_token_id=spec.eos_token_id, max_positions=spec.max_positions))
         self.sampler = Sampler(self.model.device, max_rows=max_active)
+        self._inflight = None          # (batch, device tokens, host copy in progress, request id -> row) of the last step
 
     # -- requests -------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -60,27 +61,88 @@ class GptEngine:
         return self.scheduler.add(prompt, params, max_new_tokens)
 
     def step(self) -> List[Request]:
-        """One scheduler round and one model step.  Returns the requests that finished."""
+        """One scheduler round and one model step.  Returns the requests that finished.
+
+        Decode steps are pipelined: a step is put on the device before the previous step's sampled
+        tokens have been read by the host — the device feeds them to itself — and the previous
+        tokens are read while the new step runs.  So the host's work hides behind the device's, and
+        a request that turns out to have ended (EOS) has one token computed in vain, which is dropped.
+        Whenever the next batch needs token ids on the host (a prompt portion of a recomputed
+        request, a batch the captured path does not take) the tokens in flight are read first."""
         batch = self.scheduler.schedule()
+        finished: List[Request] = []
         if not batch:
-            return []
-        entries = [StepEntry(s.request.id, s.request.tokens[s.start:s.start + s.count],
-                             [s.count - 1] if s.samples else []) for s in batch]
-        logits = self.runner.run(entries, check=False, commit=False)
+            return self._resolve_inflight()
+        on_device = [s for s in batch if s.request.pending]          # entries whose token is still on the device
+        graph = None
+        if on_device:
+            # the device can feed itself only if every entry is a decode of a token of the step in flight
+            all_decode = len(on_device) == len(batch) and all(s.count == 1 and s.samples for s in batch)
+            graph = self.runner.decode_graph(len(batch)) if (all_decode and self.runner.use_graphs) else None
+            if graph is None:
+                # the general path needs every token id on the host: read what is in flight, drop what has ended
+                finished += self._resolve_inflight()
+                kept = [s for s in batch if s.request.state == "running"]
+                if len(kept) != len(batch):
+                    batch = kept
+                    if not batch:
+                        return finished
+                on_device = []
+        if on_device:
+            logits = self._launch_on_device_tokens(batch, graph)
+        else:
+            entries = [StepEntry(s.request.id, s.request.token_slice(s.start, s.count),
+                                 [s.count - 1] if s.samples else []) for s in batch]
+            logits = self.runner.run(entries, check=False, commit=False)
+        self.scheduler.launched(batch)
         sampling = [s for s in batch if s.samples]
-        tokens: List[int] = []
+        previous = self._inflight
+        self._inflight = None
         if sampling:
             dev = self.sampler.sample(logits, [s.request.params for s in sampling], [s.request.id for s in sampling],
-                                      [len(s.request.output) for s in sampling])
-            tokens = self.sampler.to_host(dev)
-        return self.scheduler.update(batch, tokens)
+                                      [len(s.request.output) + s.request.pending - 1 for s in sampling])
+            self._inflight = (batch, dev, self.sampler.to_host_async(dev), {s.request.id: i for i, s in enumerate(sampling)})
+        if previous is not None:
+            finished += self._resolve(previous)
+        return finished
+
+    def _launch_on_device_tokens(self, batch, graph):
+        """A decode step whose input tokens are the previous step's samples, still on the device."""
+        _, prev_dev, _, prev_rows = self._inflight
+        rows = [prev_rows[s.request.id] for s in batch]
+        for s in batch:
+            self.runner.cache.reserve(s.request.id, 1)
+        if rows == list(range(len(rows))) and len(rows) == prev_dev.numel():
+            tokens = prev_dev
+        else:
+            index = torch.tensor(rows, dtype=torch.int64).pin_memory().to(self.model.device, non_blocking=True)
+            tokens = prev_dev.index_select(0, index)
+        graph.set_tokens_from_device(tokens)
+        logits = graph.replay([s.request.id for s in batch], None, tokens_on_device=True)
+        self.runner.graph_replays += 1
+        return logits[:len(batch)]
+
+    def _resolve(self, inflight) -> List[Request]:
+        batch, _, pending_copy, _ = inflight
+        return self.scheduler.resolve(batch, pending_copy())
+
+    def sync(self) -> List[Request]:
+        """Reads the tokens of the step in flight, if any; returns the requests that finished with them."""
+        return self._resolve_inflight()
+
+    def _resolve_inflight(self) -> List[Request]:
+        if self._inflight is None:
+            return []
+        inflight, self._inflight = self._inflight, None
+        return self._resolve(inflight)
 
     def run_to_completion(self) -> None:
         while self.scheduler.has_work():
             before = self.scheduler.stats.steps
-            self.step()
-            if self.scheduler.stats.steps == before and self.scheduler.has_work():
+            done = self.step()
+            if self.scheduler.stats.steps == before and not done and self._inflight is None and self.scheduler.has_work():
                 raise RuntimeError("the scheduler made no progress although requests are waiting")
+        self._resolve_inflight()
         self.runner.check_status()
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None,

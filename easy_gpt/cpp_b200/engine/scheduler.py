@@ -42,7 +42,7 @@ class SchedulerOptions:
     max_positions: int = 1 << 30       # max_position_embeddings
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     id: int
     prompt: List[int]
@@ -55,6 +55,7 @@ class Request:
     error: Optional[str] = None
     preemptions: int = 0
     admitted_at: int = -1              # admission counter, for "most recently admitted"
+    pending: int = 0                   # tokens sampled on the device whose ids the host has not read yet (0 or 1)
 
     @property
     def tokens(self) -> List[int]:
@@ -62,7 +63,20 @@ class Request:
 
     @property
     def known(self) -> int:
-        return len(self.prompt) + len(self.output)
+        """Tokens that exist for this request, the one still on its way from the device included."""
+        return len(self.prompt) + len(self.output) + self.pending
+
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """tokens[start : start + count] without building the whole list (a decode step asks for one token).
+        A token whose id is still pending cannot be given (the caller feeds it on the device)."""
+        n = len(self.prompt)
+        if start + count > n + len(self.output):
+            raise ValueError(f"request {self.id}: token {start + count - 1} is still on the device")
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
 
 
 @dataclass
@@ -119,8 +133,10 @@ class Scheduler:
     def _finish(self, req: Request, reason: str, error: Optional[str] = None) -> None:
         if self.cache.has_request(req.id):
             self.cache.end_request(req.id)
-        if req in self.running:
+        if req.state == "running":
             self.running.remove(req)
+        elif req.state == "waiting" and req in self.waiting:
+            self.waiting.remove(req)
         req.state, req.finish_reason, req.error = "finished", reason, error
         self.finished.append(req)
         if error:
@@ -153,8 +169,10 @@ class Scheduler:
 
         # 1. every request that has all its known tokens but one in the cache decodes one token
         for req in list(self.running):
-            if req not in self.running or req.known - req.computed != 1 or budget <= 0:
+            if req.state != "running" or req.known - req.computed != 1 or budget <= 0:
                 continue
+            if req.pending and (len(req.output) + req.pending >= req.max_new_tokens or req.known >= self.opt.max_positions):
+                continue                       # its pending token is its last one: it ends when the token is read
             while not self.cache.can_reserve(req.id, 1):
                 victim = max(self.running, key=lambda r: r.admitted_at)
                 scheduled_victim = next((s for s in batch if s.request is victim), None)
@@ -169,7 +187,7 @@ class Scheduler:
                         self.waiting.popleft()
                         self._finish(req, "error", "the cache cannot hold this request even alone")
                     break
-            if req not in self.running:
+            if req.state != "running":
                 continue
             self.cache.reserve(req.id, 1)
             batch.append(Scheduled(req, req.computed, 1, True))
@@ -178,8 +196,8 @@ class Scheduler:
         # 2. requests in the middle of their prompt (or being recomputed) get their next portion
         for req in self.running:
             left = req.known - req.computed
-            if left <= 1 or budget <= 0:
-                continue
+            if left <= 1 or budget <= 0 or req.pending:
+                continue                       # (a portion needs all its token ids on the host)
             n = min(left, self.opt.chunk_size, budget)
             if not self.cache.can_reserve(req.id, n):
                 continue                       # waits for pages; decoding requests will free some or be preempted
@@ -192,6 +210,8 @@ class Scheduler:
         while (self.waiting and admitted < self.opt.prefill_batch and len(self.running) < self.opt.max_active
                and budget > 0 and self.cache.free_slot_count() > 0):
             req = self.waiting[0]
+            if req.pending:
+                break                          # preempted while its last token was on its way: wait for it
             err = self._limit_error(req)
             if err:
                 self.waiting.popleft()
@@ -213,6 +233,8 @@ class Scheduler:
             budget -= n
             admitted += 1
 
+        if not batch and any(r.pending for r in self.running):
+            return batch                       # everything live waits for a token that is on its way
         if not batch and self.running:
             # nothing fits although requests are live (all stuck in their prompts): make room
             victim = max(self.running, key=lambda r: r.admitted_at)
@@ -228,8 +250,12 @@ class Scheduler:
     def update(self, batch: Sequence[Scheduled], next_tokens: Sequence[int]) -> List[Request]:
         """After the step ran: ``next_tokens`` holds one sampled token for every
         entry with ``samples`` (in batch order).  Returns the requests that finished."""
-        done = []
-        it = iter(next_tokens)
+        self.launched(batch)
+        return self.resolve(batch, next_tokens)
+
+    def launched(self, batch: Sequence[Scheduled]) -> None:
+        """The step has been handed to the device: its tokens count as cached, and every sampling
+        entry has one token on its way (``pending``) whose id ``resolve`` will bring."""
         for s in batch:
             req = s.request
             self.cache.commit(req.id, s.count)
@@ -238,9 +264,22 @@ class Scheduler:
                 self.stats.decode_tokens += 1
             else:
                 self.stats.prompt_tokens += s.count
+            if s.samples:
+                req.pending += 1
+
+    def resolve(self, batch: Sequence[Scheduled], next_tokens: Sequence[int]) -> List[Request]:
+        """The sampled tokens of a launched step have reached the host.  A request that had ended
+        meanwhile (its previous token was EOS while this step was already on the device) drops its token."""
+        done = []
+        it = iter(next_tokens)
+        for s in batch:
             if not s.samples:
                 continue
+            req = s.request
             token = int(next(it))
+            if req.state == "finished":
+                continue
+            req.pending -= 1
             req.output.append(token)
             reason = None
             if self.opt.eos_token_id >= 0 and token == self.opt.eos_token_id:
@@ -250,6 +289,7 @@ class Scheduler:
             elif req.known + 1 > self.opt.max_positions:
                 reason = "max_positions"
             if reason:
+                req.pending = 0
                 self._finish(req, reason)
                 done.append(req)
         return done

@@ -25,8 +25,13 @@ class Sampler:
         # one pinned float32 block [4, cap]: temperature, top_p, uniform, top_k (as int bits)
         self._host = torch.empty((4, self._cap), dtype=torch.float32).pin_memory()
         self._dev = torch.empty((4, self._cap), dtype=torch.float32, device=self.device)
-        self._out = torch.empty(self._cap, dtype=torch.int32, device=self.device)
-        self._out_host = torch.empty(self._cap, dtype=torch.int32).pin_memory()
+        # two output buffers in turn: a step's tokens stay readable (they feed the next step on the
+        # device, and their copy to the host is read late) while the next step's are being written
+        self._outs = [torch.empty(self._cap, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._out_hosts = [torch.empty(self._cap, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._turn = 0
+        self._out = self._outs[0]
+        self._out_host = self._out_hosts[0]
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], request_ids: Sequence[int],
                token_indices: Sequence[int]) -> torch.Tensor:
@@ -35,6 +40,8 @@ class Sampler:
         rows = logits.shape[0]
         assert len(params) == len(request_ids) == len(token_indices) == rows
         self._grow(rows)
+        self._turn ^= 1
+        self._out, self._out_host = self._outs[self._turn], self._out_hosts[self._turn]
         if all(p.is_greedy for p in params):
             kernels.argmax(logits, self._out)
             return self._out[:rows]
@@ -47,6 +54,21 @@ class Sampler:
         self._dev[:, :rows].copy_(self._host[:, :rows], non_blocking=True)
         kernels.sample(logits, self._dev[0], self._dev[3].view(torch.int32), self._dev[1], self._dev[2], self._out)
         return self._out[:rows]
+
+    def to_host_async(self, tokens: torch.Tensor):
+        """Starts the copy of ``tokens`` (the result of the last ``sample``) to pinned host memory and
+        returns a function that waits for it and gives the Python ints."""
+        n = tokens.numel()
+        host = self._out_host
+        host[:n].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+
+        def result():
+            event.synchronize()
+            return host[:n].tolist()
+
+        return result
 
     def to_host(self, tokens: torch.Tensor) -> list:
         """Device tokens -> Python ints (synchronises the stream)."""

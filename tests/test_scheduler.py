@@ -172,3 +172,39 @@ def test_waiting_requests_keep_their_order():
     sched.update(b, [fake_next(first.tokens)])
     drive(sched, cache)
     assert [r.id for r in sched.finished] == [0, 1, 2]
+
+
+def test_tokens_in_flight_launch_then_resolve():
+    """The engine launches a step before it has read the previous step's tokens: `launched` counts
+    the token as existing (pending), `resolve` brings its id; outputs are the same as step by step."""
+    sched, cache = make(num_pages=64, max_batch_tokens=32, chunk_size=8, eos_token_id=1)
+    a = sched.add([5, 6, 7], GREEDY, 6)
+    b = sched.add([9] * 11, GREEDY, 4)
+    inflight = None
+    rounds = 0
+    while sched.has_work():
+        rounds += 1
+        assert rounds < 100
+        batch = sched.schedule()
+        if not batch:
+            assert inflight is not None          # everything waits for a token on its way
+            sched.resolve(*inflight)
+            inflight = None
+            continue
+        for s in batch:
+            if s.request.pending:
+                assert s.count == 1              # only a decode may run on a token the host has not seen
+        # tokens the "device" computes: it knows every id, pending or not
+        full = {s.request.id: s.request.prompt + s.request.output + ([inflight[1][[x.request.id for x in inflight[0] if x.samples].index(s.request.id)]]
+                                                                      if s.request.pending else []) for s in batch}
+        tokens = [fake_next(full[s.request.id][:s.start + s.count]) for s in batch if s.samples]
+        sched.launched(batch)
+        if inflight is not None:
+            sched.resolve(*inflight)
+        inflight = (batch, tokens)
+        cache.check()
+    if inflight is not None:
+        sched.resolve(*inflight)
+    assert a.output == expected_output([5, 6, 7], 6) and b.output == expected_output([9] * 11, 4)
+    assert a.finish_reason == "length" and b.finish_reason == "length" and a.pending == 0
+    assert not cache.live_requests()
