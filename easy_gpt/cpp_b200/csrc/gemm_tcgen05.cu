@@ -15,6 +15,12 @@
 // stage are done).  Two CTAs fit an SM (3 stages x 32 KB each, 2 x 128 TMEM columns), so one
 // tile's epilogue overlaps the other's main loop.
 //
+// A second kernel (gemm_tcgen05_wide_kernel) takes the wide products (N % 256 == 0): tiles of 128 x 256
+// (MMA N = 256, 87 flop per operand byte instead of 64), four stages, and one persistent CTA per SM that
+// walks its tiles with TWO accumulators in TMEM (2 x 256 columns): while the epilogue warps drain one, the
+// MMA thread already fills the other (acc_full / acc_empty mbarriers).  Tiles are numbered so that the
+// CTAs running at the same time share W tiles through the L2.
+//
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread raises the CTA's
 // abort flag and EG_STATUS_WAIT_TIMEOUT in the status word; all roles then leave their loops,
 // meet at the final barrier, and the TMEM is freed as usual.  Nothing spins for ever.
@@ -81,12 +87,12 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_address) {
 }
 
 // Instruction descriptor for kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
-__device__ __forceinline__ uint32_t umma_idesc() {
+__device__ __forceinline__ uint32_t umma_idesc(int n = BN) {
     uint32_t d = 0;
     d |= 1u << 4;                                                // D format: F32
     d |= 1u << 7;                                                // A format: BF16
     d |= 1u << 10;                                               // B format: BF16
-    d |= (uint32_t)(BN >> 3) << 17;                              // N / 8
+    d |= (uint32_t)(n >> 3) << 17;                               // N / 8
     d |= (uint32_t)(BM >> 4) << 24;                              // M / 16
     return d;
 }
@@ -227,6 +233,173 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// wide products: 128 x 256 tiles, persistent CTAs, double-buffered accumulator
+// ---------------------------------------------------------------------------
+namespace wide {
+constexpr int WBN = 256;
+constexpr int WSTAGES = 4;
+constexpr int W_TILE_B_BYTES = WBN * BK * 2;
+constexpr int W_STAGE_BYTES = TILE_A_BYTES + W_TILE_B_BYTES;
+constexpr int W_SMEM_BYTES = WSTAGES * W_STAGE_BYTES + 1024;
+constexpr int W_TMEM_COLS = 512;
+}  // namespace wide
+
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+    using namespace wide;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[WSTAGES], empty_bar[WSTAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = p.K / BK;
+    const int m_tiles = (p.M + BM - 1) / BM, n_tiles = p.N / WBN;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WSTAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);                          // one arrival per epilogue warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(W_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                         // ---- TMA producer
+            int g = 0;                                           // k-blocks issued so far, over all tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int n0 = (t / m_tiles) * WBN, m0 = (t % m_tiles) * BM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = g % WSTAGES;
+                    if (g >= WSTAGES && !mbar_wait(&empty_bar[s], ((g / WSTAGES) - 1) & 1, &abort_flag, p.status)) { ok = false; break; }
+                    mbar_expect_tx(&full_bar[s], W_STAGE_BYTES);
+                    unsigned char* a = ring + s * W_STAGE_BYTES;
+                    tma_load_2d(a, &map_a, &full_bar[s], kb * BK, m0);
+                    // the W box is 128 rows: two boxes make the 256-row tile
+                    tma_load_2d(a + TILE_A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+                    tma_load_2d(a + TILE_A_BYTES + TILE_B_BYTES, &map_w, &full_bar[s], kb * BK, n0 + 128);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                         // ---- MMA issuer
+            const uint32_t idesc = umma_idesc(WBN);
+            int g = 0, local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * WBN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = g % WSTAGES;
+                    ok = mbar_wait(&full_bar[s], (g / WSTAGES) & 1, &abort_flag, p.status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a_addr = smem_addr(ring + s * W_STAGE_BYTES), b_addr = a_addr + TILE_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t adesc = umma_desc(a_addr + k * 32), bdesc = umma_desc(b_addr + k * 32);
+                        const uint32_t accumulate = (kb | k) ? 1u : 0u;
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                                     " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                                     ::"r"(tmem_acc), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&empty_bar[s])) : "memory");
+                }
+                if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&acc_full[buf])) : "memory");
+            }
+        }
+    } else {                                                     // ---- epilogue warps 2..5
+        const int quad = warp & 3;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int n0 = (t / m_tiles) * WBN, m0 = (t % m_tiles) * BM;
+            ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, &abort_flag, p.status);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!ok) break;
+            const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < WBN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * WBN + c0);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < p.M) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __uint_as_float(r[j]);
+                        if (p.bias) v[j] += p.bias[n0 + c0 + j];
+                    }
+                    if (p.epilogue == EPI_SWIGLU) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
+                            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+                            __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldo + (n0 + c0) / 2);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldo + n0 + c0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    }
+                }
+            }
+            // this warp has read its part of the accumulator: the MMA thread may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&acc_empty[buf])) : "memory");
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(W_TMEM_COLS) : "memory");
+    }
+}
+
 // A [rows, cols] bfloat16 matrix with row stride ld (elements), cut into boxes of [box_rows x 64], 128-byte swizzled.
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -248,6 +421,12 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
     if (N % BN || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 ||
         (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) || !status)
         return (int)cudaErrorInvalidValue;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
     CUtensorMap map_a, map_w;
     if (make_map(&map_a, A, M, K, lda, BM) || make_map(&map_w, W, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
     static bool configured = false;
@@ -257,6 +436,19 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
         configured = true;
     }
     Params p{(bf16*)out, ldo, bias, M, N, K, epilogue, status};
+    const int m_tiles = (M + BM - 1) / BM;
+    if (N % wide::WBN == 0 && m_tiles * (N / wide::WBN) >= sm_count) {
+        // wide product: persistent CTAs over 128 x 256 tiles
+        static bool wide_configured = false;
+        if (!wide_configured) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::W_SMEM_BYTES);
+            if (e != cudaSuccess) return (int)e;
+            wide_configured = true;
+        }
+        const int tiles = m_tiles * (N / wide::WBN);
+        gemm_tcgen05_wide_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, wide::W_SMEM_BYTES, stream>>>(map_a, map_w, p);
+        return eg_launch_status();
+    }
     dim3 grid(N / BN, (M + BM - 1) / BM);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
     return eg_launch_status();

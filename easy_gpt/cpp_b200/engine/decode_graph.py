@@ -1,10 +1,13 @@
-"""CUDA graphs for steps in which every request brings exactly one token.
+"""CUDA graphs for steps whose shape repeats.
 
-Such a step is a fixed sequence of launches whose only changing inputs are small
-integer arrays (token ids, positions, cache positions, block tables).  For each
-batch-size bucket the sequence is captured once over static buffers; a step then
-costs one host-to-device copy of the arrays and one graph launch instead of a
-few hundred launches.  (The reference captures a graph only for the attention of
+A step is a fixed sequence of launches once it is known how many tokens every
+entry brings and where logits are wanted (its *signature*); the only changing
+inputs are small integer arrays (token ids, positions, cache positions, block
+tables).  The sequence is captured once over static buffers; a step then costs
+one host-to-device copy of the arrays and one graph launch instead of a few
+hundred launches.  Decode steps (every entry brings one token) are captured per
+batch-size bucket and padded; other signatures (a prompt portion of the chunk
+size, say) are captured when they come a second time.  (The reference captures a graph only for the attention of
 one layer at batch 1 and re-captures whenever a pointer changes,
 src/cuda/ops/self_attn.cu:750-828.)
 
@@ -19,6 +22,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
 from ..parts.base import GroupTables, StepContext
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -32,15 +36,23 @@ def bucket_for(n: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, runner, bucket: int):
+    """A captured step for one batch *signature*: how many tokens each entry brings and where logits
+    are wanted.  ``padded`` (decode buckets): fewer entries than the signature's may be replayed; the
+    rest are padding rows."""
+
+    def __init__(self, runner, counts: Sequence[int], wants: Sequence[Sequence[int]], padded: bool):
         self.runner = runner
-        self.bucket = B = bucket
+        self.counts = [int(c) for c in counts]
+        self.padded = padded
+        self.bucket = n = len(self.counts)
+        self.tokens = T = sum(self.counts)
+        self.all_decode = all(c == 1 for c in self.counts)
         cache = runner.cache
         dev = runner.device
         self.widths = {g.index: cache.max_pages_per_request for g in cache.groups}
-        layout = [("token_ids", B), ("positions", B), ("seq_context", B), ("seq_slots", B)]
+        layout = [("token_ids", T), ("positions", T), ("seq_context", n), ("seq_slots", n)]
         for g in cache.groups:
-            layout += [(f"slot_map{g.index}", B), (f"table{g.index}", B * self.widths[g.index])]
+            layout += [(f"slot_map{g.index}", T), (f"table{g.index}", n * self.widths[g.index])]
         self.offsets, off = {}, 0
         for name, size in layout:
             self.offsets[name] = (off, size)
@@ -50,31 +62,42 @@ class DecodeGraph:
         self.staging = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(4)]
         self.staging_events: List = [None] * 4
         self.next_staging = 0
-        arange = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        # what depends on the signature alone
+        starts = np.zeros(n + 1, dtype=np.int32)
+        starts[1:] = np.cumsum(self.counts)
+        self.starts = starts
+        self.offsets_in_entry = (np.arange(T, dtype=np.int32) - np.repeat(starts[:-1], self.counts)).astype(np.int32)
+        token_seq = np.repeat(np.arange(n, dtype=np.int32), self.counts)
+        rows = [int(starts[i]) + int(w) for i, ws in enumerate(wants) for w in ws]
+        tile = kernels.QUERY_TILE
+        tiles = [(i, int(starts[i]) + o, min(tile, c - o)) for i, c in enumerate(self.counts) for o in range(0, c, tile)]
+        to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
 
         def view(name):
             o, size = self.offsets[name]
             return self.meta[o:o + size]
 
         self.ctx = StepContext(
-            dtype=runner.model.dtype, device=dev, num_tokens=B, num_seqs=B,
-            token_ids=view("token_ids"), positions=view("positions"), token_seq=arange[:B].clone(),
-            seq_starts=arange, seq_context=view("seq_context"), seq_slots=view("seq_slots"), status=runner.status,
-            groups={g.index: GroupTables(g.page_size, view(f"table{g.index}").view(B, self.widths[g.index]),
+            dtype=runner.model.dtype, device=dev, num_tokens=T, num_seqs=n,
+            token_ids=view("token_ids"), positions=view("positions"), token_seq=to_dev(token_seq),
+            seq_starts=to_dev(starts), seq_context=view("seq_context"), seq_slots=view("seq_slots"), status=runner.status,
+            groups={g.index: GroupTables(g.page_size, view(f"table{g.index}").view(n, self.widths[g.index]),
                                          view(f"slot_map{g.index}")) for g in cache.groups},
-            host_seq_starts=list(range(B + 1)), host_seq_context=[0] * B, host_seq_slots=[0] * B,
-            max_query_len=1, max_context_len=cache.max_pages_per_request * cache.page_size, all_decode=True)
-        self.rows = arange[:B].clone()
+            host_seq_starts=starts.tolist(), host_seq_context=[0] * n, host_seq_slots=[0] * n,
+            max_query_len=max(self.counts), max_context_len=cache.max_pages_per_request * cache.page_size,
+            all_decode=self.all_decode,
+            query_tiles=None if self.all_decode else to_dev(np.asarray(tiles, dtype=np.int32).reshape(-1, 3)))
+        self.rows = to_dev(np.asarray(rows, dtype=np.int32)) if rows else None
+        self.all_rows = rows == list(range(T))
         self._fill_padding(self.staging[0].numpy(), 0)
         self.meta.copy_(self.staging[0])
         # run once eagerly (library handles and workspaces come into being), then capture
         stream = torch.cuda.Stream(device=dev)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
-            runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
+            runner.model.forward(self.ctx, cache, self.rows, all_rows=self.all_rows)
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        from .. import kernels
         before = kernels.launch_count
         self.graph = torch.cuda.CUDAGraph()
         # No garbage collection while the stream is capturing: freeing an older engine's graphs or
@@ -84,31 +107,35 @@ class DecodeGraph:
         gc.disable()
         try:
             with torch.cuda.graph(self.graph):
-                self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=True)
+                self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=self.all_rows)
         finally:
             if was_enabled:
                 gc.enable()
         self.launches = kernels.launch_count - before      # our own kernels inside one replay
 
     def _fill_padding(self, hv: np.ndarray, start_row: int) -> None:
+        """Rows from ``start_row`` on are padding (every entry of a padded signature brings one token)."""
         cache = self.runner.cache
         B = self.bucket
-        for name in ("token_ids", "positions", "seq_context", "seq_slots"):
-            o, _ = self.offsets[name]
-            hv[o + start_row:o + B] = 0
+        first_token = int(self.starts[start_row])
+        for name, first in (("token_ids", first_token), ("positions", first_token), ("seq_context", start_row), ("seq_slots", start_row)):
+            o, size = self.offsets[name]
+            hv[o + first:o + size] = 0
         for g in cache.groups:
-            o, _ = self.offsets[f"slot_map{g.index}"]
-            hv[o + start_row:o + B] = g.scratch_page * g.page_size
+            o, size = self.offsets[f"slot_map{g.index}"]
+            hv[o + first_token:o + size] = g.scratch_page * g.page_size
             o, _ = self.offsets[f"table{g.index}"]
             W = self.widths[g.index]
             hv[o + start_row * W:o + B * W] = g.scratch_page
 
-    def replay(self, requests: Sequence, tokens: Sequence[int], tokens_on_device: bool = False) -> torch.Tensor:
-        """requests: ids of the n <= bucket live requests, each advancing by one token
-        (pages already reserved).  Returns the static logits buffer [bucket, vocab];
-        rows beyond n are padding."""
+    def replay(self, requests: Sequence, tokens, tokens_on_device: bool = False) -> torch.Tensor:
+        """requests: ids of the live requests of this step, in the signature's order (fewer than the
+        signature's only if it is padded); pages for their new tokens are already reserved.  tokens:
+        their token ids, flat, in order (ignored with tokens_on_device: the device already holds them).
+        Returns the static logits buffer; rows of padding entries are to be ignored."""
         cache = self.runner.cache
         n = len(requests)
+        assert n == self.bucket or self.padded
         i = self.next_staging
         self.next_staging = (i + 1) % len(self.staging)
         if self.staging_events[i] is not None:
@@ -116,6 +143,7 @@ class DecodeGraph:
         hv = self.staging[i].numpy()
         lengths = np.fromiter((cache.length_of(r) for r in requests), dtype=np.int32, count=n)
         slots = np.fromiter((cache.slot_of(r) for r in requests), dtype=np.int32, count=n)
+        T = int(self.starts[n])
 
         def put(name, arr):
             o, _ = self.offsets[name]
@@ -125,17 +153,23 @@ class DecodeGraph:
             put("token_ids", np.asarray(tokens, dtype=np.int32))
         # (with tokens_on_device the ids were put there by set_tokens_from_device; the rows that pad the
         # bucket keep whatever id they had: any valid id will do for them)
-        put("positions", lengths)
+        counts = self.counts[:n]
+        positions = np.repeat(lengths, counts) + self.offsets_in_entry[:T]
+        put("positions", positions)
         put("seq_context", lengths)
         put("seq_slots", slots)
+        token_entry = np.repeat(np.arange(n), counts)
         for g in cache.groups:
             W = self.widths[g.index]
             rows = g.tables[slots]                                           # [n, W]
-            pages = rows[np.arange(n), lengths // g.page_size].astype(np.int64)
-            put(f"slot_map{g.index}", (pages * g.page_size + lengths % g.page_size).astype(np.int32))
+            pages = rows[token_entry, positions // g.page_size].astype(np.int64)
+            if (pages < 0).any():
+                raise RuntimeError("a token of a captured step has no cache page")
+            put(f"slot_map{g.index}", (pages * g.page_size + positions % g.page_size).astype(np.int32))
             o, _ = self.offsets[f"table{g.index}"]
             hv[o:o + n * W] = rows.reshape(-1)
-        self._fill_padding(hv, n)
+        if n < self.bucket:
+            self._fill_padding(hv, n)
         if tokens_on_device:
             # token ids stay as the device left them (the sampler's output was copied in)
             o, size = self.offsets["token_ids"]

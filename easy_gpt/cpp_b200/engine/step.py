@@ -58,6 +58,8 @@ class StepRunner:
         self.steps_run = 0
         self.use_graphs = use_graphs and model.capturable
         self._graphs: Dict[int, object] = {}
+        self._signature_graphs: Dict[tuple, object] = {}
+        self._signature_seen: Dict[tuple, int] = {}
         self.graph_replays = 0
 
     # -- request lifetime -------------------------------------------------------
@@ -193,8 +195,8 @@ class StepRunner:
         a complaint of a kernel becomes an exception.  With ``commit`` the requests'
         cached lengths advance here; a scheduler that keeps its own count passes False
         and calls ``cache.commit`` itself."""
-        logits = self._run_captured(entries) if self.use_graphs else None
-        if logits is None:
+        captured, logits = self._run_captured(entries) if self.use_graphs else (False, None)
+        if not captured:
             ctx, rows = self.build_context(entries)
             logits = self.model.forward(ctx, self.cache, rows)
         if commit:
@@ -215,30 +217,75 @@ class StepRunner:
         if b < 0:
             return None
         if b not in self._graphs:
-            self._graphs[b] = DecodeGraph(self, b)
+            self._graphs[b] = DecodeGraph(self, [1] * b, [[0]] * b, padded=True)
         return self._graphs[b]
 
-    def _run_captured(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Steps in which every live entry brings one token and wants its logits go
-        through a captured graph; anything else returns None (the general path)."""
-        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+    MAX_SIGNATURE_GRAPHS = 6
+
+    def _signature_graph(self, entries: Sequence[StepEntry]):
+        """The captured step for this exact batch shape, once the shape has come before (None the first time)."""
+        from .decode_graph import DecodeGraph
+
+        sig = (tuple(len(e.tokens) for e in entries), tuple(tuple(e.want) for e in entries))
+        graph = self._signature_graphs.get(sig)
+        if graph is not None:
+            return graph
+        self._signature_seen[sig] = self._signature_seen.get(sig, 0) + 1
+        if self._signature_seen[sig] < 2 or sum(sig[0]) > 16384:
             return None
-        if len({e.request for e in entries}) != len(entries) or not all(self.cache.has_request(e.request) for e in entries):
-            return None
-        graph = self.decode_graph(len(entries))
-        if graph is None:
-            return None
+        if len(self._signature_graphs) >= self.MAX_SIGNATURE_GRAPHS:
+            self._signature_graphs.pop(next(iter(self._signature_graphs)))        # the oldest
+            if len(self._signature_seen) > 4096:
+                self._signature_seen.clear()
+        graph = DecodeGraph(self, sig[0], sig[1], padded=False)
+        self._signature_graphs[sig] = graph
+        return graph
+
+    def _reserve_for_step(self, entries: Sequence[StepEntry]) -> bool:
+        """Pages for every entry's new tokens, or nothing at all (False)."""
         need: Dict[int, int] = {g.index: 0 for g in self.cache.groups}
         for e in entries:
-            for gi, k in self.cache.pages_needed(e.request, 1).items():
+            if not self.cache.can_reserve(e.request, len(e.tokens)):
+                return False
+            for gi, k in self.cache.pages_needed(e.request, len(e.tokens)).items():
                 need[gi] += k
         if any(need[g.index] > g.pool.free_count for g in self.cache.groups):
-            return None                      # the general path raises the proper error
+            return False
         for e in entries:
-            self.cache.reserve(e.request, 1)
-        logits = graph.replay([e.request for e in entries], [e.tokens[0] for e in entries])
+            self.cache.reserve(e.request, len(e.tokens))
+        return True
+
+    def _run_captured(self, entries: Sequence[StepEntry]):
+        """Steps whose shape has a captured graph go through it: (True, logits or None).  Anything
+        else: (False, None), and the caller takes the general path."""
+        no = (False, None)
+        if len({e.request for e in entries}) != len(entries) or any(len(e.tokens) == 0 for e in entries):
+            return no
+        decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if decode and not all(self.cache.has_request(e.request) for e in entries):
+            return no
+        graph = self.decode_graph(len(entries)) if decode else None
+        if graph is None:
+            if any(w < 0 or w >= len(e.tokens) for e in entries for w in e.want):
+                return no
+            graph = self._signature_graph(entries)
+        if graph is None:
+            return no
+        started = [e.request for e in entries if not self.cache.has_request(e.request)]
+        if len(started) > self.cache.free_slot_count():
+            return no
+        for r in started:
+            self.cache.begin_request(r)
+        if not self._reserve_for_step(entries):
+            for r in started:
+                self.cache.end_request(r)
+            return no                        # the general path raises the proper error
+        tokens = [t for e in entries for t in e.tokens]
+        logits = graph.replay([e.request for e in entries], tokens)
         self.graph_replays += 1
-        return logits[:len(entries)]
+        if logits is None:
+            return True, None
+        return True, (logits[:len(entries)] if graph.padded else logits)
 
     def check_status(self) -> None:
         word = int(self.status.item())

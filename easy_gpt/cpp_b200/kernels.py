@@ -483,13 +483,22 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         Timeline.slot(f"skinny e={epilogue} n={int(norm)} {N}x{K} plan={rb},{ks},{split}")), "gemm_skinny")
 
 
-USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "1") != "0"
+# The package's own tcgen05/TMA product reaches 0.89 PFLOP/s on the widest prefill product against the
+# library's 1.26 (profiles/), so the library product stays the default for prompts; EASY_GPT_TCGEN05=1
+# routes gate/up + SwiGLU through ours.
+USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "0") != "0"
 
 
 def gemm_tcgen05_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
     """Shapes the tcgen05/TMA product takes: bfloat16, N a multiple of 128, K a multiple of 64."""
-    return (USE_TCGEN05 and dtype == torch.bfloat16 and tokens > SKINNY_MAX_TOKENS and out_features % 128 == 0
+    return (dtype == torch.bfloat16 and tokens > SKINNY_MAX_TOKENS and out_features % 128 == 0
             and in_features % 64 == 0)
+
+
+def gemm_tcgen05_wide_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
+    """Products wide and tall enough for the persistent 128 x 256 tile kernel (one tile per SM at least)."""
+    return (USE_TCGEN05 and gemm_tcgen05_takes(dtype, tokens, out_features, in_features) and out_features % 256 == 0
+            and -(-tokens // 128) * (out_features // 256) >= SM_COUNT)
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,

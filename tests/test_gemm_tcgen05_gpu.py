@@ -13,7 +13,8 @@ def bf(t):
 
 
 @pytest.mark.parametrize("M, N, K", [(128, 128, 64), (128, 128, 256), (200, 256, 128), (17, 128, 64), (2048, 1152, 896),
-                                      (333, 896, 4864), (1000, 9728, 896)])
+                                      (333, 896, 4864), (1000, 9728, 896), (1300, 4096, 128), (2500, 2048, 64),
+                                      (4096, 512, 320)])
 def test_store_epilogue(M, N, K):
     from easy_gpt.cpp_b200 import kernels
 
