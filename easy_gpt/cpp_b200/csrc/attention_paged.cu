@@ -23,6 +23,7 @@ namespace {
 
 constexpr int TILE_KEYS = 64;
 constexpr int THREADS = 128;
+constexpr int QUARTER_TILES = 64;      // tiles whose cache addresses are kept in shared memory at a time
 
 template <int HD>
 struct Layout {
@@ -105,27 +106,40 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     const int my_hi = min(tile_hi, my_lo + per - 1);
     const int ntiles = my_hi - my_lo + 1;                                       // may be <= 0
 
+    // Where every 16-key quarter of this CTA's tiles starts in the cache (element offset, -1: nothing to read):
+    // looked up once through the block table, so that the tile loads below touch no global metadata.
+    __shared__ long long quarter_base[QUARTER_TILES * 4];
+    int quarter_tile0 = my_lo;
+    auto fill_quarters = [&](int tile0) {
+        quarter_tile0 = tile0;
+        const int count = min(QUARTER_TILES, my_hi - tile0 + 1);
+        for (int e = threadIdx.x; e < count * 4; e += THREADS) {
+            const int kpos0 = (tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
+            long long base = -1;
+            if (kpos0 <= pos && kpos0 + 15 >= first) {
+                const int page = table[kpos0 / p.page_size];
+                if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
+            }
+            quarter_base[e] = base;
+        }
+    };
+    if (ntiles > 0) fill_quarters(my_lo);
+    __syncthreads();
+
     // mode 0: every row; 1 (before the wait): all but the fresh keys; 2 (after it): the fresh keys only
     auto load_tile = [&](int tile, int stage, int mode) {
         unsigned char* ks = smem + stage * L::STAGE_BYTES;
         unsigned char* vs = ks + L::TILE_BYTES;
+        const long long* qb = quarter_base + (tile - quarter_tile0) * 4;
         for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = tile * TILE_KEYS + row;
-            bool valid = kpos >= first && kpos <= pos;
-            const bool fresh = valid && kpos >= fresh_from;
+            const long long base = qb[row >> 4];
+            const bool valid = kpos >= first && kpos <= pos && base >= 0;
+            const bool fresh = kpos >= first && kpos <= pos && kpos >= fresh_from;
             if ((mode == 1 && fresh) || (mode == 2 && !fresh)) continue;
-            long long off = 0;
-            if (valid) {
-                const int page = table[kpos / p.page_size];
-                if (page < 0 || page >= p.num_pages) {
-                    atomicOr(p.status, EG_STATUS_BAD_PAGE);
-                    valid = false;
-                } else {
-                    off = (long long)page * p.page_stride + (long long)kvh * p.head_stride +
-                          (long long)(kpos % p.page_size) * HD + chunk * 8;
-                }
-            }
+            const long long off = valid ? base + (long long)(row & 15) * HD + chunk * 8 : 0;
             cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
             cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
         }
@@ -173,6 +187,10 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         if (it == 0) trace_scope.mark(2);
         {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
             const int nxt = it + L::STAGES - 1;
+            if (nxt < ntiles && nxt % QUARTER_TILES == 0) {                       // the next stretch of the block table
+                fill_quarters(my_lo + nxt);
+                __syncthreads();
+            }
             if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES, 0);
             cp_async_commit();
         }
@@ -444,24 +462,35 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
         }
     }
 
+    __shared__ long long quarter_base[QUARTER_TILES * 4];         // as in the decode kernel
+    int quarter_tile0 = tile_lo;
+    auto fill_quarters = [&](int tile0) {
+        quarter_tile0 = tile0;
+        const int count = min(QUARTER_TILES, tile_lo + ntiles - tile0);
+        for (int e = threadIdx.x; e < count * 4; e += THREADS) {
+            const int kpos0 = (tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
+            long long base = -1;
+            if (kpos0 <= pos_hi && kpos0 + 15 >= first) {
+                const int page = table[kpos0 / p.page_size];
+                if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
+            }
+            quarter_base[e] = base;
+        }
+    };
+    fill_quarters(tile_lo);
+    __syncthreads();
+
     auto load_tile = [&](int kt, int stage) {
         unsigned char* ks = smem + stage * PL::STAGE_BYTES;
         unsigned char* vs = ks + PL::TILE_BYTES;
+        const long long* qb = quarter_base + (kt - quarter_tile0) * 4;
         for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = kt * TILE_KEYS + row;
-            bool valid = kpos >= first && kpos <= pos_hi;
-            long long off = 0;
-            if (valid) {
-                const int page = table[kpos / p.page_size];
-                if (page < 0 || page >= p.num_pages) {
-                    atomicOr(p.status, EG_STATUS_BAD_PAGE);
-                    valid = false;
-                } else {
-                    off = (long long)page * p.page_stride + (long long)kvh * p.head_stride +
-                          (long long)(kpos % p.page_size) * HD + chunk * 8;
-                }
-            }
+            const long long base = qb[row >> 4];
+            const bool valid = kpos >= first && kpos <= pos_hi && base >= 0;
+            const long long off = valid ? base + (long long)(row & 15) * HD + chunk * 8 : 0;
             cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
             cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
         }
@@ -482,6 +511,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
         __syncthreads();
         {
             const int nxt = it + PL::STAGES - 1;
+            if (nxt < ntiles && nxt % QUARTER_TILES == 0) {
+                fill_quarters(tile_lo + nxt);
+                __syncthreads();
+            }
             if (nxt < ntiles) load_tile(tile_lo + nxt, nxt % PL::STAGES);
             cp_async_commit();
         }
