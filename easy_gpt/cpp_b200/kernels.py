@@ -280,11 +280,18 @@ def attention_paged_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> 
 
 
 def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
-    """How many CTAs share one (token, KV head): enough to give every SM about two
-    CTAs, at most one per tile of 64 keys and at most 128."""
+    """How many CTAs share one (token, KV head).  Measured on B200: the kernel is fastest with one wave of
+    128 to 256 CTAs that walk about eight tiles of 64 keys each; more, smaller CTAs pay in partial results
+    and in the merge.  So: a power of two, at most 256 CTAs in all, at least four tiles per CTA."""
+    forced = os.environ.get("EASY_GPT_ATTENTION_SPLITS")
     base = tokens * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
     tiles = max(1, -(-max_context // 64))
-    return max(1, min(tiles, 128, (2 * SM_COUNT) // max(1, base)))
+    if forced:
+        return max(1, min(int(forced), tiles, 128))
+    splits = 1
+    while splits * 2 * base <= 256 and tiles // (splits * 2) >= 4 and splits < 128:
+        splits *= 2
+    return splits
 
 
 _attention_tickets = {}
