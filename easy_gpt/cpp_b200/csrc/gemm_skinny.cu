@@ -169,14 +169,16 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     const int nwarps = blockDim.x >> 5;
     if (NORM) {
         const int quads = p.K / 4;
+        float* ss_part = gain_s + p.K;                            // [rows][parts] partial sums of squares
+        // With more warps than rows, several warps share a row (a stretch each), so that every lane's
+        // loads go out in one batch; with fewer, a warp takes several rows one after the other.
+        const int parts = p.M > 0 && nwarps >= p.M ? min(nwarps / p.M, 8) : 1;
+        const int per_part = (quads + parts - 1) / parts;
         __syncthreads();                                          // gain_s is complete
-        for (int m = warp; m < MT; m += nwarps) {
+        for (int task = warp; task < p.M * parts; task += nwarps) {
+            const int m = task / parts, part = task % parts;
+            const int q_lo = part * per_part, q_hi = min(quads, q_lo + per_part);
             uint2* dst = reinterpret_cast<uint2*>(xs + (size_t)m * xs_stride);
-            if (m >= p.M) {
-                for (int i = lane; i < quads; i += 32) dst[i] = make_uint2(0u, 0u);
-                if (lane == 0) row_factor[m] = 0.f;
-                continue;
-            }
             const float4* r = reinterpret_cast<const float4*>(p.resid_in + (size_t)m * p.K);
             const uint2* d = p.delta ? reinterpret_cast<const uint2*>(p.delta + (size_t)m * p.K) : nullptr;
             const float4* g = reinterpret_cast<const float4*>(gain_s);
@@ -186,13 +188,13 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             // four quads per lane at a time: all loads of a batch are issued before anything is
             // stored, so that they overlap (a store to the residual could alias them otherwise)
             constexpr int BATCH = 4;
-            for (int i0 = lane; i0 < quads; i0 += 32 * BATCH) {
+            for (int i0 = q_lo + lane; i0 < q_hi; i0 += 32 * BATCH) {
                 float4 rv[BATCH], gv[BATCH];
                 uint2 dv[BATCH];
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
                     const int i = i0 + 32 * b;
-                    if (i < quads) {
+                    if (i < q_hi) {
                         rv[b] = r[i];
                         gv[b] = g[i];
                         dv[b] = d ? d[i] : make_uint2(0u, 0u);
@@ -201,7 +203,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
 #pragma unroll
                 for (int b = 0; b < BATCH; ++b) {
                     const int i = i0 + 32 * b;
-                    if (i < quads) {
+                    if (i < q_hi) {
                         float4 v = rv[b];
                         const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&dv[b].x);
                         const __nv_bfloat162 d23 = *reinterpret_cast<const __nv_bfloat162*>(&dv[b].y);
@@ -213,7 +215,20 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
                 }
             }
             ss = warp_sum(ss);
-            if (lane == 0) row_factor[m] = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+            if (lane == 0) ss_part[m * parts + part] = ss;
+        }
+        // rows that only pad the token tile are zero
+        for (int e = threadIdx.x; e < (MT - p.M) * quads; e += blockDim.x)
+            reinterpret_cast<uint2*>(xs + (size_t)(p.M + e / quads) * xs_stride)[e % quads] = make_uint2(0u, 0u);
+        __syncthreads();
+        if (threadIdx.x < MT) {
+            float f = 0.f;
+            if ((int)threadIdx.x < p.M) {
+                float ss = 0.f;
+                for (int q = 0; q < parts; ++q) ss += ss_part[threadIdx.x * parts + q];      // fixed order
+                f = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+            }
+            row_factor[threadIdx.x] = f;
         }
         __syncthreads();
     }
@@ -386,7 +401,7 @@ int launch_one(cudaStream_t stream, const Params& p, int ctas, int k_split) {
     constexpr int MT = NT * 8;
     const int nwarps = p.RB * p.KS;
     const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
-    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) : 0;
+    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) + (size_t)MT * 8 * sizeof(float) : 0;
     const size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
     if (smem_bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = skinny_kernel<NT, EPI, NORM>;

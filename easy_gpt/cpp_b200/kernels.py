@@ -399,7 +399,7 @@ def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
             ks *= 2
         return rb, ks, 1
     if n_rows >= 64 * SM_COUNT:                    # wide matrices (gate/up, the head): 64 rows per CTA
-        return 4, 2, 1
+        return 4, 2, 1                             # (sixteen warps per CTA measured slower: one CTA per SM)
     rb, ks = 1, 8
     split = max(1, min(8, round(chunks / (ks * 2.5))))
     if -(-n_rows // 16) * split > 4 * SM_COUNT:
