@@ -11,8 +11,10 @@ the whole batch.  One JSON line is printed:
 
   value      decoded tokens per second, timed on the device with CUDA events
              around exactly K steps (token ids fed back on the device)
-  e2e        the same through GptEngine.step(): host token ids in, host token
-             ids out, every step
+  e2e        the same through GptEngine.step(), the call a user makes: every step
+             the packed batch metadata goes up from pinned host memory and the
+             sampled token ids come back to the host (read one step late: decode
+             steps are pipelined and the device feeds itself the token ids)
   prefill    one prompt of 2,048 tokens in one step
   roofline   bytes the decode step has to read (every weight once, the cache of
              the live requests) / its time, against the measured copy bandwidth

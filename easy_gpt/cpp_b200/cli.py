@@ -2,7 +2,8 @@
 src/main.cpp): the same option names, meanings, defaults, checks and error
 texts where the reference has them, plus the options this engine adds (a model
 folder instead of a fixed path, token-id prompts, cache and batch sizes).
-``--serve`` and its options are not provided: no server is built here.
+``--serve`` and its options are not provided: no server is built here.  Text prompts go through
+``tokenizer.py`` (the reference's whitespace-split byte-level BPE) and the fixed Qwen chat template.
 """
 from __future__ import annotations
 
@@ -229,7 +230,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         from .tokenizer import Tokenizer
 
         try:
-            tokenizer = Tokenizer.from_dir(opts.model)
+            bos = json.loads((Path(opts.model) / "config.json").read_text()).get("bos_token_id")
+            tokenizer = Tokenizer.from_dir(opts.model, bos_token_id=-1 if bos is None else int(bos))
         except FileNotFoundError as e:
             print(f"{e}; text prompts need tokenizer.json (or pass --token-ids)", file=sys.stderr)
             return 1
