@@ -392,13 +392,20 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
 
 
 // ---------------------------------------------------------------------------
-// Prompt portions: a tile of 64 consecutive query tokens of one request and one
-// query head per CTA (four warps of 16 rows), against key tiles of 64 from the
+// Prompt portions: 64 consecutive query tokens of one request (half of a listed
+// tile) and one query head per CTA (four warps of 16 rows), against key tiles of 64 from the
 // paged cache — the portion's own keys were stored there just before.  The K/V
 // tiles of a KV head are read by the CTAs of its G query heads at about the same
 // time and come from the L2 after the first.  Causal and window limits are
 // applied per element; the running softmax is the same as above.
 // ---------------------------------------------------------------------------
+
+// 2^x by the hardware's approximation (relative error about 2^-22; results below 2^-126 become 0, and -inf gives 0).
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 struct PrefillParams {
     const bf16* q;
@@ -409,7 +416,7 @@ struct PrefillParams {
     const int* block_table;
     int table_stride;
     const int* positions;      // [T]
-    const int* tiles;          // [num_tiles][3]: sequence (row of the block table), first token, tokens in the tile
+    const int* tiles;          // [num_tiles][3]: sequence (row of the block table), first token, tokens in the tile (<= 128)
     bf16* out;
     int ldo;
     int num_heads, num_kv_heads, page_size, num_pages, window;
@@ -427,18 +434,21 @@ struct PrefillLayout {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_kernel(const PrefillParams p) {
     using L = Layout<HD>;
     using PL = PrefillLayout<HD>;
     extern __shared__ __align__(128) unsigned char smem[];
     // later tiles of a request see more keys: start them first
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int item = gridDim.x - 1 - blockIdx.x;
+    const int tile = item >> 1, half = item & 1;                 // a listed tile has up to 128 tokens: two CTAs
     const int h = blockIdx.y;
     const int kvh = h / (p.num_heads / p.num_kv_heads);
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
-    const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
+    const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1] + half * TILE_KEYS;
+    const int count = min(TILE_KEYS, p.tiles[tile * 3 + 2] - half * TILE_KEYS);
+    if (count <= 0) return;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;           // positions in a tile are consecutive
     const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
@@ -540,35 +550,46 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
                 mma_bf16_16816(s[2 * kb + 1], qf[kk], b[2], b[3]);
             }
         }
+        // Scores stay unscaled here; the scale goes into the exponent's multiply-add.  Only a tile that crosses the
+        // diagonal, the window's far edge or the end of the portion needs the per-element limits.
+        const bool limits = key_base + TILE_KEYS - 1 > warp_lo || warp * 16 + 15 >= count ||
+                            (p.window > 0 && key_base <= warp_lo + 15 - p.window);
+        if (limits) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
+                    const int qp = e < 2 ? qp0 : qp1;
+                    const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+                    if (!ok) s[j][e] = -INFINITY;
+                }
+        }
         float tmax0 = -INFINITY, tmax1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
-                const int qp = e < 2 ? qp0 : qp1;
-                const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
-                s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
-                if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
-            }
+        for (int j = 0; j < 8; ++j) {
+            tmax0 = fmaxf(tmax0, fmaxf(s[j][0], s[j][1]));
+            tmax1 = fmaxf(tmax1, fmaxf(s[j][2], s[j][3]));
+        }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
-        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
+        // m0, m1: running maxima in scaled (base-2) units
+        const float mn0 = fmaxf(m0, tmax0 * scale_log2), mn1 = fmaxf(m1, tmax1 * scale_log2);
         // a row that sees nothing yet keeps m = -inf: use 0 as the reference so that exp(-inf - 0) = 0
         const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float c0 = exp2f(m0 - ref0), c1 = exp2f(m1 - ref1);
+        const float c0 = exp2_approx(m0 - ref0), c1 = exp2_approx(m1 - ref1);
         m0 = mn0;
         m1 = mn1;
         uint32_t pf[4][4];
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
-            const float e00 = exp2f(s[2 * kb][0] - ref0), e01 = exp2f(s[2 * kb][1] - ref0);
-            const float e02 = exp2f(s[2 * kb][2] - ref1), e03 = exp2f(s[2 * kb][3] - ref1);
-            const float e10 = exp2f(s[2 * kb + 1][0] - ref0), e11 = exp2f(s[2 * kb + 1][1] - ref0);
-            const float e12 = exp2f(s[2 * kb + 1][2] - ref1), e13 = exp2f(s[2 * kb + 1][3] - ref1);
+            const float e00 = exp2_approx(fmaf(s[2 * kb][0], scale_log2, -ref0)), e01 = exp2_approx(fmaf(s[2 * kb][1], scale_log2, -ref0));
+            const float e02 = exp2_approx(fmaf(s[2 * kb][2], scale_log2, -ref1)), e03 = exp2_approx(fmaf(s[2 * kb][3], scale_log2, -ref1));
+            const float e10 = exp2_approx(fmaf(s[2 * kb + 1][0], scale_log2, -ref0)), e11 = exp2_approx(fmaf(s[2 * kb + 1][1], scale_log2, -ref0));
+            const float e12 = exp2_approx(fmaf(s[2 * kb + 1][2], scale_log2, -ref1)), e13 = exp2_approx(fmaf(s[2 * kb + 1][3], scale_log2, -ref1));
             ps0 += e00 + e01 + e10 + e11;
             ps1 += e02 + e03 + e12 + e13;
             pf[kb][0] = pack_bf16(e00, e01);
@@ -621,7 +642,7 @@ int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(num_tiles, p.num_heads);
+    dim3 grid(2 * num_tiles, p.num_heads);
     attention_prefill_kernel<HD><<<grid, THREADS, PL::SMEM, stream>>>(p);
     return eg_launch_status();
 }

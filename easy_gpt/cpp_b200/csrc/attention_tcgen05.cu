@@ -1,0 +1,569 @@
+// Attention for prompt portions on the 5th-generation tensor cores.
+//
+// One CTA takes up to 128 consecutive query tokens of one request and one query head, and walks the
+// request's keys in the paged cache in tiles of 64 (the portion's own keys were stored there just before):
+//
+//   S = Q K^T      tcgen05.mma  M 128, N 64, K = head size     Q and K tiles K-major in shared memory, S in TMEM
+//   P = softmax    four warps, one query row per thread: the row of S comes out of TMEM with tcgen05.ld, the
+//                  reference maximum and the sum stay in registers, P goes back into TMEM as bfloat16 pairs
+//                  (tcgen05.st) over the first half of the S buffer it came from
+//   O += P V       tcgen05.mma  M 128, N = head size, K 64     P from TMEM, the V tile as it lies in the cache
+//                  (N-major operand in shared memory), accumulated in TMEM over all key tiles
+// The exponents are taken against a reference that follows the row's maximum lazily: only when the maximum has
+// grown by more than 2^8 since the reference was set does the row's thread move the reference, and then it scales
+// its row of O in TMEM (tcgen05.ld, multiply, tcgen05.st) and its sum; O / sum stays the same.
+//
+// Warp roles: warp 0 one thread issues the TMA loads (Q once; per key tile one box of 16 keys x 64 columns per
+// page piece, K and V, 128-byte swizzled, into a ring of stages; the block-table entries are fetched a ring ahead),
+// warp 1 allocates TMEM and one thread issues every MMA, warps 2-5 are the softmax rows.  S has two TMEM buffers:
+// the tensor core computes the scores of the next key tile while the rows work on this one.  The tensor core takes
+// its instructions in order, so the scores of tile j + 2 overwrite the buffer of S_j / P_j only after O += P_j V_j.
+// Everything else is handed over with mbarriers.  Scale, maximum, exponent and sums are 32-bit; the exponent is the
+// hardware's base-2 approximation with the scale folded into its multiply-add.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread raises the CTA's abort flag and
+// EG_STATUS_WAIT_TIMEOUT; every role then leaves its loop, the loader waits (bounded again) for the copies it
+// still has in flight, and the TMEM is freed as usual.
+//
+// Takes head sizes 64 and 128, pages of a multiple of 16 tokens, 16-byte aligned rows.  Anything else:
+// cudaErrorInvalidValue, and the caller uses the warp-level kernel.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 64;
+constexpr int THREADS = 192;                                     // loader warp, MMA warp, four softmax warps
+constexpr int TMEM_COLS = 256;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+constexpr float REFERENCE_SLACK = 8.f;                            // the exponents' reference may lag the maximum by 2^8
+constexpr int SUB_ROW_BYTES = 128;                                // 64 bfloat16: one swizzle row
+
+template <int HD>
+struct Shape {
+    static constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of Q, K, V
+    static constexpr int STAGES = HD == 64 ? 5 : 4;
+    static constexpr int Q_SUB_BYTES = BM * SUB_ROW_BYTES;        // 16 KB
+    static constexpr int KV_SUB_BYTES = BN * SUB_ROW_BYTES;       // 8 KB
+    static constexpr int Q_BYTES = SUBS * Q_SUB_BYTES;
+    static constexpr int K_BYTES = SUBS * KV_SUB_BYTES;
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;               // K then V
+    static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024;
+    static constexpr int O_COL = 2 * BN;                          // TMEM: S0/P0 [0,64) S1/P1 [64,128) then O
+    static_assert(O_COL + HD <= TMEM_COLS, "TMEM columns");
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(status, EG_STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
+// Bounded wait that does not look at the abort flag (for copies in flight at the end).
+__device__ __forceinline__ void mbar_wait_plain(uint64_t* bar, uint32_t parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_dst), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptors, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+//   K-major (Q, K, P): 16 elements of K further = 32 bytes further in the row; the leading offset is unused.
+//   N-major (V as [key][column]): the 8 x 128-byte group holds 8 keys x 64 columns; 8 keys further = the stride
+//   offset (1024 bytes), 64 columns further = the leading offset (the next sub-tile).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t address) {
+    uint64_t d = 0;
+    d |= (uint64_t)((address & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ uint64_t desc_n_major(uint32_t address, uint32_t leading_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((address & 0x3FFFF) >> 4);
+    d |= (uint64_t)((leading_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, M 128.
+__device__ __forceinline__ uint32_t idesc(int n, bool b_n_major) {
+    uint32_t d = 0;
+    d |= 1u << 4;
+    d |= 1u << 7;
+    d |= 1u << 10;
+    if (b_n_major) d |= 1u << 16;
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct Params {
+    const int* block_table;
+    int table_stride;
+    const int* positions;      // [T]
+    const int* tiles;          // [num_tiles][3]: row of the block table, first token, tokens in the tile (<= 128)
+    bf16* out;
+    long long ldo;
+    int num_heads, num_kv_heads, page_size, num_pages, window;
+    long long page_rows, head_rows;           // in rows of the cache maps: per page, per KV head
+    float scale;
+    int* status;
+    long long* trace;          // optional [32][8] clock stamps of the first CTA's first softmax warp (profiling)
+};
+
+// The 64-bit shared-memory descriptor from its constant high word and a low word (start address, leading offset).
+__device__ __forceinline__ uint64_t desc_from(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
+attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const Params p) {
+    using S = Shape<HD>;
+    constexpr int STAGES = S::STAGES;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_done[2];
+    __shared__ int piece_page[STAGES][4];                         // the loader's block-table entries, per stage
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_addr = base, ring_addr = base + S::Q_BYTES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // later tiles of a request see more keys: start them first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y;
+    const int kvh = h / (p.num_heads / p.num_kv_heads);
+    const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
+    const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;            // positions in a tile are consecutive
+    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+    const int tile_lo = first / BN, ntiles = pos_hi / BN - tile_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&s_full[b], 1);
+            mbar_init(&p_full[b], 4);                             // one arrival per softmax warp
+            mbar_init(&o_done[b], 1);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                         // ---- TMA loader
+            mbar_expect_tx(&q_full, S::Q_BYTES);
+#pragma unroll
+            for (int sub = 0; sub < S::SUBS; ++sub) tma_load_2d(q_addr + sub * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + sub * 64, t0);
+            const int* table = p.block_table + (size_t)seq * p.table_stride;
+            // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
+            auto entry_of = [&](int j, int g) {
+                const int kpos0 = (tile_lo + j) * BN + g * 16;
+                if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
+                return __ldg(table + kpos0 / p.page_size);
+            };
+            // entries of the first STAGES tiles go to shared memory at once, those of the next tile wait in registers
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s)
+#pragma unroll
+                for (int g = 0; g < 4; ++g) piece_page[s][g] = entry_of(s, g);
+            int ahead[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) ahead[g] = entry_of(STAGES, g);
+            int issued = 0;
+            for (int j = 0; j < ntiles; ++j, ++issued) {
+                const int s = j % STAGES;
+                if (j >= STAGES && !mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, &abort_flag, p.status)) break;
+                int rows[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    int page = piece_page[s][g];
+                    if (page < 0 || page >= p.num_pages) {
+                        atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                        page = p.num_pages - 1;
+                    }
+                    const int kpos0 = (tile_lo + j) * BN + g * 16;
+                    rows[g] = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+                }
+                const uint32_t k_addr = ring_addr + s * S::STAGE_BYTES, v_addr = k_addr + S::K_BYTES;
+                mbar_expect_tx(&k_full[s], S::K_BYTES);
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+#pragma unroll
+                    for (int sub = 0; sub < S::SUBS; ++sub)
+                        tma_load_2d(k_addr + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES, &map_k, &k_full[s], sub * 64, rows[g]);
+                mbar_expect_tx(&v_full[s], S::K_BYTES);
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+#pragma unroll
+                    for (int sub = 0; sub < S::SUBS; ++sub)
+                        tma_load_2d(v_addr + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES, &map_v, &v_full[s], sub * 64, rows[g]);
+                // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
+#pragma unroll
+                for (int g = 0; g < 4; ++g) piece_page[s][g] = ahead[g];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) ahead[g] = entry_of(j + STAGES + 1, g);
+            }
+            // every copy has to land before the CTA gives up its shared memory, also when a role has given up
+            mbar_wait_plain(&q_full, 0);
+            for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+                mbar_wait_plain(&k_full[j % STAGES], (j / STAGES) & 1);
+                mbar_wait_plain(&v_full[j % STAGES], (j / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                         // ---- MMA issuer
+            const uint32_t idesc_s = idesc(BN, false), idesc_o = idesc(HD, true);
+            // descriptors differ in their low word only (start address): build the words once
+            const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
+            const uint32_t q_lo = (uint32_t)desc_k_major(q_addr);
+            const uint32_t k_lo = (uint32_t)desc_k_major(ring_addr);
+            const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
+            auto issue_scores = [&](int j) {
+                const uint32_t stage_lo = k_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
+                const uint32_t d = tmem_base + (uint32_t)((j & 1) * BN);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t a = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                    const uint64_t b = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                    tc_mma(d, a, b, idesc_s, kk ? 1u : 0u);
+                }
+                tc_commit(&s_full[j & 1]);
+            };
+            bool ok = mbar_wait(&q_full, 0, &abort_flag, p.status);
+            for (int j = 0; j < 2 && j < ntiles && ok; ++j) {
+                ok = mbar_wait(&k_full[j % STAGES], 0, &abort_flag, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                issue_scores(j);
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, &abort_flag, p.status) &&
+                     mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t stage_lo = v_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
+                const uint32_t d = tmem_base + (uint32_t)S::O_COL;
+                const uint32_t pa = tmem_base + (uint32_t)((j & 1) * BN);              // P_j: 32 columns of bfloat16 pairs
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    tc_mma_a_tmem(d, pa + (uint32_t)(kk * 8), desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi), idesc_o, (j | kk) ? 1u : 0u);
+                tc_commit(&o_done[j & 1]);
+                tc_commit(&kv_empty[j % STAGES]);                // K and V of this stage have been read
+                // the scores of tile j + 2 go where S_j and P_j were: the tensor core takes them after the product above
+                if (j + 2 < ntiles) {
+                    ok = mbar_wait(&k_full[(j + 2) % STAGES], ((j + 2) / STAGES) & 1, &abort_flag, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_scores(j + 2);
+                }
+            }
+        }
+    } else {                                                     // ---- softmax rows, warps 2..5
+        const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
+        const int row = quad * 32 + lane;
+        const bool valid = row < count;
+        const int qpos = pos_lo + row;
+        const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
+        const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
+        const bool warp_has_rows = quad * 32 < count;
+        const float scale_log2 = p.scale * 1.4426950408889634f;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t o_lane = lane_base + (uint32_t)S::O_COL;
+
+        // m: the reference of the exponents, a maximum the row has seen (in scaled base-2 units); l: the sum against it
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64;
+#define STAMP(k) if (tracing && j < 32) p.trace[j * 8 + (k)] = clock64();
+        for (int j = 0; j < ntiles; ++j) {
+            const int b = j & 1;
+            STAMP(0)
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, &abort_flag, p.status));   // the warp stays together
+            if (!ok) break;
+            tc_fence_after();
+            STAMP(1)
+            const int key_base = (tile_lo + j) * BN;
+            // a key tile that lies wholly behind or before this warp's rows contributes nothing
+            const bool skip = !warp_has_rows || key_base > warp_hi || key_base + BN - 1 < warp_first;
+            uint32_t packed[32];
+            float c = 1.f;
+            if (skip) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) packed[e] = 0u;
+            } else {
+                float s[64];
+                {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(lane_base + (uint32_t)(b * BN), r0);
+                    tmem_ld32(lane_base + (uint32_t)(b * BN + 32), r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        s[e] = __uint_as_float(r0[e]);
+                        s[32 + e] = __uint_as_float(r1[e]);
+                    }
+                }
+                STAMP(2)
+                // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
+                const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count ||
+                                    (p.window > 0 && key_base <= warp_lo + 31 - p.window);
+                if (limits) {
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) {
+                        const int kpos = key_base + e;
+                        const bool see = valid && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                        if (!see) s[e] = -INFINITY;
+                    }
+                }
+                float t[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) t[e] = fmaxf(s[e], s[32 + e]);
+#pragma unroll
+                for (int w = 16; w >= 1; w >>= 1)
+#pragma unroll
+                    for (int e = 0; e < w; ++e) t[e] = fmaxf(t[e], t[e + w]);
+                const float mn = t[0] * scale_log2;
+                if (mn > m + REFERENCE_SLACK) {                   // also the first finite maximum (m = -inf)
+                    c = exp2_approx(m - mn);                     // 0 for the first
+                    m = mn;
+                }
+                STAMP(3)
+                // a row that has seen nothing keeps m = -inf: 0 as the reference makes exp(-inf - 0) = 0
+                const float ref = m == -INFINITY ? 0.f : m;
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float e0 = exp2_approx(fmaf(s[2 * e], scale_log2, -ref));
+                    const float e1 = exp2_approx(fmaf(s[2 * e + 1], scale_log2, -ref));
+                    sum0 += e0;
+                    sum1 += e1;
+                    packed[e] = pack2(e0, e1);
+                }
+                l = l * c + (sum0 + sum1);
+            }
+            STAMP(4)
+            // Rows whose reference moved scale what they have accumulated so far: the product of the tile before must be
+            // done.  (Two barriers take turns: a warp that skips tiles may be a tile ahead of the tensor core, and a
+            // parity tells two phases apart, not three.)
+            if (j > 0 && __any_sync(0xffffffffu, c != 1.f)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1, &abort_flag, p.status));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_lane + (uint32_t)c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * c);
+                    tmem_st32(o_lane + (uint32_t)c0, r);
+                }
+            }
+            STAMP(5)
+            // P_j over the first 32 columns of S_j: element pairs (2e, 2e + 1) of this row
+            tmem_st32(lane_base + (uint32_t)(b * BN), packed);
+            tmem_st_wait();
+            STAMP(6)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
+            STAMP(7)
+        }
+#undef STAMP
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, &abort_flag, p.status));
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(o_lane + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * ch + e]) * inv;
+                        dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), cut into boxes of [box_rows x 64], 128-byte swizzled.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int HD>
+int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int num_tiles) {
+    using S = Shape<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(num_tiles, p.num_heads);
+    attention_prefill_tcgen05_kernel<HD><<<grid, THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+    return eg_launch_status();
+}
+
+}  // namespace
+
+// q: [total_tokens, >= num_heads * head_dim] bfloat16 with row stride ldq; k_cache / v_cache: [num_pages][num_kv_heads]
+// [page_size][head_dim] with the same strides (in elements); the last page must hold finite numbers (pieces of a
+// key tile that no query sees are read from it); tiles as in the warp-level prefill kernel, of up to 128 tokens.
+EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
+                                        const void* v_cache, const int* block_table, int table_stride, const int* positions,
+                                        const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
+                                        int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
+                                        int window, float scale, int* status, long long* trace) {
+    if (num_tiles <= 0) return 0;
+    if ((head_dim != 64 && head_dim != 128) || page_size <= 0 || page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads ||
+        num_heads > 65535 || num_pages <= 0 || total_tokens <= 0 || !status)
+        return (int)cudaErrorInvalidValue;
+    if (ldq % 8 || ldo % 8 || (uintptr_t)q % 16 || (uintptr_t)out % 16 || (uintptr_t)k_cache % 16 || (uintptr_t)v_cache % 16 ||
+        page_stride % head_dim || head_stride % head_dim || page_stride <= 0 || head_stride <= 0)
+        return (int)cudaErrorInvalidValue;
+    Params p{};
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.positions = positions;
+    p.tiles = tiles;
+    p.out = (bf16*)out;
+    p.ldo = ldo;
+    p.num_heads = num_heads;
+    p.num_kv_heads = num_kv_heads;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.window = window;
+    p.page_rows = page_stride / head_dim;
+    p.head_rows = head_stride / head_dim;
+    p.scale = scale;
+    p.status = status;
+    p.trace = trace;
+    // rows of head_dim elements that the cache maps cover: up to the last row of the last page
+    const long long kv_rows = (long long)(num_pages - 1) * p.page_rows + (long long)(num_kv_heads - 1) * p.head_rows + page_size;
+    if (kv_rows >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_q, map_k, map_v;
+    if (make_map(&map_q, q, total_tokens, (long long)num_heads * head_dim, ldq, BM) ||
+        make_map(&map_k, k_cache, kv_rows, head_dim, head_dim, 16) || make_map(&map_v, v_cache, kv_rows, head_dim, head_dim, 16))
+        return (int)cudaErrorInvalidValue;
+    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, num_tiles) : launch<128>(stream, map_q, map_k, map_v, p, num_tiles);
+}

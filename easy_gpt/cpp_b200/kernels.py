@@ -74,6 +74,9 @@ class _Signatures:
                           c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p]
     eg_attention_prefill = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
+    eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
+                                    c_float, c_void_p, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -345,7 +348,9 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 PREFILL_ATTENTION_HEAD_DIMS = (32, 64, 128)
-QUERY_TILE = 64
+QUERY_TILE = 128               # tokens per listed tile of a prompt portion
+TCGEN05_ATTENTION = os.environ.get("EASY_GPT_TCGEN05_ATTENTION", "1") != "0"
+TCGEN05_ATTENTION_MIN_QUERY = 33   # shorter portions leave most of the 128-row tile empty: the warp-level kernel takes them
 
 
 def attention_prefill_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -357,7 +362,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
                       status: torch.Tensor) -> None:
     """bfloat16 attention for prompt portions: ``tiles`` [n, 3] int32 lists (block table row,
-    first token, count <= 64) for runs of consecutive tokens of one request."""
+    first token, count <= 128) for runs of consecutive tokens of one request (warp-level kernel)."""
     _cuda(q, k_cache, v_cache, block_table, positions, tiles, out, status)
     page_size = k_cache.shape[2]
     _need(attention_prefill_takes(q.dtype, head_dim, page_size),
@@ -375,6 +380,38 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
         page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         _ptr(status)), "attention_prefill")
+
+
+def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                              positions: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, num_heads: int,
+                              num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
+                              status: torch.Tensor, trace: Optional[torch.Tensor] = None) -> None:
+    """The same as ``attention_prefill`` on the tcgen05 tensor cores (TMA-fed, accumulators in
+    TMEM): 128 query rows per CTA.  The cache's last page must hold finite numbers."""
+    _cuda(q, k_cache, v_cache, block_table, positions, tiles, out, status)
+    page_size = k_cache.shape[2]
+    _need(attention_prefill_tcgen05_takes(q.dtype, head_dim, page_size),
+          "attention_prefill_tcgen05 takes bfloat16, head sizes 64 and 128 and pages of a multiple of 16 tokens")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "q/out/cache layout")
+    _need(q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0
+          and q.shape[1] >= num_heads * head_dim, "16-byte aligned rows")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1, "block table")
+    _need(positions.dtype == torch.int32 and tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 3
+          and tiles.is_contiguous(), "int32 positions and tiles [n, 3]")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim) and k_cache.stride() == v_cache.stride()
+          and k_cache.shape == v_cache.shape and k_cache.stride(3) == 1 and k_cache.stride(2) == head_dim
+          and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0
+          and k_cache.stride(0) % head_dim == 0 and k_cache.stride(1) % head_dim == 0,
+          "cache shape [pages, NKV, page_size, HD], strides in whole rows")
+    _check(library().eg_attention_prefill_tcgen05(
+        _stream(), _ptr(q), q.stride(0), q.shape[0], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
+        _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
+        page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
+        _ptr(status), _ptr(trace) if trace is not None else None), "attention_prefill_tcgen05")
 
 
 SKINNY_KERNEL_TOKENS = 64      # what the kernel takes

@@ -114,10 +114,13 @@ class Attention(Mixer):
         attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
         if (ctx.query_tiles is not None and ctx.max_query_len > 4
                 and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size)):
-            # prompt portions: tiles of 64 query tokens against the cache
-            kernels.attention_prefill(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
-                                      self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
-                                      ctx.status)
+            # prompt portions: tiles of query tokens against the cache, on the tcgen05 tensor cores when
+            # the portions are long enough to fill their 128-row tiles
+            tensor_core = (kernels.TCGEN05_ATTENTION and ctx.max_query_len >= kernels.TCGEN05_ATTENTION_MIN_QUERY
+                           and kernels.attention_prefill_tcgen05_takes(dtype, self.head_dim, tables.page_size))
+            run = kernels.attention_prefill_tcgen05 if tensor_core else kernels.attention_prefill
+            run(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
+                self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status)
         elif kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
             longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)

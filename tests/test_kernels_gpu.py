@@ -210,6 +210,9 @@ ATTENTION_CASES = [
     (14, 2, 64, 16, [0, 100, 5], [200, 77, 64], None),        # prompt portions over several query tiles
     (6, 3, 128, 32, [31], [150], 50),
     (4, 1, 32, 16, [0], [129], 33),
+    (14, 2, 64, 16, [1000, 0], [130, 515], None),             # many key tiles: every buffer of the pipeline comes round
+    (4, 2, 64, 16, [300], [260], 100),                        # a window shorter than the portion
+    (4, 4, 128, 16, [129], [300], None),
 ]
 
 
@@ -259,6 +262,23 @@ def test_attention_kernels(case, dtype):
         assert status.item() == 0
         err = float((out.float().cpu() - c["want"]).abs().max())
         assert err <= tol, f"prefill: {err}"
+        # listed tiles may hold up to 128 tokens
+        tiles, t0 = [], 0
+        for s_idx, n in enumerate(queries):
+            tiles += [(s_idx, t0 + o, min(128, n - o)) for o in range(0, n, 128)]
+            t0 += n
+        tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+        out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+        kernels.attention_prefill(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window, scale, status)
+        err = float((out.float().cpu() - c["want"]).abs().max())
+        assert err <= tol and status.item() == 0, f"prefill, tiles of 128: {err}"
+        if kernels.attention_prefill_tcgen05_takes(dtype, HD, ps):
+            out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+            kernels.attention_prefill_tcgen05(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window,
+                                              scale, status)
+            assert status.item() == 0
+            err = float((out.float().cpu() - c["want"]).abs().max())
+            assert err <= tol, f"prefill tcgen05: {err}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
