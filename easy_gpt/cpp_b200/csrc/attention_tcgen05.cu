@@ -13,13 +13,24 @@
 // grown by more than 2^8 since the reference was set does the row's thread move the reference, and then it scales
 // its row of O in TMEM (tcgen05.ld, multiply, tcgen05.st) and its sum; O / sum stays the same.
 //
-// Warp roles: warp 0 one thread issues the TMA loads (Q once; per key tile one box of 16 keys x 64 columns per
-// page piece, K and V, 128-byte swizzled, into a ring of stages; the block-table entries are fetched a ring ahead),
-// warp 1 allocates TMEM and one thread issues every MMA, warps 2-5 are the softmax rows.  S has two TMEM buffers:
-// the tensor core computes the scores of the next key tile while the rows work on this one.  The tensor core takes
-// its instructions in order, so the scores of tile j + 2 overwrite the buffer of S_j / P_j only after O += P_j V_j.
-// Everything else is handed over with mbarriers.  Scale, maximum, exponent and sums are 32-bit; the exponent is the
-// hardware's base-2 approximation with the scale folded into its multiply-add.
+// Warp roles (256 threads; 128 registers each and at most 113 KB of shared memory, so that two CTAs share an SM
+// and one fills the other's waits; each allocates 256 of the 512 TMEM columns):
+//   warp 0     TMA loads: Q once; per key tile one box of 16 keys x 64 columns per page piece, K and V, 128-byte
+//              swizzled, into a ring of stages.  Issuing a copy costs the issuing thread a good hundred cycles, so
+//              every box of a tile has its own lane.  Block-table entries are fetched a ring ahead.
+//   warp 1     allocates TMEM; one thread issues the score products (descriptors ready before it waits: the
+//              arithmetic of a descriptor costs more than the issue of the MMA)
+//   warps 2-5  the softmax rows
+//   warp 6     one thread issues the output products
+// S has three TMEM buffers (two for head size 128): the tensor core computes the scores of later key tiles while
+// the rows work on this one.  S_j goes where S and P of three tiles before were, once the output product of that
+// tile is done.  Everything is handed over with mbarriers; a barrier's parity tells two phases apart, so every set
+// of barriers has as many members as its buffers, and nobody waits on one from further than a phase away.
+// Scale, maximum, exponent and sums are 32-bit; the exponent is the hardware's base-2 approximation with the scale
+// folded into its multiply-add.
+//
+// A step with few query tiles cuts their key ranges over several CTAs (gridDim.z): each writes its unnormalised O,
+// reference and sum; the CTA that draws the last ticket of the query tile adds them up.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread raises the CTA's abort flag and
 // EG_STATUS_WAIT_TIMEOUT; every role then leaves its loop, the loader waits (bounded again) for the copies it
@@ -34,8 +45,8 @@
 namespace {
 
 constexpr int BM = 128, BN = 64;
-constexpr int THREADS = 192;                                     // loader warp, MMA warp, four softmax warps
-constexpr int TMEM_COLS = 256;
+constexpr int THREADS = 256;                                     // loader warp, two MMA warps (1 and 6), four softmax warps (2-5)
+constexpr int MIN_PART_TILES = 4;                                 // a CTA's share of a key range: at least 4 tiles of 64 keys
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float REFERENCE_SLACK = 8.f;                            // the exponents' reference may lag the maximum by 2^8
 constexpr int SUB_ROW_BYTES = 128;                                // 64 bfloat16: one swizzle row
@@ -43,14 +54,16 @@ constexpr int SUB_ROW_BYTES = 128;                                // 64 bfloat16
 template <int HD>
 struct Shape {
     static constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of Q, K, V
-    static constexpr int STAGES = HD == 64 ? 5 : 4;
+    static constexpr int STAGES = HD == 64 ? 5 : 2;
+    static constexpr int SCORE_BUFFERS = HD == 64 ? 3 : 2;        // TMEM buffers of S_j / P_j
     static constexpr int Q_SUB_BYTES = BM * SUB_ROW_BYTES;        // 16 KB
     static constexpr int KV_SUB_BYTES = BN * SUB_ROW_BYTES;       // 8 KB
     static constexpr int Q_BYTES = SUBS * Q_SUB_BYTES;
     static constexpr int K_BYTES = SUBS * KV_SUB_BYTES;
     static constexpr int STAGE_BYTES = 2 * K_BYTES;               // K then V
     static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024;
-    static constexpr int O_COL = 2 * BN;                          // TMEM: S0/P0 [0,64) S1/P1 [64,128) then O
+    static constexpr int O_COL = SCORE_BUFFERS * BN;              // TMEM: S0/P0 [0,64) S1/P1 [64,128) S2/P2 [128,192) then O
+    static constexpr int TMEM_COLS = 256;                         // two CTAs share the SM's 512 columns
     static_assert(O_COL + HD <= TMEM_COLS, "TMEM columns");
 };
 
@@ -98,10 +111,19 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem]; ACCUMULATE false overwrites D
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                  " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0) : "memory");
 }
 // 32 consecutive columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -114,17 +136,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // Shared-memory matrix descriptors, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes apart.
@@ -183,6 +209,11 @@ struct Params {
     float scale;
     int* status;
     long long* trace;          // optional [32][8] clock stamps of the first CTA's first softmax warp (profiling)
+    // for key ranges cut over several CTAs (gridDim.z > 1): per (tile, head, part) 128 rows of unnormalised O,
+    // and of (reference, sum); per (tile, head) a ticket that the last part leaves at zero
+    float* partial_o;
+    float* partial_ml;
+    int* tickets;
 };
 
 // The 64-bit shared-memory descriptor from its constant high word and a low word (start address, leading offset).
@@ -191,21 +222,16 @@ __device__ __forceinline__ uint64_t desc_from(uint32_t lo, uint32_t hi) {
     asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
 template <int HD>
-__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const Params p) {
     using S = Shape<HD>;
-    constexpr int STAGES = S::STAGES;
+    constexpr int STAGES = S::STAGES, SCORE_BUFFERS = S::SCORE_BUFFERS;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_done[2];
+    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[SCORE_BUFFERS], p_full[SCORE_BUFFERS], o_done[SCORE_BUFFERS];
+    __shared__ __align__(8) uint64_t parts_written, ticket_drawn;
+    __shared__ int merges_here;                                   // this CTA was the last of its query tile's parts
     __shared__ int piece_page[STAGES][4];                         // the loader's block-table entries, per stage
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -221,16 +247,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
     const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;            // positions in a tile are consecutive
     const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int tile_lo = first / BN, ntiles = pos_hi / BN - tile_lo + 1;
+    // the key tiles of this query tile, cut into parts for the CTAs along z when there are enough of them
+    const int all_lo = first / BN, all_tiles = pos_hi / BN - all_lo + 1;
+    const int parts = min((int)gridDim.z, max(1, all_tiles / MIN_PART_TILES));
+    const int part = blockIdx.z;
+    if (part >= parts) return;
+    const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
+    const int tile_lo = all_lo + part_begin, ntiles = part_end - part_begin;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
+        mbar_init(&parts_written, 4);
+        mbar_init(&ticket_drawn, 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&kv_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < SCORE_BUFFERS; ++b) {
             mbar_init(&s_full[b], 1);
             mbar_init(&p_full[b], 4);                             // one arrival per softmax warp
             mbar_init(&o_done[b], 1);
@@ -239,7 +273,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(S::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
@@ -247,61 +281,63 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp == 0) {
-        if (lane == 0) {                                         // ---- TMA loader
+    if (warp == 0) {                                             // ---- TMA loader: one lane per box of a key tile
+        // lane = sub * 8 + kv * 4 + g: 64-column sub-tile, K or V, 16-key piece.  Issuing a TMA copy costs the issuing
+        // thread a good hundred cycles; eight (sixteen) lanes issue their boxes with one instruction.
+        const int g = lane & 3, is_v = (lane >> 2) & 1, sub = lane >> 3;
+        const bool loads = lane < 8 * S::SUBS;
+        if (lane == 0) {
             mbar_expect_tx(&q_full, S::Q_BYTES);
 #pragma unroll
-            for (int sub = 0; sub < S::SUBS; ++sub) tma_load_2d(q_addr + sub * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + sub * 64, t0);
-            const int* table = p.block_table + (size_t)seq * p.table_stride;
-            // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
-            auto entry_of = [&](int j, int g) {
-                const int kpos0 = (tile_lo + j) * BN + g * 16;
-                if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
-                return __ldg(table + kpos0 / p.page_size);
-            };
-            // entries of the first STAGES tiles go to shared memory at once, those of the next tile wait in registers
+            for (int qs = 0; qs < S::SUBS; ++qs) tma_load_2d(q_addr + qs * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + qs * 64, t0);
+        }
+        const int* table = p.block_table + (size_t)seq * p.table_stride;
+        // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
+        auto entry_of = [&](int j, int piece) {
+            const int kpos0 = (tile_lo + j) * BN + piece * 16;
+            if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
+            return __ldg(table + kpos0 / p.page_size);
+        };
+        // lanes 0..3 keep the entries: those of the first STAGES tiles go to shared memory at once, those of the tile
+        // after them wait in a register; every iteration moves one tile's entries on
+        int ahead = 0;
+        if (lane < 4) {
 #pragma unroll
-            for (int s = 0; s < STAGES; ++s)
-#pragma unroll
-                for (int g = 0; g < 4; ++g) piece_page[s][g] = entry_of(s, g);
-            int ahead[4];
-#pragma unroll
-            for (int g = 0; g < 4; ++g) ahead[g] = entry_of(STAGES, g);
-            int issued = 0;
-            for (int j = 0; j < ntiles; ++j, ++issued) {
-                const int s = j % STAGES;
-                if (j >= STAGES && !mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, &abort_flag, p.status)) break;
-                int rows[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    int page = piece_page[s][g];
-                    if (page < 0 || page >= p.num_pages) {
-                        atomicOr(p.status, EG_STATUS_BAD_PAGE);
-                        page = p.num_pages - 1;
-                    }
-                    const int kpos0 = (tile_lo + j) * BN + g * 16;
-                    rows[g] = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
-                }
-                const uint32_t k_addr = ring_addr + s * S::STAGE_BYTES, v_addr = k_addr + S::K_BYTES;
-                mbar_expect_tx(&k_full[s], S::K_BYTES);
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-#pragma unroll
-                    for (int sub = 0; sub < S::SUBS; ++sub)
-                        tma_load_2d(k_addr + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES, &map_k, &k_full[s], sub * 64, rows[g]);
-                mbar_expect_tx(&v_full[s], S::K_BYTES);
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-#pragma unroll
-                    for (int sub = 0; sub < S::SUBS; ++sub)
-                        tma_load_2d(v_addr + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES, &map_v, &v_full[s], sub * 64, rows[g]);
-                // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
-#pragma unroll
-                for (int g = 0; g < 4; ++g) piece_page[s][g] = ahead[g];
-#pragma unroll
-                for (int g = 0; g < 4; ++g) ahead[g] = entry_of(j + STAGES + 1, g);
+            for (int s = 0; s < STAGES; ++s) piece_page[s][lane] = entry_of(s, lane);
+            ahead = entry_of(STAGES, lane);
+        }
+        __syncwarp();
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        int issued = 0;
+        for (int j = 0; j < ntiles; ++j, ++issued) {
+            const int s = j % STAGES;
+            if (j >= STAGES && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, &abort_flag, p.status))) break;
+            int page = piece_page[s][g];
+            if (page < 0 || page >= p.num_pages) {
+                if (loads) atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                page = p.num_pages - 1;
             }
-            // every copy has to land before the CTA gives up its shared memory, also when a role has given up
+            const int kpos0 = (tile_lo + j) * BN + g * 16;
+            const int row = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+            if (lane == 0) {
+                mbar_expect_tx(&k_full[s], S::K_BYTES);
+                mbar_expect_tx(&v_full[s], S::K_BYTES);
+            }
+            __syncwarp();
+            if (loads) {
+                const uint32_t dst = ring_addr + s * S::STAGE_BYTES + is_v * S::K_BYTES + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES;
+                tma_load_2d(dst, map, is_v ? &v_full[s] : &k_full[s], sub * 64, row);
+            }
+            __syncwarp();
+            // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
+            if (lane < 4) {
+                piece_page[s][lane] = ahead;
+                ahead = entry_of(j + STAGES + 1, lane);
+            }
+            __syncwarp();
+        }
+        // every copy has to land before the CTA gives up its shared memory, also when a role has given up
+        if (lane == 0) {
             mbar_wait_plain(&q_full, 0);
             for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
                 mbar_wait_plain(&k_full[j % STAGES], (j / STAGES) & 1);
@@ -309,54 +345,62 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {                                         // ---- MMA issuer
-            const uint32_t idesc_s = idesc(BN, false), idesc_o = idesc(HD, true);
+        if (lane == 0) {                                         // ---- issuer of the score products S_j = Q K_j^T
+            const uint32_t idesc_s = idesc(BN, false);
             // descriptors differ in their low word only (start address): build the words once
             const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
             const uint32_t q_lo = (uint32_t)desc_k_major(q_addr);
             const uint32_t k_lo = (uint32_t)desc_k_major(ring_addr);
-            const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
-            auto issue_scores = [&](int j) {
+            bool ok = mbar_wait(&q_full, 0, &abort_flag, p.status);
+            for (int j = 0; j < ntiles && ok; ++j) {
                 const uint32_t stage_lo = k_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
-                const uint32_t d = tmem_base + (uint32_t)((j & 1) * BN);
+                const uint32_t d = tmem_base + (uint32_t)((j % SCORE_BUFFERS) * BN);
+                uint64_t a[HD / 16], b[HD / 16];
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint64_t a = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
-                    const uint64_t b = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
-                    tc_mma(d, a, b, idesc_s, kk ? 1u : 0u);
+                    a[kk] = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                    b[kk] = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
                 }
-                tc_commit(&s_full[j & 1]);
-            };
-            bool ok = mbar_wait(&q_full, 0, &abort_flag, p.status);
-            for (int j = 0; j < 2 && j < ntiles && ok; ++j) {
-                ok = mbar_wait(&k_full[j % STAGES], 0, &abort_flag, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                issue_scores(j);
-            }
-            for (int j = 0; j < ntiles && ok; ++j) {
-                ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1, &abort_flag, p.status) &&
-                     mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t stage_lo = v_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
-                const uint32_t d = tmem_base + (uint32_t)S::O_COL;
-                const uint32_t pa = tmem_base + (uint32_t)((j & 1) * BN);              // P_j: 32 columns of bfloat16 pairs
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    tc_mma_a_tmem(d, pa + (uint32_t)(kk * 8), desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi), idesc_o, (j | kk) ? 1u : 0u);
-                tc_commit(&o_done[j & 1]);
-                tc_commit(&kv_empty[j % STAGES]);                // K and V of this stage have been read
-                // the scores of tile j + 2 go where S_j and P_j were: the tensor core takes them after the product above
-                if (j + 2 < ntiles) {
-                    ok = mbar_wait(&k_full[(j + 2) % STAGES], ((j + 2) / STAGES) & 1, &abort_flag, p.status);
+                // S_j goes where S_{j-3} and P_{j-3} were: the product that read P_{j-3} must be done
+                if (j >= SCORE_BUFFERS) {
+                    ok = mbar_wait(&o_done[j % SCORE_BUFFERS], (j / SCORE_BUFFERS - 1) & 1, &abort_flag, p.status);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_scores(j + 2);
                 }
+                ok = mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                tc_mma<false>(d, a[0], b[0], idesc_s);
+#pragma unroll
+                for (int kk = 1; kk < HD / 16; ++kk) tc_mma<true>(d, a[kk], b[kk], idesc_s);
+                tc_commit(&s_full[j % SCORE_BUFFERS]);
             }
         }
-    } else {                                                     // ---- softmax rows, warps 2..5
+    } else if (warp == 6) {
+        if (lane == 0) {                                         // ---- issuer of the output products O += P_j V_j
+            const uint32_t idesc_o = idesc(HD, true);
+            const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
+            const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
+            const uint32_t d = tmem_base + (uint32_t)S::O_COL;
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const uint32_t stage_lo = v_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
+                const uint32_t pa = tmem_base + (uint32_t)((j % SCORE_BUFFERS) * BN);  // P_j: 32 columns of bfloat16 pairs
+                uint64_t b[BN / 16];
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) b[kk] = desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi);
+                ok = mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status) &&
+                     mbar_wait(&p_full[j % SCORE_BUFFERS], (j / SCORE_BUFFERS) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                if (j == 0) tc_mma_a_tmem<false>(d, pa, b[0], idesc_o);
+                else tc_mma_a_tmem<true>(d, pa, b[0], idesc_o);
+#pragma unroll
+                for (int kk = 1; kk < BN / 16; ++kk) tc_mma_a_tmem<true>(d, pa + (uint32_t)(kk * 8), b[kk], idesc_o);
+                tc_commit(&o_done[j % SCORE_BUFFERS]);
+                tc_commit(&kv_empty[j % STAGES]);                // K and V of this stage have been read
+            }
+        }
+    } else if (warp >= 2 && warp < 6) {                          // ---- softmax rows, warps 2..5
         const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
         const int row = quad * 32 + lane;
         const bool valid = row < count;
@@ -374,22 +418,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64;
 #define STAMP(k) if (tracing && j < 32) p.trace[j * 8 + (k)] = clock64();
         for (int j = 0; j < ntiles; ++j) {
-            const int b = j & 1;
+            const int b = j % SCORE_BUFFERS;
             STAMP(0)
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j >> 1) & 1, &abort_flag, p.status));   // the warp stays together
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / SCORE_BUFFERS) & 1, &abort_flag, p.status));   // the warp stays together
             if (!ok) break;
             tc_fence_after();
             STAMP(1)
             const int key_base = (tile_lo + j) * BN;
             // a key tile that lies wholly behind or before this warp's rows contributes nothing
             const bool skip = !warp_has_rows || key_base > warp_hi || key_base + BN - 1 < warp_first;
-            uint32_t packed[32];
-            float c = 1.f;
-            if (skip) {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) packed[e] = 0u;
-            } else {
-                float s[64];
+            float c = 1.f, ref = 0.f;
+            float s[64];
+            if (!skip) {
                 {
                     uint32_t r0[32], r1[32];
                     tmem_ld32(lane_base + (uint32_t)(b * BN), r0);
@@ -413,11 +453,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                         if (!see) s[e] = -INFINITY;
                     }
                 }
-                float t[32];
+                float t[16];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) t[e] = fmaxf(s[e], s[32 + e]);
+                for (int e = 0; e < 16; ++e) t[e] = fmaxf(fmaxf(s[e], s[16 + e]), fmaxf(s[32 + e], s[48 + e]));
 #pragma unroll
-                for (int w = 16; w >= 1; w >>= 1)
+                for (int w = 8; w >= 1; w >>= 1)
 #pragma unroll
                     for (int e = 0; e < w; ++e) t[e] = fmaxf(t[e], t[e + w]);
                 const float mn = t[0] * scale_log2;
@@ -425,41 +465,50 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     c = exp2_approx(m - mn);                     // 0 for the first
                     m = mn;
                 }
-                STAMP(3)
                 // a row that has seen nothing keeps m = -inf: 0 as the reference makes exp(-inf - 0) = 0
-                const float ref = m == -INFINITY ? 0.f : m;
-                float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float e0 = exp2_approx(fmaf(s[2 * e], scale_log2, -ref));
-                    const float e1 = exp2_approx(fmaf(s[2 * e + 1], scale_log2, -ref));
-                    sum0 += e0;
-                    sum1 += e1;
-                    packed[e] = pack2(e0, e1);
-                }
-                l = l * c + (sum0 + sum1);
+                ref = m == -INFINITY ? 0.f : m;
             }
-            STAMP(4)
+            STAMP(3)
             // Rows whose reference moved scale what they have accumulated so far: the product of the tile before must be
-            // done.  (Two barriers take turns: a warp that skips tiles may be a tile ahead of the tensor core, and a
-            // parity tells two phases apart, not three.)
+            // done.  (The barriers take turns like the score buffers: a parity tells two phases apart, not more, and
+            // nobody who waits on one of them is ever further than one phase from it.)
             if (j > 0 && __any_sync(0xffffffffu, c != 1.f)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1, &abort_flag, p.status));
+                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(j - 1) % SCORE_BUFFERS], ((j - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(o_lane + (uint32_t)c0, r);
+                for (int c0 = 0; c0 < HD; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(o_lane + (uint32_t)c0, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * c);
-                    tmem_st32(o_lane + (uint32_t)c0, r);
+                    for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * c);
+                    tmem_st16(o_lane + (uint32_t)c0, r);
                 }
             }
+            STAMP(4)
+            // P_j over the first 32 columns of S_j, element pairs (2e, 2e + 1) of this row, sixteen columns at a time
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[16];
+                if (skip) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) packed[e] = 0u;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float e0 = exp2_approx(fmaf(s[32 * half + 2 * e], scale_log2, -ref));
+                        const float e1 = exp2_approx(fmaf(s[32 * half + 2 * e + 1], scale_log2, -ref));
+                        sum0 += e0;
+                        sum1 += e1;
+                        packed[e] = pack2(e0, e1);
+                    }
+                }
+                tmem_st16(lane_base + (uint32_t)(b * BN + 16 * half), packed);
+            }
+            l = l * c + (sum0 + sum1);
             STAMP(5)
-            // P_j over the first 32 columns of S_j: element pairs (2e, 2e + 1) of this row
-            tmem_st32(lane_base + (uint32_t)(b * BN), packed);
             tmem_st_wait();
             STAMP(6)
             tc_fence_before();
@@ -468,8 +517,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             STAMP(7)
         }
 #undef STAMP
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1, &abort_flag, p.status));
-        if (ok) {
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) % SCORE_BUFFERS], ((ntiles - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+        if (ok && parts == 1) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
@@ -488,13 +537,84 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                 }
             }
+        } else if (ok) {
+            // One of several parts: the row's unnormalised O, reference and sum go to global memory; the CTA that draws
+            // the last ticket of the query tile adds the parts up.
+            tc_fence_after();
+            const size_t slot0 = ((size_t)tile * p.num_heads + h) * gridDim.z;
+            float* my_o = p.partial_o + ((slot0 + part) * BM + row) * HD;
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(o_lane + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<uint4*>(my_o + c0 + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                }
+            }
+            if (valid) *reinterpret_cast<float2*>(p.partial_ml + ((slot0 + part) * BM + row) * 2) = make_float2(m, l);
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&parts_written);
+            if (warp == 2) {
+                const bool all_in = __all_sync(0xffffffffu, mbar_wait(&parts_written, 0, &abort_flag, p.status));
+                if (lane == 0) {
+                    int last = 0;
+                    if (all_in) {
+                        int* ticket = p.tickets + (size_t)tile * p.num_heads + h;
+                        last = atomicAdd(ticket, 1) == parts - 1;
+                        if (last) *ticket = 0;                   // every part has drawn: ready for the next launch
+                    }
+                    merges_here = last;
+                    mbar_arrive(&ticket_drawn);
+                }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(&ticket_drawn, 0, &abort_flag, p.status));
+            if (ok && merges_here && valid) {
+                __threadfence();
+                float big = -INFINITY;
+                for (int i = 0; i < parts; ++i) big = fmaxf(big, __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2));
+                float total = 0.f;
+                for (int i = 0; i < parts; ++i) {
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + ((slot0 + i) * BM + row) * 2));
+                    if (ml.x != -INFINITY) total += exp2f(ml.x - big) * ml.y;           // -inf: that part saw no key of this row
+                }
+                const float inv = total > 0.f ? 1.0f / total : 0.f;
+                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    float acc[32];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+                    for (int i = 0; i < parts; ++i) {
+                        const float mi = __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2);
+                        if (mi == -INFINITY) continue;
+                        const float w = exp2f(mi - big) * inv;
+                        const float4* src = reinterpret_cast<const float4*>(p.partial_o + ((slot0 + i) * BM + row) * HD + c0);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float4 v = __ldcg(src + e);
+                            acc[4 * e] = fmaf(w, v.x, acc[4 * e]);
+                            acc[4 * e + 1] = fmaf(w, v.y, acc[4 * e + 1]);
+                            acc[4 * e + 2] = fmaf(w, v.z, acc[4 * e + 2]);
+                            acc[4 * e + 3] = fmaf(w, v.w, acc[4 * e + 3]);
+                        }
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch)
+                        dst[c0 / 8 + ch] = make_uint4(pack2(acc[8 * ch], acc[8 * ch + 1]), pack2(acc[8 * ch + 2], acc[8 * ch + 3]),
+                                                      pack2(acc[8 * ch + 4], acc[8 * ch + 5]), pack2(acc[8 * ch + 6], acc[8 * ch + 7]));
+                }
+            }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(S::TMEM_COLS) : "memory");
     }
 }
 
@@ -511,7 +631,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }
 
 template <int HD>
-int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int num_tiles) {
+int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int num_tiles, int max_parts) {
     using S = Shape<HD>;
     static bool configured = false;
     if (!configured) {
@@ -519,7 +639,7 @@ int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(num_tiles, p.num_heads);
+    dim3 grid(num_tiles, p.num_heads, max_parts);
     attention_prefill_tcgen05_kernel<HD><<<grid, THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
     return eg_launch_status();
 }
@@ -529,12 +649,16 @@ int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map
 // q: [total_tokens, >= num_heads * head_dim] bfloat16 with row stride ldq; k_cache / v_cache: [num_pages][num_kv_heads]
 // [page_size][head_dim] with the same strides (in elements); the last page must hold finite numbers (pieces of a
 // key tile that no query sees are read from it); tiles as in the warp-level prefill kernel, of up to 128 tokens.
+// max_parts > 1 lets up to that many CTAs share a query tile's keys (at least 256 keys each): partial_o takes
+// num_tiles * num_heads * max_parts * 128 * head_dim floats, partial_ml * 128 * 2, tickets num_tiles * num_heads
+// zeroed ints (left zero).
 EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
                                         const void* v_cache, const int* block_table, int table_stride, const int* positions,
                                         const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
                                         int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
-                                        int window, float scale, int* status, long long* trace) {
+                                        int window, float scale, int* status, long long* trace, int max_parts, float* partial_o, float* partial_ml, int* tickets) {
     if (num_tiles <= 0) return 0;
+    if (max_parts < 1 || max_parts > 64 || (max_parts > 1 && (!partial_o || !partial_ml || !tickets))) return (int)cudaErrorInvalidValue;
     if ((head_dim != 64 && head_dim != 128) || page_size <= 0 || page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads ||
         num_heads > 65535 || num_pages <= 0 || total_tokens <= 0 || !status)
         return (int)cudaErrorInvalidValue;
@@ -558,6 +682,9 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     p.scale = scale;
     p.status = status;
     p.trace = trace;
+    p.partial_o = partial_o;
+    p.partial_ml = partial_ml;
+    p.tickets = tickets;
     // rows of head_dim elements that the cache maps cover: up to the last row of the last page
     const long long kv_rows = (long long)(num_pages - 1) * p.page_rows + (long long)(num_kv_heads - 1) * p.head_rows + page_size;
     if (kv_rows >= (1ll << 31)) return (int)cudaErrorInvalidValue;
@@ -565,5 +692,5 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     if (make_map(&map_q, q, total_tokens, (long long)num_heads * head_dim, ldq, BM) ||
         make_map(&map_k, k_cache, kv_rows, head_dim, head_dim, 16) || make_map(&map_v, v_cache, kv_rows, head_dim, head_dim, 16))
         return (int)cudaErrorInvalidValue;
-    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, num_tiles) : launch<128>(stream, map_q, map_k, map_v, p, num_tiles);
+    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, num_tiles, max_parts) : launch<128>(stream, map_q, map_k, map_v, p, num_tiles, max_parts);
 }

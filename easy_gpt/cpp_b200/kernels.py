@@ -76,7 +76,7 @@ class _Signatures:
                             c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
     eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
-                                    c_float, c_void_p, c_void_p]
+                                    c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -382,6 +382,30 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _ptr(status)), "attention_prefill")
 
 
+PREFILL_PARTS_SCRATCH_BYTES = 256 << 20
+_parts_scratch = {}
+
+
+def _prefill_parts_scratch(device, slots: int, parts: int, head_dim: int):
+    """Scratch of the split prompt attention: grown, never shrunk; the tickets stay zero between launches."""
+    key = (device, head_dim)
+    need = slots * parts * 128
+    have = _parts_scratch.get(key)
+    if have is None or have[0].numel() < need * head_dim or have[2].numel() < slots:
+        have = (torch.empty(need * head_dim, dtype=torch.float32, device=device),
+                torch.empty(need * 2, dtype=torch.float32, device=device),
+                torch.zeros(max(slots, 1024), dtype=torch.int32, device=device))
+        _parts_scratch[key] = have
+    return have
+
+
+def attention_prefill_parts(num_tiles: int, num_heads: int, max_context: int) -> int:
+    """How many CTAs share the keys of a query tile.  Two CTAs of the kernel fit an SM: a step
+    with fewer (tile, head) pairs than that cuts the key ranges, at least 1024 keys a part."""
+    items = max(1, num_tiles * num_heads)
+    return max(1, min(2 * SM_COUNT // items, max_context // 1024, 8))
+
+
 def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0
 
@@ -389,9 +413,10 @@ def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size
 def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                               positions: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, num_heads: int,
                               num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
-                              status: torch.Tensor, trace: Optional[torch.Tensor] = None) -> None:
+                              status: torch.Tensor, trace: Optional[torch.Tensor] = None, parts: int = 1) -> None:
     """The same as ``attention_prefill`` on the tcgen05 tensor cores (TMA-fed, accumulators in
-    TMEM): 128 query rows per CTA.  The cache's last page must hold finite numbers."""
+    TMEM): 128 query rows per CTA.  The cache's last page must hold finite numbers.  ``parts``
+    > 1 lets that many CTAs share the keys of a query tile (long contexts, few tiles)."""
     _cuda(q, k_cache, v_cache, block_table, positions, tiles, out, status)
     page_size = k_cache.shape[2]
     _need(attention_prefill_tcgen05_takes(q.dtype, head_dim, page_size),
@@ -407,11 +432,21 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
           and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0
           and k_cache.stride(0) % head_dim == 0 and k_cache.stride(1) % head_dim == 0,
           "cache shape [pages, NKV, page_size, HD], strides in whole rows")
+    parts = max(1, int(parts))
+    partial_o = partial_ml = tickets = None
+    if parts > 1:
+        slots = tiles.shape[0] * num_heads
+        if slots * parts * 128 * (head_dim + 2) * 4 > PREFILL_PARTS_SCRATCH_BYTES:
+            parts = 1
+        else:
+            partial_o, partial_ml, tickets = _prefill_parts_scratch(q.device, slots, parts, head_dim)
     _check(library().eg_attention_prefill_tcgen05(
         _stream(), _ptr(q), q.stride(0), q.shape[0], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
         _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
         page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
-        _ptr(status), _ptr(trace) if trace is not None else None), "attention_prefill_tcgen05")
+        _ptr(status), _ptr(trace) if trace is not None else None, parts,
+        _ptr(partial_o) if parts > 1 else None, _ptr(partial_ml) if parts > 1 else None,
+        _ptr(tickets) if parts > 1 else None), "attention_prefill_tcgen05")
 
 
 SKINNY_KERNEL_TOKENS = 64      # what the kernel takes

@@ -118,9 +118,16 @@ class Attention(Mixer):
             # the portions are long enough to fill their 128-row tiles
             tensor_core = (kernels.TCGEN05_ATTENTION and ctx.max_query_len >= kernels.TCGEN05_ATTENTION_MIN_QUERY
                            and kernels.attention_prefill_tcgen05_takes(dtype, self.head_dim, tables.page_size))
-            run = kernels.attention_prefill_tcgen05 if tensor_core else kernels.attention_prefill
-            run(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
-                self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status)
+            if tensor_core:
+                longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 255)
+                kernels.attention_prefill_tcgen05(
+                    qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn, self.num_heads,
+                    self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status,
+                    parts=kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads, longest))
+            else:
+                kernels.attention_prefill(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
+                                          self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                                          ctx.status)
         elif kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
             longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)

@@ -279,6 +279,13 @@ def test_attention_kernels(case, dtype):
             assert status.item() == 0
             err = float((out.float().cpu() - c["want"]).abs().max())
             assert err <= tol, f"prefill tcgen05: {err}"
+            # the keys of a query tile shared by several CTAs, merged by the last to finish; twice: the tickets return to zero
+            for parts in (2, 5, 5):
+                out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
+                kernels.attention_prefill_tcgen05(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window,
+                                                  scale, status, parts=parts)
+                err = float((out.float().cpu() - c["want"]).abs().max())
+                assert err <= tol and status.item() == 0, f"prefill tcgen05, {parts} parts: {err}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
