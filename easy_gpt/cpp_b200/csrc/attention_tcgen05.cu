@@ -46,7 +46,6 @@ namespace {
 
 constexpr int BM = 128, BN = 64;
 constexpr int THREADS = 256;                                     // loader warp, two MMA warps (1 and 6), four softmax warps (2-5)
-constexpr int MIN_PART_TILES = 4;                                 // a CTA's share of a key range: at least 4 tiles of 64 keys
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float REFERENCE_SLACK = 8.f;                            // the exponents' reference may lag the maximum by 2^8
 constexpr int SUB_ROW_BYTES = 128;                                // 64 bfloat16: one swizzle row
@@ -214,6 +213,9 @@ struct Params {
     float* partial_o;
     float* partial_ml;
     int* tickets;
+    // work queue of the persistent CTAs: [0] next unit, [1] CTAs that have left; both zero before and after a launch
+    int* queue;
+    int num_tiles, max_parts, part_tiles;
 };
 
 // The 64-bit shared-memory descriptor from its constant high word and a low word (start address, leading offset).
@@ -233,27 +235,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __shared__ __align__(8) uint64_t parts_written, ticket_drawn;
     __shared__ int merges_here;                                   // this CTA was the last of its query tile's parts
     __shared__ int piece_page[STAGES][4];                         // the loader's block-table entries, per stage
+    __shared__ int unit_slot[2];                                  // the unit the CTA works on, by round parity
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_addr = base, ring_addr = base + S::Q_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    // later tiles of a request see more keys: start them first
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int h = blockIdx.y;
-    const int kvh = h / (p.num_heads / p.num_kv_heads);
-    const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
-    const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;            // positions in a tile are consecutive
-    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    // the key tiles of this query tile, cut into parts for the CTAs along z when there are enough of them
-    const int all_lo = first / BN, all_tiles = pos_hi / BN - all_lo + 1;
-    const int parts = min((int)gridDim.z, max(1, all_tiles / MIN_PART_TILES));
-    const int part = blockIdx.z;
-    if (part >= parts) return;
-    const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
-    const int tile_lo = all_lo + part_begin, ntiles = part_end - part_begin;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
@@ -281,337 +269,392 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp == 0) {                                             // ---- TMA loader: one lane per box of a key tile
-        // lane = sub * 8 + kv * 4 + g: 64-column sub-tile, K or V, 16-key piece.  Issuing a TMA copy costs the issuing
-        // thread a good hundred cycles; eight (sixteen) lanes issue their boxes with one instruction.
-        const int g = lane & 3, is_v = (lane >> 2) & 1, sub = lane >> 3;
-        const bool loads = lane < 8 * S::SUBS;
-        if (lane == 0) {
-            mbar_expect_tx(&q_full, S::Q_BYTES);
-#pragma unroll
-            for (int qs = 0; qs < S::SUBS; ++qs) tma_load_2d(q_addr + qs * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + qs * 64, t0);
-        }
-        const int* table = p.block_table + (size_t)seq * p.table_stride;
-        // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
-        auto entry_of = [&](int j, int piece) {
-            const int kpos0 = (tile_lo + j) * BN + piece * 16;
-            if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
-            return __ldg(table + kpos0 / p.page_size);
-        };
-        // lanes 0..3 keep the entries: those of the first STAGES tiles go to shared memory at once, those of the tile
-        // after them wait in a register; every iteration moves one tile's entries on
-        int ahead = 0;
-        if (lane < 4) {
-#pragma unroll
-            for (int s = 0; s < STAGES; ++s) piece_page[s][lane] = entry_of(s, lane);
-            ahead = entry_of(STAGES, lane);
-        }
-        __syncwarp();
-        const CUtensorMap* map = is_v ? &map_v : &map_k;
-        int issued = 0;
-        for (int j = 0; j < ntiles; ++j, ++issued) {
-            const int s = j % STAGES;
-            if (j >= STAGES && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, &abort_flag, p.status))) break;
-            int page = piece_page[s][g];
-            if (page < 0 || page >= p.num_pages) {
-                if (loads) atomicOr(p.status, EG_STATUS_BAD_PAGE);
-                page = p.num_pages - 1;
+    // A unit of work: (query tile, head, part of its key range).  Units are numbered so that the query tiles listed
+    // last (of a prompt: those that see most keys) come first, and dealt out through a counter: a CTA that is done
+    // with a unit takes the next one, which evens out the SMs' loads.
+    // Every role counts alike: gt key tiles before this unit (stage and buffer indices and barrier phases run on),
+    // units before this one (phase of q_full), units in parts before this one (phases of the merge barriers).
+    const int total_units = p.num_tiles * p.num_heads * p.max_parts;
+    int gt = 0, units_done = 0, splits_done = 0;
+    for (int round = 0;; ++round) {
+        if (threadIdx.x == 0) {
+            int u;
+            for (;;) {                                           // the next unit that has keys (at most total_units probes)
+                u = atomicAdd(&p.queue[0], 1);
+                if (u >= total_units) break;
+                const int u_tile = p.num_tiles - 1 - u / (p.max_parts * p.num_heads);
+                const int u_t0 = p.tiles[u_tile * 3 + 1], u_count = p.tiles[u_tile * 3 + 2];
+                const int u_lo = p.positions[u_t0], u_hi = u_lo + u_count - 1;
+                const int u_first = (p.window > 0 && u_lo - p.window + 1 > 0) ? u_lo - p.window + 1 : 0;
+                const int u_tiles = u_hi / BN - u_first / BN + 1;
+                if (u % p.max_parts < min(p.max_parts, (u_tiles + p.part_tiles - 1) / p.part_tiles)) break;
             }
-            const int kpos0 = (tile_lo + j) * BN + g * 16;
-            const int row = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+            unit_slot[round & 1] = u;
+        }
+        __syncthreads();
+        const int unit = unit_slot[round & 1];
+        if (unit >= total_units || abort_flag) break;
+        const int part = unit % p.max_parts;
+        const int h = (unit / p.max_parts) % p.num_heads;
+        const int tile = p.num_tiles - 1 - unit / (p.max_parts * p.num_heads);
+        const int kvh = h / (p.num_heads / p.num_kv_heads);
+        const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
+        const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;        // positions in a tile are consecutive
+        const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+        // the key tiles of this query tile, and this unit's part of them
+        const int all_lo = first / BN, all_tiles = pos_hi / BN - all_lo + 1;
+        const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
+        const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
+        const int tile_lo = all_lo + part_begin, ntiles = part_end - part_begin;
+
+        if (warp == 0) {                                         // ---- TMA loader: one lane per box of a key tile
+            // lane = sub * 8 + kv * 4 + g: 64-column sub-tile, K or V, 16-key piece.  Issuing a TMA copy costs the
+            // issuing thread a good hundred cycles; eight (sixteen) lanes issue their boxes with one instruction.
+            const int g = lane & 3, is_v = (lane >> 2) & 1, sub = lane >> 3;
+            const bool loads = lane < 8 * S::SUBS;
             if (lane == 0) {
-                mbar_expect_tx(&k_full[s], S::K_BYTES);
-                mbar_expect_tx(&v_full[s], S::K_BYTES);
-            }
-            __syncwarp();
-            if (loads) {
-                const uint32_t dst = ring_addr + s * S::STAGE_BYTES + is_v * S::K_BYTES + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES;
-                tma_load_2d(dst, map, is_v ? &v_full[s] : &k_full[s], sub * 64, row);
-            }
-            __syncwarp();
-            // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
-            if (lane < 4) {
-                piece_page[s][lane] = ahead;
-                ahead = entry_of(j + STAGES + 1, lane);
-            }
-            __syncwarp();
-        }
-        // every copy has to land before the CTA gives up its shared memory, also when a role has given up
-        if (lane == 0) {
-            mbar_wait_plain(&q_full, 0);
-            for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
-                mbar_wait_plain(&k_full[j % STAGES], (j / STAGES) & 1);
-                mbar_wait_plain(&v_full[j % STAGES], (j / STAGES) & 1);
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {                                         // ---- issuer of the score products S_j = Q K_j^T
-            const uint32_t idesc_s = idesc(BN, false);
-            // descriptors differ in their low word only (start address): build the words once
-            const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
-            const uint32_t q_lo = (uint32_t)desc_k_major(q_addr);
-            const uint32_t k_lo = (uint32_t)desc_k_major(ring_addr);
-            bool ok = mbar_wait(&q_full, 0, &abort_flag, p.status);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const uint32_t stage_lo = k_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
-                const uint32_t d = tmem_base + (uint32_t)((j % SCORE_BUFFERS) * BN);
-                uint64_t a[HD / 16], b[HD / 16];
+                mbar_expect_tx(&q_full, S::Q_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    a[kk] = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
-                    b[kk] = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                for (int qs = 0; qs < S::SUBS; ++qs) tma_load_2d(q_addr + qs * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + qs * 64, t0);
+            }
+            const int* table = p.block_table + (size_t)seq * p.table_stride;
+            // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
+            auto entry_of = [&](int j, int piece) {
+                const int kpos0 = (tile_lo + j) * BN + piece * 16;
+                if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
+                return __ldg(table + kpos0 / p.page_size);
+            };
+            // lanes 0..3 keep the entries: those of the first STAGES tiles go to shared memory at once, those of the
+            // tile after them wait in a register; every iteration moves one tile's entries on
+            int ahead = 0;
+            if (lane < 4) {
+#pragma unroll
+                for (int s = 0; s < STAGES; ++s) piece_page[(gt + s) % STAGES][lane] = entry_of(s, lane);
+                ahead = entry_of(STAGES, lane);
+            }
+            __syncwarp();
+            const CUtensorMap* map = is_v ? &map_v : &map_k;
+            int issued = 0;
+            for (int j = 0; j < ntiles; ++j, ++issued) {
+                const int s = (gt + j) % STAGES, use = (gt + j) / STAGES;
+                if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[s], (use - 1) & 1, &abort_flag, p.status))) break;
+                int page = piece_page[s][g];
+                if (page < 0 || page >= p.num_pages) {
+                    if (loads) atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                    page = p.num_pages - 1;
                 }
-                // S_j goes where S_{j-3} and P_{j-3} were: the product that read P_{j-3} must be done
-                if (j >= SCORE_BUFFERS) {
-                    ok = mbar_wait(&o_done[j % SCORE_BUFFERS], (j / SCORE_BUFFERS - 1) & 1, &abort_flag, p.status);
+                const int kpos0 = (tile_lo + j) * BN + g * 16;
+                const int row = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+                if (lane == 0) {
+                    mbar_expect_tx(&k_full[s], S::K_BYTES);
+                    mbar_expect_tx(&v_full[s], S::K_BYTES);
+                }
+                __syncwarp();
+                if (loads) {
+                    const uint32_t dst = ring_addr + s * S::STAGE_BYTES + is_v * S::K_BYTES + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES;
+                    tma_load_2d(dst, map, is_v ? &v_full[s] : &k_full[s], sub * 64, row);
+                }
+                __syncwarp();
+                // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
+                if (lane < 4) {
+                    piece_page[s][lane] = ahead;
+                    ahead = entry_of(j + STAGES + 1, lane);
+                }
+                __syncwarp();
+            }
+            // every copy has to land before the CTA gives up its shared memory, also when a role has given up
+            if (lane == 0 && abort_flag) {
+                mbar_wait_plain(&q_full, units_done & 1);
+                for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+                    mbar_wait_plain(&k_full[(gt + j) % STAGES], ((gt + j) / STAGES) & 1);
+                    mbar_wait_plain(&v_full[(gt + j) % STAGES], ((gt + j) / STAGES) & 1);
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {                                     // ---- issuer of the score products S_j = Q K_j^T
+                const uint32_t idesc_s = idesc(BN, false);
+                // descriptors differ in their low word only (start address): build the words once
+                const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
+                const uint32_t q_lo = (uint32_t)desc_k_major(q_addr);
+                const uint32_t k_lo = (uint32_t)desc_k_major(ring_addr);
+                bool ok = mbar_wait(&q_full, units_done & 1, &abort_flag, p.status);
+                for (int j = 0; j < ntiles && ok; ++j) {
+                    const int n = gt + j;
+                    const uint32_t stage_lo = k_lo + (uint32_t)(((n % STAGES) * S::STAGE_BYTES) >> 4);
+                    const uint32_t d = tmem_base + (uint32_t)((n % SCORE_BUFFERS) * BN);
+                    uint64_t a[HD / 16], b[HD / 16];
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        a[kk] = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                        b[kk] = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
+                    }
+                    // S goes where the S and P of SCORE_BUFFERS tiles before were: the product that read that P must be done
+                    if (n >= SCORE_BUFFERS) {
+                        ok = mbar_wait(&o_done[n % SCORE_BUFFERS], (n / SCORE_BUFFERS - 1) & 1, &abort_flag, p.status);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    ok = mbar_wait(&k_full[n % STAGES], (n / STAGES) & 1, &abort_flag, p.status);
+                    if (!ok) break;
+                    tc_mma<false>(d, a[0], b[0], idesc_s);
+#pragma unroll
+                    for (int kk = 1; kk < HD / 16; ++kk) tc_mma<true>(d, a[kk], b[kk], idesc_s);
+                    tc_commit(&s_full[n % SCORE_BUFFERS]);
+                }
+            }
+        } else if (warp == 6) {
+            if (lane == 0) {                                     // ---- issuer of the output products O += P_j V_j
+                const uint32_t idesc_o = idesc(HD, true);
+                const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
+                const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
+                const uint32_t d = tmem_base + (uint32_t)S::O_COL;
+                bool ok = true;
+                for (int j = 0; j < ntiles && ok; ++j) {
+                    const int n = gt + j;
+                    const uint32_t stage_lo = v_lo + (uint32_t)(((n % STAGES) * S::STAGE_BYTES) >> 4);
+                    const uint32_t pa = tmem_base + (uint32_t)((n % SCORE_BUFFERS) * BN);     // P_j: 32 columns of bfloat16 pairs
+                    uint64_t b[BN / 16];
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk) b[kk] = desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi);
+                    ok = mbar_wait(&v_full[n % STAGES], (n / STAGES) & 1, &abort_flag, p.status) &&
+                         mbar_wait(&p_full[n % SCORE_BUFFERS], (n / SCORE_BUFFERS) & 1, &abort_flag, p.status);
                     if (!ok) break;
                     tc_fence_after();
+                    if (j == 0) tc_mma_a_tmem<false>(d, pa, b[0], idesc_o);
+                    else tc_mma_a_tmem<true>(d, pa, b[0], idesc_o);
+#pragma unroll
+                    for (int kk = 1; kk < BN / 16; ++kk) tc_mma_a_tmem<true>(d, pa + (uint32_t)(kk * 8), b[kk], idesc_o);
+                    tc_commit(&o_done[n % SCORE_BUFFERS]);
+                    tc_commit(&kv_empty[n % STAGES]);            // K and V of this stage have been read
                 }
-                ok = mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status);
-                if (!ok) break;
-                tc_mma<false>(d, a[0], b[0], idesc_s);
-#pragma unroll
-                for (int kk = 1; kk < HD / 16; ++kk) tc_mma<true>(d, a[kk], b[kk], idesc_s);
-                tc_commit(&s_full[j % SCORE_BUFFERS]);
             }
-        }
-    } else if (warp == 6) {
-        if (lane == 0) {                                         // ---- issuer of the output products O += P_j V_j
-            const uint32_t idesc_o = idesc(HD, true);
-            const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
-            const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
-            const uint32_t d = tmem_base + (uint32_t)S::O_COL;
-            bool ok = true;
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const uint32_t stage_lo = v_lo + (uint32_t)(((j % STAGES) * S::STAGE_BYTES) >> 4);
-                const uint32_t pa = tmem_base + (uint32_t)((j % SCORE_BUFFERS) * BN);  // P_j: 32 columns of bfloat16 pairs
-                uint64_t b[BN / 16];
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) b[kk] = desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi);
-                ok = mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, &abort_flag, p.status) &&
-                     mbar_wait(&p_full[j % SCORE_BUFFERS], (j / SCORE_BUFFERS) & 1, &abort_flag, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                if (j == 0) tc_mma_a_tmem<false>(d, pa, b[0], idesc_o);
-                else tc_mma_a_tmem<true>(d, pa, b[0], idesc_o);
-#pragma unroll
-                for (int kk = 1; kk < BN / 16; ++kk) tc_mma_a_tmem<true>(d, pa + (uint32_t)(kk * 8), b[kk], idesc_o);
-                tc_commit(&o_done[j % SCORE_BUFFERS]);
-                tc_commit(&kv_empty[j % STAGES]);                // K and V of this stage have been read
-            }
-        }
-    } else if (warp >= 2 && warp < 6) {                          // ---- softmax rows, warps 2..5
-        const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
-        const int row = quad * 32 + lane;
-        const bool valid = row < count;
-        const int qpos = pos_lo + row;
-        const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
-        const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
-        const bool warp_has_rows = quad * 32 < count;
-        const float scale_log2 = p.scale * 1.4426950408889634f;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-        const uint32_t o_lane = lane_base + (uint32_t)S::O_COL;
+        } else if (warp >= 2 && warp < 6) {                      // ---- softmax rows, warps 2..5
+            const int quad = warp & 3;                           // a warp may touch TMEM lanes 32 * (warp % 4) ..
+            const int row = quad * 32 + lane;
+            const bool valid = row < count;
+            const int qpos = pos_lo + row;
+            const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
+            const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
+            const bool warp_has_rows = quad * 32 < count;
+            const float scale_log2 = p.scale * 1.4426950408889634f;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const uint32_t o_lane = lane_base + (uint32_t)S::O_COL;
 
-        // m: the reference of the exponents, a maximum the row has seen (in scaled base-2 units); l: the sum against it
-        float m = -INFINITY, l = 0.f;
-        bool ok = true;
-        const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64;
+            // m: the reference of the exponents, a maximum the row has seen (in scaled base-2 units); l: the sum against it
+            float m = -INFINITY, l = 0.f;
+            bool ok = true;
+            const bool tracing = p.trace && blockIdx.x == 0 && round == 0 && threadIdx.x == 64;
 #define STAMP(k) if (tracing && j < 32) p.trace[j * 8 + (k)] = clock64();
-        for (int j = 0; j < ntiles; ++j) {
-            const int b = j % SCORE_BUFFERS;
-            STAMP(0)
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (j / SCORE_BUFFERS) & 1, &abort_flag, p.status));   // the warp stays together
-            if (!ok) break;
-            tc_fence_after();
-            STAMP(1)
-            const int key_base = (tile_lo + j) * BN;
-            // a key tile that lies wholly behind or before this warp's rows contributes nothing
-            const bool skip = !warp_has_rows || key_base > warp_hi || key_base + BN - 1 < warp_first;
-            float c = 1.f, ref = 0.f;
-            float s[64];
-            if (!skip) {
-                {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(lane_base + (uint32_t)(b * BN), r0);
-                    tmem_ld32(lane_base + (uint32_t)(b * BN + 32), r1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        s[e] = __uint_as_float(r0[e]);
-                        s[32 + e] = __uint_as_float(r1[e]);
-                    }
-                }
-                STAMP(2)
-                // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
-                const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count ||
-                                    (p.window > 0 && key_base <= warp_lo + 31 - p.window);
-                if (limits) {
-#pragma unroll
-                    for (int e = 0; e < 64; ++e) {
-                        const int kpos = key_base + e;
-                        const bool see = valid && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
-                        if (!see) s[e] = -INFINITY;
-                    }
-                }
-                float t[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) t[e] = fmaxf(fmaxf(s[e], s[16 + e]), fmaxf(s[32 + e], s[48 + e]));
-#pragma unroll
-                for (int w = 8; w >= 1; w >>= 1)
-#pragma unroll
-                    for (int e = 0; e < w; ++e) t[e] = fmaxf(t[e], t[e + w]);
-                const float mn = t[0] * scale_log2;
-                if (mn > m + REFERENCE_SLACK) {                   // also the first finite maximum (m = -inf)
-                    c = exp2_approx(m - mn);                     // 0 for the first
-                    m = mn;
-                }
-                // a row that has seen nothing keeps m = -inf: 0 as the reference makes exp(-inf - 0) = 0
-                ref = m == -INFINITY ? 0.f : m;
-            }
-            STAMP(3)
-            // Rows whose reference moved scale what they have accumulated so far: the product of the tile before must be
-            // done.  (The barriers take turns like the score buffers: a parity tells two phases apart, not more, and
-            // nobody who waits on one of them is ever further than one phase from it.)
-            if (j > 0 && __any_sync(0xffffffffu, c != 1.f)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(j - 1) % SCORE_BUFFERS], ((j - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+            for (int j = 0; j < ntiles; ++j) {
+                const int n = gt + j, b = n % SCORE_BUFFERS;
+                STAMP(0)
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (n / SCORE_BUFFERS) & 1, &abort_flag, p.status));   // the warp stays together
                 if (!ok) break;
                 tc_fence_after();
+                STAMP(1)
+                const int key_base = (tile_lo + j) * BN;
+                // a key tile that lies wholly behind or before this warp's rows contributes nothing
+                const bool skip = !warp_has_rows || key_base > warp_hi || key_base + BN - 1 < warp_first;
+                float c = 1.f, ref = 0.f;
+                float s[64];
+                if (!skip) {
+                    {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld32(lane_base + (uint32_t)(b * BN), r0);
+                        tmem_ld32(lane_base + (uint32_t)(b * BN + 32), r1);
+                        tmem_ld_wait();
 #pragma unroll
-                for (int c0 = 0; c0 < HD; c0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(o_lane + (uint32_t)c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * c);
-                    tmem_st16(o_lane + (uint32_t)c0, r);
-                }
-            }
-            STAMP(4)
-            // P_j over the first 32 columns of S_j, element pairs (2e, 2e + 1) of this row, sixteen columns at a time
-            float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t packed[16];
-                if (skip) {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) packed[e] = 0u;
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float e0 = exp2_approx(fmaf(s[32 * half + 2 * e], scale_log2, -ref));
-                        const float e1 = exp2_approx(fmaf(s[32 * half + 2 * e + 1], scale_log2, -ref));
-                        sum0 += e0;
-                        sum1 += e1;
-                        packed[e] = pack2(e0, e1);
-                    }
-                }
-                tmem_st16(lane_base + (uint32_t)(b * BN + 16 * half), packed);
-            }
-            l = l * c + (sum0 + sum1);
-            STAMP(5)
-            tmem_st_wait();
-            STAMP(6)
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[b]);
-            STAMP(7)
-        }
-#undef STAMP
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) % SCORE_BUFFERS], ((ntiles - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
-        if (ok && parts == 1) {
-            tc_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(o_lane + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (valid) {
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        float v[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * ch + e]) * inv;
-                        dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
-                    }
-                }
-            }
-        } else if (ok) {
-            // One of several parts: the row's unnormalised O, reference and sum go to global memory; the CTA that draws
-            // the last ticket of the query tile adds the parts up.
-            tc_fence_after();
-            const size_t slot0 = ((size_t)tile * p.num_heads + h) * gridDim.z;
-            float* my_o = p.partial_o + ((slot0 + part) * BM + row) * HD;
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(o_lane + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (valid) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 4)
-                        *reinterpret_cast<uint4*>(my_o + c0 + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
-                }
-            }
-            if (valid) *reinterpret_cast<float2*>(p.partial_ml + ((slot0 + part) * BM + row) * 2) = make_float2(m, l);
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&parts_written);
-            if (warp == 2) {
-                const bool all_in = __all_sync(0xffffffffu, mbar_wait(&parts_written, 0, &abort_flag, p.status));
-                if (lane == 0) {
-                    int last = 0;
-                    if (all_in) {
-                        int* ticket = p.tickets + (size_t)tile * p.num_heads + h;
-                        last = atomicAdd(ticket, 1) == parts - 1;
-                        if (last) *ticket = 0;                   // every part has drawn: ready for the next launch
-                    }
-                    merges_here = last;
-                    mbar_arrive(&ticket_drawn);
-                }
-            }
-            ok = __all_sync(0xffffffffu, mbar_wait(&ticket_drawn, 0, &abort_flag, p.status));
-            if (ok && merges_here && valid) {
-                __threadfence();
-                float big = -INFINITY;
-                for (int i = 0; i < parts; ++i) big = fmaxf(big, __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2));
-                float total = 0.f;
-                for (int i = 0; i < parts; ++i) {
-                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + ((slot0 + i) * BM + row) * 2));
-                    if (ml.x != -INFINITY) total += exp2f(ml.x - big) * ml.y;           // -inf: that part saw no key of this row
-                }
-                const float inv = total > 0.f ? 1.0f / total : 0.f;
-                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
-#pragma unroll 1
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    float acc[32];
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-                    for (int i = 0; i < parts; ++i) {
-                        const float mi = __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2);
-                        if (mi == -INFINITY) continue;
-                        const float w = exp2f(mi - big) * inv;
-                        const float4* src = reinterpret_cast<const float4*>(p.partial_o + ((slot0 + i) * BM + row) * HD + c0);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float4 v = __ldcg(src + e);
-                            acc[4 * e] = fmaf(w, v.x, acc[4 * e]);
-                            acc[4 * e + 1] = fmaf(w, v.y, acc[4 * e + 1]);
-                            acc[4 * e + 2] = fmaf(w, v.z, acc[4 * e + 2]);
-                            acc[4 * e + 3] = fmaf(w, v.w, acc[4 * e + 3]);
+                        for (int e = 0; e < 32; ++e) {
+                            s[e] = __uint_as_float(r0[e]);
+                            s[32 + e] = __uint_as_float(r1[e]);
                         }
                     }
+                    STAMP(2)
+                    // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
+                    const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count ||
+                                        (p.window > 0 && key_base <= warp_lo + 31 - p.window);
+                    if (limits) {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch)
-                        dst[c0 / 8 + ch] = make_uint4(pack2(acc[8 * ch], acc[8 * ch + 1]), pack2(acc[8 * ch + 2], acc[8 * ch + 3]),
-                                                      pack2(acc[8 * ch + 4], acc[8 * ch + 5]), pack2(acc[8 * ch + 6], acc[8 * ch + 7]));
+                        for (int e = 0; e < 64; ++e) {
+                            const int kpos = key_base + e;
+                            const bool see = valid && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                            if (!see) s[e] = -INFINITY;
+                        }
+                    }
+                    float t[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) t[e] = fmaxf(fmaxf(s[e], s[16 + e]), fmaxf(s[32 + e], s[48 + e]));
+#pragma unroll
+                    for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+                        for (int e = 0; e < w; ++e) t[e] = fmaxf(t[e], t[e + w]);
+                    const float mn = t[0] * scale_log2;
+                    if (mn > m + REFERENCE_SLACK) {               // also the first finite maximum (m = -inf)
+                        c = exp2_approx(m - mn);                 // 0 for the first
+                        m = mn;
+                    }
+                    // a row that has seen nothing keeps m = -inf: 0 as the reference makes exp(-inf - 0) = 0
+                    ref = m == -INFINITY ? 0.f : m;
+                }
+                STAMP(3)
+                // Rows whose reference moved scale what they have accumulated so far: the product of the tile before
+                // must be done.  (The barriers take turns like the score buffers: a parity tells two phases apart, not
+                // more, and nobody who waits on one of them is ever further than one phase from it.)
+                if (j > 0 && __any_sync(0xffffffffu, c != 1.f)) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(n - 1) % SCORE_BUFFERS], ((n - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c0 = 0; c0 < HD; c0 += 16) {
+                        uint32_t r[16];
+                        tmem_ld16(o_lane + (uint32_t)c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * c);
+                        tmem_st16(o_lane + (uint32_t)c0, r);
+                    }
+                }
+                STAMP(4)
+                // P_j over the first 32 columns of S_j, element pairs (2e, 2e + 1) of this row, sixteen columns at a time
+                float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t packed[16];
+                    if (skip) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) packed[e] = 0u;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float e0 = exp2_approx(fmaf(s[32 * half + 2 * e], scale_log2, -ref));
+                            const float e1 = exp2_approx(fmaf(s[32 * half + 2 * e + 1], scale_log2, -ref));
+                            sum0 += e0;
+                            sum1 += e1;
+                            packed[e] = pack2(e0, e1);
+                        }
+                    }
+                    tmem_st16(lane_base + (uint32_t)(b * BN + 16 * half), packed);
+                }
+                l = l * c + (sum0 + sum1);
+                STAMP(5)
+                tmem_st_wait();
+                STAMP(6)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[b]);
+                STAMP(7)
+            }
+#undef STAMP
+            const int last = gt + ntiles - 1;
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[last % SCORE_BUFFERS], (last / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+            if (ok && parts == 1) {
+                tc_fence_after();
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_lane + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * ch + e]) * inv;
+                            dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                        }
+                    }
+                }
+            } else if (ok) {
+                // One of several parts: the row's unnormalised O, reference and sum go to global memory; the CTA that
+                // draws the last ticket of the query tile adds the parts up.
+                tc_fence_after();
+                const size_t slot0 = ((size_t)tile * p.num_heads + h) * p.max_parts;
+                float* my_o = p.partial_o + ((slot0 + part) * BM + row) * HD;
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_lane + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<uint4*>(my_o + c0 + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                    }
+                }
+                if (valid) *reinterpret_cast<float2*>(p.partial_ml + ((slot0 + part) * BM + row) * 2) = make_float2(m, l);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&parts_written);
+                if (warp == 2) {
+                    const bool all_in = __all_sync(0xffffffffu, mbar_wait(&parts_written, splits_done & 1, &abort_flag, p.status));
+                    if (lane == 0) {
+                        int last_part = 0;
+                        if (all_in) {
+                            int* ticket = p.tickets + (size_t)tile * p.num_heads + h;
+                            last_part = atomicAdd(ticket, 1) == parts - 1;
+                            if (last_part) *ticket = 0;          // every part has drawn: ready for the next launch
+                        }
+                        merges_here = last_part;
+                        mbar_arrive(&ticket_drawn);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, mbar_wait(&ticket_drawn, splits_done & 1, &abort_flag, p.status));
+                if (ok && merges_here && valid) {
+                    __threadfence();
+                    float big = -INFINITY;
+                    for (int i = 0; i < parts; ++i) big = fmaxf(big, __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2));
+                    float total = 0.f;
+                    for (int i = 0; i < parts; ++i) {
+                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + ((slot0 + i) * BM + row) * 2));
+                        if (ml.x != -INFINITY) total += exp2f(ml.x - big) * ml.y;       // -inf: that part saw no key of this row
+                    }
+                    const float inv = total > 0.f ? 1.0f / total : 0.f;
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        float acc[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+                        for (int i = 0; i < parts; ++i) {
+                            const float mi = __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2);
+                            if (mi == -INFINITY) continue;
+                            const float w = exp2f(mi - big) * inv;
+                            const float4* src = reinterpret_cast<const float4*>(p.partial_o + ((slot0 + i) * BM + row) * HD + c0);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float4 v = __ldcg(src + e);
+                                acc[4 * e] = fmaf(w, v.x, acc[4 * e]);
+                                acc[4 * e + 1] = fmaf(w, v.y, acc[4 * e + 1]);
+                                acc[4 * e + 2] = fmaf(w, v.z, acc[4 * e + 2]);
+                                acc[4 * e + 3] = fmaf(w, v.w, acc[4 * e + 3]);
+                            }
+                        }
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch)
+                            dst[c0 / 8 + ch] = make_uint4(pack2(acc[8 * ch], acc[8 * ch + 1]), pack2(acc[8 * ch + 2], acc[8 * ch + 3]),
+                                                          pack2(acc[8 * ch + 4], acc[8 * ch + 5]), pack2(acc[8 * ch + 6], acc[8 * ch + 7]));
+                    }
                 }
             }
         }
+        // the unit is done when its rows are: O in TMEM and Q in shared memory may be overwritten
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        gt += ntiles;
+        ++units_done;
+        if (parts > 1) ++splits_done;
     }
-    tc_fence_before();
-    __syncthreads();
+    // the last CTA to leave puts the queue back to zero for the next launch
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&p.queue[1], 1) == (int)gridDim.x - 1) {
+            p.queue[0] = 0;
+            p.queue[1] = 0;
+        }
+    }
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(S::TMEM_COLS) : "memory");
@@ -631,7 +674,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }
 
 template <int HD>
-int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int num_tiles, int max_parts) {
+int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int ctas) {
     using S = Shape<HD>;
     static bool configured = false;
     if (!configured) {
@@ -639,8 +682,7 @@ int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(num_tiles, p.num_heads, max_parts);
-    attention_prefill_tcgen05_kernel<HD><<<grid, THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+    attention_prefill_tcgen05_kernel<HD><<<ctas, THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
     return eg_launch_status();
 }
 
@@ -649,16 +691,18 @@ int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map
 // q: [total_tokens, >= num_heads * head_dim] bfloat16 with row stride ldq; k_cache / v_cache: [num_pages][num_kv_heads]
 // [page_size][head_dim] with the same strides (in elements); the last page must hold finite numbers (pieces of a
 // key tile that no query sees are read from it); tiles as in the warp-level prefill kernel, of up to 128 tokens.
-// max_parts > 1 lets up to that many CTAs share a query tile's keys (at least 256 keys each): partial_o takes
+// A query tile's keys are cut into parts of about part_tiles key tiles (of 64), at most max_parts: partial_o takes
 // num_tiles * num_heads * max_parts * 128 * head_dim floats, partial_ml * 128 * 2, tickets num_tiles * num_heads
-// zeroed ints (left zero).
+// zeroed ints (left zero); queue: two zeroed ints (left zero).
 EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
                                         const void* v_cache, const int* block_table, int table_stride, const int* positions,
                                         const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
                                         int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
-                                        int window, float scale, int* status, long long* trace, int max_parts, float* partial_o, float* partial_ml, int* tickets) {
+                                        int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
+                                        int* tickets, int* queue) {
     if (num_tiles <= 0) return 0;
-    if (max_parts < 1 || max_parts > 64 || (max_parts > 1 && (!partial_o || !partial_ml || !tickets))) return (int)cudaErrorInvalidValue;
+    if (max_parts < 1 || max_parts > 64 || part_tiles < 1 || !queue || (max_parts > 1 && (!partial_o || !partial_ml || !tickets)))
+        return (int)cudaErrorInvalidValue;
     if ((head_dim != 64 && head_dim != 128) || page_size <= 0 || page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads ||
         num_heads > 65535 || num_pages <= 0 || total_tokens <= 0 || !status)
         return (int)cudaErrorInvalidValue;
@@ -685,6 +729,10 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     p.partial_o = partial_o;
     p.partial_ml = partial_ml;
     p.tickets = tickets;
+    p.queue = queue;
+    p.num_tiles = num_tiles;
+    p.max_parts = max_parts;
+    p.part_tiles = part_tiles;
     // rows of head_dim elements that the cache maps cover: up to the last row of the last page
     const long long kv_rows = (long long)(num_pages - 1) * p.page_rows + (long long)(num_kv_heads - 1) * p.head_rows + page_size;
     if (kv_rows >= (1ll << 31)) return (int)cudaErrorInvalidValue;
@@ -692,5 +740,14 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     if (make_map(&map_q, q, total_tokens, (long long)num_heads * head_dim, ldq, BM) ||
         make_map(&map_k, k_cache, kv_rows, head_dim, head_dim, 16) || make_map(&map_v, v_cache, kv_rows, head_dim, head_dim, 16))
         return (int)cudaErrorInvalidValue;
-    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, num_tiles, max_parts) : launch<128>(stream, map_q, map_k, map_v, p, num_tiles, max_parts);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    // persistent CTAs, two per SM, that deal the units out among themselves
+    const long long units = (long long)num_tiles * num_heads * max_parts;
+    const int ctas = (int)(units < 2ll * sm_count ? units : 2ll * sm_count);
+    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, ctas) : launch<128>(stream, map_q, map_k, map_v, p, ctas);
 }

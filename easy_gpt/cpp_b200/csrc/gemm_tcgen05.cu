@@ -86,6 +86,20 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_address) {
     return d;
 }
 
+// The same descriptor from its two words: only the low one (start address) changes from tile to tile, and putting
+// a descriptor together costs the issuing thread more than the MMA it feeds.
+__device__ __forceinline__ uint64_t umma_desc_from(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0) : "memory");
+}
+
 // Instruction descriptor for kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
 __device__ __forceinline__ uint32_t umma_idesc(int n = BN) {
     uint32_t d = 0;
@@ -150,22 +164,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         if (lane == 0) {                                         // ---- MMA issuer
             const uint32_t idesc = umma_idesc();
+            const uint32_t desc_hi = (uint32_t)(umma_desc(0) >> 32), ring_lo = (uint32_t)umma_desc(smem_addr(ring));
             bool ok = true;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
                 const int s = kb % STAGES;
-                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1, &abort_flag, p.status);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t a_addr = smem_addr(ring + s * STAGE_BYTES), b_addr = a_addr + TILE_A_BYTES;
+                // descriptors first, then the wait: 16 elements of K = 32 bytes further inside the swizzled row
+                const uint32_t a_lo = ring_lo + (uint32_t)((s * STAGE_BYTES) >> 4), b_lo = a_lo + (TILE_A_BYTES >> 4);
+                uint64_t adesc[BK / 16], bdesc[BK / 16];
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k) {
-                    // 16 elements of K = 32 bytes further inside the swizzled row
-                    const uint64_t adesc = umma_desc(a_addr + k * 32), bdesc = umma_desc(b_addr + k * 32);
-                    const uint32_t accumulate = (kb | k) ? 1u : 0u;
-                    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                                 ::"r"(tmem_base), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                    adesc[k] = umma_desc_from(a_lo + 2 * k, desc_hi);
+                    bdesc[k] = umma_desc_from(b_lo + 2 * k, desc_hi);
                 }
+                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                if (kb) umma<true>(tmem_base, adesc[0], bdesc[0], idesc);
+                else umma<false>(tmem_base, adesc[0], bdesc[0], idesc);
+#pragma unroll
+                for (int k = 1; k < BK / 16; ++k) umma<true>(tmem_base, adesc[k], bdesc[k], idesc);
                 // hands the stage back once the MMAs above have read it
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&empty_bar[s])) : "memory");
             }
@@ -302,6 +318,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else if (warp == 1) {
         if (lane == 0) {                                         // ---- MMA issuer
             const uint32_t idesc = umma_idesc(WBN);
+            const uint32_t desc_hi = (uint32_t)(umma_desc(0) >> 32), ring_lo = (uint32_t)umma_desc(smem_addr(ring));
             int g = 0, local = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
@@ -312,18 +329,19 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * WBN);
                 for (int kb = 0; kb < k_blocks; ++kb, ++g) {
                     const int s = g % WSTAGES;
-                    ok = mbar_wait(&full_bar[s], (g / WSTAGES) & 1, &abort_flag, p.status);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t a_addr = smem_addr(ring + s * W_STAGE_BYTES), b_addr = a_addr + TILE_A_BYTES;
+                    const uint32_t a_lo = ring_lo + (uint32_t)((s * W_STAGE_BYTES) >> 4), b_lo = a_lo + (TILE_A_BYTES >> 4);
+                    uint64_t adesc[BK / 16], bdesc[BK / 16];
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        const uint64_t adesc = umma_desc(a_addr + k * 32), bdesc = umma_desc(b_addr + k * 32);
-                        const uint32_t accumulate = (kb | k) ? 1u : 0u;
-                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                                     " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                                     ::"r"(tmem_acc), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+                        adesc[k] = umma_desc_from(a_lo + 2 * k, desc_hi);
+                        bdesc[k] = umma_desc_from(b_lo + 2 * k, desc_hi);
                     }
+                    ok = mbar_wait(&full_bar[s], (g / WSTAGES) & 1, &abort_flag, p.status);
+                    if (!ok) break;
+                    if (kb) umma<true>(tmem_acc, adesc[0], bdesc[0], idesc);
+                    else umma<false>(tmem_acc, adesc[0], bdesc[0], idesc);
+#pragma unroll
+                    for (int k = 1; k < BK / 16; ++k) umma<true>(tmem_acc, adesc[k], bdesc[k], idesc);
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&empty_bar[s])) : "memory");
                 }
                 if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&acc_full[buf])) : "memory");

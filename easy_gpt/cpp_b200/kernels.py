@@ -76,7 +76,7 @@ class _Signatures:
                             c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
     eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
-                                    c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+                                    c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -383,27 +383,36 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 PREFILL_PARTS_SCRATCH_BYTES = 256 << 20
+PREFILL_PART_TILES = int(os.environ.get("EASY_GPT_PREFILL_PART_TILES", "16"))     # key tiles (of 64) per part
 _parts_scratch = {}
 
 
 def _prefill_parts_scratch(device, slots: int, parts: int, head_dim: int):
-    """Scratch of the split prompt attention: grown, never shrunk; the tickets stay zero between launches."""
+    """Scratch of the prompt attention: partial results when key ranges are cut (grown, never
+    shrunk), tickets and the work queue, which stay zero between launches."""
     key = (device, head_dim)
-    need = slots * parts * 128
+    need = slots * parts * 128 if parts > 1 else 0
     have = _parts_scratch.get(key)
     if have is None or have[0].numel() < need * head_dim or have[2].numel() < slots:
-        have = (torch.empty(need * head_dim, dtype=torch.float32, device=device),
-                torch.empty(need * 2, dtype=torch.float32, device=device),
-                torch.zeros(max(slots, 1024), dtype=torch.int32, device=device))
+        have = (torch.empty(max(need * head_dim, 1), dtype=torch.float32, device=device),
+                torch.empty(max(need * 2, 1), dtype=torch.float32, device=device),
+                torch.zeros(max(slots, 1024), dtype=torch.int32, device=device),
+                have[3] if have is not None else torch.zeros(2, dtype=torch.int32, device=device))
         _parts_scratch[key] = have
     return have
 
 
-def attention_prefill_parts(num_tiles: int, num_heads: int, max_context: int) -> int:
-    """How many CTAs share the keys of a query tile.  Two CTAs of the kernel fit an SM: a step
-    with fewer (tile, head) pairs than that cuts the key ranges, at least 1024 keys a part."""
+def attention_prefill_parts(num_tiles: int, num_heads: int, max_context: int):
+    """(parts, part_tiles): into how many parts of how many key tiles (of 64) a query tile's keys
+    are cut.  A part costs its CTA a start-up and a merge, which pays only while there are fewer
+    (tile, head) pairs than the two CTAs per SM; a part has at least ``PREFILL_PART_TILES`` tiles."""
     items = max(1, num_tiles * num_heads)
-    return max(1, min(2 * SM_COUNT // items, max_context // 1024, 8))
+    wanted = 2 * SM_COUNT // items
+    key_tiles = -(-max_context // 64)
+    if wanted < 2 or key_tiles < 2 * PREFILL_PART_TILES:
+        return 1, max(key_tiles, 1)
+    part_tiles = max(PREFILL_PART_TILES, -(-key_tiles // wanted))
+    return min(-(-key_tiles // part_tiles), 16), part_tiles
 
 
 def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -413,10 +422,12 @@ def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size
 def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                               positions: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor, num_heads: int,
                               num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
-                              status: torch.Tensor, trace: Optional[torch.Tensor] = None, parts: int = 1) -> None:
+                              status: torch.Tensor, trace: Optional[torch.Tensor] = None, parts: int = 1,
+                              part_tiles: int = 0) -> None:
     """The same as ``attention_prefill`` on the tcgen05 tensor cores (TMA-fed, accumulators in
-    TMEM): 128 query rows per CTA.  The cache's last page must hold finite numbers.  ``parts``
-    > 1 lets that many CTAs share the keys of a query tile (long contexts, few tiles)."""
+    TMEM): persistent CTAs, two per SM, deal out units of (128 query rows, head, part of the key
+    range).  ``parts``: the most parts a query tile's keys are cut into, of about ``part_tiles``
+    tiles of 64 keys.  The cache's last page must hold finite numbers."""
     _cuda(q, k_cache, v_cache, block_table, positions, tiles, out, status)
     page_size = k_cache.shape[2]
     _need(attention_prefill_tcgen05_takes(q.dtype, head_dim, page_size),
@@ -433,20 +444,16 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
           and k_cache.stride(0) % head_dim == 0 and k_cache.stride(1) % head_dim == 0,
           "cache shape [pages, NKV, page_size, HD], strides in whole rows")
     parts = max(1, int(parts))
-    partial_o = partial_ml = tickets = None
-    if parts > 1:
-        slots = tiles.shape[0] * num_heads
-        if slots * parts * 128 * (head_dim + 2) * 4 > PREFILL_PARTS_SCRATCH_BYTES:
-            parts = 1
-        else:
-            partial_o, partial_ml, tickets = _prefill_parts_scratch(q.device, slots, parts, head_dim)
+    slots = tiles.shape[0] * num_heads
+    while parts > 1 and slots * parts * 128 * (head_dim + 2) * 4 > PREFILL_PARTS_SCRATCH_BYTES:
+        parts -= 1
+    partial_o, partial_ml, tickets, queue = _prefill_parts_scratch(q.device, slots, parts, head_dim)
     _check(library().eg_attention_prefill_tcgen05(
         _stream(), _ptr(q), q.stride(0), q.shape[0], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
         _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
         page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
-        _ptr(status), _ptr(trace) if trace is not None else None, parts,
-        _ptr(partial_o) if parts > 1 else None, _ptr(partial_ml) if parts > 1 else None,
-        _ptr(tickets) if parts > 1 else None), "attention_prefill_tcgen05")
+        _ptr(status), _ptr(trace) if trace is not None else None, parts, int(part_tiles or PREFILL_PART_TILES),
+        _ptr(partial_o), _ptr(partial_ml), _ptr(tickets), _ptr(queue)), "attention_prefill_tcgen05")
 
 
 SKINNY_KERNEL_TOKENS = 64      # what the kernel takes

@@ -120,10 +120,10 @@ class Attention(Mixer):
                            and kernels.attention_prefill_tcgen05_takes(dtype, self.head_dim, tables.page_size))
             if tensor_core:
                 longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 255)
+                parts, part_tiles = kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads, longest)
                 kernels.attention_prefill_tcgen05(
                     qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn, self.num_heads,
-                    self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status,
-                    parts=kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads, longest))
+                    self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status, parts=parts, part_tiles=part_tiles)
             else:
                 kernels.attention_prefill(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
                                           self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,

@@ -280,12 +280,12 @@ def test_attention_kernels(case, dtype):
             err = float((out.float().cpu() - c["want"]).abs().max())
             assert err <= tol, f"prefill tcgen05: {err}"
             # the keys of a query tile shared by several CTAs, merged by the last to finish; twice: the tickets return to zero
-            for parts in (2, 5, 5):
+            for parts, part_tiles in ((2, 4), (5, 1), (5, 1), (16, 2)):
                 out = torch.zeros(T, NH * HD, dtype=dtype, device=DEV)
                 kernels.attention_prefill_tcgen05(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window,
-                                                  scale, status, parts=parts)
+                                                  scale, status, parts=parts, part_tiles=part_tiles)
                 err = float((out.float().cpu() - c["want"]).abs().max())
-                assert err <= tol and status.item() == 0, f"prefill tcgen05, {parts} parts: {err}"
+                assert err <= tol and status.item() == 0, f"prefill tcgen05, {parts} parts of {part_tiles} tiles: {err}"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
