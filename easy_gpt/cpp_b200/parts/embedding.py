@@ -67,11 +67,14 @@ class LMHead(Part):
         return [self.linear.weight[:rows]]
 
     accepts_pending_norm = True
+    # Thousands of CTAs share the head's rows, and each would repeat the add + norm of the few tokens in front of its
+    # product: normalising once in a kernel of its own measured 1.7% faster per decode step at batch 8.
+    fuse_norm = False
 
     def forward(self, x):
         """x: normalised rows [R, hidden] or a PendingNorm; returns float32 logits [R, vocab]."""
         if isinstance(x, PendingNorm):
-            if x.fusable:
+            if x.fusable and self.fuse_norm:
                 out = torch.empty((x.residual.shape[0], self.vocab), device=x.residual.device, dtype=torch.float32)
                 kernels.gemm_skinny(self.linear.weight, None, out, kernels.EPI_F32, **x.fused_args())
                 return out
