@@ -418,6 +418,242 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// few rows (17 .. 128 tokens: the larger decode batches, short prompt portions): the weights stream once
+// ---------------------------------------------------------------------------
+// The tokens are the MMA's 128 rows (rows past M come zero-filled from the TMA and are not stored), a CTA takes BN
+// output columns (32, 64 or 128: narrow tiles, so that most SMs get one) and one of gridDim.y slices of K.  With
+// several slices every CTA writes its float32 partial tile to scratch memory and draws a ticket; the CTA that draws
+// the last one of its column tile adds the slices in order and applies the epilogue.  Nobody waits for another CTA.
+// The kernel is launched with programmatic dependent launch: W tiles are requested before the kernel in front has
+// finished (weights do not depend on it), A tiles after.
+namespace few {
+constexpr int FSTAGES = 4;
+enum { EPI_F32 = 1 };
+template <int FBN>
+struct Cfg {
+    static constexpr int W_BYTES = FBN * BK * 2;
+    static constexpr int STAGE = TILE_A_BYTES + W_BYTES;
+    static constexpr int SMEM = FSTAGES * STAGE + 1024;
+    static constexpr int TMEM = FBN < 32 ? 32 : FBN;
+};
+struct FewParams {
+    void* out;                 // bfloat16 [M, N] (store), [M, N/2] (swiglu) or float32 [M, N]
+    long long ldo;
+    const float* bias;
+    int M, N, K;
+    int epilogue;
+    float* partial;            // [column tiles][slices][128][BN] float32, when gridDim.y > 1
+    int* tickets;              // [column tiles], zero before and after
+    int* status;
+};
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// 32 columns of one token row: bias, then store / SwiGLU / float32
+__device__ __forceinline__ void few_epilogue(const FewParams& p, int row, int col0, float (&v)[32]) {
+    if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += p.bias[col0 + j];
+    }
+    if (p.epilogue == EPI_SWIGLU) {
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
+            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+            __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* dst = reinterpret_cast<uint4*>((bf16*)p.out + (size_t)row * p.ldo + col0 / 2);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else if (p.epilogue == EPI_F32) {
+        float4* dst = reinterpret_cast<float4*>((float*)p.out + (size_t)row * p.ldo + col0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* dst = reinterpret_cast<uint4*>((bf16*)p.out + (size_t)row * p.ldo + col0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+    }
+}
+
+template <int FBN>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_few_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const FewParams p) {
+    using C = Cfg<FBN>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[FSTAGES], empty_bar[FSTAGES], acc_bar, parts_written, ticket_drawn;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag, reduces_here;
+
+    grid_dependents_launch();
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * FBN;
+    const int slices = gridDim.y, slice = blockIdx.y;
+    const int all_blocks = p.K / BK;
+    const int kb0 = (int)((long long)all_blocks * slice / slices), kb1 = (int)((long long)all_blocks * (slice + 1) / slices);
+    const int k_blocks = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < FSTAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        mbar_init(&parts_written, 4);
+        mbar_init(&ticket_drawn, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(C::TMEM) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                         // ---- TMA producer
+            // the W tiles of the first stages go out before the kernel in front is known to be done, the A tiles after
+            const int early = k_blocks < FSTAGES ? k_blocks : FSTAGES;
+            for (int kb = 0; kb < early; ++kb) {
+                mbar_expect_tx(&full_bar[kb], C::STAGE);
+                tma_load_2d(ring + kb * C::STAGE + TILE_A_BYTES, &map_w, &full_bar[kb], (kb0 + kb) * BK, n0);
+            }
+            grid_dependency_wait();
+            for (int kb = 0; kb < early; ++kb) tma_load_2d(ring + kb * C::STAGE, &map_a, &full_bar[kb], (kb0 + kb) * BK, 0);
+            for (int kb = early; kb < k_blocks; ++kb) {
+                const int s = kb % FSTAGES;
+                if (!mbar_wait(&empty_bar[s], ((kb / FSTAGES) - 1) & 1, &abort_flag, p.status)) break;
+                mbar_expect_tx(&full_bar[s], C::STAGE);
+                tma_load_2d(ring + s * C::STAGE + TILE_A_BYTES, &map_w, &full_bar[s], (kb0 + kb) * BK, n0);
+                tma_load_2d(ring + s * C::STAGE, &map_a, &full_bar[s], (kb0 + kb) * BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                         // ---- MMA issuer
+            const uint32_t idesc = umma_idesc(FBN);
+            const uint32_t desc_hi = (uint32_t)(umma_desc(0) >> 32), ring_lo = (uint32_t)umma_desc(smem_addr(ring));
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % FSTAGES;
+                const uint32_t a_lo = ring_lo + (uint32_t)((s * C::STAGE) >> 4), b_lo = a_lo + (TILE_A_BYTES >> 4);
+                uint64_t adesc[BK / 16], bdesc[BK / 16];
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    adesc[k] = umma_desc_from(a_lo + 2 * k, desc_hi);
+                    bdesc[k] = umma_desc_from(b_lo + 2 * k, desc_hi);
+                }
+                ok = mbar_wait(&full_bar[s], (kb / FSTAGES) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                if (kb) umma<true>(tmem_base, adesc[0], bdesc[0], idesc);
+                else umma<false>(tmem_base, adesc[0], bdesc[0], idesc);
+#pragma unroll
+                for (int k = 1; k < BK / 16; ++k) umma<true>(tmem_base, adesc[k], bdesc[k], idesc);
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&empty_bar[s])) : "memory");
+            }
+            if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(&acc_bar)) : "memory");
+        }
+    } else {                                                     // ---- epilogue warps 2..5: one token row per thread
+        bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_bar, 0, &abort_flag, p.status));
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
+        const int row = quad * 32 + lane;
+        const bool valid = row < p.M;
+        float* my_partial = p.partial + (((size_t)blockIdx.x * slices + slice) * BM + row) * FBN;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < FBN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (!valid) continue;
+                if (slices == 1) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    few_epilogue(p, row, n0 + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(my_partial + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
+            }
+        }
+        if (slices > 1) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&parts_written);
+            if (warp == 2) {
+                const bool all_in = __all_sync(0xffffffffu, mbar_wait(&parts_written, 0, &abort_flag, p.status)) && ok;
+                if (lane == 0) {
+                    int last = 0;
+                    if (all_in) {
+                        last = atomicAdd(p.tickets + blockIdx.x, 1) == slices - 1;
+                        if (last) p.tickets[blockIdx.x] = 0;     // every slice has drawn: ready for the next launch
+                    }
+                    reduces_here = last;
+                    mbar_arrive(&ticket_drawn);
+                }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(&ticket_drawn, 0, &abort_flag, p.status));
+            if (ok && reduces_here && valid) {
+                __threadfence();
+                const float* base = p.partial + ((size_t)blockIdx.x * slices * BM + row) * FBN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < FBN; c0 += 32) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                    for (int i = 0; i < slices; ++i) {           // in order: the sum does not depend on who came last
+                        const float4* src = reinterpret_cast<const float4*>(base + (size_t)i * BM * FBN + c0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 t = __ldcg(src + j);
+                            v[4 * j] += t.x;
+                            v[4 * j + 1] += t.y;
+                            v[4 * j + 2] += t.z;
+                            v[4 * j + 3] += t.w;
+                        }
+                    }
+                    few_epilogue(p, row, n0 + c0, v);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(C::TMEM) : "memory");
+    }
+}
+}  // namespace few
+
 // A [rows, cols] bfloat16 matrix with row stride ld (elements), cut into boxes of [box_rows x 64], 128-byte swizzled.
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -470,4 +706,50 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
     dim3 grid(N / BN, (M + BM - 1) / BM);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
     return eg_launch_status();
+}
+
+namespace {
+template <int FBN>
+int launch_few(cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_w, const few::FewParams& p, int slices, int use_pdl) {
+    using C = few::Cfg<FBN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(few::gemm_tcgen05_few_kernel<FBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.N / FBN, slices);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, few::gemm_tcgen05_few_kernel<FBN>, map_a, map_w, p);
+}
+}  // namespace
+
+// Products of at most 128 rows.  epilogue: 0 store bfloat16 [M, N], 1 float32 [M, N], 2 swiglu on interleaved columns
+// (bfloat16 [M, N/2]).  tile_n: 32, 64 or 128 columns per CTA (N % tile_n == 0); slices of K (<= K / 64); with more
+// than one slice, partial takes (N / tile_n) * slices * 128 * tile_n floats and tickets N / tile_n zeroed ints (left zero).
+EG_API int eg_gemm_tcgen05_few(cudaStream_t stream, int epilogue, int use_pdl, const void* A, long long lda, const void* W, long long ldw,
+                               const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int slices,
+                               float* partial, int* tickets, int* status) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > BM || (tile_n != 32 && tile_n != 64 && tile_n != 128) || N % tile_n || K % BK || K <= 0 || slices < 1 || slices > K / BK ||
+        lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16 || !status ||
+        (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != few::EPI_F32) || (slices > 1 && (!partial || !tickets)) ||
+        (epilogue == few::EPI_F32 ? ldo % 4 : ldo % 8))
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_w;
+    if (make_map(&map_a, A, M, K, lda, BM) || make_map(&map_w, W, N, K, ldw, tile_n)) return (int)cudaErrorInvalidValue;
+    few::FewParams p{out, ldo, bias, M, N, K, epilogue, partial, tickets, status};
+    switch (tile_n) {
+        case 32: return launch_few<32>(stream, map_a, map_w, p, slices, use_pdl);
+        case 64: return launch_few<64>(stream, map_a, map_w, p, slices, use_pdl);
+        default: return launch_few<128>(stream, map_a, map_w, p, slices, use_pdl);
+    }
 }

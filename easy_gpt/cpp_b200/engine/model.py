@@ -154,4 +154,4 @@ class Model:
             return None
         pending = PendingNorm(self.final_norm, residual, delta, spare, work, rows=None if all_rows else logit_rows,
                               max_fused_rows=kernels.FUSED_NORM_MAX_TOKENS)
-        return self.lm_head.forward(pending if self.lm_head.accepts_pending_norm else pending.materialize())
+        return self.lm_head.forward(pending if self.lm_head.accepts_pending_norm else pending.materialize(), status=ctx.status)

@@ -83,6 +83,8 @@ class _Signatures:
                       c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p]
     eg_gemm_tcgen05 = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
                        c_int, c_void_p]
+    eg_gemm_tcgen05_few = [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                           c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
@@ -604,6 +606,73 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     _check(library().eg_gemm_tcgen05(_stream(), EPI_SWIGLU if swiglu_epilogue else EPI_STORE, _ptr(x), x.stride(0),
                                      _ptr(weight), weight.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
                                      _ptr(status)), "gemm_tcgen05")
+
+
+FEW_ROWS_MAX = 128             # rows of the tcgen05 product for the larger decode batches and short prompt portions
+# Measured at 64 rows against the library product (microseconds, L2 flushed): qkv 7.2 / 4.6, gate+up 9.5 / 7.7,
+# down 14.3 / 9.7, head 80 / 57; a decode step at batch 64 takes 2.54 ms with it and 1.81 ms without.  A tile's
+# start-up (TMEM, barriers, the first TMA round trip) is too long for products this small, so it is off by default.
+USE_TCGEN05_FEW = os.environ.get("EASY_GPT_TCGEN05_FEW", "0") != "0"
+_few_scratch = {}
+
+
+def gemm_tcgen05_few_plan(out_features: int, in_features: int):
+    """(tile_n, slices): output columns per CTA and slices of K, so that about two CTAs per SM
+    stream the weights; None if the kernel does not take the shape."""
+    if in_features % 64 or out_features % 32:
+        return None
+    tile_n = 32
+    for t in (128, 64):
+        if out_features % t == 0 and out_features // t >= 2 * SM_COUNT:
+            tile_n = t
+            break
+    tiles = out_features // tile_n
+    slices = max(1, min(round(2 * SM_COUNT / tiles), in_features // 64, 8))
+    return tile_n, slices
+
+
+def gemm_tcgen05_few_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
+    return (USE_TCGEN05_FEW and dtype == torch.bfloat16 and SKINNY_MAX_TOKENS < tokens <= FEW_ROWS_MAX
+            and gemm_tcgen05_few_plan(out_features, in_features) is not None)
+
+
+def gemm_tcgen05_few(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                     status: torch.Tensor, epilogue: int = 0, plan=None) -> None:
+    """out = f(x @ weight^T + bias) for at most 128 rows on the tcgen05 tensor cores: narrow
+    column tiles and slices of K so that every SM streams a share of the weights once; slices
+    are added up by the CTA that finishes last.  Epilogues: EPI_STORE (bfloat16), EPI_F32,
+    EPI_SWIGLU (interleaved gate/up rows, out [M, N/2])."""
+    _cuda(x, weight, bias, out, status)
+    M, K = x.shape
+    N = weight.shape[0]
+    plan = plan or gemm_tcgen05_few_plan(N, K)
+    _need(plan is not None and 0 < M <= FEW_ROWS_MAX, "gemm_tcgen05_few takes at most 128 rows, N % 32 == 0 and K % 64 == 0")
+    tile_n, slices = plan
+    _need(x.dtype == weight.dtype == torch.bfloat16 and weight.shape[1] == K, "bfloat16 x and weight")
+    _need(epilogue in (EPI_STORE, EPI_F32, EPI_SWIGLU), "epilogue")
+    _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+          and tuple(out.shape) == (M, N // 2 if epilogue == EPI_SWIGLU else N), "out dtype and shape")
+    _need(x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1, "unit inner strides")
+    _need(x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+          and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0, "16-byte aligned rows")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
+    partial = tickets = None
+    if slices > 1:
+        tiles = N // tile_n
+        floats = tiles * slices * 128 * tile_n
+        key = str(x.device)
+        have = _few_scratch.get(key)
+        if have is None or have[0].numel() < floats or have[1].numel() < tiles:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("the product's scratch must be allocated before a CUDA graph is captured "
+                                  "(run the step once eagerly first)")
+            have = (torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=x.device),
+                    torch.zeros(max(tiles, 1 << 12), dtype=torch.int32, device=x.device))
+            _few_scratch[key] = have
+        partial, tickets = have
+    _check(library().eg_gemm_tcgen05_few(_stream(), epilogue, int(USE_PDL), _ptr(x), x.stride(0), _ptr(weight), weight.stride(0),
+                                         _ptr(bias), _ptr(out), out.stride(0), M, N, K, tile_n, slices, _ptr(partial),
+                                         _ptr(tickets), _ptr(status)), "gemm_tcgen05_few")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

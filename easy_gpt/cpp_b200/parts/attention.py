@@ -103,7 +103,7 @@ class Attention(Mixer):
         else:
             if pending is not None:
                 x = pending.materialize()
-            qkv = self.qkv(x)
+            qkv = self.qkv(x, status=ctx.status)
             store = (tables.slot_map, cache.k, cache.v) if cache.writes else (None, None, None)
             if rot.rotary_dim == self.head_dim and self.head_dim % 8 == 0:
                 kernels.rope_cache_table(qkv, rot.table(ctx), *store, self.num_heads, self.num_kv_heads, self.head_dim,
@@ -139,7 +139,7 @@ class Attention(Mixer):
             kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                       self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
                                       ctx.status)
-        return self.out(attn, prefetch=self._hint(1))
+        return self.out(attn, prefetch=self._hint(1), status=ctx.status)
 
 
 register_part("mixer", "attention", Attention)

@@ -40,7 +40,9 @@ class Linear:
         return self.weight.numel() * self.weight.element_size()
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                 prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 prefetch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``status``: the step's status word; with it the tcgen05 product for 17..128 rows may run
+        (its bounded waits report there)."""
         M = x.shape[0]
         out_dtype = out_dtype or self.dtype
         if self.dtype == torch.float32:
@@ -51,6 +53,12 @@ class Linear:
             out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype)
             kernels.gemm_skinny(self.weight, self.bias_f32, out,
                                 kernels.EPI_F32 if out_dtype == torch.float32 else kernels.EPI_STORE, x=x, prefetch=prefetch)
+            return out
+        if (status is not None and kernels.gemm_tcgen05_few_takes(self.dtype, M, self.out_features, self.in_features)
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1):
+            out = torch.empty((M, self.out_features), device=x.device, dtype=out_dtype)
+            kernels.gemm_tcgen05_few(x, self.weight, self.bias_f32, out, status,
+                                     epilogue=kernels.EPI_F32 if out_dtype == torch.float32 else kernels.EPI_STORE)
             return out
         if out_dtype == torch.float32:
             out = torch.mm(x, self.weight.t(), out_dtype=torch.float32)

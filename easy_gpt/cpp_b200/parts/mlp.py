@@ -66,12 +66,15 @@ class SwiGLU(FeedForward):
             if kernels.gemm_skinny_takes(ctx.dtype, T, self.hidden):
                 kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, x=x,
                                     prefetch=self._hint(0))
+            elif kernels.gemm_tcgen05_few_takes(ctx.dtype, T, 2 * self.inter, self.hidden) and x.stride(0) % 8 == 0:
+                # the larger decode batches and short portions: tcgen05 product over narrow column tiles, SwiGLU in its epilogue
+                kernels.gemm_tcgen05_few(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, epilogue=kernels.EPI_SWIGLU)
             elif kernels.gemm_tcgen05_wide_takes(ctx.dtype, T, 2 * self.inter, self.hidden):
                 # prefill: the product on the tcgen05 tensor cores with SwiGLU in its epilogue
                 kernels.gemm_tcgen05(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, swiglu_epilogue=True)
             else:
                 kernels.swiglu(self.gate_up(x), act)
-        return self.down(act, prefetch=self._hint(1))
+        return self.down(act, prefetch=self._hint(1), status=ctx.status)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

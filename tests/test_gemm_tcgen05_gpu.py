@@ -63,3 +63,53 @@ def test_refuses_other_shapes():
     with pytest.raises(kernels.KernelError, match="N % 128"):
         kernels.gemm_tcgen05(x, w, None, torch.empty(64, 100, dtype=torch.bfloat16, device=DEV),
                              torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("M, N, K", [(17, 32, 64), (64, 1152, 896), (128, 896, 4864), (33, 9728, 896), (100, 96, 640),
+                                      (64, 151936 // 4, 896)])
+def test_few_rows_product(M, N, K):
+    """At most 128 rows: every tile width and several slices of K, each epilogue, twice (the tickets return to zero)."""
+    from easy_gpt.cpp_b200 import kernels
+
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = bf(torch.randn(M, K, generator=g)).to(DEV)
+    w = bf(torch.randn(N, K, generator=g) * 0.1).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().t() + b
+    scale = float(want.abs().max())
+    plans = [None] + [(t, s) for t in (32, 64, 128) if N % t == 0 for s in sorted({1, min(3, K // 64), min(K // 64, 8)})]
+    for plan in plans + plans[:2]:
+        out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tcgen05_few(x, w, b, out, status, plan=plan)
+        assert status.item() == 0
+        assert float((out.float() - want).abs().max()) <= 8e-3 * scale, plan
+        out32 = torch.empty((M, N), dtype=torch.float32, device=DEV)
+        kernels.gemm_tcgen05_few(x, w, None, out32, status, epilogue=kernels.EPI_F32, plan=plan)
+        assert float((out32 - (want - b)).abs().max()) <= 1e-4 * scale, plan
+    # SwiGLU on interleaved gate / up rows
+    gv, uv = want[:, 0::2] - b[0::2], want[:, 1::2] - b[1::2]
+    act = torch.empty((M, N // 2), dtype=torch.bfloat16, device=DEV)
+    for plan in plans:
+        kernels.gemm_tcgen05_few(x, w, None, act, status, epilogue=kernels.EPI_SWIGLU, plan=plan)
+        ref = uv * (gv / (1 + torch.exp(-gv)))
+        assert float((act.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max()) + 1e-6, plan
+    assert status.item() == 0
+    # a strided input (a slice of a wider buffer)
+    wide = bf(torch.randn(M, K + 64, generator=g)).to(DEV)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05_few(wide[:, 8:8 + K], w, None, out, status)
+    ref = wide[:, 8:8 + K].float() @ w.float().t()
+    assert float((out.float() - ref).abs().max()) <= 8e-3 * float(ref.abs().max())
+
+
+def test_few_rows_refuses():
+    from easy_gpt.cpp_b200 import kernels
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = torch.zeros(129, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tcgen05_few(x, w, None, torch.empty(129, 64, dtype=torch.bfloat16, device=DEV), status)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tcgen05_few(x[:8, :48], w[:, :48], None, torch.empty(8, 64, dtype=torch.bfloat16, device=DEV), status)
