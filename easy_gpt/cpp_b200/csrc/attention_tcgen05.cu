@@ -207,12 +207,11 @@ struct Params {
     long long page_rows, head_rows;           // in rows of the cache maps: per page, per KV head
     float scale;
     int* status;
-    long long* trace;          // optional [32][8] clock stamps of the first CTA's first softmax warp (profiling)
-    // for key ranges cut over several CTAs (gridDim.z > 1): per (tile, head, part) 128 rows of unnormalised O,
-    // and of (reference, sum); per (tile, head) a ticket that the last part leaves at zero
+    long long* trace;          // optional (profiling): [32][8] clock stamps of the first CTA's first softmax warp, then per unit
+                               // [4]: start, end (ns), SM, key tiles
+    // for key ranges cut into parts: per (tile, head, part) 128 rows of unnormalised O, and of (reference, sum)
     float* partial_o;
     float* partial_ml;
-    int* tickets;
     // work queue of the persistent CTAs: [0] next unit, [1] CTAs that have left; both zero before and after a launch
     int* queue;
     int num_tiles, max_parts, part_tiles;
@@ -232,8 +231,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr int STAGES = S::STAGES, SCORE_BUFFERS = S::SCORE_BUFFERS;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[SCORE_BUFFERS], p_full[SCORE_BUFFERS], o_done[SCORE_BUFFERS];
-    __shared__ __align__(8) uint64_t parts_written, ticket_drawn;
-    __shared__ int merges_here;                                   // this CTA was the last of its query tile's parts
     __shared__ int piece_page[STAGES][4];                         // the loader's block-table entries, per stage
     __shared__ int unit_slot[2];                                  // the unit the CTA works on, by round parity
     __shared__ uint32_t tmem_base_slot;
@@ -245,8 +242,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        mbar_init(&parts_written, 4);
-        mbar_init(&ticket_drawn, 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
@@ -273,9 +268,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // last (of a prompt: those that see most keys) come first, and dealt out through a counter: a CTA that is done
     // with a unit takes the next one, which evens out the SMs' loads.
     // Every role counts alike: gt key tiles before this unit (stage and buffer indices and barrier phases run on),
-    // units before this one (phase of q_full), units in parts before this one (phases of the merge barriers).
+    // units before this one (phase of q_full).
     const int total_units = p.num_tiles * p.num_heads * p.max_parts;
-    int gt = 0, units_done = 0, splits_done = 0;
+    int gt = 0, units_done = 0;
     for (int round = 0;; ++round) {
         if (threadIdx.x == 0) {
             int u;
@@ -306,6 +301,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
         const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
         const int tile_lo = all_lo + part_begin, ntiles = part_end - part_begin;
+        if (p.trace && threadIdx.x == 0) {                      // profiling: per unit start, end (ns), SM, key tiles
+            unsigned long long now;
+            unsigned smid;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            p.trace[256 + unit * 4] = (long long)now;
+            p.trace[256 + unit * 4 + 2] = smid;
+            p.trace[256 + unit * 4 + 3] = ntiles;
+        }
 
         if (warp == 0) {                                         // ---- TMA loader: one lane per box of a key tile
             // lane = sub * 8 + kv * 4 + g: 64-column sub-tile, K or V, 16-key piece.  Issuing a TMA copy costs the
@@ -567,8 +571,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                 }
             } else if (ok) {
-                // One of several parts: the row's unnormalised O, reference and sum go to global memory; the CTA that
-                // draws the last ticket of the query tile adds the parts up.
+                // One of several parts: the row's unnormalised O, reference and sum go to global memory; a kernel behind
+                // this one adds the parts up.
                 tc_fence_after();
                 const size_t slot0 = ((size_t)tile * p.num_heads + h) * p.max_parts;
                 float* my_o = p.partial_o + ((slot0 + part) * BM + row) * HD;
@@ -584,68 +588,19 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                 }
                 if (valid) *reinterpret_cast<float2*>(p.partial_ml + ((slot0 + part) * BM + row) * 2) = make_float2(m, l);
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&parts_written);
-                if (warp == 2) {
-                    const bool all_in = __all_sync(0xffffffffu, mbar_wait(&parts_written, splits_done & 1, &abort_flag, p.status));
-                    if (lane == 0) {
-                        int last_part = 0;
-                        if (all_in) {
-                            int* ticket = p.tickets + (size_t)tile * p.num_heads + h;
-                            last_part = atomicAdd(ticket, 1) == parts - 1;
-                            if (last_part) *ticket = 0;          // every part has drawn: ready for the next launch
-                        }
-                        merges_here = last_part;
-                        mbar_arrive(&ticket_drawn);
-                    }
-                }
-                ok = __all_sync(0xffffffffu, mbar_wait(&ticket_drawn, splits_done & 1, &abort_flag, p.status));
-                if (ok && merges_here && valid) {
-                    __threadfence();
-                    float big = -INFINITY;
-                    for (int i = 0; i < parts; ++i) big = fmaxf(big, __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2));
-                    float total = 0.f;
-                    for (int i = 0; i < parts; ++i) {
-                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml + ((slot0 + i) * BM + row) * 2));
-                        if (ml.x != -INFINITY) total += exp2f(ml.x - big) * ml.y;       // -inf: that part saw no key of this row
-                    }
-                    const float inv = total > 0.f ? 1.0f / total : 0.f;
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        float acc[32];
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-                        for (int i = 0; i < parts; ++i) {
-                            const float mi = __ldcg(p.partial_ml + ((slot0 + i) * BM + row) * 2);
-                            if (mi == -INFINITY) continue;
-                            const float w = exp2f(mi - big) * inv;
-                            const float4* src = reinterpret_cast<const float4*>(p.partial_o + ((slot0 + i) * BM + row) * HD + c0);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float4 v = __ldcg(src + e);
-                                acc[4 * e] = fmaf(w, v.x, acc[4 * e]);
-                                acc[4 * e + 1] = fmaf(w, v.y, acc[4 * e + 1]);
-                                acc[4 * e + 2] = fmaf(w, v.z, acc[4 * e + 2]);
-                                acc[4 * e + 3] = fmaf(w, v.w, acc[4 * e + 3]);
-                            }
-                        }
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch)
-                            dst[c0 / 8 + ch] = make_uint4(pack2(acc[8 * ch], acc[8 * ch + 1]), pack2(acc[8 * ch + 2], acc[8 * ch + 3]),
-                                                          pack2(acc[8 * ch + 4], acc[8 * ch + 5]), pack2(acc[8 * ch + 6], acc[8 * ch + 7]));
-                    }
-                }
             }
         }
         // the unit is done when its rows are: O in TMEM and Q in shared memory may be overwritten
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
+        if (p.trace && threadIdx.x == 0) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            p.trace[256 + unit * 4 + 1] = (long long)now;
+        }
         gt += ntiles;
         ++units_done;
-        if (parts > 1) ++splits_done;
     }
     // the last CTA to leave puts the queue back to zero for the next launch
     if (threadIdx.x == 0) {
@@ -658,6 +613,65 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(S::TMEM_COLS) : "memory");
+    }
+}
+
+// Adds up the parts of the query tiles whose key ranges were cut: one CTA per (query tile, head), a thread per
+// (row, 16 columns); every part's numbers are requested before the first is used.
+constexpr int MERGE_MAX_PARTS = 8;
+template <int HD>
+__global__ void __launch_bounds__(256)
+attention_merge_parts_kernel(const Params p) {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
+    const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;
+    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+    const int all_tiles = pos_hi / BN - first / BN + 1;
+    const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
+    if (parts <= 1) return;
+    const size_t slot0 = ((size_t)tile * p.num_heads + h) * p.max_parts;
+    constexpr int GROUPS = HD / 16;
+    for (int item = threadIdx.x; item < BM * GROUPS; item += blockDim.x) {
+        const int row = item / GROUPS, c0 = (item % GROUPS) * 16;
+        if (row >= count) continue;
+        float2 ml[MERGE_MAX_PARTS];
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PARTS; ++i)
+            ml[i] = i < parts ? __ldcg(reinterpret_cast<const float2*>(p.partial_ml + ((slot0 + i) * BM + row) * 2)) : make_float2(-INFINITY, 0.f);
+        float4 v[MERGE_MAX_PARTS][4];
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PARTS; ++i) {
+            const float4* src = reinterpret_cast<const float4*>(p.partial_o + ((slot0 + (i < parts ? i : 0)) * BM + row) * HD + c0);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[i][e] = i < parts ? __ldcg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float big = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PARTS; ++i) big = fmaxf(big, ml[i].x);
+        float total = 0.f, w[MERGE_MAX_PARTS];
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PARTS; ++i) {
+            w[i] = ml[i].x == -INFINITY ? 0.f : exp2f(ml[i].x - big);                     // -inf: that part saw no key of this row
+            total += w[i] * ml[i].y;
+        }
+        const float inv = total > 0.f ? 1.0f / total : 0.f;
+        float acc[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_PARTS; ++i) {                                       // in order: the sum is the same every time
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[4 * e] = fmaf(w[i], v[i][e].x, acc[4 * e]);
+                acc[4 * e + 1] = fmaf(w[i], v[i][e].y, acc[4 * e + 1]);
+                acc[4 * e + 2] = fmaf(w[i], v[i][e].z, acc[4 * e + 2]);
+                acc[4 * e + 3] = fmaf(w[i], v[i][e].w, acc[4 * e + 3]);
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD + c0);
+        dst[0] = make_uint4(pack2(acc[0] * inv, acc[1] * inv), pack2(acc[2] * inv, acc[3] * inv), pack2(acc[4] * inv, acc[5] * inv), pack2(acc[6] * inv, acc[7] * inv));
+        dst[1] = make_uint4(pack2(acc[8] * inv, acc[9] * inv), pack2(acc[10] * inv, acc[11] * inv), pack2(acc[12] * inv, acc[13] * inv), pack2(acc[14] * inv, acc[15] * inv));
     }
 }
 
@@ -691,17 +705,17 @@ int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map
 // q: [total_tokens, >= num_heads * head_dim] bfloat16 with row stride ldq; k_cache / v_cache: [num_pages][num_kv_heads]
 // [page_size][head_dim] with the same strides (in elements); the last page must hold finite numbers (pieces of a
 // key tile that no query sees are read from it); tiles as in the warp-level prefill kernel, of up to 128 tokens.
-// A query tile's keys are cut into parts of about part_tiles key tiles (of 64), at most max_parts: partial_o takes
-// num_tiles * num_heads * max_parts * 128 * head_dim floats, partial_ml * 128 * 2, tickets num_tiles * num_heads
-// zeroed ints (left zero); queue: two zeroed ints (left zero).
+// A query tile's keys are cut into parts of about part_tiles key tiles (of 64), at most max_parts (<= 8): partial_o
+// takes num_tiles * num_heads * max_parts * 128 * head_dim floats, partial_ml * 128 * 2; queue: two zeroed ints
+// (left zero).
 EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
                                         const void* v_cache, const int* block_table, int table_stride, const int* positions,
                                         const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
                                         int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
                                         int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
-                                        int* tickets, int* queue) {
+                                        int* queue) {
     if (num_tiles <= 0) return 0;
-    if (max_parts < 1 || max_parts > 64 || part_tiles < 1 || !queue || (max_parts > 1 && (!partial_o || !partial_ml || !tickets)))
+    if (max_parts < 1 || max_parts > MERGE_MAX_PARTS || part_tiles < 1 || !queue || (max_parts > 1 && (!partial_o || !partial_ml)))
         return (int)cudaErrorInvalidValue;
     if ((head_dim != 64 && head_dim != 128) || page_size <= 0 || page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads ||
         num_heads > 65535 || num_pages <= 0 || total_tokens <= 0 || !status)
@@ -728,7 +742,6 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     p.trace = trace;
     p.partial_o = partial_o;
     p.partial_ml = partial_ml;
-    p.tickets = tickets;
     p.queue = queue;
     p.num_tiles = num_tiles;
     p.max_parts = max_parts;
@@ -749,5 +762,18 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     // persistent CTAs, two per SM, that deal the units out among themselves
     const long long units = (long long)num_tiles * num_heads * max_parts;
     const int ctas = (int)(units < 2ll * sm_count ? units : 2ll * sm_count);
-    return head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, ctas) : launch<128>(stream, map_q, map_k, map_v, p, ctas);
+    int code = head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, ctas) : launch<128>(stream, map_q, map_k, map_v, p, ctas);
+    if (code || max_parts == 1) return code;
+    // the parts are added up behind the main kernel (launched early: it waits for it by itself)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_tiles, num_heads);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)(head_dim == 64 ? cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<64>, p)
+                                : cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<128>, p));
 }

@@ -76,7 +76,7 @@ class _Signatures:
                             c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
     eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
-                                    c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+                                    c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -385,7 +385,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 PREFILL_PARTS_SCRATCH_BYTES = 256 << 20
-PREFILL_PART_TILES = int(os.environ.get("EASY_GPT_PREFILL_PART_TILES", "16"))     # key tiles (of 64) per part
+PREFILL_PART_TILES = int(os.environ.get("EASY_GPT_PREFILL_PART_TILES", "4"))      # fewest key tiles (of 64) per part
 _parts_scratch = {}
 
 
@@ -406,15 +406,15 @@ def _prefill_parts_scratch(device, slots: int, parts: int, head_dim: int):
 
 def attention_prefill_parts(num_tiles: int, num_heads: int, max_context: int):
     """(parts, part_tiles): into how many parts of how many key tiles (of 64) a query tile's keys
-    are cut.  A part costs its CTA a start-up and a merge, which pays only while there are fewer
-    (tile, head) pairs than the two CTAs per SM; a part has at least ``PREFILL_PART_TILES`` tiles."""
+    are cut.  A part costs its CTA a start-up of some microseconds and a pass of the merge kernel,
+    which pays only while there are fewer (tile, head) pairs than the two CTAs per SM."""
     items = max(1, num_tiles * num_heads)
-    wanted = 2 * SM_COUNT // items
+    wanted = min(2 * SM_COUNT // items, 8)
     key_tiles = -(-max_context // 64)
     if wanted < 2 or key_tiles < 2 * PREFILL_PART_TILES:
         return 1, max(key_tiles, 1)
     part_tiles = max(PREFILL_PART_TILES, -(-key_tiles // wanted))
-    return min(-(-key_tiles // part_tiles), 16), part_tiles
+    return min(-(-key_tiles // part_tiles), 8), part_tiles
 
 
 def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -445,7 +445,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
           and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0
           and k_cache.stride(0) % head_dim == 0 and k_cache.stride(1) % head_dim == 0,
           "cache shape [pages, NKV, page_size, HD], strides in whole rows")
-    parts = max(1, int(parts))
+    parts = max(1, min(int(parts), 8))
     slots = tiles.shape[0] * num_heads
     while parts > 1 and slots * parts * 128 * (head_dim + 2) * 4 > PREFILL_PARTS_SCRATCH_BYTES:
         parts -= 1
@@ -455,7 +455,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
         _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(out), out.stride(0), num_heads, num_kv_heads, head_dim,
         page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         _ptr(status), _ptr(trace) if trace is not None else None, parts, int(part_tiles or PREFILL_PART_TILES),
-        _ptr(partial_o), _ptr(partial_ml), _ptr(tickets), _ptr(queue)), "attention_prefill_tcgen05")
+        _ptr(partial_o), _ptr(partial_ml), _ptr(queue)), "attention_prefill_tcgen05")
 
 
 SKINNY_KERNEL_TOKENS = 64      # what the kernel takes
