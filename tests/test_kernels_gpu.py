@@ -38,12 +38,12 @@ def test_embedding_gather_and_bad_ids(dtype):
 
 # -- norm ----------------------------------------------------------------------
 
-@pytest.mark.parametrize("hidden, eps", [(70, 1e-6), (896, 1e-5), (3584, 1e-6), (5000, 3e-4)])
+@pytest.mark.parametrize("hidden, eps, rows", [(70, 1e-6, 9), (896, 1e-5, 9), (3584, 1e-6, 9), (5000, 3e-4, 9),
+                                               (896, 1e-6, 203), (200, 1e-5, 64), (2048, 1e-6, 77), (1540, 1e-5, 130)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_add_rmsnorm(hidden, eps, dtype):
+def test_add_rmsnorm(hidden, eps, rows, dtype):
     from easy_gpt.cpp_b200 import kernels
 
-    rows = 9
     resid = torch.randn(rows, hidden, generator=gen(1)) * 3
     delta = (torch.randn(rows, hidden, generator=gen(2))).to(dtype)
     gain = 1 + 0.2 * torch.randn(hidden, generator=gen(3))
