@@ -25,14 +25,18 @@ constexpr int TILE_KEYS = 64;
 constexpr int THREADS = 128;
 constexpr int QUARTER_TILES = 64;      // tiles whose cache addresses are kept in shared memory at a time
 
-template <int HD>
+// DEEP: as many stages as fit about 96 KB (up to five tiles in flight per CTA, two CTAs per SM): for steps with few
+// CTAs, where each has to keep its own loads going.  Otherwise three stages, so that four CTAs share an SM: with
+// many CTAs it is their number in flight that hides a tile's latency.
+template <int HD, bool DEEP = true>
 struct Layout {
     static constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per key row
     static constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
     static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;          // K or V
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     // up to five tiles in flight per CTA, within about 96 KB of shared memory (two stages at least)
-    static constexpr int STAGES = (96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((96 * 1024 / STAGE_BYTES) >= 2 ? (96 * 1024 / STAGE_BYTES) : 2);
+    static constexpr int DEEP_STAGES = (96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((96 * 1024 / STAGE_BYTES) >= 2 ? (96 * 1024 / STAGE_BYTES) : 2);
+    static constexpr int STAGES = DEEP ? DEEP_STAGES : (DEEP_STAGES < 3 ? DEEP_STAGES : 3);
     static constexpr int MERGE_BYTES = 4 * 16 * (HD + 2) * 4;
     static constexpr int SMEM = (STAGES * STAGE_BYTES > MERGE_BYTES) ? STAGES * STAGE_BYTES : MERGE_BYTES;
     __device__ static __forceinline__ int offset(int row, int chunk) {      // bytes inside a K or V tile
@@ -65,9 +69,9 @@ struct Params {
     unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
 };
 
-template <int HD>
+template <int HD, bool DEEP>
 __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p) {
-    using L = Layout<HD>;
+    using L = Layout<HD, DEEP>;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int is_last;
     TraceScope trace_scope(p.trace);
@@ -367,18 +371,17 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
 }
 
-template <int HD>
-int launch(cudaStream_t stream, const Params& p, int tokens) {
-    using L = Layout<HD>;
+template <int HD, bool DEEP>
+int launch_with(cudaStream_t stream, const Params& p, dim3 grid) {
+    using L = Layout<HD, DEEP>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int G = p.num_heads / p.num_kv_heads;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
+    cfg.gridDim = grid;
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = L::SMEM;
     cfg.stream = stream;
@@ -387,7 +390,21 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = p.use_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD>, p);
+    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP>, p);
+}
+
+template <int HD>
+int launch(cudaStream_t stream, const Params& p, int tokens) {
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    const int G = p.num_heads / p.num_kv_heads;
+    const dim3 grid(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
+    const long long ctas = (long long)grid.x * grid.y * grid.z;
+    return ctas <= 2ll * sm_count ? launch_with<HD, true>(stream, p, grid) : launch_with<HD, false>(stream, p, grid);
 }
 
 
