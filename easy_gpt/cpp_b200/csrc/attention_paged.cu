@@ -67,6 +67,7 @@ struct Params {
     int* counters;                // [tokens * gridDim.y] tickets, zero before and after every launch
     int use_pdl;
     unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
+    const int* token_list;        // optional: the tokens this launch works on (blockIdx.x indexes it); null: all, in order
 };
 
 template <int HD, bool DEEP>
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int is_last;
     TraceScope trace_scope(p.trace);
-    const int t = blockIdx.x;
+    const int t = p.token_list ? p.token_list[blockIdx.x] : blockIdx.x;
     const int G = p.num_heads / p.num_kv_heads;
     const int gblocks = (G + 15) / 16;
     const int kvh = blockIdx.y / gblocks;
@@ -671,12 +672,14 @@ int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
 // partial_acc / partial_ml: scratch of tokens*heads*splits*(head_dim + 2) floats, and counters: one zeroed int
 // per (token, KV head block) (left zero), needed when splits > 1.  seq_context (may be null): per block-table row, the
 // number of keys that were in the cache before this step; those may be fetched before the kernel in front has finished.
+// token_list (may be null): `tokens` indices of the tokens to work on (scratch and counters are indexed by token index,
+// so they cover all tokens of the step either way).
 EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
                               const int* block_table, int table_stride, const int* token_seq, const int* positions,
                               const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
                               int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
                               int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
-                              long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace) {
+                              long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list) {
     if (tokens <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
         splits > 128 || (splits > 1 && (!partial_acc || !partial_ml || !counters)))
@@ -684,7 +687,7 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
     Params p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
              table_stride, token_seq, positions, seq_context, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
              page_size, num_pages, window, splits, scale, status, prefetch_bytes >= 16 ? prefetch : nullptr, prefetch_bytes,
-             counters, use_pdl, trace};
+             counters, use_pdl, trace, token_list};
     switch (head_dim) {
         case 32: return launch<32>(stream, p, tokens);
         case 64: return launch<64>(stream, p, tokens);

@@ -69,8 +69,7 @@ class DecodeGraph:
         self.offsets_in_entry = (np.arange(T, dtype=np.int32) - np.repeat(starts[:-1], self.counts)).astype(np.int32)
         token_seq = np.repeat(np.arange(n, dtype=np.int32), self.counts)
         rows = [int(starts[i]) + int(w) for i, ws in enumerate(wants) for w in ws]
-        tile = kernels.QUERY_TILE
-        tiles = [(i, int(starts[i]) + o, min(tile, c - o)) for i, c in enumerate(self.counts) for o in range(0, c, tile)]
+        tiles, small = kernels.query_tiles_of(starts, self.counts)
         to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
 
         def view(name):
@@ -86,7 +85,8 @@ class DecodeGraph:
             host_seq_starts=starts.tolist(), host_seq_context=[0] * n, host_seq_slots=[0] * n,
             max_query_len=max(self.counts), max_context_len=cache.max_pages_per_request * cache.page_size,
             all_decode=self.all_decode,
-            query_tiles=None if self.all_decode else to_dev(np.asarray(tiles, dtype=np.int32).reshape(-1, 3)))
+            query_tiles=to_dev(np.asarray(tiles, dtype=np.int32).reshape(-1, 3)) if tiles else None,
+            small_tokens=to_dev(np.asarray(small, dtype=np.int32)) if tiles and small else None)
         self.rows = to_dev(np.asarray(rows, dtype=np.int32)) if rows else None
         self.all_rows = rows == list(range(T))
         self._fill_padding(self.staging[0].numpy(), 0)

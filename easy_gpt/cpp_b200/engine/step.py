@@ -135,10 +135,9 @@ class StepRunner:
         total_len = context.astype(np.int64) + counts
         width = {g.index: int(-(-int(total_len.max()) // g.page_size)) for g in cache.groups}
 
-        tile = kernels.QUERY_TILE
-        tiles = [(i, int(starts[i]) + o, min(tile, int(counts[i]) - o)) for i in range(n) for o in range(0, int(counts[i]), tile)]
+        tiles, small = kernels.query_tiles_of(starts, counts)
         layout = [("token_ids", T), ("positions", T), ("token_seq", T), ("seq_starts", n + 1), ("seq_context", n),
-                  ("seq_slots", n), ("logit_rows", R), ("query_tiles", 3 * len(tiles))]
+                  ("seq_slots", n), ("logit_rows", R), ("query_tiles", 3 * len(tiles)), ("small_tokens", len(small))]
         for g in cache.groups:
             layout += [(f"slot_map{g.index}", T), (f"table{g.index}", n * width[g.index])]
         offsets, off = {}, 0
@@ -160,6 +159,7 @@ class StepRunner:
         put("seq_slots", slots)
         put("logit_rows", np.asarray(rows, dtype=np.int32))
         put("query_tiles", np.asarray(tiles, dtype=np.int32).reshape(-1))
+        put("small_tokens", np.asarray(small, dtype=np.int32))
         rids = [e.request for e in entries]
         for g in cache.groups:
             sm = np.concatenate([cache.slot_positions(g.index, e.request, int(context[i]), int(counts[i]))
@@ -185,7 +185,8 @@ class StepRunner:
             host_seq_starts=starts.tolist(), host_seq_context=context.tolist(), host_seq_slots=slots.tolist(),
             max_query_len=int(counts.max()), max_context_len=int(total_len.max()),
             all_decode=bool((counts == 1).all()),
-            query_tiles=view("query_tiles").view(len(tiles), 3),
+            query_tiles=view("query_tiles").view(len(tiles), 3) if tiles else None,
+            small_tokens=view("small_tokens") if tiles and small else None,
         )
         return ctx, (view("logit_rows") if R else None)
 

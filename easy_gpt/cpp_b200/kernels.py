@@ -71,7 +71,7 @@ class _Signatures:
                             c_float, c_void_p]
     eg_attention_paged = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float,
-                          c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p]
+                          c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p]
     eg_attention_prefill = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_float, c_void_p]
     eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -321,12 +321,14 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, num_heads: int,
                     num_kv_heads: int, head_dim: int, window: Optional[int], scale: float, splits: int,
                     status: torch.Tensor, prefetch: Optional[torch.Tensor] = None,
-                    seq_context: Optional[torch.Tensor] = None) -> None:
+                    seq_context: Optional[torch.Tensor] = None, token_list: Optional[torch.Tensor] = None) -> None:
     """bfloat16 attention over the paged cache on the tensor cores; same contract as
     ``attention_generic``.  With splits > 1 it uses scratch memory for the partial results.
     ``seq_context`` (int32 per block-table row): keys cached before this step; given it, the kernel
-    fetches those while the kernel in front of it (which writes the new keys) is still running."""
-    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status)
+    fetches those while the kernel in front of it (which writes the new keys) is still running.
+    ``token_list`` (int32): only these tokens (the decoded tokens of a step that also holds prompt portions)."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out, status, token_list)
+    _need(token_list is None or (token_list.dtype == torch.int32 and token_list.dim() == 1 and token_list.is_contiguous()), "int32 token list")
     T = q.shape[0]
     page_size = k_cache.shape[2]
     _need(attention_paged_takes(q.dtype, head_dim, page_size),
@@ -345,15 +347,30 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         counters = _attention_counters(q.device, T * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16)))
     _check(library().eg_attention_paged(
         _stream(), _ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.stride(0),
-        _ptr(token_seq), _ptr(positions), _ptr(seq_context), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml), T, num_heads, num_kv_heads,
+        _ptr(token_seq), _ptr(positions), _ptr(seq_context), _ptr(out), out.stride(0), _ptr(acc), _ptr(ml),
+        T if token_list is None else token_list.numel(), num_heads, num_kv_heads,
         head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         int(splits), _ptr(status), _ptr(prefetch) if PREFETCH_WEIGHTS else None,
         prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
-        _ptr(counters), int(USE_PDL), Timeline.slot(f"attention s={splits}")), "attention_paged")
+        _ptr(counters), int(USE_PDL), Timeline.slot(f"attention s={splits}"), _ptr(token_list)), "attention_paged")
 
 
 PREFILL_ATTENTION_HEAD_DIMS = (32, 64, 128)
 QUERY_TILE = 128               # tokens per listed tile of a prompt portion
+SMALL_ENTRY_TOKENS = 4         # entries of up to this many tokens go through the decode attention kernel, token by token
+
+
+def query_tiles_of(starts, counts):
+    """(tiles, small_tokens) of a step: tiles [(entry, first token, count <= QUERY_TILE)] of the entries that
+    bring more than SMALL_ENTRY_TOKENS tokens, and the token indices of all other entries."""
+    tiles, small = [], []
+    for i, c in enumerate(counts):
+        c, s0 = int(c), int(starts[i])
+        if c > SMALL_ENTRY_TOKENS:
+            tiles += [(i, s0 + o, min(QUERY_TILE, c - o)) for o in range(0, c, QUERY_TILE)]
+        else:
+            small += list(range(s0, s0 + c))
+    return tiles, small
 TCGEN05_ATTENTION = os.environ.get("EASY_GPT_TCGEN05_ATTENTION", "1") != "0"
 TCGEN05_ATTENTION_MIN_QUERY = 33   # shorter portions leave most of the 128-row tile empty: the warp-level kernel takes them
 

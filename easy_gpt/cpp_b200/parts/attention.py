@@ -112,14 +112,13 @@ class Attention(Mixer):
                 kernels.rope_cache(qkv, None, ctx.positions, *store, rot.inv_freq, self.num_heads, self.num_kv_heads,
                                    self.head_dim, rot.rotary_dim, tables.page_size, ctx.status)
         attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
-        if (ctx.query_tiles is not None and ctx.max_query_len > 4
-                and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size)):
+        longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 255)
+        if ctx.query_tiles is not None and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size):
             # prompt portions: tiles of query tokens against the cache, on the tcgen05 tensor cores when
             # the portions are long enough to fill their 128-row tiles
             tensor_core = (kernels.TCGEN05_ATTENTION and ctx.max_query_len >= kernels.TCGEN05_ATTENTION_MIN_QUERY
                            and kernels.attention_prefill_tcgen05_takes(dtype, self.head_dim, tables.page_size))
             if tensor_core:
-                longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 255)
                 parts, part_tiles = kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads, longest)
                 kernels.attention_prefill_tcgen05(
                     qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn, self.num_heads,
@@ -128,8 +127,14 @@ class Attention(Mixer):
                 kernels.attention_prefill(qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn,
                                           self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
                                           ctx.status)
+            if ctx.small_tokens is not None:
+                # the decoded tokens beside them: token by token, split over their keys
+                count = ctx.small_tokens.numel()
+                kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
+                                        self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                                        kernels.attention_paged_splits(count, self.num_heads, self.num_kv_heads, longest),
+                                        ctx.status, token_list=ctx.small_tokens)
         elif kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
-            longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 63)
             splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                     self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, splits,

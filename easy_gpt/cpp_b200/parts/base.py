@@ -78,8 +78,11 @@ class StepContext:
     max_query_len: int = 0
     max_context_len: int = 0       # longest context + query of the batch
     all_decode: bool = False       # every entry brings exactly one token
-    # runs of up to 64 consecutive tokens of one entry: int32 [n, 3] = (entry, first token, count); None in captured steps
+    # runs of up to 128 consecutive tokens of the entries that bring more than SMALL_ENTRY_TOKENS tokens (prompt
+    # portions): int32 [n, 3] = (entry, first token, count); None if there is no such entry
     query_tiles: Optional[torch.Tensor] = None
+    # token indices of the entries too short for tiles (decoded tokens beside prompt portions); None if there are none
+    small_tokens: Optional[torch.Tensor] = None
     # per-step data that parts share between layers (cleared at the start of every forward)
     scratch: Dict = field(default_factory=dict)
 

@@ -246,6 +246,16 @@ def test_attention_kernels(case, dtype):
                                 seq_context=torch.tensor(contexts, dtype=torch.int32, device=DEV))
         err = float((out.float().cpu() - c["want"]).abs().max())
         assert err <= tol and status.item() == 0, f"paged with seq_context: {err}"
+        # only some tokens of the step (decoded tokens beside prompt portions): the others' rows stay as they were
+        some = torch.arange(T - 1, -1, -2, dtype=torch.int32, device=DEV)
+        out = torch.full((T, NH * HD), 5.0, dtype=dtype, device=DEV)
+        kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, 2, status, token_list=some)
+        picked = some.long().cpu()
+        err = float((out.float().cpu()[picked] - c["want"][picked]).abs().max())
+        assert err <= tol and status.item() == 0, f"paged with a token list: {err}"
+        rest = torch.ones(T, dtype=torch.bool)
+        rest[picked] = False
+        assert bool((out.float().cpu()[rest] == 5.0).all())
     else:
         assert dtype == torch.float32 or HD == 80 or ps % 16
         if dtype == torch.bfloat16:
