@@ -424,17 +424,14 @@ def _prefill_parts_scratch(device, slots: int, parts: int, head_dim: int):
     return have
 
 
-def attention_prefill_parts(num_tiles: int, num_heads: int, max_context: int):
-    """(parts, part_tiles): into how many parts of how many key tiles (of 64) a query tile's keys
-    are cut.  A part costs its CTA a start-up of some microseconds and a pass of the merge kernel,
-    which pays only while there are fewer (tile, head) pairs than the two CTAs per SM."""
-    items = max(1, num_tiles * num_heads)
-    wanted = min(2 * SM_COUNT // items, 8)
-    key_tiles = -(-max_context // 64)
-    if wanted < 2 or key_tiles < 2 * PREFILL_PART_TILES:
-        return 1, max(key_tiles, 1)
-    part_tiles = max(PREFILL_PART_TILES, -(-key_tiles // wanted))
-    return min(-(-key_tiles // part_tiles), 8), part_tiles
+def attention_prefill_parts(num_tiles: int, num_heads: int):
+    """(parts, part_tiles): the most parts a query tile's keys are cut into, and the fewest key tiles
+    (of 64) of a part; the kernel cuts a tile's keys into min(parts, key tiles / part_tiles) parts, so
+    the cut follows the contexts of the step at hand (a captured step is replayed with others).
+    A part costs its CTA a start-up of some microseconds and a pass of the merge kernel, which pays
+    only while there are fewer (tile, head) pairs than the two CTAs per SM."""
+    wanted = min(2 * SM_COUNT // max(1, num_tiles * num_heads), 8)
+    return (wanted, PREFILL_PART_TILES) if wanted >= 2 else (1, 1 << 20)
 
 
 def attention_prefill_tcgen05_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
