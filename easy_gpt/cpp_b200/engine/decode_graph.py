@@ -100,17 +100,26 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = kernels.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        # No garbage collection while the stream is capturing: freeing an older engine's graphs or
-        # tensors there is a CUDA call that is not allowed during a capture and would invalidate it.
-        gc.collect()
+        # Captured by hand rather than with torch.cuda.graph(): that context collects garbage and empties the
+        # allocator's cache on entry, tens of milliseconds per capture, and every eager step after it pays for
+        # fresh device allocations.  No garbage collection while the stream is capturing either: freeing an older
+        # graph or tensor there is a CUDA call that is not allowed during a capture and would invalidate it.
+        # All captured steps of a runner share one memory pool: they never run at the same time.
         was_enabled = gc.isenabled()
         gc.disable()
+        capture_stream = torch.cuda.Stream(device=dev)
+        capture_stream.wait_stream(torch.cuda.current_stream())
         try:
-            with torch.cuda.graph(self.graph):
-                self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=self.all_rows)
+            with torch.cuda.stream(capture_stream):
+                self.graph.capture_begin(pool=runner.graph_pool())
+                try:
+                    self.logits = runner.model.forward(self.ctx, cache, self.rows, all_rows=self.all_rows)
+                finally:
+                    self.graph.capture_end()
         finally:
             if was_enabled:
                 gc.enable()
+        torch.cuda.current_stream().wait_stream(capture_stream)
         self.launches = kernels.launch_count - before      # our own kernels inside one replay
 
     def _fill_padding(self, hv: np.ndarray, start_row: int) -> None:

@@ -59,6 +59,7 @@ class StepRunner:
         self.use_graphs = use_graphs and model.capturable
         self._graphs: Dict[int, object] = {}
         self._signature_graphs: Dict[tuple, object] = {}
+        self._graph_pool = None
         self._signature_seen: Dict[tuple, int] = {}
         self.graph_replays = 0
 
@@ -221,7 +222,13 @@ class StepRunner:
             self._graphs[b] = DecodeGraph(self, [1] * b, [[0]] * b, padded=True)
         return self._graphs[b]
 
-    MAX_SIGNATURE_GRAPHS = 6
+    MAX_SIGNATURE_GRAPHS = 48
+
+    def graph_pool(self):
+        """The memory pool that all captured steps of this runner share."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
 
     def _signature_graph(self, entries: Sequence[StepEntry]):
         """The captured step for this exact batch shape, once the shape has come before (None the first time)."""
@@ -230,12 +237,13 @@ class StepRunner:
         sig = (tuple(len(e.tokens) for e in entries), tuple(tuple(e.want) for e in entries))
         graph = self._signature_graphs.get(sig)
         if graph is not None:
+            self._signature_graphs[sig] = self._signature_graphs.pop(sig)         # most recently used last
             return graph
         self._signature_seen[sig] = self._signature_seen.get(sig, 0) + 1
         if self._signature_seen[sig] < 2 or sum(sig[0]) > 16384:
             return None
         if len(self._signature_graphs) >= self.MAX_SIGNATURE_GRAPHS:
-            self._signature_graphs.pop(next(iter(self._signature_graphs)))        # the oldest
+            self._signature_graphs.pop(next(iter(self._signature_graphs)))        # the least recently used
             if len(self._signature_seen) > 4096:
                 self._signature_seen.clear()
         graph = DecodeGraph(self, sig[0], sig[1], padded=False)
