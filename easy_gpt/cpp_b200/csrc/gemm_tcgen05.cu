@@ -100,6 +100,16 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0) : "memory");
 }
 
+// silu(g) * u for an epilogue whose result is rounded to bfloat16: the hardware's base-2 exponent and reciprocal
+// (relative error about 2^-22 each) instead of expf and a division, which cost the epilogue warps more than the
+// main loop costs the tensor core.
+__device__ __forceinline__ float swiglu_fast(float g, float u) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return u * (g * r);
+}
+
 // Instruction descriptor for kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
 __device__ __forceinline__ uint32_t umma_idesc(int n = BN) {
     uint32_t d = 0;
@@ -218,8 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
-                            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+                            const float y0 = swiglu_fast(g0, u0), y1 = swiglu_fast(g1, u1);
                             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
                             packed[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
@@ -254,6 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // wide products: 128 x 256 tiles, persistent CTAs, double-buffered accumulator
 // ---------------------------------------------------------------------------
 namespace wide {
+constexpr int WTHREADS = 320;                                    // TMA warp, MMA warp, eight epilogue warps (two per 32 rows)
 constexpr int WBN = 256;
 constexpr int WSTAGES = 4;
 constexpr int W_TILE_B_BYTES = WBN * BK * 2;
@@ -262,7 +272,7 @@ constexpr int W_SMEM_BYTES = WSTAGES * W_STAGE_BYTES + 1024;
 constexpr int W_TMEM_COLS = 512;
 }  // namespace wide
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(wide::WTHREADS)
 gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
     using namespace wide;
     extern __shared__ unsigned char smem_raw[];
@@ -283,7 +293,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);                          // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], 8);                          // one arrival per epilogue warp
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -348,7 +358,8 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
         }
     } else {                                                     // ---- epilogue warps 2..5
-        const int quad = warp & 3;
+        const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
+        const int col_lo = ((warp - 2) >> 2) * (WBN / 2);        // the two warps of a quad share its rows' columns
         int local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
@@ -359,7 +370,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (!ok) break;
             const int row = m0 + quad * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < WBN; c0 += 32) {
+            for (int c0 = col_lo; c0 < col_lo + WBN / 2; c0 += 32) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * WBN + c0);
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -383,8 +394,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
-                            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+                            const float y0 = swiglu_fast(g0, u0), y1 = swiglu_fast(g1, u1);
                             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
                             packed[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
@@ -466,8 +476,7 @@ __device__ __forceinline__ void few_epilogue(const FewParams& p, int row, int co
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-            const float y0 = u0 * (g0 * (1.0f / (1.0f + expf(-g0))));
-            const float y1 = u1 * (g1 * (1.0f / (1.0f + expf(-g1))));
+            const float y0 = swiglu_fast(g0, u0), y1 = swiglu_fast(g1, u1);
             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
             packed[j] = *reinterpret_cast<uint32_t*>(&h);
         }
@@ -700,7 +709,7 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
             wide_configured = true;
         }
         const int tiles = m_tiles * (N / wide::WBN);
-        gemm_tcgen05_wide_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, wide::W_SMEM_BYTES, stream>>>(map_a, map_w, p);
+        gemm_tcgen05_wide_kernel<<<tiles < sm_count ? tiles : sm_count, wide::WTHREADS, wide::W_SMEM_BYTES, stream>>>(map_a, map_w, p);
         return eg_launch_status();
     }
     dim3 grid(N / BN, (M + BM - 1) / BM);

@@ -595,10 +595,12 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
         Timeline.slot(f"skinny e={epilogue} n={int(norm)} {N}x{K} plan={rb},{ks},{split}")), "gemm_skinny")
 
 
-# The package's own tcgen05/TMA product reaches 0.89 PFLOP/s on the widest prefill product against the
-# library's 1.26 (profiles/), so the library product stays the default for prompts; EASY_GPT_TCGEN05=1
-# routes gate/up + SwiGLU through ours.
-USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "0") != "0"
+# The package's own tcgen05/TMA product reaches 0.85 PFLOP/s on the widest prefill product against the library's
+# 1.22 (profiles/), but with SwiGLU in its epilogue it saves the separate activation kernel and the round trip of the
+# [tokens, 2 x intermediate] product through memory: a 2,048-token prefill takes 3.00 ms with it and 3.26 ms with the
+# library product plus the SwiGLU kernel.  So gate/up + SwiGLU goes through ours where the wide kernel takes the
+# shape; the other products of a prompt stay with the library.  EASY_GPT_TCGEN05=0 switches it off.
+USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "1") != "0"
 
 
 def gemm_tcgen05_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:

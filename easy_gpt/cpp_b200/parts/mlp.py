@@ -70,7 +70,7 @@ class SwiGLU(FeedForward):
                 # the larger decode batches and short portions: tcgen05 product over narrow column tiles, SwiGLU in its epilogue
                 kernels.gemm_tcgen05_few(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, epilogue=kernels.EPI_SWIGLU)
             elif kernels.gemm_tcgen05_wide_takes(ctx.dtype, T, 2 * self.inter, self.hidden):
-                # prefill: the product on the tcgen05 tensor cores with SwiGLU in its epilogue
+                # prompts: the product on the tcgen05 tensor cores (persistent 128 x 256 tiles) with SwiGLU in its epilogue
                 kernels.gemm_tcgen05(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, swiglu_epilogue=True)
             else:
                 kernels.swiglu(self.gate_up(x), act)
