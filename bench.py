@@ -356,7 +356,9 @@ def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
         ours = graph_us([(lambda w=w: kernels.gemm_tcgen05(x, w, None, out, status)) for w in ws])
         lib = graph_us([(lambda w=w: torch.nn.functional.linear(x, w)) for w in ws])
         flops = 2 * tokens * N * K
-        print(f"  {name:8s} [{N} x {K}]  tcgen05 {ours:7.2f} us {flops / ours / 1e6:7.1f}   library {lib:7.2f} us {flops / lib / 1e6:7.1f}")
+        us = graph_us([(lambda w=w: kernels.gemm_tcgen05(x, w, None, out, status, pair=True)) for w in ws])
+        pair = f"   CTA pairs {us:7.2f} us {flops / us / 1e6:7.1f}"
+        print(f"  {name:8s} [{N} x {K}]  tcgen05 {ours:7.2f} us {flops / ours / 1e6:7.1f}   library {lib:7.2f} us {flops / lib / 1e6:7.1f}{pair}")
     assert status.item() == 0
     return 0
 

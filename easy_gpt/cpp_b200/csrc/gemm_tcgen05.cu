@@ -128,6 +128,7 @@ struct Params {
     int M, N, K;
     int epilogue;
     int* status;
+    long long* trace;          // optional (profiling): clock stamps of the first pair's MMA thread, three per step of K
 };
 
 __global__ void __launch_bounds__(THREADS)
@@ -428,6 +429,267 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// wide products on CTA pairs: 256 x 256 tiles, each CTA of a pair loads half of either operand
+// ---------------------------------------------------------------------------
+// Two CTAs of a cluster (two neighbouring SMs) compute one 256 x 256 tile: CTA r holds rows r * 128 .. of the A tile and
+// rows r * 128 .. of the W tile in its shared memory, the leader (rank 0) issues tcgen05.mma.cta_group::2 (M 256, N 256),
+// which reads both CTAs' shared memory, and each CTA's TMEM receives its 128 rows of the accumulator.  A 64-deep step
+// of K costs a CTA 32 KB of operands for 4.2 MFLOP, where the single-CTA kernel above moves 48 KB.
+//   warp 0   (both CTAs) TMA loads of the CTA's halves; the bytes are counted on the leader's full barrier
+//   warp 1   allocates TMEM (both CTAs, cta_group::2); in the leader one thread issues the MMAs and commits to the
+//            empty and accumulator barriers of both CTAs (multicast commit)
+//   warps 2-9 (both CTAs) read the CTA's accumulator rows, apply the epilogue, and arrive on the leader's
+//            accumulator-empty barrier (a remote arrive for the second CTA)
+// Persistent: a pair walks the tiles pair, pair + pairs, ...; two accumulators of 256 columns alternate.
+namespace pairk {
+constexpr int PTHREADS = 320;
+constexpr int PBK = 128;                                         // K per stage: two 64-wide boxes per operand, eight MMAs per barrier round
+constexpr int EPI_BOX_BYTES = 32 * 128;                           // an epilogue warp's [32 rows x 64 bfloat16] box
+// PBN: columns of the pair's tile, 256 or 128 (narrow products: more tiles, so that most pairs get one)
+template <int PBN>
+struct PairCfg {
+    static constexpr int STAGES = PBN == 256 ? 3 : 4;
+    static constexpr int A_SUB_BYTES = 128 * BK * 2;              // a [128 x 64] box of A
+    static constexpr int W_SUB_BYTES = (PBN / 2) * BK * 2;        // a [PBN/2 x 64] box of W: this CTA's half of the tile's columns
+    static constexpr int STAGE_BYTES = 2 * A_SUB_BYTES + 2 * W_SUB_BYTES;     // A low K, A high K, W low K, W high K
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * EPI_BOX_BYTES + 1024;
+    static constexpr int TMEM_COLS = 2 * PBN;
+};
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;                  // clears the bit that tells the pair's CTAs apart in a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The CTA's own load, counted on the barrier at the same place in the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_addr(smem_dst)), "l"(map), "r"(smem_addr(bar) & PEER_BIT_MASK), "r"(x), "r"(y) : "memory");
+}
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0) : "memory");
+}
+// arrives on the barrier at this place in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_addr(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void arrive_at_leader(uint64_t* bar) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_addr(bar)), "r"(0));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
+}
+
+template <int PBN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PTHREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_out, const Params p) {
+    using C = PairCfg<PBN>;
+    constexpr int PSTAGES = C::STAGES, P_STAGE_BYTES = C::STAGE_BYTES, P_TMEM_COLS = C::TMEM_COLS;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[PSTAGES], empty_bar[PSTAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int k_blocks = (p.K + PBK - 1) / PBK;                  // a last half block reads zeros past K (the TMA fills them)
+    const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = p.N / PBN;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 16);                         // one arrival per epilogue warp of either CTA
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(P_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    cluster_sync();                                              // both CTAs' barriers exist before anyone arrives on them
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                         // ---- TMA producer, in both CTAs
+            int g = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += pairs) {
+                const int n0 = (t / m_tiles) * PBN + rank * (PBN / 2), m0 = (t % m_tiles) * 2 * BM + rank * BM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = g % PSTAGES;
+                    if (g >= PSTAGES && !mbar_wait(&empty_bar[s], ((g / PSTAGES) - 1) & 1, &abort_flag, p.status)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * P_STAGE_BYTES);
+                    unsigned char* a = ring + s * P_STAGE_BYTES;
+                    tma_load_2d_pair(a, &map_a, &full_bar[s], kb * PBK, m0);
+                    tma_load_2d_pair(a + C::A_SUB_BYTES, &map_a, &full_bar[s], kb * PBK + BK, m0);
+                    tma_load_2d_pair(a + 2 * C::A_SUB_BYTES, &map_w, &full_bar[s], kb * PBK, n0);
+                    tma_load_2d_pair(a + 2 * C::A_SUB_BYTES + C::W_SUB_BYTES, &map_w, &full_bar[s], kb * PBK + BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {                            // ---- MMA issuer, in the leader
+            uint32_t idesc = 0;                                  // D float32, A and B bfloat16 K-major, M 256, N = PBN
+            idesc |= 1u << 4;
+            idesc |= 1u << 7;
+            idesc |= 1u << 10;
+            idesc |= (uint32_t)(PBN >> 3) << 17;
+            idesc |= (uint32_t)((2 * BM) >> 4) << 24;
+            const uint32_t desc_hi = (uint32_t)(umma_desc(0) >> 32), ring_lo = (uint32_t)umma_desc(smem_addr(ring));
+            int g = 0, local = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += pairs, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, &abort_flag, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * PBN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+                    const int s = g % PSTAGES;
+                    const uint32_t a_lo = ring_lo + (uint32_t)((s * P_STAGE_BYTES) >> 4), b_lo = a_lo + (2 * C::A_SUB_BYTES >> 4);
+                    uint64_t adesc[PBK / 16], bdesc[PBK / 16];
+#pragma unroll
+                    for (int k = 0; k < PBK / 16; ++k) {             // 16 of K = 32 bytes in the row; 64 of K = the next box
+                        adesc[k] = umma_desc_from(a_lo + (k / 4) * (C::A_SUB_BYTES >> 4) + 2 * (k % 4), desc_hi);
+                        bdesc[k] = umma_desc_from(b_lo + (k / 4) * (C::W_SUB_BYTES >> 4) + 2 * (k % 4), desc_hi);
+                    }
+                    const bool tr = p.trace && blockIdx.x == 0 && g < 64;
+                    if (tr) p.trace[g * 3] = clock64();
+                    ok = mbar_wait(&full_bar[s], (g / PSTAGES) & 1, &abort_flag, p.status);
+                    if (!ok) break;
+                    if (tr) p.trace[g * 3 + 1] = clock64();
+                    if (kb) umma_pair<true>(tmem_acc, adesc[0], bdesc[0], idesc);
+                    else umma_pair<false>(tmem_acc, adesc[0], bdesc[0], idesc);
+#pragma unroll
+                    for (int k = 1; k < PBK / 16; ++k) umma_pair<true>(tmem_acc, adesc[k], bdesc[k], idesc);
+                    commit_pair(&empty_bar[s]);
+                    if (tr) p.trace[g * 3 + 2] = clock64();
+                }
+                if (ok) commit_pair(&acc_full[buf]);
+            }
+        }
+    } else {                                                     // ---- epilogue warps 2..9, in both CTAs
+        // A warp takes 32 rows x PBN / 2 accumulator columns.  Its results go through a [32 x 64] bfloat16 box in shared
+        // memory (128-byte rows, swizzled like the TMA's tiles: a lane writes its own row without bank conflicts)
+        // and leave with a TMA store: rows of a tile are 19 KB apart in the output, and 32 scattered 16-byte stores
+        // per instruction kept the load/store path busy enough to hold up the MMA thread's barrier traffic.
+        const int quad = warp & 3;                               // a warp may touch TMEM lanes 32 * (warp % 4) ..
+        const int half = (warp - 2) >> 2;                        // the two warps of a quad share its rows' columns
+        unsigned char* box = ring + PSTAGES * P_STAGE_BYTES + (warp - 2) * EPI_BOX_BYTES;
+        const uint32_t box_row = smem_addr(box) + (uint32_t)lane * 128u;
+        int local = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += pairs, ++local) {
+            const int buf = local & 1;
+            const int n0 = (t / m_tiles) * PBN, m0 = (t % m_tiles) * 2 * BM + rank * BM;
+            ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, &abort_flag, p.status);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!ok) break;
+            const int row0 = m0 + quad * 32;
+            // The warp has PBN / 2 accumulator columns.  Store: a box per 64 of them.  SwiGLU (PBN 256 only): its 128
+            // columns give one box of 64 outputs.
+            const int boxes = p.epilogue == EPI_SWIGLU ? 1 : PBN / 128;
+#pragma unroll 1
+            for (int bx = 0; bx < boxes; ++bx) {
+                const int cols_per_box = p.epilogue == EPI_SWIGLU ? 128 : 64;
+                const int c_first = half * (PBN / 2) + bx * 64;  // first accumulator column of this box
+                // the box in shared memory must have left with the store before it is written again
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+                __syncwarp();
+#pragma unroll 1
+                for (int c0 = 0; c0 < cols_per_box; c0 += 32) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PBN + c_first + c0);
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                                 : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __uint_as_float(r[j]);
+                        if (p.bias) v[j] += p.bias[n0 + c_first + c0 + j];
+                    }
+                    if (p.epilogue == EPI_SWIGLU) {
+                        // 32 accumulator columns = 16 outputs = two 16-byte pieces of the box row
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float y0 = swiglu_fast(v[4 * j], v[4 * j + 1]), y1 = swiglu_fast(v[4 * j + 2], v[4 * j + 3]);
+                            __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const uint32_t dst = box_row + (uint32_t)((((c0 / 32) * 2 + q) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
+                                         "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3]) : "memory");
+                        }
+                    } else {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t dst = box_row + (uint32_t)((((c0 / 32) * 4 + q) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
+                                         "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3]) : "memory");
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = p.epilogue == EPI_SWIGLU ? (n0 + c_first) / 2 : n0 + c_first;
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                                 ::"l"(&map_out), "r"(smem_addr(box)), "r"(x), "r"(row0) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                }
+            }
+            // this warp has read its part of the accumulator: the leader's MMA thread may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) arrive_at_leader(&acc_empty[buf]);
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");      // the last boxes have been written
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    cluster_sync();                                              // nobody leaves while its partner may still read its shared memory
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(P_TMEM_COLS) : "memory");
+    }
+}
+}  // namespace pairk
 
 // ---------------------------------------------------------------------------
 // few rows (17 .. 128 tokens: the larger decode batches, short prompt portions): the weights stream once
@@ -761,4 +1023,45 @@ EG_API int eg_gemm_tcgen05_few(cudaStream_t stream, int epilogue, int use_pdl, c
         case 64: return launch_few<64>(stream, map_a, map_w, p, slices, use_pdl);
         default: return launch_few<128>(stream, map_a, map_w, p, slices, use_pdl);
     }
+}
+
+namespace {
+template <int PBN>
+int launch_pair(cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_out, const Params& p, int sm_count) {
+    using C = pairk::PairCfg<PBN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(pairk::gemm_tcgen05_pair_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * (p.N / PBN);
+    const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+    pairk::gemm_tcgen05_pair_kernel<PBN><<<2 * pairs, pairk::PTHREADS, C::SMEM_BYTES, stream>>>(map_a, map_w, map_out, p);
+    return eg_launch_status();
+}
+}  // namespace
+
+// The same product on CTA pairs (tcgen05.mma.cta_group::2): tiles of 256 x tile_n, tile_n 256 or 128 (N % tile_n == 0),
+// K % 64 == 0; epilogues as eg_gemm_tcgen05 (SwiGLU with tile_n 256 only).
+EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
+                                const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status,
+                                long long* trace) {
+    if (M <= 0 || N <= 0) return 0;
+    if ((tile_n != 128 && tile_n != 256) || N % tile_n || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 ||
+        (uintptr_t)W % 16 || (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) ||
+        (epilogue == EPI_SWIGLU && tile_n != 256) || !status)
+        return (int)cudaErrorInvalidValue;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    CUtensorMap map_a, map_w, map_out;
+    if (make_map(&map_a, A, M, K, lda, BM) || make_map(&map_w, W, N, K, ldw, tile_n / 2) ||
+        make_map(&map_out, out, M, epilogue == EPI_SWIGLU ? N / 2 : N, ldo, 32))
+        return (int)cudaErrorInvalidValue;
+    Params p{(bf16*)out, ldo, bias, M, N, K, epilogue, status, trace};
+    return tile_n == 256 ? launch_pair<256>(stream, map_a, map_w, map_out, p, sm_count) : launch_pair<128>(stream, map_a, map_w, map_out, p, sm_count);
 }

@@ -83,6 +83,8 @@ class _Signatures:
                       c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p]
     eg_gemm_tcgen05 = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
                        c_int, c_void_p]
+    eg_gemm_tcgen05_pair = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                            c_int, c_int, c_void_p, c_void_p]
     eg_gemm_tcgen05_few = [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
@@ -601,6 +603,8 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
 # library product plus the SwiGLU kernel.  So gate/up + SwiGLU goes through ours where the wide kernel takes the
 # shape; the other products of a prompt stay with the library.  EASY_GPT_TCGEN05=0 switches it off.
 USE_TCGEN05 = os.environ.get("EASY_GPT_TCGEN05", "1") != "0"
+# the wide products on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles, TMA-store epilogue); 0: one CTA per 128 x 256 tile
+USE_TCGEN05_PAIR = os.environ.get("EASY_GPT_TCGEN05_PAIR", "1") != "0"
 
 
 def gemm_tcgen05_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
@@ -616,7 +620,8 @@ def gemm_tcgen05_wide_takes(dtype: torch.dtype, tokens: int, out_features: int, 
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                 status: torch.Tensor, swiglu_epilogue: bool = False) -> None:
+                 status: torch.Tensor, swiglu_epilogue: bool = False, pair: bool = False,
+                 trace: Optional[torch.Tensor] = None) -> None:
     """out = x @ weight^T + bias on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM).  With
     ``swiglu_epilogue`` the weight's rows are interleaved gate/up and out is [M, N/2]."""
     _cuda(x, weight, bias, out, status)
@@ -629,6 +634,13 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
           and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0, "16-byte aligned rows")
     _need(tuple(out.shape) == (M, N // 2 if swiglu_epilogue else N), "out shape")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
+    if pair:
+        tile_n = 256 if (N % 256 == 0 and (swiglu_epilogue or -(-M // 256) * (N // 256) >= SM_COUNT // 2)) else 128
+        _need(N % tile_n == 0, "SwiGLU on CTA pairs takes N % 256 == 0")
+        _check(library().eg_gemm_tcgen05_pair(_stream(), EPI_SWIGLU if swiglu_epilogue else EPI_STORE, _ptr(x), x.stride(0),
+                                              _ptr(weight), weight.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
+                                              tile_n, _ptr(status), _ptr(trace)), "gemm_tcgen05_pair")
+        return
     _check(library().eg_gemm_tcgen05(_stream(), EPI_SWIGLU if swiglu_epilogue else EPI_STORE, _ptr(x), x.stride(0),
                                      _ptr(weight), weight.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
                                      _ptr(status)), "gemm_tcgen05")

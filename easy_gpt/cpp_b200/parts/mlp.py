@@ -71,7 +71,8 @@ class SwiGLU(FeedForward):
                 kernels.gemm_tcgen05_few(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, epilogue=kernels.EPI_SWIGLU)
             elif kernels.gemm_tcgen05_wide_takes(ctx.dtype, T, 2 * self.inter, self.hidden):
                 # prompts: the product on the tcgen05 tensor cores (persistent 128 x 256 tiles) with SwiGLU in its epilogue
-                kernels.gemm_tcgen05(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, swiglu_epilogue=True)
+                kernels.gemm_tcgen05(x, self.gate_up.weight, self.gate_up.bias_f32, act, ctx.status, swiglu_epilogue=True,
+                                     pair=kernels.USE_TCGEN05_PAIR)
             else:
                 kernels.swiglu(self.gate_up(x), act)
         return self.down(act, prefetch=self._hint(1), status=ctx.status)

@@ -113,3 +113,47 @@ def test_few_rows_refuses():
         kernels.gemm_tcgen05_few(x, w, None, torch.empty(129, 64, dtype=torch.bfloat16, device=DEV), status)
     with pytest.raises(kernels.KernelError):
         kernels.gemm_tcgen05_few(x[:8, :48], w[:, :48], None, torch.empty(8, 64, dtype=torch.bfloat16, device=DEV), status)
+
+
+@pytest.mark.parametrize("M, N, K", [(256, 256, 64), (256, 128, 64), (300, 896, 192), (2048, 1152, 896), (333, 640, 320),
+                                      (1000, 9728, 896), (130, 2304, 4864)])
+def test_cta_pair_product(M, N, K):
+    """Two CTAs per 256-row tile (tcgen05.mma.cta_group::2), both tile widths, rows and a last K step that end inside a
+    tile, TMA-store epilogue; twice in a row."""
+    from easy_gpt.cpp_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + N + K)
+    x = bf(torch.randn(M, K, generator=g)).to(DEV)
+    w = bf(torch.randn(N, K, generator=g) * 0.1).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().t() + b
+    for _ in range(2):
+        out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tcgen05(x, w, b, out, status, pair=True)
+        assert status.item() == 0
+        assert float((out.float() - want).abs().max()) <= 8e-3 * float(want.abs().max())
+    # a strided input and a strided output (slices of wider buffers)
+    wide = bf(torch.randn(M, K + 64, generator=g)).to(DEV)
+    out_wide = torch.full((M, N + 64), 3.0, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tcgen05(wide[:, 8:8 + K], w, None, out_wide[:, 32:32 + N], status, pair=True)
+    ref = wide[:, 8:8 + K].float() @ w.float().t()
+    assert float((out_wide[:, 32:32 + N].float() - ref).abs().max()) <= 8e-3 * float(ref.abs().max())
+    assert bool((out_wide[:, :32] == 3.0).all()) and bool((out_wide[:, 32 + N:] == 3.0).all()) and status.item() == 0
+
+
+@pytest.mark.parametrize("M, I, K", [(256, 128, 64), (300, 384, 192), (2048, 4864, 896)])
+def test_cta_pair_swiglu(M, I, K):
+    from easy_gpt.cpp_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + I)
+    x = bf(torch.randn(M, K, generator=g)).to(DEV)
+    gate, up = bf(torch.randn(I, K, generator=g) * 0.05), bf(torch.randn(I, K, generator=g) * 0.05)
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).to(DEV)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.gemm_tcgen05(x, w, None, out, status, swiglu_epilogue=True, pair=True)
+    gv, uv = x.float() @ gate.float().to(DEV).t(), x.float() @ up.float().to(DEV).t()
+    want = uv * (gv / (1 + torch.exp(-gv)))
+    assert status.item() == 0
+    assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
