@@ -38,7 +38,7 @@
 //
 // Takes head sizes 64 and 128, pages of a multiple of 16 tokens, 16-byte aligned rows.  Anything else:
 // cudaErrorInvalidValue, and the caller uses the warp-level kernel.
-#include <cuda.h>
+#define EG_NEEDS_TENSOR_MAPS
 
 #include "common.cuh"
 
@@ -681,9 +681,11 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const eg_encode_tiled_fn encode = eg_encode_tiled();
+    if (!encode) return (int)cudaErrorNotSupported;
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 

@@ -102,7 +102,7 @@ def library_path(verbose: bool = True) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objects = list(pool.map(compile_one, sources))
     tmp_lib = out_dir / (LIB_NAME + f".{os.getpid()}.tmp")
-    r = subprocess.run([nvcc, "-shared", "-o", str(tmp_lib), *objects, "-lcuda"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", str(tmp_lib), *objects], capture_output=True, text=True)
     if r.returncode != 0:
         raise BuildError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp_lib, out_dir / LIB_NAME)

@@ -72,10 +72,30 @@ struct TraceScope {
     __device__ __forceinline__ ~TraceScope() {
         if (slot && threadIdx.x == 0) atomicMax(slot + 1, now());
     }
-    // Phase stamps of the launch's first CTA: slot[2 + i], i < 14.
+    // Phase stamps, the latest over the launch's CTAs: slot[2 + i], i < 14.
     __device__ __forceinline__ void mark(int i) const {
-        if (slot && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) slot[2 + i] = now();
+        if (slot && threadIdx.x == 0) atomicMax(slot + 2 + i, now());
     }
 };
 
 static inline int eg_launch_status() { return (int)cudaGetLastError(); }
+
+#ifdef EG_NEEDS_TENSOR_MAPS
+#include <cuda.h>
+// The driver's tensor-map encoder, looked up through the runtime at the first call: the library then has no
+// link-time dependency on the driver and loads (for the build check) on a machine without one.
+typedef CUresult (*eg_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static inline eg_encode_tiled_fn eg_encode_tiled() {
+    static eg_encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) == cudaSuccess &&
+            found == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<eg_encode_tiled_fn>(entry);
+    }
+    return fn;
+}
+#endif
