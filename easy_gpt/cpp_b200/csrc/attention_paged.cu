@@ -28,6 +28,8 @@ constexpr int QUARTER_TILES = 64;      // tiles whose cache addresses are kept i
 // DEEP: as many stages as fit about 96 KB (up to five tiles in flight per CTA, two CTAs per SM): for steps with few
 // CTAs, where each has to keep its own loads going.  Otherwise three stages, so that four CTAs share an SM: with
 // many CTAs it is their number in flight that hides a tile's latency.
+constexpr int MAX_SPLITS = 128;
+
 template <int HD, bool DEEP = true>
 struct Layout {
     static constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per key row
@@ -37,7 +39,9 @@ struct Layout {
     // up to five tiles in flight per CTA, within about 96 KB of shared memory (two stages at least)
     static constexpr int DEEP_STAGES = (96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((96 * 1024 / STAGE_BYTES) >= 2 ? (96 * 1024 / STAGE_BYTES) : 2);
     static constexpr int STAGES = DEEP ? DEEP_STAGES : (DEEP_STAGES < 3 ? DEEP_STAGES : 3);
-    static constexpr int MERGE_BYTES = 4 * 16 * (HD + 2) * 4;
+    static constexpr int WARP_MERGE_BYTES = 4 * 16 * (HD + 2) * 4;            // the four warps' partial results
+    static constexpr int SPLIT_MERGE_BYTES = (2 * 16 * MAX_SPLITS + 16) * 4;  // (m, l) of every row and split, 1/l per row
+    static constexpr int MERGE_BYTES = WARP_MERGE_BYTES > SPLIT_MERGE_BYTES ? WARP_MERGE_BYTES : SPLIT_MERGE_BYTES;
     static constexpr int SMEM = (STAGES * STAGE_BYTES > MERGE_BYTES) ? STAGES * STAGE_BYTES : MERGE_BYTES;
     __device__ static __forceinline__ int offset(int row, int chunk) {      // bytes inside a K or V tile
         return (row * CHUNKS + (chunk ^ (row & SWZ))) * 16;
@@ -100,7 +104,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
     // Positions and block tables were uploaded before the step and the cached keys were written by earlier
     // steps, so everything up to the first fresh key can be fetched before the kernel in front has finished.
-    if (p.use_pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::);
+    if (p.use_pdl == 1) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int pos = p.positions[t];
     const int fresh_from = p.seq_context ? p.seq_context[p.token_seq[t]] : 0;
     const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
@@ -162,6 +166,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
     trace_scope.mark(0);
     if (p.use_pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");     // q and the fresh keys come from the kernel in front
+    if (p.use_pdl == 2) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     trace_scope.mark(1);
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s)
@@ -337,38 +342,69 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     trace_scope.mark(5);
     if (!is_last) return;
     __threadfence();
-    // 1. every row's maximum and per-split factor e^{m_s - m}; the loads of all splits are in flight together
-    float* fac = reinterpret_cast<float*>(smem);                                  // [rows][splits]
-    float* inv_l = fac + 16 * p.splits;                                            // [rows]
+    // Every load of the merge is issued before anything waits: (m, l) of all (row, split) pairs, and the first
+    // MERGE_BATCH splits of the accumulators, a float4 of one row per thread.  One trip to the L2 instead of several.
+    constexpr int MERGE_BATCH = 16;
+    constexpr int QUADS = HD / 4;
+    float* fac = reinterpret_cast<float*>(smem);                                  // [rows][splits]: m_s, then e^{m_s - m}
+    float* lpart = fac + 16 * p.splits;                                            // [rows][splits]: l_s
+    float* inv_l = lpart + 16 * p.splits;                                          // [rows]
+    const size_t head0 = (size_t)t * p.num_heads + kvh * G + g0;
     for (int e = threadIdx.x; e < rows * p.splits; e += THREADS) {
-        const int r = e / p.splits, s2 = e % p.splits;
-        const size_t slot = ((size_t)t * p.num_heads + kvh * G + g0 + r) * p.splits + s2;
-        fac[r * p.splits + s2] = __ldcg(p.partial_ml + slot * 2);                  // m_s for now
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml) + head0 * p.splits + e);   // rows are consecutive heads
+        fac[e] = ml.x;
+        lpart[e] = ml.y;
     }
-    __syncthreads();
-    if (threadIdx.x < rows) {
-        const int r = threadIdx.x;
-        float m = -INFINITY;
-        for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, fac[r * p.splits + s2]);
-        const size_t base = ((size_t)t * p.num_heads + kvh * G + g0 + r) * p.splits;
-        float l = 0.f;
-        for (int s2 = 0; s2 < p.splits; ++s2) {
-            const float f = m > -INFINITY ? exp2f(fac[r * p.splits + s2] - m) : 0.f;
-            fac[r * p.splits + s2] = f;
-            l += __ldcg(p.partial_ml + (base + s2) * 2 + 1) * f;
+    for (int q0 = 0; q0 < rows * QUADS; q0 += THREADS) {
+        const int q = q0 + threadIdx.x;
+        const bool mine = q < rows * QUADS;
+        const int r = mine ? q / QUADS : 0, dq = mine ? q % QUADS : 0;
+        const float4* src = reinterpret_cast<const float4*>(p.partial_acc + (head0 + r) * p.splits * HD) + dq;
+        float4 part[MERGE_BATCH];
+#pragma unroll
+        for (int i = 0; i < MERGE_BATCH; ++i)
+            if (mine && i < p.splits) part[i] = __ldcg(src + (size_t)i * QUADS);
+        if (q0 == 0) {
+            __syncthreads();
+            if (threadIdx.x < rows) {
+                float* f = fac + threadIdx.x * p.splits;
+                const float* lp = lpart + threadIdx.x * p.splits;
+                float m = -INFINITY;
+                for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, f[s2]);
+                float l = 0.f;
+                for (int s2 = 0; s2 < p.splits; ++s2) {                             // in order
+                    const float w = m > -INFINITY ? exp2f(f[s2] - m) : 0.f;
+                    f[s2] = w;
+                    l += lp[s2] * w;
+                }
+                inv_l[threadIdx.x] = l > 0.f ? 1.0f / l : 0.f;
+            }
+            __syncthreads();
         }
-        inv_l[r] = l > 0.f ? 1.0f / l : 0.f;
-    }
-    __syncthreads();
-    // 2. the weighted sum of the splits' accumulators
-    for (int e = threadIdx.x; e < rows * HD; e += THREADS) {
-        const int r = e / HD, d = e % HD;
+        if (!mine) continue;
+        const float* f = fac + r * p.splits;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < MERGE_BATCH; ++i)
+            if (i < p.splits) {
+                const float w = f[i];
+                a.x += part[i].x * w; a.y += part[i].y * w; a.z += part[i].z * w; a.w += part[i].w * w;
+            }
+        for (int s0 = MERGE_BATCH; s0 < p.splits; s0 += MERGE_BATCH) {             // further splits, a batch in flight at a time
+#pragma unroll
+            for (int i = 0; i < MERGE_BATCH; ++i)
+                if (s0 + i < p.splits) part[i] = __ldcg(src + (size_t)(s0 + i) * QUADS);
+#pragma unroll
+            for (int i = 0; i < MERGE_BATCH; ++i)
+                if (s0 + i < p.splits) {
+                    const float w = f[s0 + i];
+                    a.x += part[i].x * w; a.y += part[i].y * w; a.z += part[i].z * w; a.w += part[i].w * w;
+                }
+        }
+        const float il = inv_l[r];
         const int h = kvh * G + g0 + r;
-        const float* src = p.partial_acc + ((size_t)t * p.num_heads + h) * p.splits * HD + d;
-        float a = 0.f;
-#pragma unroll 8
-        for (int s2 = 0; s2 < p.splits; ++s2) a += __ldcg(src + (size_t)s2 * HD) * fac[r * p.splits + s2];
-        p.out[(size_t)t * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(a * inv_l[r]);
+        *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + (size_t)h * HD + dq * 4) =
+            make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
     }
 }
 
@@ -682,7 +718,7 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
                               long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list) {
     if (tokens <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
-        splits > 128 || (splits > 1 && (!partial_acc || !partial_ml || !counters)))
+        splits > MAX_SPLITS || (splits > 1 && (!partial_acc || !partial_ml || !counters || ldo % 4 || (uintptr_t)out % 8)))
         return (int)cudaErrorInvalidValue;
     Params p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
              table_stride, token_seq, positions, seq_context, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,

@@ -21,13 +21,24 @@
 //              the row's factor 1/sqrt(mean + eps) multiplies the product's result
 //              instead of every x (the product is linear in x).  CTA 0 also writes v to
 //              residual_out (another buffer, so that no CTA reads what CTA 0 has
-//              already updated).  Meant for a few tokens: every CTA repeats it.
+//              already updated).  Meant for a few tokens: every CTA repeats it.  The input
+//              rows come into shared memory by bulk copies (one trip to the L2).
+//   prenormed  the kernel in front (epilogue resid_norm) has already added its result to the
+//              residual and left bfloat16(gain * v) and, per CTA of its own, the partial sums
+//              of squares of v: the rows come in by bulk copy and every CTA only adds up the
+//              partial sums, in their order, for the rows' factors.
 // Epilogues (what happens to y):
 //   store      + bias -> bfloat16 [M, N]
 //   f32        + bias -> float32 [M, N] (logits)
 //   swiglu     rows of W interleaved (2i = gate_i, 2i+1 = up_i): up * silu(gate) -> bfloat16 [M, N/2]
 //   qkv_rope   one CTA per head (RB*16 == head_dim): + bias, q and k rotated
 //              (src/ops.cpp:404-421), q -> bfloat16 [M, NH*HD], k and v -> paged cache
+//   resid_norm the result (rounded to bfloat16, as a stored delta would be) is added to the
+//              float32 residual in place, v = residual + y; bfloat16(gain * v) goes to xn_out
+//              and this CTA's sum of v^2 per token to ss_out[CTA][tokens]: the input of the
+//              next kernel's prenormed prologue, so that the add and the norm that follow a
+//              product are computed once, by the product's own CTAs, and not by every CTA
+//              of the next one.
 //
 // Every kernel starts streaming its weights before it waits for the kernel in front
 // of it (programmatic dependent launch), so the pipeline of small kernels overlaps.
@@ -41,7 +52,7 @@ constexpr int MAX_THREADS = 512;
 constexpr int UNROLL = 4;            // 64-wide k chunks in flight per warp (256 bytes per thread)
 constexpr int CHUNK = 64;
 
-enum { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3 };
+enum { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3, EPI_RESID_NORM = 4 };
 
 struct Params {
     const bf16* W;
@@ -69,6 +80,14 @@ struct Params {
     int* status;
     int RB, KS;
     int use_pdl;
+    int stage_norm;              // the norm prologue's input comes through one bulk copy into shared memory
+    int norm_mode;               // 1: add + norm here; 2: prenormed rows (delta = xn) and partial sums (ss_in)
+    const float* ss_in;          // [ss_parts][padded tokens] partial sums of squares, prenormed prologue
+    int ss_parts;
+    float* resid_inout;          // resid_norm epilogue: the residual, updated in place
+    const float* gain_out;       //   the following norm's gain
+    bf16* xn_out;                //   bfloat16(gain_out * v) [M, N]
+    float* ss_out;               //   [gridDim.x][padded tokens]
     const void* prefetch;        // weights of a kernel that runs soon: pulled into L2 meanwhile
     long long prefetch_bytes;
     float* scratch;              // [gridDim.y][gridDim.x][RB*16][tokens] partial sums when K is cut across CTAs
@@ -106,15 +125,34 @@ __device__ __forceinline__ void prefetch_next_weights(const void* base, long lon
     }
 }
 
+// ---- one bulk copy of the norm prologue's input, completion counted on an mbarrier; the wait is bounded
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bulk_copy_to_smem(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-template <int NT, int EPI, bool NORM>
+template <int NT, int EPI, int NORM>
 __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     extern __shared__ __align__(32) unsigned char smem[];
     __shared__ int is_last;
+    __shared__ __align__(8) uint64_t staged_bar;
     TraceScope trace_scope(p.trace);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((NORM == 2 || (NORM == 1 && p.stage_norm)) && threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(&staged_bar)), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
     const int gid = lane >> 2, tig = lane & 3;
     const int rb = warp % p.RB, ks = warp / p.RB;
     const int rows_per_cta = p.RB * 16;
@@ -131,7 +169,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
 
     // The next kernel may start at once: what it does before its own wait (weights, cached keys) does not
     // depend on this kernel, and its wait still covers this kernel's completion.
-    if (p.use_pdl) grid_dependents_launch();
+    if (p.use_pdl == 1) grid_dependents_launch();
 
     // ---- start the weight stream: UNROLL chunks per row in registers
     W32 wra[UNROLL], wrb[UNROLL];
@@ -154,13 +192,14 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     // before the wait, so that its trip from HBM is off the critical path.
     const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;     // bytes; rows 16 banks apart
     float* gain_s = reinterpret_cast<float*>(smem + (size_t)MT * xs_stride + MT * sizeof(float));
-    if (NORM) {
+    if (NORM == 1) {
         const float4* g = reinterpret_cast<const float4*>(p.gain);
         for (int i = threadIdx.x; i < p.K / 4; i += blockDim.x) reinterpret_cast<float4*>(gain_s)[i] = g[i];
     }
 
     trace_scope.mark(0);
     if (p.use_pdl) grid_dependency_wait();                        // from here on the previous kernel's results are read
+    if (p.use_pdl == 2) grid_dependents_launch();
     trace_scope.mark(1);
 
     // ---- x: staged into shared memory by the norm prologue, or read from global memory
@@ -174,13 +213,63 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         // loads go out in one batch; with fewer, a warp takes several rows one after the other.
         const int parts = p.M > 0 && nwarps >= p.M ? min(nwarps / p.M, 8) : 1;
         const int per_part = (quads + parts - 1) / parts;
-        __syncthreads();                                          // gain_s is complete
+        // The residual (and the delta, straight into its row of xs, where the normalised value replaces it) come
+        // in one batch of bulk copies: one trip to the L2 for the whole input, instead of one per pass of the loop.
+        const float* staged_resid = reinterpret_cast<const float*>(ss_part + MT * 8);
+        __syncthreads();                                          // gain_s is complete, and everyone sees the barrier's init
+        if (NORM == 2) {
+            // rows bfloat16(gain * v) straight into xs, the partial sums of squares where the residual would be staged
+            float* ss_s = const_cast<float*>(staged_resid);       // [ss_parts][MT]
+            if (warp == 0) {
+                if (lane == 0) {
+                    const unsigned bytes = (unsigned)p.M * (unsigned)p.K * 2u + (unsigned)p.ss_parts * MT * 4u;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(&staged_bar)), "r"(bytes) : "memory");
+                    bulk_copy_to_smem(ss_s, p.ss_in, (unsigned)p.ss_parts * MT * 4u, &staged_bar);
+                }
+                __syncwarp();
+                for (int m = lane; m < p.M; m += 32)
+                    bulk_copy_to_smem(xs + (size_t)m * xs_stride, p.delta + (size_t)m * p.K, (unsigned)p.K * 2u, &staged_bar);
+            }
+            for (int e = threadIdx.x; e < (MT - p.M) * quads; e += blockDim.x)      // rows that only pad the token tile
+                reinterpret_cast<uint2*>(xs + (size_t)(p.M + e / quads) * xs_stride)[e % quads] = make_uint2(0u, 0u);
+            bool landed = false;
+            for (unsigned i = 0; i < WAIT_LIMIT && !landed; ++i) landed = mbar_try_wait(&staged_bar, 0);
+            if (!landed && p.status) atomicOr(p.status, EG_STATUS_WAIT_TIMEOUT);
+            if (threadIdx.x < MT) {
+                float f = 0.f;
+                if ((int)threadIdx.x < p.M) {
+                    float ss = 0.f;
+                    for (int q = 0; q < p.ss_parts; ++q) ss += ss_s[q * MT + threadIdx.x];      // fixed order
+                    f = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+                }
+                row_factor[threadIdx.x] = f;
+            }
+            __syncthreads();
+        } else {
+        if (p.stage_norm) {
+            if (warp == 0) {
+                if (lane == 0) {
+                    const unsigned bytes = (unsigned)p.M * (unsigned)p.K * (p.delta ? 6u : 4u);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(&staged_bar)), "r"(bytes) : "memory");
+                    bulk_copy_to_smem(const_cast<float*>(staged_resid), p.resid_in, (unsigned)p.M * (unsigned)p.K * 4u, &staged_bar);
+                }
+                __syncwarp();
+                if (p.delta)
+                    for (int m = lane; m < p.M; m += 32)
+                        bulk_copy_to_smem(xs + (size_t)m * xs_stride, p.delta + (size_t)m * p.K, (unsigned)p.K * 2u, &staged_bar);
+            }
+            bool landed = false;
+            for (unsigned i = 0; i < WAIT_LIMIT && !landed; ++i) landed = mbar_try_wait(&staged_bar, 0);
+            if (!landed && p.status) atomicOr(p.status, EG_STATUS_WAIT_TIMEOUT);
+        }
         for (int task = warp; task < p.M * parts; task += nwarps) {
             const int m = task / parts, part = task % parts;
             const int q_lo = part * per_part, q_hi = min(quads, q_lo + per_part);
             uint2* dst = reinterpret_cast<uint2*>(xs + (size_t)m * xs_stride);
-            const float4* r = reinterpret_cast<const float4*>(p.resid_in + (size_t)m * p.K);
-            const uint2* d = p.delta ? reinterpret_cast<const uint2*>(p.delta + (size_t)m * p.K) : nullptr;
+            const float4* r = reinterpret_cast<const float4*>((p.stage_norm ? staged_resid : p.resid_in) + (size_t)m * p.K);
+            const uint2* d = !p.delta ? nullptr
+                             : p.stage_norm ? reinterpret_cast<const uint2*>(xs + (size_t)m * xs_stride)
+                                            : reinterpret_cast<const uint2*>(p.delta + (size_t)m * p.K);
             const float4* g = reinterpret_cast<const float4*>(gain_s);
             float4* ro = (blockIdx.x == 0 && blockIdx.y == 0 && p.resid_out)
                              ? reinterpret_cast<float4*>(p.resid_out + (size_t)m * p.K) : nullptr;
@@ -231,9 +320,23 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             row_factor[threadIdx.x] = f;
         }
         __syncthreads();
+        }
     }
 
     trace_scope.mark(2);
+    // resid_norm epilogue: this thread's first output (token, column) is known now; its residual element and gain
+    // are asked for here, so that their trip from the L2 runs beside the product
+    float resid_first = 0.f, gain_first = 0.f;
+    if (EPI == EPI_RESID_NORM) {
+        const int e = threadIdx.x;
+        if (e < rows_per_cta * p.M) {
+            const int m = e / rows_per_cta, n = n0 + e % rows_per_cta;
+            if (n < p.N) {
+                resid_first = p.resid_inout[(size_t)m * p.N + n];
+                gain_first = p.gain_out[n];
+            }
+        }
+    }
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -353,6 +456,28 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             const float sig = 1.0f / (1.0f + expf(-g));
             p.out[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(u * (g * sig));
         }
+    } else if (EPI == EPI_RESID_NORM) {
+        float* sq = red;                                              // [rows_per_cta][MT] squares (the slices' memory is free)
+        for (int e = threadIdx.x; e < rows_per_cta * MT; e += blockDim.x) sq[e] = 0.f;
+        __syncthreads();
+        for (int e = threadIdx.x; e < rows_per_cta * p.M; e += blockDim.x) {
+            const int m = e / rows_per_cta, r = e % rows_per_cta;
+            const int n = n0 + r;
+            if (n >= p.N) continue;
+            const bool first = e == (int)threadIdx.x;
+            const float y = __bfloat162float(__float2bfloat16_rn(value(r, m)));      // what a stored delta would hold
+            const float v = (first ? resid_first : p.resid_inout[(size_t)m * p.N + n]) + y;
+            const float g = first ? gain_first : p.gain_out[n];
+            p.resid_inout[(size_t)m * p.N + n] = v;
+            p.xn_out[(size_t)m * p.N + n] = __float2bfloat16_rn(g * v);
+            sq[r * MT + m] = v * v;
+        }
+        __syncthreads();
+        if (threadIdx.x < MT) {
+            float ss = 0.f;
+            for (int r = 0; r < rows_per_cta; ++r) ss += sq[r * MT + threadIdx.x];   // fixed order
+            p.ss_out[(size_t)blockIdx.x * MT + threadIdx.x] = ss;
+        }
     } else {   // EPI_QKV_ROPE: this CTA holds one whole head
         const int HD = p.head_dim, half = HD / 2;
         const int head = blockIdx.x;
@@ -396,12 +521,24 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     }
 }
 
-template <int NT, int EPI, bool NORM>
-int launch_one(cudaStream_t stream, const Params& p, int ctas, int k_split) {
+template <int NT, int EPI, int NORM>
+int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
     constexpr int MT = NT * 8;
+    Params p = p_in;
     const int nwarps = p.RB * p.KS;
     const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
-    const size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) + (size_t)MT * 8 * sizeof(float) : 0;
+    size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) + (size_t)MT * 8 * sizeof(float) : 0;
+    // the residual rows staged in shared memory, where they fit and the copies' alignment rule (16 bytes) holds
+    const size_t staged_bytes = (size_t)p.M * p.K * sizeof(float);
+    if (NORM == 2) {
+        const size_t parts_bytes = (size_t)p.ss_parts * MT * sizeof(float);
+        if ((uintptr_t)p.delta % 16 || (uintptr_t)p.ss_in % 16 || (size_t)p.M * p.K * 2 + parts_bytes >= (1u << 20))
+            return (int)cudaErrorInvalidValue;
+        xs_bytes += parts_bytes;
+    }
+    p.stage_norm = NORM == 1 && xs_bytes + staged_bytes <= 200 * 1024 && (uintptr_t)p.resid_in % 16 == 0 && (uintptr_t)p.delta % 16 == 0 &&
+                   (size_t)p.M * p.K * 6 < (1u << 20);
+    if (p.stage_norm) xs_bytes += staged_bytes;
     const size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
     if (smem_bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = skinny_kernel<NT, EPI, NORM>;
@@ -424,7 +561,7 @@ int launch_one(cudaStream_t stream, const Params& p, int ctas, int k_split) {
     return (int)cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-template <int EPI, bool NORM>
+template <int EPI, int NORM>
 int launch_nt(cudaStream_t stream, const Params& p, int ctas, int k_split) {
     if (p.M <= 8) return launch_one<1, EPI, NORM>(stream, p, ctas, k_split);
     if (p.M <= 16) return launch_one<2, EPI, NORM>(stream, p, ctas, k_split);
@@ -436,7 +573,10 @@ int launch_nt(cudaStream_t stream, const Params& p, int ctas, int k_split) {
 }  // namespace
 
 // epilogue: 0 store bf16, 1 store f32, 2 swiglu (interleaved rows), 3 qkv + rope + cache (one CTA per head).
-// norm != 0: x = gain * rmsnorm(resid_in + delta) (delta may be null), resid_out (may be null) receives the sum.
+// epilogue 4 (resid_norm): resid_inout is the residual [M, N], updated in place; gain_out [N], xn_out bfloat16 [M, N],
+// ss_out float32 [ceil(N / (row_blocks*16))][padded tokens] receive what the next kernel's norm == 2 prologue reads.
+// norm == 1: x = gain * rmsnorm(resid_in + delta) (delta may be null), resid_out (may be null) receives the sum.
+// norm == 2: delta holds bfloat16(gain * v) [M, K] and ss_in [ss_parts][padded tokens] the partial sums of v^2.
 // row_blocks x k_slices warps per CTA (their product 1..16); k_split CTAs share the K range of a row group and
 // then need `scratch` (k_split * ceil(N / (row_blocks*16)) * row_blocks*16 * padded tokens floats) and `counters`
 // (one zeroed int per row group; left zero).  Takes M <= 64, K % 16 == 0, 32-byte aligned rows of W, 16-byte
@@ -448,8 +588,12 @@ EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_p
                           int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache,
                           void* v_cache, const float* inv_freq, int page_size, long long page_stride,
                           long long head_stride, long long pool_slots, int* status, const void* prefetch,
-                          long long prefetch_bytes, unsigned long long* trace) {
+                          long long prefetch_bytes, unsigned long long* trace, const float* ss_in, int ss_parts,
+                          float* resid_inout, const float* gain_out, void* xn_out, float* ss_out) {
     if (M <= 0 || N <= 0) return 0;
+    if (norm < 0 || norm > 2 || (norm == 2 && (!delta || !ss_in || ss_parts < 1)) ||
+        (epilogue == EPI_RESID_NORM && (!resid_inout || !gain_out || !xn_out || !ss_out)))
+        return (int)cudaErrorInvalidValue;
     if (M > 64 || K % 16 || ldw % 16 || (!norm && ldx % 8) || row_blocks < 1 || k_slices < 1 ||
         row_blocks * k_slices > MAX_THREADS / 32 || k_split < 1 || k_split > 64 || (k_split > 1 && (!scratch || !counters)))
         return (int)cudaErrorInvalidValue;
@@ -466,14 +610,18 @@ EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_p
     p.status = status; p.RB = row_blocks; p.KS = k_slices; p.use_pdl = use_pdl;
     p.prefetch = prefetch_bytes >= 16 ? prefetch : nullptr; p.prefetch_bytes = prefetch_bytes;
     p.scratch = scratch; p.counters = counters; p.trace = trace;
+    p.norm_mode = norm; p.ss_in = ss_in; p.ss_parts = ss_parts;
+    p.resid_inout = resid_inout; p.gain_out = gain_out; p.xn_out = (bf16*)xn_out; p.ss_out = ss_out;
     const int ctas = (N + row_blocks * 16 - 1) / (row_blocks * 16);
 #define EG_SKINNY(E)                                                                             \
-    case E: return norm ? launch_nt<E, true>(stream, p, ctas, k_split) : launch_nt<E, false>(stream, p, ctas, k_split);
+    case E: return norm == 2 ? launch_nt<E, 2>(stream, p, ctas, k_split)                          \
+                   : norm ? launch_nt<E, 1>(stream, p, ctas, k_split) : launch_nt<E, 0>(stream, p, ctas, k_split);
     switch (epilogue) {
         EG_SKINNY(EPI_STORE)
         EG_SKINNY(EPI_F32)
         EG_SKINNY(EPI_SWIGLU)
         EG_SKINNY(EPI_QKV_ROPE)
+        EG_SKINNY(EPI_RESID_NORM)
         default: return (int)cudaErrorInvalidValue;
     }
 #undef EG_SKINNY

@@ -15,7 +15,7 @@ from .. import architectures, parts  # noqa: F401  (registers what the framework
 from ..cache.manager import CacheManager
 from ..config.spec import LayerSpec, ModelSpec
 from .. import kernels
-from ..parts.base import PendingNorm, StepContext
+from ..parts.base import FollowingNorm, PendingNorm, StepContext
 from ..registry import model_spec_from_config, part_class
 from ..weights.loader import load_checked
 
@@ -38,16 +38,28 @@ class Block:
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
 
-    def forward(self, residual, spare, delta, ctx: StepContext, cache, work):
+    @staticmethod
+    def _offer(part, norm, pending, ctx, fused_rows):
+        """The add and norm after ``part`` as an offer to it, where the part fuses such things, the norm is a plain
+        RMSNorm and the step is small enough for the decode kernels."""
+        if (part.fuses_following_norm and norm is not None and norm.rms_parameters() is not None
+                and ctx.dtype == torch.bfloat16 and 0 < ctx.num_tokens <= fused_rows):
+            return dict(follow=FollowingNorm(norm, pending))
+        return {}
+
+    def forward(self, residual, spare, delta, ctx: StepContext, cache, work, next_norm=None):
         """Returns (residual, spare, delta): the buffer that now holds the residual
-        stream, the other one, and the feed-forward's output still to be added."""
+        stream, the other one, and the feed-forward's output still to be added (or the
+        PreNormed it left for ``next_norm``, the norm that runs after this block)."""
         fused_rows = kernels.FUSED_NORM_MAX_TOKENS
         pending = PendingNorm(self.mixer_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
-        delta = self.mixer.forward(pending if self.mixer.accepts_pending_norm else pending.materialize(), ctx, cache)
+        delta = self.mixer.forward(pending if self.mixer.accepts_pending_norm else pending.materialize(), ctx, cache,
+                                   **self._offer(self.mixer, self.ff_norm, pending, ctx, fused_rows))
         assert pending.consumed, "a mixer that accepts a pending norm must use it"
         residual, spare = pending.residual_after, pending.spare_after
         pending = PendingNorm(self.ff_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
-        delta = self.feed_forward.forward(pending if self.feed_forward.accepts_pending_norm else pending.materialize(), ctx)
+        delta = self.feed_forward.forward(pending if self.feed_forward.accepts_pending_norm else pending.materialize(), ctx,
+                                          **self._offer(self.feed_forward, next_norm, pending, ctx, fused_rows))
         assert pending.consumed, "a feed-forward that accepts a pending norm must use it"
         return pending.residual_after, pending.spare_after, delta
 
@@ -147,9 +159,11 @@ class Model:
         work = torch.empty((T, H), device=self.device, dtype=self.dtype)
         self.embedding.forward(ctx.token_ids, residual, ctx.status)
         delta = None
-        for e in self.spec.run_order:
+        order = self.spec.run_order
+        for i, e in enumerate(order):
+            next_norm = self.blocks[order[i + 1].layer].mixer_norm if i + 1 < len(order) else self.final_norm
             residual, spare, delta = self.blocks[e.layer].forward(residual, spare, delta, ctx,
-                                                                  cache.view(e.cache, e.writes_cache), work)
+                                                                  cache.view(e.cache, e.writes_cache), work, next_norm)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         pending = PendingNorm(self.final_norm, residual, delta, spare, work, rows=None if all_rows else logit_rows,

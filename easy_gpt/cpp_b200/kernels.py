@@ -80,7 +80,8 @@ class _Signatures:
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
-                      c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p]
+                      c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                      c_void_p, c_void_p]
     eg_gemm_tcgen05 = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
                        c_int, c_void_p]
     eg_gemm_tcgen05_pair = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int,
@@ -361,7 +362,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         head_dim, page_size, k_cache.stride(0), k_cache.stride(1), k_cache.shape[0], int(window or 0), float(scale),
         int(splits), _ptr(status), _ptr(prefetch) if PREFETCH_WEIGHTS else None,
         prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
-        _ptr(counters), int(USE_PDL), Timeline.slot(f"attention s={splits}"), _ptr(token_list)), "attention_paged")
+        _ptr(counters), USE_PDL, Timeline.slot(f"attention s={splits}"), _ptr(token_list)), "attention_paged")
 
 
 PREFILL_ATTENTION_HEAD_DIMS = (32, 64, 128)
@@ -488,9 +489,12 @@ SKINNY_KERNEL_TOKENS = 64      # what the kernel takes
 SKINNY_MAX_TOKENS = 16         # up to where it beats the library product (the policy of ``gemm_skinny_takes``)
 PREFETCH_WEIGHTS = os.environ.get("EASY_GPT_PREFETCH", "0") != "0"
 FUSED_NORM_MAX_TOKENS = 16     # every CTA repeats the norm prologue: worth it only for a few tokens
-EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE = 0, 1, 2, 3
+EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE, EPI_RESID_NORM = 0, 1, 2, 3, 4
 # programmatic dependent launch between the decode kernels (EASY_GPT_PDL=0 switches it off)
-USE_PDL = os.environ.get("EASY_GPT_PDL", "1") != "0"
+# Programmatic dependent launch between the decode kernels.  2: a kernel lets the next one start when it has
+# passed its own wait (the next one then streams its first weights while this one works); 1: at its very start, so
+# that several kernels' CTAs sit waiting on the SMs (measured 5% slower per decode step); 0: no overlap.
+USE_PDL = int(os.environ.get("EASY_GPT_PDL", "2"))
 
 
 def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
@@ -536,23 +540,44 @@ def _scratch_for(device, floats: int, row_groups: int):
     return have
 
 
-def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int, *,
+def skinny_padded_tokens(tokens: int) -> int:
+    """The token tile of ``gemm_skinny`` for this many tokens (8, 16, 32 or 64)."""
+    return 8 if tokens <= 8 else 16 if tokens <= 16 else 32 if tokens <= 32 else 64
+
+
+def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor], epilogue: int, *,
                 x: Optional[torch.Tensor] = None, resid_in: Optional[torch.Tensor] = None,
                 resid_out: Optional[torch.Tensor] = None, delta: Optional[torch.Tensor] = None,
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, tokens: Optional[int] = None,
-                plan=None, rope: Optional[dict] = None, prefetch: Optional[torch.Tensor] = None) -> None:
+                plan=None, rope: Optional[dict] = None, prefetch: Optional[torch.Tensor] = None,
+                status: Optional[torch.Tensor] = None, prenormed: Optional[tuple] = None,
+                follow: Optional[dict] = None):
     """Decode-step product out = f(x W^T + bias) for up to 64 tokens, bfloat16 weights
-    streamed once.  Either ``x`` (bfloat16 [M, K]) or the norm prologue (``resid_in``,
-    optional ``delta`` and ``resid_out``, ``gain``, ``eps``) gives the input.  Epilogues:
+    streamed once.  The input is ``x`` (bfloat16 [M, K]), or the norm prologue (``resid_in``,
+    optional ``delta`` and ``resid_out``, ``gain``, ``eps``), or ``prenormed`` = (xn, ss_parts)
+    with ``eps``: what an EPI_RESID_NORM product in front has left.  Epilogues:
     EPI_STORE (bfloat16), EPI_F32, EPI_SWIGLU (interleaved gate/up rows), EPI_QKV_ROPE
     (``rope``: num_heads, num_kv_heads, head_dim, positions, slot_map, k_cache, v_cache,
-    inv_freq, status).  ``plan``: (row_blocks, k_slices, k_split), by default ``skinny_plan``.
-    ``prefetch``: a contiguous tensor (weights of a kernel that runs soon) that this kernel
-    asks the L2 to fetch while it works."""
-    _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain, prefetch)
+    inv_freq, status), EPI_RESID_NORM (``follow``: residual float32 [M, N], updated in place,
+    and gain float32 [N] of the norm that follows; ``out`` is None and the call returns
+    (xn, ss_parts) for the next product's ``prenormed``).  ``plan``: (row_blocks, k_slices,
+    k_split), by default ``skinny_plan``.  ``prefetch``: a contiguous tensor (weights of a
+    kernel that runs soon) that this kernel asks the L2 to fetch while it works.  ``status``:
+    the step's status word, where the bounded wait for the prologue's staged input reports
+    if it gives up."""
+    _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain, prefetch, status)
     N, K = weight.shape
-    norm = x is None
-    if norm:
+    ss_in, ss_parts = None, 0
+    if prenormed is not None:
+        xn, ss_in = prenormed
+        _cuda(xn, ss_in)
+        M = tokens if tokens is not None else xn.shape[0]
+        _need(xn.dtype == torch.bfloat16 and xn.is_contiguous() and xn.shape[-1] == K, "prenormed rows: bfloat16 [M, K]")
+        _need(ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.dim() == 2
+              and ss_in.shape[1] == skinny_padded_tokens(M), "partial sums: float32 [parts, padded tokens]")
+        norm_mode, delta, ss_parts = 2, xn, ss_in.shape[0]
+    elif x is None:
+        norm_mode = 1
         _need(resid_in is not None and gain is not None and resid_in.dtype == gain.dtype == torch.float32
               and resid_in.is_contiguous() and resid_in.shape[-1] == K, "norm prologue: float32 residual [M, K] and gain")
         _need(delta is None or (delta.dtype == torch.bfloat16 and delta.is_contiguous() and delta.shape[-1] == K), "delta bfloat16 [M, K]")
@@ -560,6 +585,7 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
                                     and resid_out.data_ptr() != resid_in.data_ptr()), "resid_out: another float32 buffer")
         M = tokens if tokens is not None else resid_in.shape[0]
     else:
+        norm_mode = 0
         _need(x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == K and x.stride(1) == 1
               and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "x: bfloat16 [M, K], 16-byte aligned rows")
         M = x.shape[0]
@@ -568,6 +594,8 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
     _need(0 < M <= SKINNY_KERNEL_TOKENS and K % 16 == 0, f"gemm_skinny takes 1..{SKINNY_KERNEL_TOKENS} tokens and K % 16 == 0")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
     r = rope or {}
+    result = None
+    follow_args = (None, None, None, None)
     if epilogue == EPI_QKV_ROPE:
         kc, vc = r["k_cache"], r["v_cache"]
         _need(out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape[1] == r["num_heads"] * r["head_dim"], "q out")
@@ -578,23 +606,35 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.T
                  _ptr(vc), _ptr(r["inv_freq"]), kc.shape[2], kc.stride(0), kc.stride(1), kc.shape[0] * kc.shape[2],
                  _ptr(r["status"]))
     else:
-        want = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
-        cols = N // 2 if epilogue == EPI_SWIGLU else N
-        _need(out.dtype == want and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == cols, "out shape")
         rb, ks, split = plan or skinny_plan(N, K)
-        extra = (0, 0, 0, None, None, None, None, None, 0, 0, 0, 0, None)
+        if epilogue == EPI_RESID_NORM:
+            residual, gain_out = follow["residual"], follow["gain"]
+            _cuda(residual, gain_out)
+            _need(residual.dtype == gain_out.dtype == torch.float32 and residual.is_contiguous() and residual.dim() == 2
+                  and residual.shape[0] >= M and residual.shape[1] == N and gain_out.numel() == N,
+                  "follow: float32 residual [M, N] and gain [N]")
+            xn_out = torch.empty((M, N), device=weight.device, dtype=torch.bfloat16)
+            ss_out = torch.empty((-(-N // (rb * 16)), skinny_padded_tokens(M)), device=weight.device, dtype=torch.float32)
+            follow_args = (_ptr(residual), _ptr(gain_out), _ptr(xn_out), _ptr(ss_out))
+            result = (xn_out, ss_out)
+        else:
+            want = torch.float32 if epilogue == EPI_F32 else torch.bfloat16
+            cols = N // 2 if epilogue == EPI_SWIGLU else N
+            _need(out.dtype == want and out.dim() == 2 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == cols, "out shape")
+        extra = (0, 0, 0, None, None, None, None, None, 0, 0, 0, 0, _ptr(status))
     scratch = counters = None
     if split > 1:
         groups = -(-N // (rb * 16))
-        padded = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
-        scratch, counters = _scratch_for(weight.device, split * groups * rb * 16 * padded, groups)
+        scratch, counters = _scratch_for(weight.device, split * groups * rb * 16 * skinny_padded_tokens(M), groups)
     _check(library().eg_gemm_skinny(
-        _stream(), epilogue, int(norm), int(USE_PDL), _ptr(weight), weight.stride(0), _ptr(bias), M, N, K,
-        _ptr(x), 0 if norm else x.stride(0), _ptr(resid_in), _ptr(resid_out), _ptr(delta), _ptr(gain), float(eps),
-        _ptr(out), out.stride(0), rb, ks, split, _ptr(scratch), _ptr(counters), *extra,
+        _stream(), epilogue, norm_mode, USE_PDL, _ptr(weight), weight.stride(0), _ptr(bias), M, N, K,
+        _ptr(x), 0 if norm_mode else x.stride(0), _ptr(resid_in), _ptr(resid_out), _ptr(delta), _ptr(gain), float(eps),
+        _ptr(out), out.stride(0) if out is not None else 0, rb, ks, split, _ptr(scratch), _ptr(counters), *extra,
         _ptr(prefetch) if PREFETCH_WEIGHTS else None,
         prefetch.numel() * prefetch.element_size() if (prefetch is not None and PREFETCH_WEIGHTS) else 0,
-        Timeline.slot(f"skinny e={epilogue} n={int(norm)} {N}x{K} plan={rb},{ks},{split}")), "gemm_skinny")
+        Timeline.slot(f"skinny e={epilogue} n={norm_mode} {N}x{K} plan={rb},{ks},{split}"),
+        _ptr(ss_in), ss_parts, *follow_args), "gemm_skinny")
+    return result
 
 
 # The package's own tcgen05/TMA product reaches 0.85 PFLOP/s on the widest prefill product against the library's

@@ -80,9 +80,11 @@ class Attention(Mixer):
 
     # -- forward ----------------------------------------------------------
     accepts_pending_norm = True
+    fuses_following_norm = True
 
-    def forward(self, x, ctx: StepContext, cache: CacheView) -> torch.Tensor:
-        """x: the normalised input [T, hidden], or a PendingNorm that stands for it."""
+    def forward(self, x, ctx: StepContext, cache: CacheView, follow=None):
+        """x: the normalised input [T, hidden], or a PendingNorm that stands for it.  ``follow``: the add
+        and norm that come next; the output product of a decode step takes them over."""
         T = ctx.num_tokens
         tables = ctx.groups[cache.group]
         rot = self.position
@@ -144,6 +146,8 @@ class Attention(Mixer):
             kernels.attention_generic(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                       self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
                                       ctx.status)
+        if follow is not None and self.out.takes_following_norm(attn):
+            return self.out.with_following_norm(attn, follow, prefetch=self._hint(1), status=ctx.status)
         return self.out(attn, prefetch=self._hint(1), status=ctx.status)
 
 

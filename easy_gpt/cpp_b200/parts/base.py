@@ -152,6 +152,34 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class FollowingNorm:
+    """The add and the norm that come right after a part: ``residual`` (float32 [T, hidden]) gets the
+    part's output added, and ``norm`` (a plain RMSNorm: ``gain``, ``eps``) normalises the sum for the
+    part that runs next.  A block offers this to a part that sets ``fuses_following_norm``; such a part
+    may let its last kernel do both (it then updates ``residual`` in place and returns a ``PreNormed``
+    instead of its delta) or ignore the offer and return the delta as ever."""
+
+    def __init__(self, norm: "Norm", pending: "PendingNorm"):
+        self.norm = norm
+        self.gain, self.eps = norm.rms_parameters()
+        self._pending = pending
+
+    @property
+    def residual(self) -> torch.Tensor:
+        """The buffer that holds the residual stream once the part's own input norm has run."""
+        assert self._pending.consumed
+        return self._pending.residual_after
+
+
+class PreNormed:
+    """Returned by a part in place of its delta when it took a ``FollowingNorm`` over: the residual
+    already holds the sum v; ``rows`` is bfloat16(gain * v) [T, hidden] and ``ss_parts`` float32
+    [parts, padded T] the partial sums of v^2 per token, to be added up in their order."""
+
+    def __init__(self, norm: "Norm", rows: torch.Tensor, ss_parts: torch.Tensor):
+        self.norm, self.rows, self.ss_parts = norm, rows, ss_parts
+
+
 class PendingNorm:
     """x = norm(residual + delta), not computed yet.
 
@@ -170,9 +198,14 @@ class PendingNorm:
         self.spare_after = spare
         self.consumed = False
         rms = norm.rms_parameters()
+        # the part in front has already added its output to the residual and prepared the rows for this norm
+        self.prenormed = delta if isinstance(delta, PreNormed) else None
+        if self.prenormed is not None:
+            assert self.prenormed.norm is norm, "a PreNormed belongs to the norm it was prepared for"
+            self.delta = None
         self.fusable = (rms is not None and rows is None and work.dtype == torch.bfloat16
                         and 0 < residual.shape[0] <= max_fused_rows
-                        and (delta is None or delta.dtype == torch.bfloat16))
+                        and (self.delta is None or self.delta.dtype == torch.bfloat16))
         self._rms = rms
 
     def materialize(self) -> torch.Tensor:
@@ -185,6 +218,8 @@ class PendingNorm:
         assert not self.consumed and self.fusable
         self.consumed = True
         gain, eps = self._rms
+        if self.prenormed is not None:
+            return dict(prenormed=(self.prenormed.rows, self.prenormed.ss_parts), eps=eps)
         if self.delta is not None:
             self.residual_after, self.spare_after = self.spare, self.residual
         return dict(resid_in=self.residual, resid_out=self.spare if self.delta is not None else None,
@@ -193,6 +228,7 @@ class PendingNorm:
 
 class Mixer(Part):
     accepts_pending_norm = False       # True: forward() takes a PendingNorm instead of a tensor
+    fuses_following_norm = False       # True: forward() takes follow=FollowingNorm and may return a PreNormed
 
     def __init__(self, params: Mapping, prefix: str, position: Optional[PositionEncoding] = None):
         super().__init__(params, prefix)
@@ -209,6 +245,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_pending_norm = False
+    fuses_following_norm = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

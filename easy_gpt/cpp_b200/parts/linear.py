@@ -39,6 +39,20 @@ class Linear:
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    def takes_following_norm(self, x: torch.Tensor) -> bool:
+        """Whether ``with_following_norm`` can run for this input (the decode kernel takes it)."""
+        return (self.dtype == torch.bfloat16 and kernels.gemm_skinny_takes(self.dtype, x.shape[0], self.in_features)
+                and x.shape[0] <= kernels.FUSED_NORM_MAX_TOKENS and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+    def with_following_norm(self, x: torch.Tensor, follow, prefetch: Optional[torch.Tensor] = None,
+                            status: Optional[torch.Tensor] = None):
+        """The product, the add to the residual and the preparation of the norm that follows, in one
+        kernel: follow.residual += x W^T + b (in place); returns a PreNormed for follow.norm."""
+        from .base import PreNormed
+        rows, ss_parts = kernels.gemm_skinny(self.weight, self.bias_f32, None, kernels.EPI_RESID_NORM, x=x, prefetch=prefetch,
+                                             status=status, follow=dict(residual=follow.residual, gain=follow.gain))
+        return PreNormed(follow.norm, rows, ss_parts)
+
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  prefetch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``status``: the step's status word; with it the tcgen05 product for 17..128 rows may run

@@ -51,15 +51,17 @@ class SwiGLU(FeedForward):
         return [self.gate_up.weight, self.down.weight]
 
     accepts_pending_norm = True
+    fuses_following_norm = True
 
-    def forward(self, x, ctx):
-        """x: the normalised input [T, hidden], or a PendingNorm that stands for it."""
+    def forward(self, x, ctx, follow=None):
+        """x: the normalised input [T, hidden], or a PendingNorm that stands for it.  ``follow``: the add
+        and norm that come next; the down product of a decode step takes them over."""
         T = ctx.num_tokens
         act = torch.empty((T, self.inter), device=ctx.device, dtype=ctx.dtype)
         if isinstance(x, PendingNorm) and x.fusable:
             # decode: add + norm + gate/up product + SwiGLU in one kernel
             kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, tokens=T,
-                                prefetch=self._hint(0), **x.fused_args())
+                                prefetch=self._hint(0), status=ctx.status, **x.fused_args())
         else:
             if isinstance(x, PendingNorm):
                 x = x.materialize()
@@ -75,6 +77,8 @@ class SwiGLU(FeedForward):
                                      pair=kernels.USE_TCGEN05_PAIR)
             else:
                 kernels.swiglu(self.gate_up(x), act)
+        if follow is not None and self.down.takes_following_norm(act):
+            return self.down.with_following_norm(act, follow, prefetch=self._hint(1), status=ctx.status)
         return self.down(act, prefetch=self._hint(1), status=ctx.status)
 
 

@@ -412,6 +412,44 @@ def test_gemm_skinny_norm_prologue_and_swiglu(M):
     assert float((out2.float() - out.float()).abs().max()) <= 1e-2 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("M, H, I, plan", [(1, 896, 4864, None), (8, 896, 4864, None), (5, 208, 304, (1, 4, 1)),
+                                          (13, 80, 176, (2, 2, 3)), (16, 1536, 2048, None)])
+def test_gemm_skinny_residual_norm_epilogue_feeds_prenormed_prologue(M, H, I, plan):
+    """A product that adds its result to the residual and prepares the next norm (down or O product), and a
+    second product that starts from those rows and partial sums (gate/up): against add, RMSNorm and the
+    products one by one."""
+    from easy_gpt.cpp_b200 import kernels
+
+    act = bf(torch.randn(M, I, generator=gen(61)))
+    w_down = bf(torch.randn(H, I, generator=gen(62)) * 0.05)
+    bias = torch.randn(H, generator=gen(63)) * 0.1
+    resid = torch.randn(M, H, generator=gen(64)) * 2
+    gain = 1 + 0.1 * torch.randn(H, generator=gen(65))
+    gate, up = torch.randn(72, H, generator=gen(66)) * 0.05, torch.randn(72, H, generator=gen(67)) * 0.05
+    w_next = bf(torch.stack([gate, up], dim=1).reshape(144, H))
+    eps = 1e-5
+    delta = bf(act.float() @ w_down.float().t() + bias).float()
+    summed = resid + delta
+    xn = bf(plain_model.rms_norm(summed, gain, eps)).float()
+    g, u = xn @ bf(gate).float().t(), xn @ bf(up).float().t()
+    want = u * (g / (1 + torch.exp(-g)))
+
+    r = resid.to(DEV)
+    rows, ss_parts = kernels.gemm_skinny(w_down.to(DEV), bias.to(DEV), None, kernels.EPI_RESID_NORM, x=act.to(DEV), plan=plan,
+                                         follow=dict(residual=r, gain=gain.to(DEV)))
+    # the sum differs from the reference's by the rounding of the product only (the delta is rounded to bfloat16)
+    assert float((r.cpu() - summed).abs().max()) <= 2 ** -7 * float(delta.abs().max()) + 1e-6
+    assert ss_parts.shape[1] == kernels.skinny_padded_tokens(M)
+    v = r.cpu()
+    assert torch.allclose(ss_parts.sum(0).cpu()[:M], (v * v).sum(1), rtol=1e-5)
+    assert torch.equal(rows.cpu(), bf(gain * v))
+    out = torch.empty(M, 72, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.gemm_skinny(w_next.to(DEV), None, out, kernels.EPI_SWIGLU, prenormed=(rows, ss_parts), eps=eps, status=status)
+    assert int(status.item()) == 0
+    assert float((out.float().cpu() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("NH, NKV, HD", [(14, 2, 64), (6, 2, 32), (3, 1, 128), (4, 4, 16)])
 def test_gemm_skinny_qkv_rope_cache(NH, NKV, HD):
     """The fused kernel against the unfused chain: norm, product, rope_cache."""
