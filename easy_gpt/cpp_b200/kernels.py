@@ -486,12 +486,13 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
 
 
 SKINNY_KERNEL_TOKENS = 64      # what the kernel takes
-SKINNY_MAX_TOKENS = 16         # up to where it beats the library product (the policy of ``gemm_skinny_takes``)
+# up to where it beats the library product (the policy of ``gemm_skinny_takes``); EASY_GPT_SKINNY_MAX_TOKENS moves it
+SKINNY_MAX_TOKENS = int(os.environ.get("EASY_GPT_SKINNY_MAX_TOKENS", "16"))
 PREFETCH_WEIGHTS = os.environ.get("EASY_GPT_PREFETCH", "0") != "0"
-FUSED_NORM_MAX_TOKENS = 16     # every CTA repeats the norm prologue: worth it only for a few tokens
+# every CTA repeats the norm prologue: worth it only for a few tokens (EASY_GPT_FUSED_NORM_MAX_TOKENS moves it)
+FUSED_NORM_MAX_TOKENS = int(os.environ.get("EASY_GPT_FUSED_NORM_MAX_TOKENS", "16"))
 EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE, EPI_RESID_NORM = 0, 1, 2, 3, 4
-# programmatic dependent launch between the decode kernels (EASY_GPT_PDL=0 switches it off)
-# Programmatic dependent launch between the decode kernels.  2: a kernel lets the next one start when it has
+# Programmatic dependent launch between the decode kernels (EASY_GPT_PDL).  2: a kernel lets the next one start when it has
 # passed its own wait (the next one then streams its first weights while this one works); 1: at its very start, so
 # that several kernels' CTAs sit waiting on the SMs (measured 5% slower per decode step); 0: no overlap.
 USE_PDL = int(os.environ.get("EASY_GPT_PDL", "2"))
