@@ -45,6 +45,15 @@ CONFIG_05B = {
     "tie_word_embeddings": True, "max_position_embeddings": 32768, "bos_token_id": -1, "eos_token_id": -1,
     "use_sliding_window": False,
 }
+# Layer sizes of the larger models of the family, for `--only` runs at further sizes (the default
+# run and its JSON line are always the 0.5B sizes above).
+SIZES = {
+    "0.5b": {},
+    "1.5b": {"num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2,
+             "intermediate_size": 8960},
+    "7b": {"num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+           "intermediate_size": 18944, "vocab_size": 152064, "tie_word_embeddings": False},
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -369,7 +378,10 @@ def run_ours(args):
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device; this engine has no CPU path"}))
         return 1
-    config = dict(CONFIG_05B)
+    config = dict(CONFIG_05B, **SIZES[args.sizes])
+    if args.sizes != "0.5b" and not args.only:
+        print("bench.py: --sizes other than 0.5b goes with --only (the JSON line is defined for the 0.5B sizes)")
+        return 2
     layers_full = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
@@ -377,7 +389,7 @@ def run_ours(args):
     folder = model_folder(config)
     if args.only == "decode":
         r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": config["num_hidden_layers"], "context": CONTEXT,
+        print(json.dumps({"only": "decode", "sizes": args.sizes, "batch": args.batch, "layers": config["num_hidden_layers"], "context": CONTEXT,
                           "tok_s": round(r["tok_s"], 1), "ms_per_step": round(1e3 * r["seconds"] / args.steps, 4),
                           "gb_s": round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9, 1)}))
         return 0
@@ -387,7 +399,7 @@ def run_ours(args):
         return print_gemm_comparison(config)
     if args.only == "prefill":
         s = measure_prefill(folder, config)
-        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": config["num_hidden_layers"],
+        print(json.dumps({"only": "prefill", "sizes": args.sizes, "tokens": PREFILL_TOKENS, "layers": config["num_hidden_layers"],
                           "ms": round(s * 1e3, 3), "tflops": round(prefill_flops(config, PREFILL_TOKENS) / s / 1e12, 1)}))
         return 0
     main = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=True)
@@ -436,6 +448,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
+    ap.add_argument("--sizes", choices=list(SIZES), default="0.5b", help="layer sizes for --only runs")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()

@@ -51,7 +51,7 @@ class Block:
         """Returns (residual, spare, delta): the buffer that now holds the residual
         stream, the other one, and the feed-forward's output still to be added (or the
         PreNormed it left for ``next_norm``, the norm that runs after this block)."""
-        fused_rows = kernels.FUSED_NORM_MAX_TOKENS
+        fused_rows = kernels.fused_norm_max_tokens(residual.shape[1])
         pending = PendingNorm(self.mixer_norm, residual, delta, spare, work, max_fused_rows=fused_rows)
         delta = self.mixer.forward(pending if self.mixer.accepts_pending_norm else pending.materialize(), ctx, cache,
                                    **self._offer(self.mixer, self.ff_norm, pending, ctx, fused_rows))
@@ -167,5 +167,5 @@ class Model:
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         pending = PendingNorm(self.final_norm, residual, delta, spare, work, rows=None if all_rows else logit_rows,
-                              max_fused_rows=kernels.FUSED_NORM_MAX_TOKENS)
+                              max_fused_rows=kernels.fused_norm_max_tokens(H))
         return self.lm_head.forward(pending if self.lm_head.accepts_pending_norm else pending.materialize(), status=ctx.status)

@@ -498,6 +498,19 @@ EPI_STORE, EPI_F32, EPI_SWIGLU, EPI_QKV_ROPE, EPI_RESID_NORM = 0, 1, 2, 3, 4
 USE_PDL = int(os.environ.get("EASY_GPT_PDL", "2"))
 
 
+def fused_norm_max_tokens(width: int) -> int:
+    """Up to how many tokens a step's add + RMSNorm over rows of ``width`` can ride in the decode product's
+    prologue: the policy's limit, lowered where the rows of a token tile (8 or 16 tokens, bfloat16, padded),
+    the gain and the partial sums of squares of a product in front (one per 16 output rows at most) would not
+    fit the kernel's 200 KB of shared memory.  0: the norm runs as a kernel of its own."""
+    for tile in (16, 8):
+        row = -(-2 * width // 128) * 128 + 64
+        need = tile * row + tile * 4 + width * 4 + tile * 32 + -(-width // 16) * tile * 4
+        if need <= 200 * 1024:
+            return min(tile, FUSED_NORM_MAX_TOKENS)
+    return 0
+
+
 def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
     """(row_blocks, k_slices, k_split): how the warps of a CTA and the CTAs of the grid share a
     [n_rows, in_features] weight matrix.  Every warp should have about four 64-wide chunks of K to
