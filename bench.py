@@ -222,8 +222,12 @@ def measure_decode(folder, config, batch, steps, warmup, want_e2e):
 
     total_steps = warmup + steps + (warmup + steps if want_e2e else 0) + 4
     start_context = CONTEXT - (2 * (warmup + steps) + 4 if want_e2e else warmup + steps + 4)
-    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (CONTEXT + 64), max_active=batch,
-                       prefill_batch=batch, max_batch_tokens=4096, chunk_size=2048, max_tokens_per_request=CONTEXT + 64)
+    # the prompts are prefilled in large steps, so that the requests admitted first decode only a few tokens
+    # while the others' prompts are still on their way (those tokens get room of their own)
+    prefill_budget = 32768
+    room = CONTEXT + 64 + -(-batch * start_context // prefill_budget) + 1
+    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (room + 63), max_active=batch,
+                       prefill_batch=batch, max_batch_tokens=prefill_budget, chunk_size=4096, max_tokens_per_request=room)
     reqs = prepare_decode(engine, batch, start_context, total_steps + 64, config["vocab_size"], seed=batch)
     out = {}
     with ClockSampler() as clocks:
@@ -295,10 +299,13 @@ def print_timeline(folder, config, batch):
     from easy_gpt.cpp_b200.engine import GptEngine
 
     kernels.Timeline.start()
-    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (CONTEXT + 64), max_active=batch,
-                       prefill_batch=batch, max_batch_tokens=4096, chunk_size=2048, max_tokens_per_request=CONTEXT + 64)
+    start_context = CONTEXT - 40
+    prefill_budget = 32768
+    room = CONTEXT + 64 + -(-batch * start_context // prefill_budget) + 1
+    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (room + 63), max_active=batch,
+                       prefill_batch=batch, max_batch_tokens=prefill_budget, chunk_size=4096, max_tokens_per_request=room)
     kernels.Timeline.names = []
-    prepare_decode(engine, batch, CONTEXT - 40, 100, config["vocab_size"], seed=1)
+    prepare_decode(engine, batch, start_context, 100, config["vocab_size"], seed=1)
     for _ in range(5):
         engine.step()
     torch.cuda.synchronize()
