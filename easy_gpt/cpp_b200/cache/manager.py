@@ -20,17 +20,19 @@ and it hands attention a padded copy of all of them each step,
 src/models/cache_batching.cpp:25-81.  Slots are its ``free_slots_`` stack,
 src/continuous_batch_server.cpp:44-47.)
 
-All bookkeeping is host code and runs without a GPU (device=None allocates no
-tensors).
+All bookkeeping is host code (C++, ``csrc/host/cache_core.hpp``; this module is its
+face in Python and owns the device tensors) and runs without a GPU (device=None
+allocates no tensors).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+import ctypes
+from typing import Dict, Hashable, List, Mapping, Optional, Sequence
 
 import numpy as np
 import torch
 
+from .. import host
 from ..parts.base import CacheView, PagedKVNeed, StateNeed
 from .page_pool import OutOfPages, PagePool
 
@@ -39,25 +41,19 @@ class OutOfSlots(RuntimeError):
     pass
 
 
-@dataclass
-class _Request:
-    slot: int
-    length: int = 0                                        # tokens committed to the cache
-    reserved: int = 0                                      # tokens for which pages exist (>= length)
-    first_live_page: Dict[int, int] = field(default_factory=dict)   # per group: logical pages below were given back
-
-
 class CacheGroup:
-    def __init__(self, index: int, need: PagedKVNeed, cache_ids: List[int], page_size: int, num_pages: int,
-                 max_slots: int, max_pages_per_request: int):
+    """One group of caches with the same needs: its page pool and block tables live in the C++
+    bookkeeping; ``tables`` is a view of them ([slots, max pages per request], -1 where no page is held)."""
+
+    def __init__(self, index: int, need: PagedKVNeed, cache_ids: List[int], page_size: int, pool: PagePool,
+                 tables: np.ndarray, max_pages_per_request: int):
         self.index = index
         self.need = need
         self.cache_ids = cache_ids
         self.page_size = page_size
-        self.pool = PagePool(num_pages)
+        self.pool = pool
         self.max_pages_per_request = max_pages_per_request
-        # host block tables by slot; -1 where no page is held
-        self.tables = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
+        self.tables = tables
         self.kv: Optional[torch.Tensor] = None
         self.scratch_page = -1
 
@@ -82,11 +78,15 @@ class CacheManager:
         """needs: cache id -> PagedKVNeed | StateNeed | None.  num_pages: pages of every group's pool."""
         if page_size <= 0 or max_slots <= 0 or max_tokens_per_request <= 0:
             raise ValueError("page_size, max_slots and max_tokens_per_request must be positive")
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
         self.page_size = page_size
         self.max_slots = max_slots
         self.max_pages_per_request = -(-max_tokens_per_request // page_size)
         self.device = device
         self.dtype = dtype
+        self._lib = host.library()
+        self.core = self._lib.egh_cache_create(page_size, max_slots, self.max_pages_per_request)
         self.groups: List[CacheGroup] = []
         self.group_of_cache: Dict[int, int] = {}
         self.state: Dict[int, torch.Tensor] = {}
@@ -97,7 +97,11 @@ class CacheManager:
             if isinstance(need, PagedKVNeed):
                 g = by_need.get(need)
                 if g is None:
-                    g = CacheGroup(len(self.groups), need, [], page_size, num_pages, max_slots, self.max_pages_per_request)
+                    index = self._lib.egh_cache_add_group(self.core, num_pages, -1 if need.window is None else int(need.window))
+                    pool = PagePool(num_pages, _borrowed=(self._lib.egh_cache_group_pool(self.core, index), self))
+                    tables = np.ctypeslib.as_array(self._lib.egh_cache_group_table(self.core, index),
+                                                   shape=(max_slots, self.max_pages_per_request))
+                    g = CacheGroup(index, need, [], page_size, pool, tables, self.max_pages_per_request)
                     by_need[need] = g
                     self.groups.append(g)
                 g.cache_ids.append(cache_id)
@@ -106,8 +110,13 @@ class CacheManager:
                 self._state_needs[cache_id] = need
             elif need is not None:
                 raise TypeError(f"cache {cache_id}: unknown need {need!r}")
-        self._free_slots: List[int] = list(range(max_slots - 1, -1, -1))     # slot 0 first
-        self._requests: Dict[object, _Request] = {}
+        # requests are known to the bookkeeping by a 64-bit handle: a non-negative int is its own handle
+        # (the scheduler's request ids), anything else gets a negative one
+        self._handles: Dict[Hashable, int] = {}
+        self._named: Dict[int, Hashable] = {}
+        self._next_named = -1
+        self._needed = (ctypes.c_int * max(1, len(self.groups)))()
+        self._info = (ctypes.c_int * 3)()
         if device is not None:
             for g in self.groups:
                 # one page beyond the pool (id num_pages): rows that pad a captured batch write there
@@ -117,114 +126,124 @@ class CacheManager:
             for cache_id, need in self._state_needs.items():
                 self.state[cache_id] = torch.zeros((max_slots, *need.shape), device=device, dtype=torch.float32)
 
+    def __del__(self):
+        core = getattr(self, "core", None)
+        if core:
+            self.core = None
+            for g in self.groups:
+                g.tables = None            # the views die with the memory they look at
+            self._lib.egh_cache_destroy(core)
+
+    # -- handles -------------------------------------------------------------
+    def handle(self, rid, create: bool = False) -> Optional[int]:
+        """The bookkeeping's 64-bit name of a request (None: unknown and not to be created)."""
+        if isinstance(rid, (int, np.integer)) and not isinstance(rid, bool) and 0 <= int(rid) < (1 << 62):
+            return int(rid)
+        h = self._handles.get(rid)
+        if h is None and create:
+            h = self._next_named
+            self._next_named -= 1
+            self._handles[rid] = h
+            self._named[h] = rid
+        return h
+
+    def _live_handle(self, rid) -> int:
+        h = self.handle(rid)
+        if h is None or self._lib.egh_cache_query(self.core, h, 0) < 0:
+            raise KeyError(rid)
+        return h
+
+    def _forget(self, rid, h: int) -> None:
+        if h < 0:
+            self._handles.pop(rid, None)
+            self._named.pop(h, None)
+
     # -- requests -----------------------------------------------------------
     def has_request(self, rid) -> bool:
-        return rid in self._requests
+        h = self.handle(rid)
+        return h is not None and self._lib.egh_cache_query(self.core, h, 0) >= 0
 
     def live_requests(self) -> List[object]:
-        return list(self._requests)
+        buf = (ctypes.c_longlong * self.max_slots)()
+        n = self._lib.egh_cache_live(self.core, buf, self.max_slots)
+        return [self._named.get(h, h) for h in sorted(buf[:n], key=lambda h: (h < 0, abs(h)))]
 
     def free_slot_count(self) -> int:
-        return len(self._free_slots)
+        return int(self._lib.egh_cache_free_slots(self.core))
 
     def begin_request(self, rid) -> int:
-        if rid in self._requests:
+        known = self.handle(rid) is not None
+        h = self.handle(rid, create=True)
+        slot = self._lib.egh_cache_begin(self.core, h)
+        if slot == host.ALREADY_LIVE:
             raise KeyError(f"request {rid!r} is already live")
-        if not self._free_slots:
+        if slot == host.OUT_OF_SLOTS:
+            if not known:
+                self._forget(rid, h)
             raise OutOfSlots(f"all {self.max_slots} request slots are taken")
-        slot = self._free_slots.pop()
-        self._requests[rid] = _Request(slot, first_live_page={g.index: 0 for g in self.groups})
         for t in self.state.values():
             t[slot].zero_()
-        return slot
+        return int(slot)
 
     def slot_of(self, rid) -> int:
-        return self._requests[rid].slot
+        return int(self._lib.egh_cache_query(self.core, self._live_handle(rid), 0))
 
     def length_of(self, rid) -> int:
-        return self._requests[rid].length
+        return int(self._lib.egh_cache_query(self.core, self._live_handle(rid), 1))
 
     def pages_needed(self, rid, new_tokens: int) -> Dict[int, int]:
         """Pages each group would have to hand out so that ``new_tokens`` more tokens fit."""
-        r = self._requests[rid]
-        target = r.length + new_tokens
-        out = {}
-        for g in self.groups:
-            have = -(-r.reserved // g.page_size)
-            want = -(-target // g.page_size)
-            out[g.index] = max(0, want - have)
-        return out
+        self._lib.egh_cache_pages_needed(self.core, self._live_handle(rid), int(new_tokens), self._needed)
+        return {g.index: int(self._needed[g.index]) for g in self.groups}
 
     def can_reserve(self, rid, new_tokens: int, spare: int = 0) -> bool:
-        r = self._requests[rid]
-        if -(-(r.length + new_tokens) // self.page_size) > self.max_pages_per_request:
-            return False
-        return all(self.groups[gi].pool.free_count - spare >= n for gi, n in self.pages_needed(rid, new_tokens).items())
+        return self._lib.egh_cache_can_reserve(self.core, self._live_handle(rid), int(new_tokens), int(spare)) == 1
 
     def reserve(self, rid, new_tokens: int) -> None:
         """Pages for positions length .. length+new_tokens-1 in every group, or
         ``OutOfPages`` with nothing changed."""
-        r = self._requests[rid]
-        target = r.length + new_tokens
-        if -(-target // self.page_size) > self.max_pages_per_request:
-            raise OutOfPages(f"request {rid!r} would hold {target} tokens; a request may hold at most "
+        rc = self._lib.egh_cache_reserve(self.core, self._live_handle(rid), int(new_tokens), self._info)
+        if rc == host.TOO_LONG:
+            raise OutOfPages(f"request {rid!r} would hold {self.length_of(rid) + new_tokens} tokens; a request may hold at most "
                              f"{self.max_pages_per_request * self.page_size}")
-        needed = self.pages_needed(rid, new_tokens)
-        for gi, n in needed.items():
-            if self.groups[gi].pool.free_count < n:
-                raise OutOfPages(f"group {gi}: {n} pages wanted for request {rid!r}, "
-                                 f"{self.groups[gi].pool.free_count} free")
-        for gi, n in needed.items():
-            g = self.groups[gi]
-            have = -(-r.reserved // g.page_size)
-            pages = g.pool.alloc(n)
-            g.tables[r.slot, have:have + n] = pages
-        r.reserved = max(r.reserved, target)
+        if rc == host.OUT_OF_PAGES:
+            raise OutOfPages(f"group {self._info[0]}: {self._info[1]} pages wanted for request {rid!r}, {self._info[2]} free")
+        if rc != host.OK:
+            raise RuntimeError(f"cache bookkeeping: reserve failed with status {rc}")
 
     def commit(self, rid, new_tokens: int) -> None:
         """The step has written ``new_tokens`` more tokens.  Pages that no coming
         token can see any more (a window has passed them) are given back."""
-        r = self._requests[rid]
-        if r.length + new_tokens > r.reserved:
+        rc = self._lib.egh_cache_commit(self.core, self._live_handle(rid), int(new_tokens))
+        if rc == host.EXCEEDS_RESERVED:
             raise ValueError(f"request {rid!r}: commit of {new_tokens} tokens exceeds what was reserved")
-        r.length += new_tokens
-        for g in self.groups:
-            first = g.first_needed_page(r.length)
-            old = r.first_live_page[g.index]
-            if first > old:
-                row = g.tables[r.slot]
-                g.pool.free([int(p) for p in row[old:first]])
-                row[old:first] = -1
-                r.first_live_page[g.index] = first
+        if rc != host.OK:
+            raise RuntimeError(f"cache bookkeeping: commit failed with status {rc}")
 
     def end_request(self, rid) -> None:
-        r = self._requests.pop(rid)
-        for g in self.groups:
-            row = g.tables[r.slot]
-            held = row[row >= 0]
-            g.pool.free([int(p) for p in held])
-            row[:] = -1
-        self._free_slots.append(r.slot)
+        h = self._live_handle(rid)
+        rc = self._lib.egh_cache_end(self.core, h)
+        if rc != host.OK:
+            raise RuntimeError(f"cache bookkeeping: ending request {rid!r} failed with status {rc}")
+        self._forget(rid, h)
 
     def reset(self) -> None:
-        for rid in list(self._requests):
+        for rid in self.live_requests():
             self.end_request(rid)
 
     # -- what a step needs ---------------------------------------------------
     def slot_positions(self, group: int, rid, start: int, count: int) -> np.ndarray:
         """Physical cache positions (page * page_size + offset) of the request's
         logical positions start .. start+count-1."""
-        g = self.groups[group]
-        r = self._requests[rid]
-        pos = np.arange(start, start + count, dtype=np.int64)
-        pages = g.tables[r.slot, pos // g.page_size].astype(np.int64)
-        if (pages < 0).any():
+        out = np.empty(max(count, 1), dtype=np.int32)
+        rc = self._lib.egh_cache_slot_positions(self.core, group, self._live_handle(rid), int(start), int(count), out.ctypes.data)
+        if rc == host.NO_PAGE:
             raise ValueError(f"request {rid!r}: a position in {start}..{start + count - 1} has no page in group {group}")
-        return (pages * g.page_size + pos % g.page_size).astype(np.int32)
+        return out[:count]
 
     def table_rows(self, group: int, rids: Sequence, width: int) -> np.ndarray:
         g = self.groups[group]
-        slots = [self._requests[r].slot for r in rids]
+        slots = [self.slot_of(r) for r in rids]
         return g.tables[slots, :width]
 
     def view(self, cache_id: int, writes: bool = True) -> CacheView:
@@ -248,15 +267,7 @@ class CacheManager:
 
     def check(self) -> None:
         """No page lost, none held twice: the pages in all block tables are exactly
-        the pages the pools consider held."""
-        for g in self.groups:
-            g.pool.check()
-            held = g.tables[g.tables >= 0]
-            assert len(held) == len(set(held.tolist())), f"group {g.index}: a page is in two places of the block tables"
-            assert len(held) == g.pool.used_count, f"group {g.index}: {g.pool.used_count} pages held, {len(held)} in tables"
-            live_slots = {r.slot for r in self._requests.values()}
-            for s in range(self.max_slots):
-                if s not in live_slots:
-                    assert (g.tables[s] < 0).all(), f"group {g.index}: free slot {s} still holds pages"
-        assert len(set(self._free_slots)) == len(self._free_slots)
-        assert len(self._free_slots) + len(self._requests) == self.max_slots
+        the pages the pools consider held; free slots hold nothing."""
+        why = ctypes.create_string_buffer(256)
+        rc = self._lib.egh_cache_check(self.core, why, 256)
+        assert rc == host.OK, why.value.decode()

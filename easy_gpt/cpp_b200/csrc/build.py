@@ -111,5 +111,49 @@ def library_path(verbose: bool = True) -> Path:
     return out_dir / LIB_NAME
 
 
+HOST_LIB_NAME = "libeasygpt_host.so"
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
+
+def _host_fingerprint() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list((HERE / "host").glob("*.cpp")) + list((HERE / "host").glob("*.hpp"))):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()
+
+
+def host_library_path(verbose: bool = True) -> Path:
+    """Path of an up-to-date library of the host runtime (``host/*.cpp``: page pools, cache
+    bookkeeping, step packing, scheduler), built by the C++ compiler; no CUDA is involved."""
+    fp = _host_fingerprint()
+    in_tree = (HERE / HOST_LIB_NAME, HERE / "_build" / "host_stamp.json")
+    if _current(*in_tree, fp):
+        return in_tree[0]
+    if _writable(HERE / "_build") and _writable(HERE):
+        out_dir, build_dir = HERE, HERE / "_build"
+    else:
+        base = Path(tempfile.gettempdir()) / f"easy_gpt_b200_build_{os.getuid()}"
+        out_dir, build_dir = base, base / "_build"
+        build_dir.mkdir(parents=True, exist_ok=True)
+        if _current(out_dir / HOST_LIB_NAME, build_dir / "host_stamp.json", fp):
+            return out_dir / HOST_LIB_NAME
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise BuildError("no C++ compiler was found (set CXX or put g++ on PATH); the host runtime cannot be built")
+    if verbose:
+        print(f"[easy_gpt.cpp_b200] building the host runtime into {out_dir} (first call only)", file=sys.stderr, flush=True)
+    tmp_lib = out_dir / (HOST_LIB_NAME + f".{os.getpid()}.tmp")
+    sources = [str(p) for p in sorted((HERE / "host").glob("*.cpp"))]
+    r = subprocess.run([cxx, *HOST_FLAGS, "-I", str(HERE / "host"), *sources, "-o", str(tmp_lib)], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"building {HOST_LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp_lib, out_dir / HOST_LIB_NAME)
+    (build_dir / "host_stamp.json").write_text(json.dumps({"fingerprint": fp}))
+    return out_dir / HOST_LIB_NAME
+
+
 if __name__ == "__main__":
     print(library_path())
+    print(host_library_path())

@@ -1,0 +1,110 @@
+// C interface of the host runtime (page pools, cache bookkeeping, step packing, scheduler) for the
+// Python bindings.  Handles are opaque pointers; functions return 0 or a positive result, or a
+// negative Status.  Nothing here touches a GPU.
+#include <cstring>
+
+#include "cache_core.hpp"
+#include "step_pack.hpp"
+
+using namespace easygpt::host;
+
+#define EGH_API extern "C" __attribute__((visibility("default")))
+
+// -- page pool ----------------------------------------------------------------------------------
+EGH_API void* egh_pool_create(int num_pages) { return num_pages > 0 ? new PagePool(num_pages) : nullptr; }
+EGH_API void egh_pool_destroy(void* p) { delete static_cast<PagePool*>(p); }
+EGH_API int egh_pool_alloc(void* p, int n, int32_t* out) { return static_cast<PagePool*>(p)->alloc(n, out); }
+EGH_API int egh_pool_free(void* p, const int32_t* pages, int n, int* bad) { return static_cast<PagePool*>(p)->free(pages, n, bad); }
+EGH_API int egh_pool_check(void* p) { return static_cast<PagePool*>(p)->check(); }
+// what: 0 pages, 1 free, 2 high-water mark, 3 pages handed out over the pool's life
+EGH_API long long egh_pool_stat(void* p, int what) {
+    const PagePool* pool = static_cast<PagePool*>(p);
+    switch (what) {
+        case 0: return pool->num_pages();
+        case 1: return pool->free_count();
+        case 2: return pool->high_water();
+        case 3: return pool->total_allocated();
+    }
+    return BAD_ARGUMENT;
+}
+
+// -- cache bookkeeping ----------------------------------------------------------------------------
+EGH_API void* egh_cache_create(int page_size, int max_slots, int max_pages_per_request) {
+    if (page_size <= 0 || max_slots <= 0 || max_pages_per_request <= 0) return nullptr;
+    return new CacheCore(page_size, max_slots, max_pages_per_request);
+}
+EGH_API void egh_cache_destroy(void* c) { delete static_cast<CacheCore*>(c); }
+EGH_API int egh_cache_add_group(void* c, int num_pages, int window) {
+    return num_pages > 0 ? static_cast<CacheCore*>(c)->add_group(num_pages, window) : BAD_ARGUMENT;
+}
+// borrowed: lives as long as the cache
+EGH_API void* egh_cache_group_pool(void* c, int g) { return &static_cast<CacheCore*>(c)->group(g).pool; }
+EGH_API int32_t* egh_cache_group_table(void* c, int g) { return static_cast<CacheCore*>(c)->group(g).tables.data(); }
+EGH_API int egh_cache_begin(void* c, long long rid) { return static_cast<CacheCore*>(c)->begin_request(rid); }
+EGH_API int egh_cache_end(void* c, long long rid) { return static_cast<CacheCore*>(c)->end_request(rid); }
+// what: 0 slot, 1 tokens committed, 2 tokens reserved
+EGH_API long long egh_cache_query(void* c, long long rid, int what) {
+    const CachedRequest* r = static_cast<CacheCore*>(c)->find(rid);
+    if (!r) return UNKNOWN_REQUEST;
+    return what == 0 ? r->slot : what == 1 ? r->length : r->reserved;
+}
+EGH_API int egh_cache_pages_needed(void* c, long long rid, long long new_tokens, int* out) {
+    return static_cast<CacheCore*>(c)->pages_needed(rid, new_tokens, out);
+}
+EGH_API int egh_cache_can_reserve(void* c, long long rid, long long new_tokens, int spare) {
+    return static_cast<CacheCore*>(c)->can_reserve(rid, new_tokens, spare);
+}
+EGH_API int egh_cache_reserve(void* c, long long rid, long long new_tokens, int* info) {
+    return static_cast<CacheCore*>(c)->reserve(rid, new_tokens, info);
+}
+EGH_API int egh_cache_commit(void* c, long long rid, long long new_tokens) { return static_cast<CacheCore*>(c)->commit(rid, new_tokens); }
+EGH_API int egh_cache_free_slots(void* c) { return static_cast<CacheCore*>(c)->free_slot_count(); }
+EGH_API int egh_cache_slot_positions(void* c, int g, long long rid, long long start, int count, int32_t* out) {
+    return static_cast<CacheCore*>(c)->slot_positions(g, rid, start, count, out);
+}
+// ids of the live requests into out (at most cap); returns how many are live
+EGH_API int egh_cache_live(void* c, long long* out, int cap) {
+    int n = 0;
+    static_cast<CacheCore*>(c)->for_each_request([&](int64_t rid, const CachedRequest&) {
+        if (n < cap) out[n] = rid;
+        ++n;
+    });
+    return n;
+}
+EGH_API int egh_cache_check(void* c, char* why, int cap) {
+    std::string msg;
+    const int rc = static_cast<CacheCore*>(c)->check(&msg);
+    if (why && cap > 0) {
+        std::strncpy(why, msg.c_str(), cap - 1);
+        why[cap - 1] = 0;
+    }
+    return rc;
+}
+
+// -- a step's pages and packed metadata ---------------------------------------------------------------
+EGH_API int egh_step_reserve(void* c, int n, const long long* rids, const long long* counts, int* info) {
+    return reserve_step(*static_cast<CacheCore*>(c), n, (const int64_t*)rids, (const int64_t*)counts, info);
+}
+EGH_API long long egh_step_bound(void* c, int n, long long tokens, long long wanted, int query_tile) {
+    return packed_step_bound(*static_cast<CacheCore*>(c), n, tokens, wanted, query_tile);
+}
+// scalars (8 long longs): ints used, tokens, wanted rows, longest entry, longest context, all entries
+// bring one token, query tiles, tokens outside tiles
+EGH_API int egh_step_pack(void* c, int n, const long long* rids, const long long* counts, const long long* token_ids,
+                          const long long* want_offsets, const long long* wants, int query_tile, int small_entry_tokens,
+                          int32_t* buf, long long cap, long long* layout, int* widths, long long* scalars) {
+    PackedStep out;
+    const int rc = pack_step(*static_cast<CacheCore*>(c), n, (const int64_t*)rids, (const int64_t*)counts, (const int64_t*)token_ids,
+                             (const int64_t*)want_offsets, (const int64_t*)wants, query_tile, small_entry_tokens, buf, cap,
+                             layout, widths, &out);
+    if (rc != OK) return rc;
+    scalars[0] = out.total; scalars[1] = out.tokens; scalars[2] = out.rows; scalars[3] = out.max_query_len;
+    scalars[4] = out.max_context_len; scalars[5] = out.all_decode; scalars[6] = out.num_tiles; scalars[7] = out.num_small;
+    return OK;
+}
+EGH_API int egh_replay_pack(void* c, int n, const long long* rids, const int32_t* counts, int32_t* buf, long long off_positions,
+                            long long off_context, long long off_slots, const long long* off_slot_map, const long long* off_table,
+                            int table_width) {
+    return pack_replay(*static_cast<CacheCore*>(c), n, (const int64_t*)rids, counts, buf, off_positions, off_context, off_slots,
+                       off_slot_map, off_table, table_width);
+}
