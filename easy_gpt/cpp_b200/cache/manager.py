@@ -181,9 +181,13 @@ class CacheManager:
             if not known:
                 self._forget(rid, h)
             raise OutOfSlots(f"all {self.max_slots} request slots are taken")
+        self.zero_state(slot)
+        return int(slot)
+
+    def zero_state(self, slot: int) -> None:
+        """A request that takes a slot starts from zeroed per-request state."""
         for t in self.state.values():
             t[slot].zero_()
-        return int(slot)
 
     def slot_of(self, rid) -> int:
         return int(self._lib.egh_cache_query(self.core, self._live_handle(rid), 0))

@@ -22,7 +22,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 import torch
 
-from .. import kernels
+from .. import host, kernels
 from ..parts.base import GroupTables, StepContext
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -66,7 +66,9 @@ class DecodeGraph:
         starts = np.zeros(n + 1, dtype=np.int32)
         starts[1:] = np.cumsum(self.counts)
         self.starts = starts
-        self.offsets_in_entry = (np.arange(T, dtype=np.int32) - np.repeat(starts[:-1], self.counts)).astype(np.int32)
+        self._counts32 = np.asarray(self.counts, dtype=np.int32)
+        self._off_slot_map = np.asarray([self.offsets[f"slot_map{g.index}"][0] for g in cache.groups] or [0], dtype=np.int64)
+        self._off_table = np.asarray([self.offsets[f"table{g.index}"][0] for g in cache.groups] or [0], dtype=np.int64)
         token_seq = np.repeat(np.arange(n, dtype=np.int32), self.counts)
         rows = [int(starts[i]) + int(w) for i, ws in enumerate(wants) for w in ws]
         tiles, small = kernels.query_tiles_of(starts, self.counts)
@@ -150,33 +152,19 @@ class DecodeGraph:
         if self.staging_events[i] is not None:
             self.staging_events[i].synchronize()
         hv = self.staging[i].numpy()
-        lengths = np.fromiter((cache.length_of(r) for r in requests), dtype=np.int32, count=n)
-        slots = np.fromiter((cache.slot_of(r) for r in requests), dtype=np.int32, count=n)
-        T = int(self.starts[n])
-
-        def put(name, arr):
-            o, _ = self.offsets[name]
-            hv[o:o + len(arr)] = arr
-
         if not tokens_on_device:
-            put("token_ids", np.asarray(tokens, dtype=np.int32))
+            o, _ = self.offsets["token_ids"]
+            hv[o:o + int(self.starts[n])] = np.asarray(tokens, dtype=np.int32)
         # (with tokens_on_device the ids were put there by set_tokens_from_device; the rows that pad the
         # bucket keep whatever id they had: any valid id will do for them)
-        counts = self.counts[:n]
-        positions = np.repeat(lengths, counts) + self.offsets_in_entry[:T]
-        put("positions", positions)
-        put("seq_context", lengths)
-        put("seq_slots", slots)
-        token_entry = np.repeat(np.arange(n), counts)
-        for g in cache.groups:
-            W = self.widths[g.index]
-            rows = g.tables[slots]                                           # [n, W]
-            pages = rows[token_entry, positions // g.page_size].astype(np.int64)
-            if (pages < 0).any():
-                raise RuntimeError("a token of a captured step has no cache page")
-            put(f"slot_map{g.index}", (pages * g.page_size + positions % g.page_size).astype(np.int32))
-            o, _ = self.offsets[f"table{g.index}"]
-            hv[o:o + n * W] = rows.reshape(-1)
+        # positions, cached lengths, slots, cache positions and block-table rows: packed by the host runtime
+        handles = np.fromiter((cache.handle(r) for r in requests), dtype=np.int64, count=n)
+        rc = cache._lib.egh_replay_pack(cache.core, n, handles.ctypes.data, self._counts32.ctypes.data, self.staging[i].data_ptr(),
+                                        self.offsets["positions"][0], self.offsets["seq_context"][0], self.offsets["seq_slots"][0],
+                                        self._off_slot_map.ctypes.data, self._off_table.ctypes.data, cache.max_pages_per_request)
+        if rc != 0:
+            raise RuntimeError("a token of a captured step has no cache page" if rc == host.NO_PAGE
+                               else f"packing a captured step failed with status {rc}")
         if n < self.bucket:
             self._fill_padding(hv, n)
         if tokens_on_device:

@@ -19,7 +19,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .. import kernels
+from .. import host, kernels
 from ..cache.manager import CacheManager
 from ..parts.base import GroupTables, StepContext
 from .model import Model
@@ -96,78 +96,46 @@ class StepRunner:
             for w in e.want:
                 if not 0 <= w < len(e.tokens):
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
-        started = []
-        try:
-            for e in entries:
-                if not cache.has_request(e.request):
-                    cache.begin_request(e.request)
-                    started.append(e.request)
-            # all-or-nothing over the batch: check first, then take
-            spare: Dict[int, int] = {g.index: 0 for g in cache.groups}
-            for e in entries:
-                for gi, n in cache.pages_needed(e.request, len(e.tokens)).items():
-                    spare[gi] += n
-            for g in cache.groups:
-                if spare[g.index] > g.pool.free_count:
-                    from ..cache.page_pool import OutOfPages
-                    raise OutOfPages(f"group {g.index}: the step needs {spare[g.index]} new pages, "
-                                     f"{g.pool.free_count} are free")
-            for e in entries:
-                cache.reserve(e.request, len(e.tokens))
-        except Exception:
-            for r in started:
-                cache.end_request(r)
-            raise
-
         n = len(entries)
-        counts = np.array([len(e.tokens) for e in entries], dtype=np.int64)
+        handles = np.fromiter((cache.handle(e.request, create=True) for e in entries), dtype=np.int64, count=n)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
+        self._reserve(entries, handles, counts)
         T = int(counts.sum())
-        starts = np.zeros(n + 1, dtype=np.int32)
-        starts[1:] = np.cumsum(counts)
-        context = np.array([cache.length_of(e.request) for e in entries], dtype=np.int32)
-        slots = np.array([cache.slot_of(e.request) for e in entries], dtype=np.int32)
-        token_seq = np.repeat(np.arange(n, dtype=np.int32), counts)
-        positions = (np.arange(T, dtype=np.int32) - np.repeat(starts[:-1], counts) + np.repeat(context, counts)).astype(np.int32)
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-        if token_ids.min() < -(1 << 31) or token_ids.max() >= (1 << 31):
-            raise StepError("token ids do not fit 32 bits")
-        rows = [int(starts[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-        R = len(rows)
-        total_len = context.astype(np.int64) + counts
-        width = {g.index: int(-(-int(total_len.max()) // g.page_size)) for g in cache.groups}
-
-        tiles, small = kernels.query_tiles_of(starts, counts)
-        layout = [("token_ids", T), ("positions", T), ("token_seq", T), ("seq_starts", n + 1), ("seq_context", n),
-                  ("seq_slots", n), ("logit_rows", R), ("query_tiles", 3 * len(tiles)), ("small_tokens", len(small))]
+        want_offsets = np.zeros(n + 1, dtype=np.int64)
+        want_offsets[1:] = np.cumsum([len(e.want) for e in entries])
+        R = int(want_offsets[n])
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int64, count=R)
+        G = len(cache.groups)
+        lib = cache._lib
+        bound = int(lib.egh_step_bound(cache.core, n, T, R, kernels.QUERY_TILE))
+        ring_index, host_buf, dev = self._buffers(bound)
+        layout = np.zeros(2 * (9 + 2 * G), dtype=np.int64)
+        widths = np.zeros(max(G, 1), dtype=np.int32)
+        scalars = np.zeros(8, dtype=np.int64)
+        rc = lib.egh_step_pack(cache.core, n, handles.ctypes.data, counts.ctypes.data, token_ids.ctypes.data,
+                               want_offsets.ctypes.data, wants.ctypes.data, kernels.QUERY_TILE, kernels.SMALL_ENTRY_TOKENS,
+                               host_buf.data_ptr(), host_buf.numel(), layout.ctypes.data, widths.ctypes.data, scalars.ctypes.data)
+        if rc != 0:
+            if token_ids.min() < -(1 << 31) or token_ids.max() >= (1 << 31):
+                raise StepError("token ids do not fit 32 bits")
+            raise StepError(f"packing the step failed with status {rc}")
+        off = int(scalars[0])
+        names = ["token_ids", "positions", "token_seq", "seq_starts", "seq_context", "seq_slots", "logit_rows",
+                 "query_tiles", "small_tokens"]
         for g in cache.groups:
-            layout += [(f"slot_map{g.index}", T), (f"table{g.index}", n * width[g.index])]
-        offsets, off = {}, 0
-        for name, size in layout:
-            offsets[name] = (off, size)
-            off += _pad4(size)
-        ring_index, host, dev = self._buffers(off)
-        hv = host.numpy()
+            names += [f"slot_map{g.index}", f"table{g.index}"]
+        offsets = {name: (int(layout[2 * i]), int(layout[2 * i + 1])) for i, name in enumerate(names)}
+        width = {g.index: int(widths[g.index]) for g in cache.groups}
+        num_tiles, num_small = int(scalars[6]), int(scalars[7])
+        hv = host_buf.numpy()
 
-        def put(name, arr):
+        def host_list(name):
             o, size = offsets[name]
-            hv[o:o + size] = arr
+            return hv[o:o + size].tolist()
 
-        put("token_ids", token_ids.astype(np.int32))
-        put("positions", positions)
-        put("token_seq", token_seq)
-        put("seq_starts", starts)
-        put("seq_context", context)
-        put("seq_slots", slots)
-        put("logit_rows", np.asarray(rows, dtype=np.int32))
-        put("query_tiles", np.asarray(tiles, dtype=np.int32).reshape(-1))
-        put("small_tokens", np.asarray(small, dtype=np.int32))
-        rids = [e.request for e in entries]
-        for g in cache.groups:
-            sm = np.concatenate([cache.slot_positions(g.index, e.request, int(context[i]), int(counts[i]))
-                                 for i, e in enumerate(entries)])
-            put(f"slot_map{g.index}", sm)
-            put(f"table{g.index}", cache.table_rows(g.index, rids, width[g.index]).reshape(-1))
-        dev[:off].copy_(host[:off], non_blocking=True)
+        starts, context, slots = host_list("seq_starts"), host_list("seq_context"), host_list("seq_slots")
+        dev[:off].copy_(host_buf[:off], non_blocking=True)
         if self._ring_events[ring_index] is None:
             self._ring_events[ring_index] = torch.cuda.Event()
         self._ring_events[ring_index].record()
@@ -183,11 +151,11 @@ class StepRunner:
             status=self.status,
             groups={g.index: GroupTables(g.page_size, view(f"table{g.index}").view(n, width[g.index]),
                                          view(f"slot_map{g.index}")) for g in cache.groups},
-            host_seq_starts=starts.tolist(), host_seq_context=context.tolist(), host_seq_slots=slots.tolist(),
-            max_query_len=int(counts.max()), max_context_len=int(total_len.max()),
-            all_decode=bool((counts == 1).all()),
-            query_tiles=view("query_tiles").view(len(tiles), 3) if tiles else None,
-            small_tokens=view("small_tokens") if tiles and small else None,
+            host_seq_starts=starts, host_seq_context=context, host_seq_slots=slots,
+            max_query_len=int(scalars[3]), max_context_len=int(scalars[4]),
+            all_decode=bool(scalars[5]),
+            query_tiles=view("query_tiles").view(num_tiles, 3) if num_tiles else None,
+            small_tokens=view("small_tokens") if num_tiles and num_small else None,
         )
         return ctx, (view("logit_rows") if R else None)
 
@@ -250,18 +218,42 @@ class StepRunner:
         self._signature_graphs[sig] = graph
         return graph
 
+    def _reserve(self, entries: Sequence[StepEntry], handles: np.ndarray, counts: np.ndarray) -> None:
+        """Begins the step's new requests and takes the pages for every entry's tokens: all of it, or an
+        exception with nothing changed."""
+        from ..cache.manager import OutOfSlots
+        from ..cache.page_pool import OutOfPages
+
+        cache = self.cache
+        info = np.zeros(3, dtype=np.int32)
+        fresh = [e.request for e in entries if not cache.has_request(e.request)] if cache.state else ()
+        rc = cache._lib.egh_step_reserve(cache.core, len(entries), handles.ctypes.data, counts.ctypes.data, info.ctypes.data)
+        if rc == 0:
+            for r in fresh:                  # a request that takes a slot starts from zeroed state
+                cache.zero_state(cache.slot_of(r))
+            return
+        for e in entries:                    # names that were made for requests which did not come to life
+            if not cache.has_request(e.request):
+                cache._forget(e.request, cache.handle(e.request))
+        if rc == host.OUT_OF_PAGES:
+            raise OutOfPages(f"group {info[0]}: the step needs {info[1]} new pages, {info[2]} are free")
+        if rc == host.TOO_LONG:
+            e = entries[int(info[0])]
+            raise OutOfPages(f"request {e.request!r} would hold more tokens than a request may hold "
+                             f"({cache.max_pages_per_request * cache.page_size})")
+        if rc == host.OUT_OF_SLOTS:
+            raise OutOfSlots(f"all {cache.max_slots} request slots are taken")
+        raise StepError(f"reserving the step's pages failed with status {rc}")
+
     def _reserve_for_step(self, entries: Sequence[StepEntry]) -> bool:
-        """Pages for every entry's new tokens, or nothing at all (False)."""
-        need: Dict[int, int] = {g.index: 0 for g in self.cache.groups}
-        for e in entries:
-            if not self.cache.can_reserve(e.request, len(e.tokens)):
-                return False
-            for gi, k in self.cache.pages_needed(e.request, len(e.tokens)).items():
-                need[gi] += k
-        if any(need[g.index] > g.pool.free_count for g in self.cache.groups):
+        """Pages for every entry's new tokens (new requests are begun), or nothing at all (False)."""
+        n = len(entries)
+        handles = np.fromiter((self.cache.handle(e.request, create=True) for e in entries), dtype=np.int64, count=n)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
+        try:
+            self._reserve(entries, handles, counts)
+        except Exception:
             return False
-        for e in entries:
-            self.cache.reserve(e.request, len(e.tokens))
         return True
 
     def _run_captured(self, entries: Sequence[StepEntry]):
@@ -280,14 +272,7 @@ class StepRunner:
             graph = self._signature_graph(entries)
         if graph is None:
             return no
-        started = [e.request for e in entries if not self.cache.has_request(e.request)]
-        if len(started) > self.cache.free_slot_count():
-            return no
-        for r in started:
-            self.cache.begin_request(r)
         if not self._reserve_for_step(entries):
-            for r in started:
-                self.cache.end_request(r)
             return no                        # the general path raises the proper error
         tokens = [t for e in entries for t in e.tokens]
         logits = graph.replay([e.request for e in entries], tokens)
