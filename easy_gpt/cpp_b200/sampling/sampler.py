@@ -22,8 +22,12 @@ class Sampler:
         if rows <= self._cap:
             return
         self._cap = max(rows, 2 * self._cap)
-        # one pinned float32 block [4, cap]: temperature, top_p, uniform, top_k (as int bits)
-        self._host = torch.empty((4, self._cap), dtype=torch.float32).pin_memory()
+        # pinned float32 blocks [4, cap]: temperature, top_p, uniform, top_k (as int bits).  Several in turn, each
+        # with the event of the copy that last read it: the host runs ahead of the device, and a block written
+        # again before its copy has run would hand that step the next step's numbers.
+        self._hosts = [torch.empty((4, self._cap), dtype=torch.float32).pin_memory() for _ in range(4)]
+        self._host_events = [None] * len(self._hosts)
+        self._host_turn = 0
         self._dev = torch.empty((4, self._cap), dtype=torch.float32, device=self.device)
         # two output buffers in turn: a step's tokens stay readable (they feed the next step on the
         # device, and their copy to the host is read late) while the next step's are being written
@@ -45,13 +49,21 @@ class Sampler:
         if all(p.is_greedy for p in params):
             kernels.argmax(logits, self._out)
             return self._out[:rows]
-        h = self._host.numpy()
+        i = self._host_turn
+        self._host_turn = (i + 1) % len(self._hosts)
+        if self._host_events[i] is not None:
+            self._host_events[i].synchronize()
+        host = self._hosts[i]
+        h = host.numpy()
         for r, p in enumerate(params):
             h[0, r] = 0.0 if p.is_greedy else p.temperature
             h[1, r] = p.top_p
             h[2, r] = 0.0 if p.is_greedy else uniform(p.seed, int(request_ids[r]), int(token_indices[r]))
         h[3, :rows].view(np.int32)[:] = [p.top_k for p in params]
-        self._dev[:, :rows].copy_(self._host[:, :rows], non_blocking=True)
+        self._dev[:, :rows].copy_(host[:, :rows], non_blocking=True)
+        if self._host_events[i] is None:
+            self._host_events[i] = torch.cuda.Event()
+        self._host_events[i].record()
         kernels.sample(logits, self._dev[0], self._dev[3].view(torch.int32), self._dev[1], self._dev[2], self._out)
         return self._out[:rows]
 
