@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "cache_core.hpp"
+#include "scheduler_core.hpp"
 #include "step_pack.hpp"
 
 using namespace easygpt::host;
@@ -108,3 +109,83 @@ EGH_API int egh_replay_pack(void* c, int n, const long long* rids, const int32_t
     return pack_replay(*static_cast<CacheCore*>(c), n, (const int64_t*)rids, counts, buf, off_positions, off_context, off_slots,
                        off_slot_map, off_table, table_width);
 }
+
+// -- scheduler ------------------------------------------------------------------------------------------
+// A batch crosses this interface as 4 long longs per entry: request id, start, count, samples.
+namespace {
+std::vector<ScheduledEntry> entries_of(const long long* flat, int n) {
+    std::vector<ScheduledEntry> out(n);
+    for (int i = 0; i < n; ++i) out[i] = {flat[4 * i], flat[4 * i + 1], flat[4 * i + 2], (int)flat[4 * i + 3]};
+    return out;
+}
+}  // namespace
+
+// the cache must outlive the scheduler
+EGH_API void* egh_sched_create(void* cache, long long max_batch_tokens, long long chunk_size, int max_active, int prefill_batch,
+                               long long eos_token_id, long long max_positions) {
+    if (!cache || max_batch_tokens <= 0 || chunk_size <= 0 || max_active <= 0 || prefill_batch <= 0) return nullptr;
+    SchedulerOptions opt;
+    opt.max_batch_tokens = max_batch_tokens;
+    opt.chunk_size = chunk_size;
+    opt.max_active = max_active;
+    opt.prefill_batch = prefill_batch;
+    opt.eos_token_id = eos_token_id;
+    opt.max_positions = max_positions;
+    return new SchedulerCore(static_cast<CacheCore*>(cache), opt);
+}
+EGH_API void egh_sched_destroy(void* s) { delete static_cast<SchedulerCore*>(s); }
+EGH_API long long egh_sched_add(void* s, long long prompt_len, long long max_new_tokens) {
+    if (prompt_len < 0 || max_new_tokens <= 0) return BAD_ARGUMENT;
+    return static_cast<SchedulerCore*>(s)->add(prompt_len, max_new_tokens);
+}
+EGH_API int egh_sched_has_work(void* s) { return static_cast<SchedulerCore*>(s)->has_work() ? 1 : 0; }
+// The next step's batch into out, 5 long longs per entry (id, start, count, samples, and the request's tokens
+// that are still on the device), at most cap entries; returns the number of entries.
+EGH_API int egh_sched_schedule(void* s, long long* out, int cap) {
+    std::vector<ScheduledEntry> batch;
+    SchedulerCore* sc = static_cast<SchedulerCore*>(s);
+    sc->schedule(batch);
+    if ((int)batch.size() > cap) return BAD_ARGUMENT;
+    for (size_t i = 0; i < batch.size(); ++i) {
+        out[5 * i] = batch[i].id;
+        out[5 * i + 1] = batch[i].start;
+        out[5 * i + 2] = batch[i].count;
+        out[5 * i + 3] = batch[i].samples;
+        out[5 * i + 4] = sc->find(batch[i].id)->pending;
+    }
+    return (int)batch.size();
+}
+EGH_API int egh_sched_launched(void* s, const long long* batch, int n) {
+    const auto entries = entries_of(batch, n);
+    return static_cast<SchedulerCore*>(s)->launched(entries.data(), n);
+}
+EGH_API int egh_sched_resolve(void* s, const long long* batch, int n, const long long* tokens, int* actions) {
+    const auto entries = entries_of(batch, n);
+    return static_cast<SchedulerCore*>(s)->resolve(entries.data(), n, tokens, actions);
+}
+EGH_API int egh_sched_advance(void* s, long long id, long long n) { return static_cast<SchedulerCore*>(s)->advance(id, n); }
+// out (10 long longs): prompt length, output length, max new tokens, computed, state, finish reason, error,
+// pending, preemptions, admission counter
+EGH_API int egh_sched_request(void* s, long long id, long long* out) {
+    const SchedRequest* r = static_cast<SchedulerCore*>(s)->find(id);
+    if (!r) return UNKNOWN_REQUEST;
+    out[0] = r->prompt_len; out[1] = r->output_len; out[2] = r->max_new_tokens; out[3] = r->computed; out[4] = r->state;
+    out[5] = r->reason; out[6] = r->error; out[7] = r->pending; out[8] = r->preemptions; out[9] = r->admitted_at;
+    return OK;
+}
+// which: 0 waiting (queue order), 1 running (admission order), 2 finished (in the order they ended); returns the count
+EGH_API int egh_sched_list(void* s, int which, long long* out, int cap) {
+    const SchedulerCore* sc = static_cast<SchedulerCore*>(s);
+    int n = 0;
+    auto put = [&](int64_t id) { if (n < cap) out[n] = id; ++n; };
+    if (which == 0) for (int64_t id : sc->waiting()) put(id);
+    else if (which == 1) for (int64_t id : sc->running()) put(id);
+    else for (int64_t id : sc->finished()) put(id);
+    return n;
+}
+// out (6 long longs): steps, prompt tokens, decode tokens, preemptions, finished, failed
+EGH_API void egh_sched_stats(void* s, long long* out) {
+    const SchedulerStats& st = static_cast<SchedulerCore*>(s)->stats();
+    out[0] = st.steps; out[1] = st.prompt_tokens; out[2] = st.decode_tokens; out[3] = st.preemptions; out[4] = st.finished; out[5] = st.failed;
+}
+EGH_API void egh_sched_forget(void* s, long long id) { static_cast<SchedulerCore*>(s)->forget(id); }

@@ -73,7 +73,7 @@ class GptEngine:
         finished: List[Request] = []
         if not batch:
             return self._resolve_inflight()
-        on_device = [s for s in batch if s.request.pending]          # entries whose token is still on the device
+        on_device = [s for s in batch if s.pending]                  # entries whose token is still on the device
         graph = None
         if on_device:
             # the device can feed itself only if every entry is a decode of a token of the step in flight
@@ -82,6 +82,8 @@ class GptEngine:
             if graph is None:
                 # the general path needs every token id on the host: read what is in flight, drop what has ended
                 finished += self._resolve_inflight()
+                for s in batch:
+                    s.pending = 0            # read by now: the token is in the request's output
                 kept = [s for s in batch if s.request.state == "running"]
                 if len(kept) != len(batch):
                     batch = kept
@@ -100,7 +102,7 @@ class GptEngine:
         self._inflight = None
         if sampling:
             dev = self.sampler.sample(logits, [s.request.params for s in sampling], [s.request.id for s in sampling],
-                                      [len(s.request.output) + s.request.pending - 1 for s in sampling])
+                                      [len(s.request.output) + s.pending for s in sampling])
             self._inflight = (batch, dev, self.sampler.to_host_async(dev), {s.request.id: i for i, s in enumerate(sampling)})
         if previous is not None:
             finished += self._resolve(previous)

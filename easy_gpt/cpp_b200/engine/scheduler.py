@@ -1,7 +1,9 @@
 """The scheduler: admits requests, cuts prompts into portions under a token
-budget, decodes, finishes and frees.  Pure host code over the cache manager's
+budget, decodes, finishes and frees.  Host code over the cache manager's
 bookkeeping; it never touches the device, so its decisions are tested without
-one.
+one.  The decisions are made in C++ (``csrc/host/scheduler_core.hpp``), which
+knows requests by their lengths; this module is its face in Python and keeps
+what the decisions do not need: token ids and sampling parameters.
 
 It follows the rounds of the reference's ContinuousBatchServer
 (src/continuous_batch_server.cpp:71-86): a FIFO of waiting requests, at most
@@ -24,10 +26,14 @@ When pages run out
 """
 from __future__ import annotations
 
+import ctypes
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Deque, Dict, List, Optional, Sequence
 
+import numpy as np
+
+from .. import host
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
@@ -42,20 +48,58 @@ class SchedulerOptions:
     max_positions: int = 1 << 30       # max_position_embeddings
 
 
-@dataclass(eq=False)
+_STATES = ("waiting", "running", "finished")
+_REASONS = (None, "empty", "eos", "length", "max_positions", "error")
+# fields of egh_sched_request
+_PROMPT_LEN, _OUTPUT_LEN, _MAX_NEW, _COMPUTED, _STATE, _REASON, _ERROR, _PENDING, _PREEMPTIONS, _ADMITTED_AT = range(10)
+
+
 class Request:
-    id: int
-    prompt: List[int]
-    params: SamplingParams
-    max_new_tokens: int
-    output: List[int] = field(default_factory=list)
-    computed: int = 0                  # tokens whose keys/values are in the cache
-    state: str = "waiting"             # waiting | running | finished
-    finish_reason: Optional[str] = None
-    error: Optional[str] = None
-    preemptions: int = 0
-    admitted_at: int = -1              # admission counter, for "most recently admitted"
-    pending: int = 0                   # tokens sampled on the device whose ids the host has not read yet (0 or 1)
+    """A request as its owner sees it: token ids, sampling parameters and the output so far are kept here;
+    how far it has come (``computed``, ``state``, ``pending``, ...) is read from the scheduler."""
+
+    def __init__(self, scheduler: "Scheduler", rid: int, prompt: List[int], params: SamplingParams, max_new_tokens: int):
+        self._scheduler = scheduler
+        self.id = rid
+        self.prompt = prompt
+        self.params = params
+        self.max_new_tokens = max_new_tokens
+        self.output: List[int] = []
+
+    def _field(self, index: int) -> int:
+        return self._scheduler._request_fields(self.id)[index]
+
+    @property
+    def computed(self) -> int:
+        """Tokens whose keys/values are in the cache."""
+        return self._field(_COMPUTED)
+
+    @property
+    def state(self) -> str:
+        """waiting | running | finished"""
+        return _STATES[self._field(_STATE)]
+
+    @property
+    def finish_reason(self) -> Optional[str]:
+        return _REASONS[self._field(_REASON)]
+
+    @property
+    def error(self) -> Optional[str]:
+        return self._scheduler._error_text(self, self._field(_ERROR))
+
+    @property
+    def preemptions(self) -> int:
+        return self._field(_PREEMPTIONS)
+
+    @property
+    def admitted_at(self) -> int:
+        """Admission counter, for "most recently admitted"."""
+        return self._field(_ADMITTED_AT)
+
+    @property
+    def pending(self) -> int:
+        """Tokens sampled on the device whose ids the host has not read yet (0 or 1 between steps)."""
+        return self._field(_PENDING)
 
     @property
     def tokens(self) -> List[int]:
@@ -78,6 +122,9 @@ class Request:
             return self.prompt[start:start + count]
         return self.prompt[start:] + self.output[:start + count - n]
 
+    def __repr__(self):
+        return f"Request(id={self.id}, prompt={len(self.prompt)} tokens, output={len(self.output)} tokens, state={self.state})"
+
 
 @dataclass
 class Scheduled:
@@ -85,6 +132,7 @@ class Scheduled:
     start: int                         # first position fed this step
     count: int                         # tokens fed
     samples: bool                      # the portion reaches the last known token: its logits give the next token
+    pending: int = 0                   # the request's tokens still on the device when the step was scheduled (0 or 1)
 
 
 @dataclass
@@ -103,149 +151,91 @@ class Scheduler:
             raise ValueError("scheduler limits must be positive")
         self.cache = cache
         self.opt = options
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
-        self.finished: List[Request] = []
-        self.stats = SchedulerStats()
-        self._admissions = 0
-        self._next_id = 0
+        self._lib = host.library()
+        self._core = self._lib.egh_sched_create(cache.core, options.max_batch_tokens, options.chunk_size, options.max_active,
+                                                options.prefill_batch, options.eos_token_id, options.max_positions)
+        if not self._core:
+            raise ValueError("the scheduler could not be made from these options")
+        self._requests: Dict[int, Request] = {}
+        self._fields = (ctypes.c_longlong * 10)()
+        self._batch_cap = max(options.max_active, cache.max_slots) + 1
+        self._batch = np.zeros(5 * self._batch_cap, dtype=np.int64)
+
+    def __del__(self):
+        core = getattr(self, "_core", None)
+        if core:
+            self._core = None
+            self._lib.egh_sched_destroy(core)
+
+    # -- what the C++ side knows ---------------------------------------------------
+    def _request_fields(self, rid: int):
+        if self._lib.egh_sched_request(self._core, rid, self._fields) != host.OK:
+            raise KeyError(rid)
+        return self._fields
+
+    def _error_text(self, req: Request, code: int) -> Optional[str]:
+        if code == 0:
+            return None
+        if code == 1:
+            return (f"prompt of {len(req.prompt)} tokens leaves no room under "
+                    f"max_position_embeddings={self.opt.max_positions}")
+        if code == 2:
+            return f"prompt of {len(req.prompt)} tokens cannot fit the cache even alone"
+        return "the cache cannot hold this request even alone"
+
+    def _listed(self, which: int) -> List[Request]:
+        cap = len(self._requests) + 1
+        ids = (ctypes.c_longlong * cap)()
+        n = self._lib.egh_sched_list(self._core, which, ids, cap)
+        return [self._requests[i] for i in ids[:n]]
+
+    @property
+    def waiting(self) -> Deque[Request]:
+        return deque(self._listed(0))
+
+    @property
+    def running(self) -> List[Request]:
+        return self._listed(1)
+
+    @property
+    def finished(self) -> List[Request]:
+        return self._listed(2)
+
+    @property
+    def stats(self) -> SchedulerStats:
+        out = (ctypes.c_longlong * 6)()
+        self._lib.egh_sched_stats(self._core, out)
+        return SchedulerStats(*[int(v) for v in out])
 
     # -- intake ---------------------------------------------------------------
     def add(self, prompt: Sequence[int], params: SamplingParams, max_new_tokens: int) -> Request:
         if max_new_tokens <= 0:
             raise ValueError("max_new_tokens must be positive")
-        req = Request(self._next_id, list(prompt), params, max_new_tokens)
-        self._next_id += 1
-        if not req.prompt:
-            # the reference answers an empty prompt at once (src/continuous_batch_server.cpp:285-291)
-            self._finish(req, "empty")
-            return req
-        self.waiting.append(req)
+        prompt = list(prompt)
+        # an empty prompt is answered at once (src/continuous_batch_server.cpp:285-291)
+        rid = int(self._lib.egh_sched_add(self._core, len(prompt), int(max_new_tokens)))
+        req = Request(self, rid, prompt, params, max_new_tokens)
+        self._requests[rid] = req
         return req
 
+    def forget(self, req: Request) -> None:
+        """Drops the record of a finished request (a long-running caller that has read its output)."""
+        if req.state == "finished":
+            self._lib.egh_sched_forget(self._core, req.id)
+            self._requests.pop(req.id, None)
+
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
-
-    # -- helpers ------------------------------------------------------------------
-    def _pool_tokens(self) -> int:
-        return min(g.pool.num_pages for g in self.cache.groups) * self.cache.page_size if self.cache.groups else 1 << 60
-
-    def _finish(self, req: Request, reason: str, error: Optional[str] = None) -> None:
-        if self.cache.has_request(req.id):
-            self.cache.end_request(req.id)
-        if req.state == "running":
-            self.running.remove(req)
-        elif req.state == "waiting" and req in self.waiting:
-            self.waiting.remove(req)
-        req.state, req.finish_reason, req.error = "finished", reason, error
-        self.finished.append(req)
-        if error:
-            self.stats.failed += 1
-        else:
-            self.stats.finished += 1
-
-    def _preempt(self, victim: Request) -> None:
-        self.cache.end_request(victim.id)
-        self.running.remove(victim)
-        victim.computed = 0
-        victim.state = "waiting"
-        victim.preemptions += 1
-        self.stats.preemptions += 1
-        self.waiting.appendleft(victim)
-
-    def _limit_error(self, req: Request) -> Optional[str]:
-        total = len(req.prompt) + 1
-        if total > self.opt.max_positions:
-            return f"prompt of {len(req.prompt)} tokens leaves no room under max_position_embeddings={self.opt.max_positions}"
-        if total > self._pool_tokens() or total > self.cache.max_pages_per_request * self.cache.page_size:
-            return f"prompt of {len(req.prompt)} tokens cannot fit the cache even alone"
-        return None
+        return bool(self._lib.egh_sched_has_work(self._core))
 
     # -- one round -----------------------------------------------------------------
     def schedule(self) -> List[Scheduled]:
         """Decides the next step's batch and reserves its cache pages."""
-        budget = self.opt.max_batch_tokens
-        batch: List[Scheduled] = []
-
-        # 1. every request that has all its known tokens but one in the cache decodes one token
-        for req in list(self.running):
-            if req.state != "running" or req.known - req.computed != 1 or budget <= 0:
-                continue
-            if req.pending and (len(req.output) + req.pending >= req.max_new_tokens or req.known >= self.opt.max_positions):
-                continue                       # its pending token is its last one: it ends when the token is read
-            while not self.cache.can_reserve(req.id, 1):
-                victim = max(self.running, key=lambda r: r.admitted_at)
-                scheduled_victim = next((s for s in batch if s.request is victim), None)
-                if scheduled_victim is not None:
-                    batch.remove(scheduled_victim)
-                    budget += scheduled_victim.count
-                only_one = len(self.running) == 1
-                self._preempt(victim)
-                if victim is req:
-                    if only_one:
-                        # alone and still too large: it can never go on
-                        self.waiting.popleft()
-                        self._finish(req, "error", "the cache cannot hold this request even alone")
-                    break
-            if req.state != "running":
-                continue
-            self.cache.reserve(req.id, 1)
-            batch.append(Scheduled(req, req.computed, 1, True))
-            budget -= 1
-
-        # 2. requests in the middle of their prompt (or being recomputed) get their next portion
-        for req in self.running:
-            left = req.known - req.computed
-            if left <= 1 or budget <= 0 or req.pending:
-                continue                       # (a portion needs all its token ids on the host)
-            n = min(left, self.opt.chunk_size, budget)
-            if not self.cache.can_reserve(req.id, n):
-                continue                       # waits for pages; decoding requests will free some or be preempted
-            self.cache.reserve(req.id, n)
-            batch.append(Scheduled(req, req.computed, n, req.computed + n == req.known))
-            budget -= n
-
-        # 3. admissions, FIFO, while slots, pages and budget last
-        admitted = 0
-        while (self.waiting and admitted < self.opt.prefill_batch and len(self.running) < self.opt.max_active
-               and budget > 0 and self.cache.free_slot_count() > 0):
-            req = self.waiting[0]
-            if req.pending:
-                break                          # preempted while its last token was on its way: wait for it
-            err = self._limit_error(req)
-            if err:
-                self.waiting.popleft()
-                self._finish(req, "error", err)
-                continue
-            n = min(req.known, self.opt.chunk_size, budget)
-            # keep one page per running request in reserve, so that admissions do not starve decoding
-            self.cache.begin_request(req.id)
-            if not self.cache.can_reserve(req.id, n, spare=len(self.running)):
-                self.cache.end_request(req.id)
-                break
-            self.cache.reserve(req.id, n)
-            self.waiting.popleft()
-            req.state = "running"
-            req.admitted_at = self._admissions
-            self._admissions += 1
-            self.running.append(req)
-            batch.append(Scheduled(req, 0, n, n == req.known))
-            budget -= n
-            admitted += 1
-
-        if not batch and any(r.pending for r in self.running):
-            return batch                       # everything live waits for a token that is on its way
-        if not batch and self.running:
-            # nothing fits although requests are live (all stuck in their prompts): make room
-            victim = max(self.running, key=lambda r: r.admitted_at)
-            if len(self.running) == 1:
-                self._finish(victim, "error", "the cache cannot hold this request even alone")
-            else:
-                self._preempt(victim)
-            return self.schedule()
-        if batch:
-            self.stats.steps += 1
-        return batch
+        n = self._lib.egh_sched_schedule(self._core, self._batch.ctypes.data, self._batch_cap)
+        if n < 0:
+            raise RuntimeError(f"the scheduler failed with status {n}")
+        flat = self._batch[:5 * n].tolist()
+        requests = self._requests
+        return [Scheduled(requests[flat[i]], flat[i + 1], flat[i + 2], bool(flat[i + 3]), flat[i + 4]) for i in range(0, 5 * n, 5)]
 
     def update(self, batch: Sequence[Scheduled], next_tokens: Sequence[int]) -> List[Request]:
         """After the step ran: ``next_tokens`` holds one sampled token for every
@@ -253,43 +243,45 @@ class Scheduler:
         self.launched(batch)
         return self.resolve(batch, next_tokens)
 
+    @staticmethod
+    def _flat(batch: Sequence[Scheduled]) -> np.ndarray:
+        return np.array([v for s in batch for v in (s.request.id, s.start, s.count, int(s.samples))], dtype=np.int64)
+
     def launched(self, batch: Sequence[Scheduled]) -> None:
         """The step has been handed to the device: its tokens count as cached, and every sampling
         entry has one token on its way (``pending``) whose id ``resolve`` will bring."""
-        for s in batch:
-            req = s.request
-            self.cache.commit(req.id, s.count)
-            req.computed += s.count
-            if s.count == 1 and s.start >= len(req.prompt):
-                self.stats.decode_tokens += 1
-            else:
-                self.stats.prompt_tokens += s.count
-            if s.samples:
-                req.pending += 1
+        flat = self._flat(batch)
+        rc = self._lib.egh_sched_launched(self._core, flat.ctypes.data, len(batch))
+        if rc == host.EXCEEDS_RESERVED:
+            raise ValueError("a launched entry exceeds what was reserved for its request")
+        if rc != host.OK:
+            raise RuntimeError(f"the scheduler failed with status {rc}")
 
     def resolve(self, batch: Sequence[Scheduled], next_tokens: Sequence[int]) -> List[Request]:
         """The sampled tokens of a launched step have reached the host.  A request that had ended
         meanwhile (its previous token was EOS while this step was already on the device) drops its token."""
+        sampling = [s for s in batch if s.samples]
+        tokens = np.array([int(t) for t in next_tokens], dtype=np.int64)
+        if len(tokens) < len(sampling):
+            raise ValueError("fewer tokens than sampling entries")
+        flat = self._flat(batch)
+        actions = np.zeros(max(len(sampling), 1), dtype=np.int32)
+        rc = self._lib.egh_sched_resolve(self._core, flat.ctypes.data, len(batch), tokens.ctypes.data, actions.ctypes.data)
+        if rc < 0:
+            raise RuntimeError(f"the scheduler failed with status {rc}")
         done = []
-        it = iter(next_tokens)
-        for s in batch:
-            if not s.samples:
+        for s, token, action in zip(sampling, tokens.tolist(), actions.tolist()):
+            if action == 0:
                 continue
-            req = s.request
-            token = int(next(it))
-            if req.state == "finished":
-                continue
-            req.pending -= 1
-            req.output.append(token)
-            reason = None
-            if self.opt.eos_token_id >= 0 and token == self.opt.eos_token_id:
-                reason = "eos"                                  # the EOS token itself is emitted
-            elif len(req.output) >= req.max_new_tokens:
-                reason = "length"
-            elif req.known + 1 > self.opt.max_positions:
-                reason = "max_positions"
-            if reason:
-                req.pending = 0
-                self._finish(req, reason)
-                done.append(req)
+            s.request.output.append(token)
+            if action == 2:
+                done.append(s.request)
         return done
+
+    def advance_decoded(self, req: Request, tokens: Sequence[int]) -> None:
+        """Tokens decoded outside the scheduler (a benchmark loop that feeds the device itself): they join the
+        output, and all but the last count as cached, which the caller has committed to the cache manager."""
+        rc = self._lib.egh_sched_advance(self._core, req.id, len(tokens))
+        if rc != host.OK:
+            raise ValueError(f"request {req.id} cannot be advanced by {len(tokens)} tokens")
+        req.output += [int(t) for t in tokens]

@@ -47,6 +47,18 @@ _SIGNATURES = {
                               c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
     "egh_replay_pack": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong,
                                 c_void_p, c_void_p, c_int]),
+    "egh_sched_create": (c_void_p, [c_void_p, c_longlong, c_longlong, c_int, c_int, c_longlong, c_longlong]),
+    "egh_sched_destroy": (None, [c_void_p]),
+    "egh_sched_add": (c_longlong, [c_void_p, c_longlong, c_longlong]),
+    "egh_sched_has_work": (c_int, [c_void_p]),
+    "egh_sched_schedule": (c_int, [c_void_p, c_void_p, c_int]),
+    "egh_sched_launched": (c_int, [c_void_p, c_void_p, c_int]),
+    "egh_sched_resolve": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "egh_sched_advance": (c_int, [c_void_p, c_longlong, c_longlong]),
+    "egh_sched_request": (c_int, [c_void_p, c_longlong, c_void_p]),
+    "egh_sched_list": (c_int, [c_void_p, c_int, c_void_p, c_int]),
+    "egh_sched_stats": (None, [c_void_p, c_void_p]),
+    "egh_sched_forget": (None, [c_void_p, c_longlong]),
 }
 
 _lib = None
