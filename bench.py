@@ -378,6 +378,45 @@ def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
     return 0
 
 
+def measure_serving(folder, config, requests=64, new_tokens=512, chunk=512, budget=2048, seed=0, repeats=2):
+    """Continuous batching through GptEngine: `requests` concurrent requests with prompt lengths uniform in
+    [128, 4096] and `new_tokens` generated tokens each, prompts cut into portions of `chunk` tokens that share
+    steps with the decoding requests.  Wall clock from the first add_request to the last token on the host;
+    the first repeat warms up (graphs of the step shapes are captured), the last one is reported."""
+    import numpy as np
+    import torch
+
+    from easy_gpt.cpp_b200.engine import GptEngine
+    from easy_gpt.cpp_b200.sampling import GREEDY
+
+    rng = np.random.default_rng(seed)
+    lengths = rng.integers(128, 4097, size=requests)
+    prompts = [rng.integers(0, config["vocab_size"], size=int(n)).tolist() for n in lengths]
+    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=requests * (4096 + new_tokens + 64),
+                       max_active=requests, prefill_batch=4, max_batch_tokens=budget, chunk_size=chunk,
+                       max_tokens_per_request=4096 + new_tokens + 64)
+    out = {}
+    for _ in range(repeats):
+        steps0 = engine.scheduler.stats.steps
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reqs = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts]
+        engine.run_to_completion()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        assert all(len(r.output) == new_tokens and not r.error for r in reqs)
+        stats = engine.scheduler.stats
+        out = {"requests": requests, "prompt_tokens": int(lengths.sum()), "generated_tokens": requests * new_tokens,
+               "seconds": round(seconds, 3), "steps": stats.steps - steps0, "preemptions": stats.preemptions,
+               "generated_tok_s": round(requests * new_tokens / seconds, 1),
+               "all_tok_s": round((int(lengths.sum()) + requests * new_tokens) / seconds, 1),
+               "ms_per_step": round(1e3 * seconds / max(1, stats.steps - steps0), 3), "graph_replays": engine.runner.graph_replays}
+        for r in reqs:
+            engine.scheduler.forget(r)
+    engine.runner.check_status()
+    return out
+
+
 def run_ours(args):
     import torch
 
@@ -398,6 +437,10 @@ def run_ours(args):
         print(json.dumps({"only": "decode", "sizes": args.sizes, "batch": args.batch, "layers": config["num_hidden_layers"], "context": CONTEXT,
                           "tok_s": round(r["tok_s"], 1), "ms_per_step": round(1e3 * r["seconds"] / args.steps, 4),
                           "gb_s": round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9, 1)}))
+        return 0
+    if args.only == "serve":
+        print(json.dumps({"only": "serve", "sizes": args.sizes, "layers": config["num_hidden_layers"],
+                          **measure_serving(folder, config, requests=args.batch if args.batch != 8 else 64)}))
         return 0
     if args.only == "timeline":
         return print_timeline(folder, config, args.batch)
@@ -455,7 +498,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
     ap.add_argument("--sizes", choices=list(SIZES), default="0.5b", help="layer sizes for --only runs")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "serve"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -191,6 +191,7 @@ class StepRunner:
         return self._graphs[b]
 
     MAX_SIGNATURE_GRAPHS = 48
+    CAPTURE_MIXED_AFTER = 4            # times a shape of several entries is seen before it is captured
 
     def graph_pool(self):
         """The memory pool that all captured steps of this runner share."""
@@ -208,7 +209,11 @@ class StepRunner:
             self._signature_graphs[sig] = self._signature_graphs.pop(sig)         # most recently used last
             return graph
         self._signature_seen[sig] = self._signature_seen.get(sig, 0) + 1
-        if self._signature_seen[sig] < 2 or sum(sig[0]) > 16384:
+        # A capture costs about as much as six eager steps.  One request's portions come again and again; a batch
+        # of several requests rarely comes twice in the same shape (the number of decoding requests moves), so it
+        # has to show that it does before it is captured.
+        capture_after = 2 if len(sig[0]) == 1 else self.CAPTURE_MIXED_AFTER
+        if self._signature_seen[sig] < capture_after or sum(sig[0]) > 16384:
             return None
         if len(self._signature_graphs) >= self.MAX_SIGNATURE_GRAPHS:
             self._signature_graphs.pop(next(iter(self._signature_graphs)))        # the least recently used
