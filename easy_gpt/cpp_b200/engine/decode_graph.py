@@ -17,7 +17,7 @@ scratch page, so they read and write nothing that belongs to a request.
 from __future__ import annotations
 
 import gc
-from typing import Dict, List, Sequence
+from typing import List, Sequence
 
 import numpy as np
 import torch

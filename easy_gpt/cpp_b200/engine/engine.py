@@ -6,7 +6,6 @@ through the scheduler and the one step function, on the device.
 """
 from __future__ import annotations
 
-import json
 import tempfile
 from pathlib import Path
 from typing import List, Optional, Sequence

@@ -13,7 +13,7 @@ every position, :203-211.)
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -34,10 +34,6 @@ class StepEntry:
 
 class StepError(RuntimeError):
     pass
-
-
-def _pad4(n: int) -> int:
-    return (n + 3) & ~3
 
 
 class StepRunner:

@@ -152,3 +152,32 @@ def test_random_orders_keep_the_books_straight(ops, page_size, num_pages):
     m.reset()
     m.check()
     assert all(g.pool.free_count == g.pool.num_pages for g in m.groups)
+
+
+def test_pool_free_is_all_or_nothing():
+    p = PagePool(6)
+    p.alloc(4)
+    with pytest.raises(ValueError, match="freed twice"):
+        p.free([0, 1, 1])                            # a page named twice in one call
+    with pytest.raises(ValueError, match="freed twice"):
+        p.free([2, 5])                               # page 5 is not held
+    assert p.free_count == 2 and p.used_count == 4   # neither call gave anything back
+    p.check()
+    p.free([3, 0])
+    assert p.alloc(2) == [3, 0] and p.total_allocated == 6 and p.high_water == 4      # the first of a batch comes out first
+
+
+def test_requests_are_known_by_any_hashable_name():
+    m = manager(slots=3)
+    m.begin_request("a")
+    m.begin_request(7)
+    m.begin_request(("t", 1))
+    assert sorted(map(str, m.live_requests())) == ["('t', 1)", "7", "a"]
+    assert not m.has_request("b") and not m.has_request(8)
+    with pytest.raises(KeyError):
+        m.length_of("b")
+    m.end_request(("t", 1))
+    with pytest.raises(KeyError):
+        m.end_request(("t", 1))
+    assert set(m.live_requests()) == {7, "a"}
+    m.check()

@@ -208,3 +208,45 @@ def test_tokens_in_flight_launch_then_resolve():
     assert a.output == expected_output([5, 6, 7], 6) and b.output == expected_output([9] * 11, 4)
     assert a.finish_reason == "length" and b.finish_reason == "length" and a.pending == 0
     assert not cache.live_requests()
+
+
+def test_scheduled_entries_say_whether_a_token_is_still_on_the_device():
+    sched, cache = make(num_pages=64, max_batch_tokens=32)
+    a = sched.add([5, 6, 7], GREEDY, 4)
+    first = sched.schedule()
+    assert [(s.start, s.count, s.samples, s.pending) for s in first] == [(0, 3, True, 0)]
+    sched.launched(first)
+    assert a.pending == 1 and a.computed == 3 and a.known == 4
+    second = sched.schedule()                                 # decodes the token that has not been read yet
+    assert [(s.start, s.count, s.samples, s.pending) for s in second] == [(3, 1, True, 1)]
+    with pytest.raises(ValueError, match="still on the device"):
+        a.token_slice(3, 1)
+    sched.launched(second)
+    assert sched.resolve(first, [11]) == [] and a.output == [11] and a.pending == 1
+    assert sched.resolve(second, [12]) == [] and a.output == [11, 12] and a.pending == 0
+
+
+def test_tokens_decoded_outside_the_scheduler_and_forgetting():
+    sched, cache = make(num_pages=64)
+    a = sched.add([1, 2, 3, 4], GREEDY, 10)
+    sched.update(sched.schedule(), [9])
+    # a loop of its own decodes three more tokens: it feeds 9, x, y and commits them
+    for _ in range(3):
+        cache.reserve(a.id, 1)
+        cache.commit(a.id, 1)
+    sched.advance_decoded(a, [21, 22, 23])
+    assert a.output == [9, 21, 22, 23] and a.computed == cache.length_of(a.id) == 7 and a.known == 8
+    batch = sched.schedule()
+    assert [(s.start, s.count) for s in batch] == [(7, 1)]
+    sched.update(batch, [30])
+    while sched.has_work():
+        b = sched.schedule()
+        sched.update(b, [31] * sum(s.samples for s in b))
+    assert a.state == "finished" and a.finish_reason == "length" and len(a.output) == 10
+    assert [r.id for r in sched.finished] == [a.id]
+    sched.forget(a)
+    assert sched.finished == []
+    with pytest.raises(KeyError):
+        a.state
+    with pytest.raises(ValueError):
+        sched.advance_decoded(a, [1])

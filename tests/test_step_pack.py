@@ -1,7 +1,6 @@
 """The host runtime's packing of a step's metadata (no GPU): against a restatement in numpy, for
 random batches over a cache whose pages have been used before."""
 import numpy as np
-import pytest
 from hypothesis import given, settings, strategies as st
 
 from easy_gpt.cpp_b200 import host
