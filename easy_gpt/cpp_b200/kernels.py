@@ -502,7 +502,10 @@ def fused_norm_max_tokens(width: int) -> int:
     """Up to how many tokens a step's add + RMSNorm over rows of ``width`` can ride in the decode product's
     prologue: the policy's limit, lowered where the rows of a token tile (8 or 16 tokens, bfloat16, padded),
     the gain and the partial sums of squares of a product in front (one per 16 output rows at most) would not
-    fit the kernel's 200 KB of shared memory.  0: the norm runs as a kernel of its own."""
+    fit the kernel's 200 KB of shared memory.  0: the norm runs as a kernel of its own (also for widths that
+    are no multiple of 16, which the decode product does not take)."""
+    if width % 16:
+        return 0
     for tile in (16, 8):
         row = -(-2 * width // 128) * 128 + 64
         need = tile * row + tile * 4 + width * 4 + tile * 32 + -(-width // 16) * tile * 4

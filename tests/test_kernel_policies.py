@@ -10,6 +10,7 @@ def test_fused_norm_limit_follows_the_width():
     # 16 rows of 8192 bfloat16 values do not fit 200 KB of shared memory, 8 rows do
     assert kernels.fused_norm_max_tokens(8192) == min(8, kernels.FUSED_NORM_MAX_TOKENS)
     assert kernels.fused_norm_max_tokens(20000) == 0
+    assert kernels.fused_norm_max_tokens(120) == 0            # rows of 240 bytes: the decode product wants multiples of 32
 
 
 def test_decode_product_policy():

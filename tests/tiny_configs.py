@@ -37,7 +37,17 @@ CONFIG_C = {
 }
 RANDOM_C = dict(seed=5, std=0.06, bias_std=0.0, gain_std=0.05)
 
-CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C)}
+# D: a head size that is no power of two (48), as many KV heads as query heads (no groups), five of them
+CONFIG_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 120, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 48,
+    "intermediate_size": 176, "vocab_size": 130, "rope_theta": 100000.0, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 512, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_D = dict(seed=7, std=0.07, bias_std=0.05, gain_std=0.1)
+
+CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D)}
 
 
 def write_tiny(name: str, folder=None, store_dtype="float32") -> Path:
