@@ -17,13 +17,13 @@ F32_ATOL = 1e-4
 BF16_REL = 3e-2
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def tiny(request, tmp_path_factory):
     name = request.param
     folder = tiny_configs.write_tiny(name, tmp_path_factory.mktemp(f"tiny_{name}"))
     cfg = tiny_configs.CONFIGS[name][0]
     lengths = {"A": [5, 70, 131, 97, 33, 120], "B": [40, 77, 130, 64, 201, 18], "C": [90, 150, 33, 260, 75],
-               "D": [61, 140, 35, 99]}[name]
+               "D": [61, 140, 35, 99], "E": [50, 133, 41]}[name]
     requests = {f"r{i}": tiny_configs.random_tokens(cfg["vocab_size"], n, 100 + i) for i, n in enumerate(lengths)}
     refs = {}
     for mode, rounded in (("float32", False), ("bfloat16", True)):

@@ -47,7 +47,19 @@ CONFIG_D = {
 }
 RANDOM_D = dict(seed=7, std=0.07, bias_std=0.05, gain_std=0.1)
 
-CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D)}
+# E: sizes that break every alignment a kernel might lean on: width 100 (rows of 200 bytes), feed-forward
+# width 72, vocabulary 77, three query heads on one KV head
+CONFIG_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16,
+    "intermediate_size": 72, "vocab_size": 77, "rope_theta": 20000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 512, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_E = dict(seed=9, std=0.08, bias_std=0.05, gain_std=0.1)
+
+CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D),
+           "E": (CONFIG_E, RANDOM_E)}
 
 
 def write_tiny(name: str, folder=None, store_dtype="float32") -> Path:
