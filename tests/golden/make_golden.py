@@ -2,7 +2,7 @@
 its CMakeLists.txt hard-codes the bfloat16 build), runs ref_harness.cpp on the
 tiny golden model and stores the logits as ref_logits.npy beside this file.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The committed ref_logits.npy came from exactly this script.
 """
@@ -19,7 +19,9 @@ import golden_model  # noqa: E402
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/reference (a checkout of the reference's sources)")
+    ref = Path(sys.argv[1])
     here = Path(__file__).resolve().parent
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)
