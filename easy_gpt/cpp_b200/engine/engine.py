@@ -153,10 +153,13 @@ class GptEngine:
         params = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, seed=seed, greedy=greedy)
         requests = [self.add_request(p, params, max_new_tokens, max_steps) for p in prompts]
         self.run_to_completion()
+        errors = [(r.id, r.error) for r in requests if r.error]
+        outputs = [list(r.output) for r in requests]
         for r in requests:
-            if r.error:
-                raise RuntimeError(f"request {r.id}: {r.error}")
-        return [list(r.output) for r in requests]
+            self.scheduler.forget(r)         # their records are not needed any more: the engine may live long
+        if errors:
+            raise RuntimeError(f"request {errors[0][0]}: {errors[0][1]}")
+        return outputs
 
 
 def engine_with_random_weights(config: dict, seed: int, folder=None, store_dtype="bfloat16", **engine_options) -> GptEngine:
