@@ -250,3 +250,29 @@ def test_tokens_decoded_outside_the_scheduler_and_forgetting():
         a.state
     with pytest.raises(ValueError):
         sched.advance_decoded(a, [1])
+
+
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.tuples(st.integers(1, 60), st.integers(1, 20)), min_size=1, max_size=10),
+       st.integers(6, 60), st.sampled_from([2, 4, 8]), st.integers(3, 70), st.integers(2, 40), st.integers(1, 5), st.integers(1, 4))
+def test_random_workloads_end_with_the_outputs_of_an_undisturbed_run(work, num_pages, page_size, budget, chunk, active, admit):
+    """Whatever the limits: every request either fails because it cannot fit even alone or ends with exactly the
+    tokens it would have got alone, every round keeps the budget, and in the end nothing is held."""
+    sched, cache = make(num_pages=num_pages, page_size=page_size, max_batch_tokens=budget, chunk_size=chunk,
+                        max_active=active, prefill_batch=admit)
+    reqs = [sched.add([(7 * i + j) % 50 + 3 for j in range(n)], GREEDY, new) for i, (n, new) in enumerate(work)]
+    drive(sched, cache)
+    pool_tokens = num_pages * page_size
+    for r, (n, new) in zip(reqs, work):
+        assert r.state == "finished"
+        if r.error:
+            assert n + new > pool_tokens                      # only a request that outgrows the whole pool may fail
+            assert r.output == expected_output(r.prompt, len(r.output))
+        else:
+            assert r.output == expected_output(r.prompt, new)
+    assert not cache.live_requests() and cache.free_pages(0) == num_pages
+    st_ = sched.stats
+    assert st_.finished + st_.failed == len(reqs)
