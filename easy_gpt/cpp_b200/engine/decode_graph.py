@@ -7,7 +7,7 @@ tables).  The sequence is captured once over static buffers; a step then costs
 one host-to-device copy of the arrays and one graph launch instead of a few
 hundred launches.  Decode steps (every entry brings one token) are captured per
 batch-size bucket and padded; other signatures (a prompt portion of the chunk
-size, say) are captured when they come a second time.  (The reference captures a graph only for the attention of
+size, say) are captured when they come a second time (batches of several entries: a fourth time).  (The reference captures a graph only for the attention of
 one layer at batch 1 and re-captures whenever a pointer changes,
 src/cuda/ops/self_attn.cu:750-828.)
 
