@@ -365,6 +365,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _ptr(counters), USE_PDL, Timeline.slot(f"attention s={splits}"), _ptr(token_list)), "attention_paged")
 
 
+MAX_HEAD_DIM = 256             # the generic attention kernel keeps up to eight dimensions of a head per lane
 PREFILL_ATTENTION_HEAD_DIMS = (32, 64, 128)
 QUERY_TILE = 128               # tokens per listed tile of a prompt portion
 SMALL_ENTRY_TOKENS = 4         # entries of up to this many tokens go through the decode attention kernel, token by token

@@ -40,6 +40,8 @@ class Attention(Mixer):
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive")
+        if not 0 < self.head_dim <= kernels.MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {self.head_dim} is outside what the attention kernels take (1..{kernels.MAX_HEAD_DIM})")
         self.scale = 1.0 / math.sqrt(self.head_dim)
         self.qkv = self.out = None
 

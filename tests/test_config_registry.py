@@ -87,3 +87,14 @@ def test_run_order_is_checked():
         ModelSpec(run_order=(RunEntry(0, 0), RunEntry(1, 3, writes_cache=False)), **kw)
     with pytest.raises(ValueError, match="before entry"):
         ModelSpec(run_order=(RunEntry(0, 1, writes_cache=False), RunEntry(1, 1)), **kw)
+
+
+def test_a_head_size_beyond_the_kernels_is_refused_when_the_model_is_built():
+    import torch
+
+    from easy_gpt.cpp_b200.engine.model import Model
+
+    config = dict(tiny_configs.CONFIG_A, head_dim=272)
+    with pytest.raises(ValueError, match="head_dim 272 is outside what the attention kernels take"):
+        Model(model_spec_from_config(config), "cpu", torch.float32)
+    Model(model_spec_from_config(dict(tiny_configs.CONFIG_A, head_dim=256)), "cpu", torch.float32)
