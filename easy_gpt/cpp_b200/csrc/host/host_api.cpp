@@ -3,6 +3,7 @@
 // negative Status.  Nothing here touches a GPU.
 #include <cstring>
 
+#include "bpe_tokenizer.hpp"
 #include "cache_core.hpp"
 #include "scheduler_core.hpp"
 #include "step_pack.hpp"
@@ -189,3 +190,43 @@ EGH_API void egh_sched_stats(void* s, long long* out) {
     out[0] = st.steps; out[1] = st.prompt_tokens; out[2] = st.decode_tokens; out[3] = st.preemptions; out[4] = st.finished; out[5] = st.failed;
 }
 EGH_API void egh_sched_forget(void* s, long long id) { static_cast<SchedulerCore*>(s)->forget(id); }
+
+// -- tokenizer --------------------------------------------------------------------------------------------
+// Strings cross this interface as UTF-8 bytes: lists of them as one blob with n + 1 offsets.
+EGH_API void* egh_bpe_create() { return new BpeTokenizer(); }
+EGH_API void egh_bpe_destroy(void* t) { delete static_cast<BpeTokenizer*>(t); }
+EGH_API void egh_bpe_add_tokens(void* t, const char* blob, const long long* offsets, const int32_t* ids, int n) {
+    for (int i = 0; i < n; ++i) static_cast<BpeTokenizer*>(t)->add_token(std::string(blob + offsets[i], blob + offsets[i + 1]), ids[i]);
+}
+EGH_API void egh_bpe_add_merges(void* t, const char* left, const long long* left_offsets, const char* right,
+                                const long long* right_offsets, int n) {
+    for (int i = 0; i < n; ++i)
+        static_cast<BpeTokenizer*>(t)->add_merge(std::string(left + left_offsets[i], left + left_offsets[i + 1]),
+                                                 std::string(right + right_offsets[i], right + right_offsets[i + 1]));
+}
+// longest first
+EGH_API void egh_bpe_add_specials(void* t, const char* blob, const long long* offsets, int n) {
+    for (int i = 0; i < n; ++i) static_cast<BpeTokenizer*>(t)->add_special(std::string(blob + offsets[i], blob + offsets[i + 1]));
+}
+EGH_API void egh_bpe_set_bos(void* t, int id) { static_cast<BpeTokenizer*>(t)->set_bos(id); }
+// The three below return how much there is; what fits cap is written (a caller that got more than cap asks again).
+EGH_API long long egh_bpe_encode(void* t, const char* text, long long length, int32_t* out, long long cap) {
+    const std::vector<int32_t> ids = static_cast<BpeTokenizer*>(t)->encode(std::string(text, text + length));
+    for (size_t i = 0; i < ids.size() && (long long)i < cap; ++i) out[i] = ids[i];
+    return (long long)ids.size();
+}
+// tokens as UTF-8, each followed by a zero byte
+EGH_API long long egh_bpe_tokenize(void* t, const char* text, long long length, char* out, long long cap) {
+    std::string joined;
+    for (const std::string& token : static_cast<BpeTokenizer*>(t)->tokenize(std::string(text, text + length))) {
+        joined += token;
+        joined += '\0';
+    }
+    std::memcpy(out, joined.data(), (size_t)std::min<long long>(cap, (long long)joined.size()));
+    return (long long)joined.size();
+}
+EGH_API long long egh_bpe_decode(void* t, const int32_t* ids, long long n, char* out, long long cap) {
+    const std::string raw = static_cast<BpeTokenizer*>(t)->decode(ids, (size_t)n);
+    std::memcpy(out, raw.data(), (size_t)std::min<long long>(cap, (long long)raw.size()));
+    return (long long)raw.size();
+}

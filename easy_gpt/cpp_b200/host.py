@@ -59,6 +59,15 @@ _SIGNATURES = {
     "egh_sched_list": (c_int, [c_void_p, c_int, c_void_p, c_int]),
     "egh_sched_stats": (None, [c_void_p, c_void_p]),
     "egh_sched_forget": (None, [c_void_p, c_longlong]),
+    "egh_bpe_create": (c_void_p, []),
+    "egh_bpe_destroy": (None, [c_void_p]),
+    "egh_bpe_add_tokens": (None, [c_void_p, c_char_p, c_void_p, c_void_p, c_int]),
+    "egh_bpe_add_merges": (None, [c_void_p, c_char_p, c_void_p, c_char_p, c_void_p, c_int]),
+    "egh_bpe_add_specials": (None, [c_void_p, c_char_p, c_void_p, c_int]),
+    "egh_bpe_set_bos": (None, [c_void_p, c_int]),
+    "egh_bpe_encode": (c_longlong, [c_void_p, c_char_p, c_longlong, c_void_p, c_longlong]),
+    "egh_bpe_tokenize": (c_longlong, [c_void_p, c_char_p, c_longlong, c_void_p, c_longlong]),
+    "egh_bpe_decode": (c_longlong, [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong]),
 }
 
 _lib = None

@@ -12,24 +12,27 @@ special tokens, ``tokenizer_config.json``), with the reference's rules:
 * tokens that are not in the vocabulary are dropped; BOS is put in front if ``bos_token_id >= 0``
   (src/tokenizer.cpp:129-142).
 
-The engine itself works on token ids; only ``bin/easy_llm`` with a text prompt needs this.
+The engine itself works on token ids; only ``bin/easy_llm`` with a text prompt needs this.  The rules
+run in C++ (``csrc/host/bpe_tokenizer.hpp``); this module reads the JSON files and is its face in Python.
 """
 from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import host
 
 
-def _byte_table() -> Dict[int, str]:
-    keep = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
-    table = {b: chr(b) for b in keep}
-    extra = 0
-    for b in range(256):
-        if b not in table:
-            table[b] = chr(256 + extra)
-            extra += 1
-    return table
+def _blob(strings: Sequence[str]):
+    """UTF-8 bytes of the strings in a row, and the n + 1 offsets that cut them apart."""
+    encoded = [s.encode("utf-8") for s in strings]
+    offsets = np.zeros(len(encoded) + 1, dtype=np.int64)
+    if encoded:
+        offsets[1:] = np.cumsum([len(e) for e in encoded])
+    return b"".join(encoded), offsets
 
 
 class Tokenizer:
@@ -43,11 +46,25 @@ class Tokenizer:
                 self.token_to_id[token] = idx
         self.specials.sort(key=lambda t: (-len(t), t))                       # longest first
         self.id_to_token = {i: t for t, i in self.token_to_id.items()}
-        self.rank = {pair: r for r, pair in enumerate(merges)}
         self.bos_token_id = bos_token_id
-        self.byte_to_char = _byte_table()
-        self.char_to_byte = {c: b for b, c in self.byte_to_char.items()}
-        self._cache: Dict[str, List[str]] = {}
+        self._lib = host.library()
+        self._core = self._lib.egh_bpe_create()
+        tokens = list(self.token_to_id)
+        blob, offsets = _blob(tokens)
+        ids = np.asarray([self.token_to_id[t] for t in tokens], dtype=np.int32)
+        self._lib.egh_bpe_add_tokens(self._core, blob, offsets.ctypes.data, ids.ctypes.data, len(tokens))
+        left, left_offsets = _blob([m[0] for m in merges])
+        right, right_offsets = _blob([m[1] for m in merges])
+        self._lib.egh_bpe_add_merges(self._core, left, left_offsets.ctypes.data, right, right_offsets.ctypes.data, len(merges))
+        blob, offsets = _blob(self.specials)
+        self._lib.egh_bpe_add_specials(self._core, blob, offsets.ctypes.data, len(self.specials))
+        self._lib.egh_bpe_set_bos(self._core, int(bos_token_id))
+
+    def __del__(self):
+        core = getattr(self, "_core", None)
+        if core:
+            self._core = None
+            self._lib.egh_bpe_destroy(core)
 
     @staticmethod
     def from_dir(model_dir, bos_token_id: int = -1) -> "Tokenizer":
@@ -65,66 +82,32 @@ class Tokenizer:
                     specials[info["content"]] = int(idx)
         return Tokenizer(data["model"]["vocab"], merges, specials, bos_token_id)
 
+    def _twice(self, call, first_capacity: int, dtype):
+        """Runs ``call(buffer, capacity)``, which returns how much there is; a second time if it did not fit."""
+        cap = max(16, first_capacity)
+        for _ in range(2):
+            buf = np.empty(cap, dtype=dtype)
+            n = int(call(buf.ctypes.data, cap))
+            if n <= cap:
+                return buf[:n]
+            cap = n
+        raise RuntimeError("the tokenizer's answer changed between two calls")
+
     # -- encoding -------------------------------------------------------------
-    def _merge_word(self, word: str) -> List[str]:
-        if word in self._cache:
-            return self._cache[word]
-        parts = list(word)
-        while len(parts) > 1:
-            best, where = None, -1
-            for i in range(len(parts) - 1):
-                r = self.rank.get((parts[i], parts[i + 1]))
-                if r is not None and (best is None or r < best):
-                    best, where = r, i
-            if where < 0:
-                break
-            parts[where:where + 2] = [parts[where] + parts[where + 1]]
-        self._cache[word] = parts
-        return parts
-
-    def _plain(self, text: str, first_word: bool, out: List[str]) -> bool:
-        """Tokens of a stretch without special tokens; returns whether it held a word."""
-        saw = False
-        for word in text.split():
-            raw = word if first_word else " " + word
-            first_word = False
-            saw = True
-            mapped = "".join(self.byte_to_char[b] for b in raw.encode("utf-8"))
-            out.extend(self._merge_word(mapped))
-        return saw
-
     def tokenize(self, text: str) -> List[str]:
-        out: List[str] = []
-        first_word, no_space_next, pos = True, False, 0
-        while pos < len(text):
-            hit, hit_at = None, len(text)
-            for s in self.specials:                                             # longest first; earliest wins
-                at = text.find(s, pos)
-                if at != -1 and at < hit_at:
-                    hit, hit_at = s, at
-            if hit_at > pos:
-                if self._plain(text[pos:hit_at], first_word or no_space_next, out):
-                    first_word = False
-            if hit is None:
-                break
-            out.append(hit)
-            end = hit_at + len(hit)
-            no_space_next = (hit_at > 0 and not text[hit_at - 1].isspace()) and (end < len(text) and not text[end].isspace())
-            pos = end
-        return out
+        raw = text.encode("utf-8")
+        out = self._twice(lambda buf, cap: self._lib.egh_bpe_tokenize(self._core, raw, len(raw), buf, cap), 4 * len(raw) + 64, np.uint8)
+        joined = out.tobytes()
+        return [t.decode("utf-8") for t in joined.split(b"\0")[:-1]] if joined else []
 
     def encode(self, text: str) -> List[int]:
-        ids = [self.bos_token_id] if self.bos_token_id >= 0 else []
-        ids += [self.token_to_id[t] for t in self.tokenize(text) if t in self.token_to_id]
-        return ids
+        raw = text.encode("utf-8")
+        out = self._twice(lambda buf, cap: self._lib.egh_bpe_encode(self._core, raw, len(raw), buf, cap), len(raw) + 8, np.int32)
+        return out.tolist()
 
     # -- decoding ---------------------------------------------------------------
     def decode(self, ids) -> str:
-        text = "".join(self.id_to_token.get(int(i), "") for i in ids)
-        raw = bytearray()
-        for ch in text:
-            if ch in self.char_to_byte:
-                raw.append(self.char_to_byte[ch])
-            else:
-                raw += ch.encode("utf-8")
-        return raw.decode("utf-8", errors="replace")
+        arr = np.asarray([int(i) for i in ids], dtype=np.int32)
+        out = self._twice(lambda buf, cap: self._lib.egh_bpe_decode(self._core, arr.ctypes.data, len(arr), buf, cap),
+                          8 * len(arr) + 64, np.uint8)
+        return out.tobytes().decode("utf-8", errors="replace")

@@ -44,6 +44,15 @@ def test_bytes_round_trip(tmp_path):
     assert ids == [17, 18] and tok.decode(ids) == "é"
 
 
+def test_every_kind_of_white_space_splits_words(tmp_path):
+    tok, sp = make(tmp_path)
+    for gap in ("\u00a0", "\u2003", "\u3000", "\x85", "\x1c", " \u2028\t"):
+        assert tok.tokenize("hello" + gap + "world") == ["hello", sp + "wor", "ld"], repr(gap)
+    # white space beside a special token decides whether the next word gets its space
+    assert tok.tokenize("hello<|im|>\u00a0world") == ["hello", "<|im|>", sp + "wor", "ld"]
+    assert tok.tokenize("") == [] and tok.encode("   ") == [] and tok.decode([]) == ""
+
+
 def test_missing_file(tmp_path):
     import pytest
 
