@@ -7,6 +7,7 @@
 #include <string>
 #include <vector>
 
+#include "bpe_tokenizer.hpp"
 #include "cache_core.hpp"
 #include "scheduler_core.hpp"
 #include "step_pack.hpp"
@@ -123,7 +124,30 @@ static void the_scheduler_finishes_everything_although_pages_run_out() {
     CHECK(cache.live_count() == 0 && cache.group(0).pool.free_count() == 24);
 }
 
+static void the_tokenizer_follows_the_rules() {
+    BpeTokenizer tok;
+    const std::string sp = "\xC4\xA0";                       // the stand-in of the space byte (U+0120)
+    const std::vector<std::string> vocab = {"h", "e", "l", "o", "w", "r", "d", sp, "he", "ll", "hell", "hello", sp + "w", "or",
+                                            sp + "wor", "ld", "!"};
+    for (size_t i = 0; i < vocab.size(); ++i) tok.add_token(vocab[i], (int32_t)i);
+    tok.add_token("<|im_end|>", 101);
+    const std::pair<std::string, std::string> merges[] = {{"h", "e"}, {"l", "l"}, {"he", "ll"}, {"hell", "o"}, {sp, "w"},
+                                                          {"o", "r"}, {sp + "w", "or"}, {"l", "d"}};
+    for (auto& m : merges) tok.add_merge(m.first, m.second);
+    tok.add_special("<|im_end|>");
+    CHECK((tok.tokenize("hello   \n world") == std::vector<std::string>{"hello", sp + "wor", "ld"}));
+    CHECK((tok.encode("hello world") == std::vector<int32_t>{11, 14, 15}));
+    CHECK((tok.encode("hello<|im_end|>world") == std::vector<int32_t>{11, 101, 4, 13, 15}));      // no space between specials and text
+    CHECK((tok.encode("hello <|im_end|> world") == std::vector<int32_t>{11, 101, 14, 15}));
+    CHECK((tok.encode("hello xyz") == std::vector<int32_t>{11, 7}));                              // unknown pieces are dropped
+    const std::vector<int32_t> ids = {11, 14, 15, 101};
+    CHECK(tok.decode(ids.data(), ids.size()) == "hello world<|im_end|>");
+    tok.set_bos(9);
+    CHECK(tok.encode("hello").front() == 9);
+}
+
 int main() {
+    the_tokenizer_follows_the_rules();
     pools();
     cache_with_a_window();
     a_step_is_reserved_whole_or_not_at_all();
