@@ -14,7 +14,7 @@ def test_host_runtime_in_cpp(tmp_path):
     if cxx is None:
         pytest.skip("no C++ compiler")
     exe = tmp_path / "host_runtime_test"
-    subprocess.run([cxx, "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", "-I", str(ROOT / "easy_gpt" / "cpp_b200" / "csrc" / "host"),
+    subprocess.run([cxx, "-std=c++17", "-O1", "-Wall", "-Wextra", "-I", str(ROOT / "easy_gpt" / "cpp_b200" / "csrc" / "host"),
                     str(ROOT / "tests" / "native" / "host_runtime_test.cpp"), "-o", str(exe)], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
