@@ -22,6 +22,13 @@ the whole batch.  One JSON line is printed:
 
 Inputs of a step (about 1.3 GB of weights and cache) are larger than the L2, so
 no flush is needed between steps.
+
+For profiling and for further sizes (one short line each, never the JSON line above):
+
+    python bench.py --only decode|prefill|timeline|gemm|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
+
+`serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
+decoding requests, 512 new tokens each) through GptEngine and reports wall-clock tokens a second.
 """
 from __future__ import annotations
 
