@@ -72,7 +72,7 @@ def peaks():
         try:
             d = json.loads(p.read_text())
             return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
-        except (ValueError, KeyError):
+        except (ValueError, KeyError, TypeError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
 
