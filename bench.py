@@ -494,6 +494,38 @@ def run_ours(args):
     return 0
 
 
+def run_reference(args):
+    """The unmodified reference through its own command line (baseline/reference_arm.py): the same model
+    sizes, batch, context and K last decode steps; the line has the shape of the other arm's."""
+    from baseline import reference_arm
+
+    config = dict(CONFIG_05B)
+    try:
+        folder = model_folder(config)
+        with ClockSampler() as clocks:
+            r = reference_arm.run(folder, config, args.batch, CONTEXT, args.steps, prompt_tokens=args.ref_prompt)
+    except reference_arm.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    print(json.dumps({
+        "metric": "decode tok/s", "value": round(r["tok_s"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": r["decode_steps"] - args.steps, "ms_per_step": round(r["ms_per_step"], 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "qwen2.5-0.5b-sizes-random-weights", "global_batch": args.batch, "seq_len": CONTEXT,
+                   "parallelism": "single-gpu", "layers": config["num_hidden_layers"], "layers_full": config["num_hidden_layers"],
+                   "hidden": config["hidden_size"], "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
+                   "head_dim": config["hidden_size"] // config["num_attention_heads"], "intermediate": config["intermediate_size"],
+                   "vocab": config["vocab_size"], "tied_head": True, "context_end": CONTEXT, "prompt_tokens": r["prompt_tokens"],
+                   "sampling": "greedy", "build": "cmake RelWithDebInfo, CUDA backend, sm_100",
+                   "timing": "host clock of the reference's own log lines around the last K decode steps"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(r["tok_s"], 2), "unit": "tokens/s", "note": "its loop takes and returns host token ids every step"},
+        "whole_run": {"decode_steps": r["decode_steps"], "avg_ms_per_step": r["avg_ms_per_step_whole_run"],
+                      "wall_s": round(r["wall_s"], 1)},
+    }))
+    return 0
+
+
 def main():
     global CONTEXT
     ap = argparse.ArgumentParser()
@@ -505,6 +537,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
     ap.add_argument("--sizes", choices=list(SIZES), default="0.5b", help="layer sizes for --only runs")
+    ap.add_argument("--ref-prompt", type=int, default=0,
+                    help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "serve"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
@@ -515,10 +549,7 @@ def main():
         args.warmup = 3
     CONTEXT = args.context
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a C++/CMake program without setup.py or pyproject.toml: pip cannot install it, "
-                          "and its CUDA backend names only sm_120"}))
-        return 0
+        return run_reference(args)
     return run_ours(args)
 
 
