@@ -11,8 +11,8 @@ a page back as soon as every position in it has left the window of all tokens
 still to come.  When a request ends, everything it holds is given back.
 
 Memory of a group: one tensor [caches, pages, 2 (k, v), kv_heads, page_size,
-head_dim] in the engine's dtype.  State: one float32 tensor [slots, *shape] per
-cache that asked for it, zeroed when a request takes the slot.
+head_dim] in the engine's dtype.  State: one tensor [slots, *shape] (of the dtype the
+need names) per cache that asked for it, zeroed when a request takes the slot.
 
 (The reference has no pages: its per-sample caches grow by concatenation,
 src/models/self_attn.cpp:369-389, or by doubling, src/cuda/ops/self_attn_detail.cuh:951-1022,
@@ -117,6 +117,7 @@ class CacheManager:
         self._next_named = -1
         self._needed = (ctypes.c_int * max(1, len(self.groups)))()
         self._info = (ctypes.c_int * 3)()
+        self._fresh = (ctypes.c_int * max_slots)()
         if device is not None:
             for g in self.groups:
                 # one page beyond the pool (id num_pages): rows that pad a captured batch write there
@@ -124,7 +125,7 @@ class CacheManager:
                 g.kv = torch.zeros((len(g.cache_ids), g.pool.num_pages + 1, 2, g.need.num_kv_heads, page_size, g.need.head_dim),
                                    device=device, dtype=dtype)
             for cache_id, need in self._state_needs.items():
-                self.state[cache_id] = torch.zeros((max_slots, *need.shape), device=device, dtype=torch.float32)
+                self.state[cache_id] = torch.zeros((max_slots, *need.shape), device=device, dtype=getattr(torch, need.dtype))
 
     def __del__(self):
         core = getattr(self, "core", None)
@@ -181,13 +182,24 @@ class CacheManager:
             if not known:
                 self._forget(rid, h)
             raise OutOfSlots(f"all {self.max_slots} request slots are taken")
-        self.zero_state(slot)
+        self.zero_fresh_state()
         return int(slot)
 
     def zero_state(self, slot: int) -> None:
         """A request that takes a slot starts from zeroed per-request state."""
         for t in self.state.values():
             t[slot].zero_()
+
+    def zero_fresh_state(self) -> None:
+        """Clears the state of every slot that a request has taken since the last call, whoever began
+        the request (this class, the step's reservation or the scheduler, which all begin requests in
+        the C++ bookkeeping).  The step function calls it before every forward pass, captured or not,
+        so a request never sees what the slot's former owner left (a preempted request that comes back
+        starts from zero too: its tokens are computed again)."""
+        n = self._lib.egh_cache_take_fresh(self.core, self._fresh, self.max_slots)
+        if self.state:
+            for slot in self._fresh[:n]:
+                self.zero_state(slot)
 
     def slot_of(self, rid) -> int:
         return int(self._lib.egh_cache_query(self.core, self._live_handle(rid), 0))

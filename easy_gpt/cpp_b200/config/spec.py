@@ -2,8 +2,9 @@
 
 An architecture's builder (see ``registry.register_architecture``) turns its
 typed configuration into a :class:`ModelSpec`: a list of layers, each naming
-its mixer, feed-forward, norms and position encoding by *kind* with every size
-and constant as a parameter, and a run order.  Nothing below this file knows
+its sub-layers (mixer, feed-forward, their norms and where these stand) and its
+position encoding by *kind* with every size and constant as a parameter, and a
+run order.  Nothing below this file knows
 which model it is in.
 """
 from __future__ import annotations
@@ -23,14 +24,57 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class SubLayerSpec:
+    """One residual sub-layer of a layer: a part (``role`` "mixer" or "feed_forward") and where its
+    norms stand.  With x the residual stream and f the part:
+
+    * ``norm`` given, ``norm_placement`` "pre" (the default):  x = x + f(norm(x))
+    * ``norm`` given, ``norm_placement`` "post":               x = norm(x + f(x))
+    * ``norm`` None:                                           x = x + f(x)
+    * ``output_norm`` given as well (a "sandwich"):            the part's output is normalised by it before
+      it is added: x = x + output_norm(f(norm(x)))
+    """
+    role: str
+    part: PartSpec
+    norm: Optional[PartSpec] = None
+    norm_placement: str = "pre"
+    output_norm: Optional[PartSpec] = None
+
+    def __post_init__(self):
+        if self.role not in ("mixer", "feed_forward"):
+            raise ValueError(f"a sub-layer's role is 'mixer' or 'feed_forward', not {self.role!r}")
+        if self.norm_placement not in ("pre", "post"):
+            raise ValueError(f"norm_placement is 'pre' or 'post', not {self.norm_placement!r}")
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """A pre-norm residual block: x += mixer(norm1(x)); x += ff(norm2(x)).
-    The position encoding belongs to the layer and is handed to the mixer."""
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    """A layer: residual sub-layers in the order they run (``sublayers``), and the position encoding
+    that is handed to its mixer.  The common pre-norm block x += mixer(norm1(x)); x += ff(norm2(x))
+    can be written with the four fields ``mixer``, ``feed_forward``, ``mixer_norm`` and
+    ``feed_forward_norm`` instead; ``sublayers`` is then derived from them.  A layer has at most one
+    mixer (the run order gives a layer one cache); it may have no feed-forward, or several."""
+    mixer: Optional[PartSpec] = None
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
     position: Optional[PartSpec] = None
+    sublayers: Sequence[SubLayerSpec] = ()
+
+    def __post_init__(self):
+        if not self.sublayers:
+            subs = []
+            if self.mixer is not None:
+                subs.append(SubLayerSpec("mixer", self.mixer, self.mixer_norm))
+            if self.feed_forward is not None:
+                subs.append(SubLayerSpec("feed_forward", self.feed_forward, self.feed_forward_norm))
+            object.__setattr__(self, "sublayers", tuple(subs))
+        elif self.mixer is not None or self.feed_forward is not None:
+            raise ValueError("give a layer either sublayers or mixer/feed_forward, not both")
+        if not self.sublayers:
+            raise ValueError("a layer needs at least one sub-layer")
+        if sum(s.role == "mixer" for s in self.sublayers) > 1:
+            raise ValueError("a layer has at most one mixer")
 
 
 @dataclass(frozen=True)
@@ -57,6 +101,9 @@ class ModelSpec:
     lm_head: PartSpec
     bos_token_id: int = -1
     eos_token_id: int = -1
+    # a position encoding that works on the residual stream right after the token embedding
+    # (learned absolute positions, say); None: positions reach the model through the layers' own
+    embedding_position: Optional[PartSpec] = None
 
     def __post_init__(self):
         owners = {}

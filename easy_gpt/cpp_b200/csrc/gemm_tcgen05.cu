@@ -30,6 +30,7 @@
 #define EG_NEEDS_TENSOR_MAPS
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 namespace {
 
@@ -44,29 +45,10 @@ constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 2 };
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
 // Bounded wait: false if it gave up (or another role already did).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicOr(status, EG_STATUS_WAIT_TIMEOUT);
-    return false;
+    return mbar_wait_bounded(bar, parity, abort_flag, status, WAIT_LIMIT);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -723,9 +705,6 @@ struct FewParams {
 
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
 
 // 32 columns of one token row: bias, then store / SwiGLU / float32
 __device__ __forceinline__ void few_epilogue(const FewParams& p, int row, int col0, float (&v)[32]) {

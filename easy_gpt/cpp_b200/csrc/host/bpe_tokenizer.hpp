@@ -46,11 +46,10 @@ inline uint32_t utf8_decode(const std::string& s, size_t at, int* length) {
     return cp;
 }
 
-// what splits words: the white space of the Unicode database
-inline bool is_space(uint32_t cp) {
-    return (cp >= 0x09 && cp <= 0x0D) || (cp >= 0x1C && cp <= 0x20) || cp == 0x85 || cp == 0xA0 || cp == 0x1680 ||
-           (cp >= 0x2000 && cp <= 0x200A) || cp == 0x2028 || cp == 0x2029 || cp == 0x202F || cp == 0x205F || cp == 0x3000;
-}
+// What splits words: the six ASCII white-space characters, as in the reference, which reads words with
+// `iss >> word` in the classic locale (src/bpe.cpp:32-62) and asks std::isspace about the bytes beside a
+// special token (src/tokenizer.cpp:83-90).  Other Unicode spaces (U+00A0, U+3000, ...) are bytes of a word.
+inline bool is_space(uint32_t cp) { return (cp >= 0x09 && cp <= 0x0D) || cp == 0x20; }
 
 class BpeTokenizer {
 public:

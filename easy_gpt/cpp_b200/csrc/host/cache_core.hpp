@@ -38,6 +38,7 @@ public:
     CacheCore(int page_size, int max_slots, int max_pages_per_request)
         : page_size_(page_size), max_slots_(max_slots), max_pages_(max_pages_per_request) {
         for (int s = max_slots - 1; s >= 0; --s) free_slots_.push_back(s);   // slot 0 first
+        slot_is_fresh_.assign(max_slots, 0);
     }
 
     int add_group(int num_pages, int window) {
@@ -74,8 +75,26 @@ public:
         r.slot = free_slots_.back();
         free_slots_.pop_back();
         r.first_live_page.assign(groups_.size(), 0);
+        if (!slot_is_fresh_[r.slot]) {
+            slot_is_fresh_[r.slot] = 1;
+            fresh_slots_.push_back(r.slot);
+        }
         requests_.emplace(rid, std::move(r));
         return requests_[rid].slot;
+    }
+
+    // Slots that requests have taken since the last call (each once), whoever began them: the owner of
+    // per-request state of fixed size clears those slots before the next step runs.  Writes at most cap
+    // of them to out and forgets what it wrote; returns how many were written.
+    int take_fresh_slots(int* out, int cap) {
+        int n = 0;
+        while (n < cap && !fresh_slots_.empty()) {
+            const int s = fresh_slots_.back();
+            fresh_slots_.pop_back();
+            slot_is_fresh_[s] = 0;
+            out[n++] = s;
+        }
+        return n;
     }
 
     int end_request(int64_t rid) {
@@ -228,6 +247,8 @@ private:
     int page_size_, max_slots_, max_pages_;
     std::vector<std::unique_ptr<CacheGroup>> groups_;
     std::vector<int> free_slots_;
+    std::vector<int> fresh_slots_;          // taken since take_fresh_slots() was last called
+    std::vector<char> slot_is_fresh_;
     std::unordered_map<int64_t, CachedRequest> requests_;
 };
 

@@ -43,6 +43,7 @@ EGH_API int egh_cache_add_group(void* c, int num_pages, int window) {
 EGH_API void* egh_cache_group_pool(void* c, int g) { return &static_cast<CacheCore*>(c)->group(g).pool; }
 EGH_API int32_t* egh_cache_group_table(void* c, int g) { return static_cast<CacheCore*>(c)->group(g).tables.data(); }
 EGH_API int egh_cache_begin(void* c, long long rid) { return static_cast<CacheCore*>(c)->begin_request(rid); }
+EGH_API int egh_cache_take_fresh(void* c, int* out, int cap) { return static_cast<CacheCore*>(c)->take_fresh_slots(out, cap); }
 EGH_API int egh_cache_end(void* c, long long rid) { return static_cast<CacheCore*>(c)->end_request(rid); }
 // what: 0 slot, 1 tokens committed, 2 tokens reserved
 EGH_API long long egh_cache_query(void* c, long long rid, int what) {

@@ -214,11 +214,16 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, const f
         for (int i = tid; i < vocab; i += blockDim.x) gt += order_key(row[i]) > tk;
         need_k = k - block_sum_int(gt, i_scratch);
     }
-    int eq_tk = 0;
-    for (int i = tid; i < vocab; i += blockDim.x) eq_tk += order_key(row[i]) == tk;
-    eq_tk = block_sum_int(eq_tk, i_scratch);
-    need_k = min(need_k, eq_tk);
-    // with top-k off, tk is 0 (below every real logit) and nothing equals it
+    // Key 0 is what NaN sorts as, below every real logit: it is never kept.  tk is 0 with top-k off,
+    // and with top-k on when the row has fewer than k logits that are numbers.
+    if (tk == 0u) {
+        need_k = 0;
+    } else {
+        int eq_tk = 0;
+        for (int i = tid; i < vocab; i += blockDim.x) eq_tk += order_key(row[i]) == tk;
+        eq_tk = block_sum_int(eq_tk, i_scratch);
+        need_k = min(need_k, eq_tk);
+    }
     const float p_tk = need_k > 0 ? expf((key_value(tk) - mx) * inv_t) : 0.0f;
 
     // mass of the kept tokens whose key is >= t (t >= tk is what matters)

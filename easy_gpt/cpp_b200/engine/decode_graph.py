@@ -177,6 +177,7 @@ class DecodeGraph:
         if self.staging_events[i] is None:
             self.staging_events[i] = torch.cuda.Event()
         self.staging_events[i].record()
+        cache.zero_fresh_state()             # slots taken since the last step start from zeroed state
         self.graph.replay()
         return self.logits
 

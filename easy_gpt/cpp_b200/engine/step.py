@@ -164,6 +164,7 @@ class StepRunner:
         captured, logits = self._run_captured(entries) if self.use_graphs else (False, None)
         if not captured:
             ctx, rows = self.build_context(entries)
+            self.cache.zero_fresh_state()    # slots taken since the last step (by this step or by the scheduler)
             logits = self.model.forward(ctx, self.cache, rows)
         if commit:
             for e in entries:
@@ -227,11 +228,8 @@ class StepRunner:
 
         cache = self.cache
         info = np.zeros(3, dtype=np.int32)
-        fresh = [e.request for e in entries if not cache.has_request(e.request)] if cache.state else ()
         rc = cache._lib.egh_step_reserve(cache.core, len(entries), handles.ctypes.data, counts.ctypes.data, info.ctypes.data)
         if rc == 0:
-            for r in fresh:                  # a request that takes a slot starts from zeroed state
-                cache.zero_state(cache.slot_of(r))
             return
         for e in entries:                    # names that were made for requests which did not come to life
             if not cache.has_request(e.request):

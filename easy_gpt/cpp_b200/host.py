@@ -32,6 +32,7 @@ _SIGNATURES = {
     "egh_cache_group_table": (_I32_P, [c_void_p, c_int]),
     "egh_cache_begin": (c_int, [c_void_p, c_longlong]),
     "egh_cache_end": (c_int, [c_void_p, c_longlong]),
+    "egh_cache_take_fresh": (c_int, [c_void_p, c_void_p, c_int]),
     "egh_cache_query": (c_longlong, [c_void_p, c_longlong, c_int]),
     "egh_cache_pages_needed": (c_int, [c_void_p, c_longlong, c_longlong, c_void_p]),
     "egh_cache_can_reserve": (c_int, [c_void_p, c_longlong, c_longlong, c_int]),

@@ -90,6 +90,7 @@ class _Signatures:
                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
     eg_swiglu = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]
     eg_argmax = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+    eg_wait_probe = [c_void_p, ctypes.c_uint, c_int, c_void_p, c_void_p]
     eg_sample = [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
 
 
@@ -208,12 +209,17 @@ def rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch
                inv_freq: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
                page_size: int, status: torch.Tensor) -> None:
     """Rotates q and k of qkv [T, (NH+2NKV)*HD] (q in place) and stores k, v at
-    slot_map[t] of caches shaped [pages, NKV, page_size, HD] (slices of one pool)."""
+    slot_map[t] of caches shaped [pages, NKV, page_size, HD] (slices of one pool).
+    rotary_dim 0: no rotation, only the store (inv_freq may be None)."""
     _cuda(qkv, bias, positions, slot_map, k_cache, v_cache, inv_freq, status)
     T = qkv.shape[0]
     _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "qkv row layout")
-    _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float32, "positions int32, inv_freq float32")
-    _need(inv_freq.numel() * 2 == rotary_dim, "inv_freq has rotary_dim/2 entries")
+    _need(positions.dtype == torch.int32, "positions int32")
+    if rotary_dim:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rotary_dim,
+              "inv_freq: float32 with rotary_dim/2 entries")
+    else:
+        inv_freq = None                                  # nothing is rotated: q and k pass through, k and v are stored
     page_stride = head_stride = pool_slots = 0
     if slot_map is not None:
         _need(k_cache is not None and v_cache is not None and slot_map.dtype == torch.int32, "cache and int32 slot map")
@@ -286,7 +292,23 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 PAGED_ATTENTION_HEAD_DIMS = (32, 64, 128, 256)
-SM_COUNT = 148
+_sm_count = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (launch plans hang off it).  EASY_GPT_SM_COUNT
+    sets it by hand; without a device (plans are also computed on machines that have none) it is the
+    B200's 148."""
+    global _sm_count
+    if _sm_count is None:
+        forced = os.environ.get("EASY_GPT_SM_COUNT")
+        if forced:
+            _sm_count = int(forced)
+        elif torch.cuda.is_available():
+            _sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+        else:
+            _sm_count = 148
+    return _sm_count
 
 
 def attention_paged_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -305,7 +327,7 @@ def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_c
     tiles = max(1, -(-max_context // 64))
     if forced:
         return max(1, min(int(forced), tiles, 128))
-    most = 256 if tokens <= SKINNY_MAX_TOKENS else 4 * SM_COUNT
+    most = 256 if tokens <= SKINNY_MAX_TOKENS else 4 * sm_count()
     splits = 1
     while splits * 2 * base <= most and tiles // (splits * 2) >= 4 and splits < 128:
         splits *= 2
@@ -441,7 +463,7 @@ def attention_prefill_parts(num_tiles: int, num_heads: int):
     the cut follows the contexts of the step at hand (a captured step is replayed with others).
     A part costs its CTA a start-up of some microseconds and a pass of the merge kernel, which pays
     only while there are fewer (tile, head) pairs than the two CTAs per SM."""
-    wanted = min(2 * SM_COUNT // max(1, num_tiles * num_heads), 8)
+    wanted = min(2 * sm_count() // max(1, num_tiles * num_heads), 8)
     return (wanted, PREFILL_PART_TILES) if wanted >= 2 else (1, 1 << 20)
 
 
@@ -527,11 +549,11 @@ def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
         while ks * 2 * rb <= 16 and chunks > 4 * ks:
             ks *= 2
         return rb, ks, 1
-    if n_rows >= 64 * SM_COUNT:                    # wide matrices (gate/up, the head): 64 rows per CTA
+    if n_rows >= 64 * sm_count():                    # wide matrices (gate/up, the head): 64 rows per CTA
         return 4, 2, 1                             # (sixteen warps per CTA measured slower: one CTA per SM)
     rb, ks = 1, 8
     split = max(1, min(8, round(chunks / (ks * 2.5))))
-    if -(-n_rows // 16) * split > 4 * SM_COUNT:
+    if -(-n_rows // 16) * split > 4 * sm_count():
         split = 1
     return rb, ks, split
 
@@ -569,7 +591,7 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optiona
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, tokens: Optional[int] = None,
                 plan=None, rope: Optional[dict] = None, prefetch: Optional[torch.Tensor] = None,
                 status: Optional[torch.Tensor] = None, prenormed: Optional[tuple] = None,
-                follow: Optional[dict] = None):
+                follow: Optional[dict] = None, norm=None):
     """Decode-step product out = f(x W^T + bias) for up to 64 tokens, bfloat16 weights
     streamed once.  The input is ``x`` (bfloat16 [M, K]), or the norm prologue (``resid_in``,
     optional ``delta`` and ``resid_out``, ``gain``, ``eps``), or ``prenormed`` = (xn, ss_parts)
@@ -580,9 +602,17 @@ def gemm_skinny(weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optiona
     and gain float32 [N] of the norm that follows; ``out`` is None and the call returns
     (xn, ss_parts) for the next product's ``prenormed``).  ``plan``: (row_blocks, k_slices,
     k_split), by default ``skinny_plan``.  ``prefetch``: a contiguous tensor (weights of a
-    kernel that runs soon) that this kernel asks the L2 to fetch while it works.  ``status``:
+    kernel that runs soon) that this kernel asks the L2 to fetch while it works.  ``norm``: the
+    same input given as one object with the fields eps, gain, residual, delta, residual_out,
+    prepared_rows, prepared_sums (``parts.base.NormInFront``).  ``status``:
     the step's status word, where the bounded wait for the prologue's staged input reports
     if it gives up."""
+    if norm is not None:
+        eps = norm.eps
+        if norm.prepared_rows is not None:
+            prenormed = (norm.prepared_rows, norm.prepared_sums)
+        else:
+            resid_in, resid_out, delta, gain = norm.residual, norm.residual_out, norm.delta, norm.gain
     _cuda(weight, bias, out, x, resid_in, resid_out, delta, gain, prefetch, status)
     N, K = weight.shape
     ss_in, ss_parts = None, 0
@@ -674,7 +704,7 @@ def gemm_tcgen05_takes(dtype: torch.dtype, tokens: int, out_features: int, in_fe
 def gemm_tcgen05_wide_takes(dtype: torch.dtype, tokens: int, out_features: int, in_features: int) -> bool:
     """Products wide and tall enough for the persistent 128 x 256 tile kernel (one tile per SM at least)."""
     return (USE_TCGEN05 and gemm_tcgen05_takes(dtype, tokens, out_features, in_features) and out_features % 256 == 0
-            and -(-tokens // 128) * (out_features // 256) >= SM_COUNT)
+            and -(-tokens // 128) * (out_features // 256) >= sm_count())
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -693,7 +723,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     _need(tuple(out.shape) == (M, N // 2 if swiglu_epilogue else N), "out shape")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == N), "bias float32 [N]")
     if pair:
-        tile_n = 256 if (N % 256 == 0 and (swiglu_epilogue or -(-M // 256) * (N // 256) >= SM_COUNT // 2)) else 128
+        tile_n = 256 if (N % 256 == 0 and (swiglu_epilogue or -(-M // 256) * (N // 256) >= sm_count() // 2)) else 128
         _need(N % tile_n == 0, "SwiGLU on CTA pairs takes N % 256 == 0")
         _check(library().eg_gemm_tcgen05_pair(_stream(), EPI_SWIGLU if swiglu_epilogue else EPI_STORE, _ptr(x), x.stride(0),
                                               _ptr(weight), weight.stride(0), _ptr(bias), _ptr(out), out.stride(0), M, N, K,
@@ -719,11 +749,11 @@ def gemm_tcgen05_few_plan(out_features: int, in_features: int):
         return None
     tile_n = 32
     for t in (128, 64):
-        if out_features % t == 0 and out_features // t >= 2 * SM_COUNT:
+        if out_features % t == 0 and out_features // t >= 2 * sm_count():
             tile_n = t
             break
     tiles = out_features // tile_n
-    slices = max(1, min(round(2 * SM_COUNT / tiles), in_features // 64, 8))
+    slices = max(1, min(round(2 * sm_count() / tiles), in_features // 64, 8))
     return tile_n, slices
 
 
@@ -822,6 +852,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _need(min(temperature.numel(), top_k.numel(), top_p.numel(), uniform.numel(), out.numel()) >= rows, "one value per row")
     _check(library().eg_sample(_stream(), _ptr(logits), logits.stride(0), rows, logits.shape[1], _ptr(temperature),
                                _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out)), "sample")
+
+
+def wait_probe(limit: int, threads: int, status: torch.Tensor) -> int:
+    """Launches one CTA of ``threads`` threads that all wait, through the kernels' bounded wait with a limit of
+    ``limit`` polls, on a barrier that nothing completes.  The wait runs out, EG_STATUS_WAIT_TIMEOUT is
+    set in ``status`` and the kernel returns.  Returns how many threads gave up (all of them).  For
+    tests: it shows on a healthy GPU what the host sees when a wait inside a kernel runs out."""
+    _cuda(status)
+    _need(status.dtype == torch.int32, "status int32")
+    gave_up = torch.zeros(1, dtype=torch.int32, device=status.device)
+    _check(library().eg_wait_probe(_stream(), int(limit), int(threads), _ptr(status), _ptr(gave_up)), "wait_probe")
+    return int(gave_up.item())
 
 
 def describe_status(word: int) -> str:

@@ -1,8 +1,9 @@
 """Grouped-query attention over the paged cache.
 
 Per token: q, k, v = x Wq^T + bq, ... (src/models/self_attn.cpp:225-227) as ONE
-product with the three weights stacked; q and k are rotated and k, v stored in
-the cache by one kernel; every query head h attends the keys of KV head
+product with the three weights stacked; q and k are changed by the layer's position
+encoding (a half rotation is applied by the kernel that also stores k, v in the
+cache; another encoding changes q and k itself; none is fine too); every query head h attends the keys of KV head
 h / (NH/NKV) of its own request up to its own position (optionally only the last
 ``window`` of them); the heads are concatenated head-major and projected by Wo
 (src/models/self_attn.cpp:255-258).  Scale 1/sqrt(head_dim) (:253).
@@ -84,22 +85,30 @@ class Attention(Mixer):
     accepts_pending_norm = True
     fuses_following_norm = True
 
+    @staticmethod
+    def _rotation_table(rot, ctx):
+        """cos/sin [T, rotary_dim/2, 2] of this step's positions: computed by the first layer that asks and
+        shared by every layer whose rotation has the same key."""
+        key = ("rotation table",) + tuple(rot.key) if rot.key else ("rotation table", rot.inv_freq.data_ptr())
+        if key not in ctx.scratch:
+            ctx.scratch[key] = kernels.rope_table(ctx.positions, rot.inv_freq)
+        return ctx.scratch[key]
+
     def forward(self, x, ctx: StepContext, cache: CacheView, follow=None):
         """x: the normalised input [T, hidden], or a PendingNorm that stands for it.  ``follow``: the add
         and norm that come next; the output product of a decode step takes them over."""
         T = ctx.num_tokens
         tables = ctx.groups[cache.group]
-        rot = self.position
-        if rot is None:
-            raise NotImplementedError("attention without a rotary encoding is not built")
         pending = x if isinstance(x, PendingNorm) else None
         dtype, device = ctx.dtype, ctx.device
-        if (pending is not None and pending.fusable and cache.writes and rot.rotary_dim == self.head_dim
-                and self.head_dim in (16, 32, 64, 128)):
+        # what the layer's position encoding offers: a half rotation that the kernels apply themselves,
+        # or a change of q and k of its own making, or nothing at all (no position encoding)
+        rot = self.position.half_rotation() if self.position is not None else None
+        if (pending is not None and pending.fusable and cache.writes and rot is not None
+                and rot.rotary_dim == self.head_dim and self.head_dim in (16, 32, 64, 128)):
             # decode: add + norm + QKV product + bias + rotation + cache write in one kernel
             q = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
-            kernels.gemm_skinny(self.qkv.weight, self.qkv.bias_f32, q, kernels.EPI_QKV_ROPE, tokens=T,
-                                **pending.fused_args(),
+            kernels.gemm_skinny(self.qkv.weight, self.qkv.bias_f32, q, kernels.EPI_QKV_ROPE, tokens=T, norm=pending.fused(),
                                 rope=dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                                           positions=ctx.positions, slot_map=tables.slot_map, k_cache=cache.k,
                                           v_cache=cache.v, inv_freq=rot.inv_freq, status=ctx.status))
@@ -109,12 +118,19 @@ class Attention(Mixer):
                 x = pending.materialize()
             qkv = self.qkv(x, status=ctx.status)
             store = (tables.slot_map, cache.k, cache.v) if cache.writes else (None, None, None)
-            if rot.rotary_dim == self.head_dim and self.head_dim % 8 == 0:
-                kernels.rope_cache_table(qkv, rot.table(ctx), *store, self.num_heads, self.num_kv_heads, self.head_dim,
-                                         tables.page_size, ctx.status)
-            else:
+            if rot is not None and rot.rotary_dim == self.head_dim and self.head_dim % 8 == 0:
+                kernels.rope_cache_table(qkv, self._rotation_table(rot, ctx), *store, self.num_heads, self.num_kv_heads,
+                                         self.head_dim, tables.page_size, ctx.status)
+            elif rot is not None:
                 kernels.rope_cache(qkv, None, ctx.positions, *store, rot.inv_freq, self.num_heads, self.num_kv_heads,
                                    self.head_dim, rot.rotary_dim, tables.page_size, ctx.status)
+            else:
+                if self.position is not None:
+                    q_width, k_width = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+                    self.position.apply_to_query_key(qkv[:, :q_width].view(T, self.num_heads, self.head_dim),
+                                                     qkv[:, q_width:q_width + k_width].view(T, self.num_kv_heads, self.head_dim), ctx)
+                kernels.rope_cache(qkv, None, ctx.positions, *store, None, self.num_heads, self.num_kv_heads,
+                                   self.head_dim, 0, tables.page_size, ctx.status)
         attn = torch.empty((T, self.num_heads * self.head_dim), device=device, dtype=dtype)
         longest = ctx.max_context_len if self.window is None else min(ctx.max_context_len, self.window + 255)
         if ctx.query_tiles is not None and kernels.attention_prefill_takes(dtype, self.head_dim, tables.page_size):

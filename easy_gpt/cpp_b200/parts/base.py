@@ -39,8 +39,10 @@ class PagedKVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A tensor of fixed shape per live request (float32), zeroed when a request starts."""
+    """A tensor of fixed shape per live request, zeroed when a request starts.  ``dtype`` is the name of
+    a torch dtype ("float32", "bfloat16", "int32", ...)."""
     shape: Tuple[int, ...]
+    dtype: str = "float32"
 
 
 # ---------------------------------------------------------------------------
@@ -134,8 +136,40 @@ class Part:
         return self.prefetch_hints[i] if i < len(self.prefetch_hints) else None
 
 
+@dataclass(frozen=True)
+class HalfRotation:
+    """What a rotary encoding hands to a consumer whose kernels rotate by themselves: for k <
+    rotary_dim / 2 the pair (x[k], x[k + rotary_dim / 2]) of every head turns by the angle
+    float32(position) * inv_freq[k]; dimensions from rotary_dim on pass through."""
+    inv_freq: torch.Tensor          # float32 [rotary_dim / 2] on the device
+    rotary_dim: int
+    key: tuple = ()                 # equal keys mean equal tables: consumers may share what they derive from one
+
+
 class PositionEncoding(Part):
-    """Built once per layer; the mixer calls whatever its kind offers."""
+    """How positions reach the model.  A position encoding is built once per layer (or once for the
+    embedding) and offers any of three things; a consumer asks for what it can use and every method has
+    a default that does nothing, so an encoding implements only what it is:
+
+    * ``half_rotation()``: a :class:`HalfRotation` if the encoding is a half rotation of queries and
+      keys that attention kernels can apply themselves (fused with the cache write), else None;
+    * ``apply_to_query_key(q, k, ctx)``: changes q [T, heads, head_dim] and k [T, kv heads, head_dim]
+      (views into the step's buffers) in place, for encodings that are no half rotation; it is called
+      only when ``half_rotation()`` returns None;
+    * ``add_to_embedding(residual, ctx)``: adds to the float32 residual stream [T, hidden] right
+      after the token embedding (learned absolute positions); called for the model's
+      ``embedding_position``.
+
+    Positions are ``ctx.positions`` (int32, absolute position of each token in its request)."""
+
+    def half_rotation(self) -> Optional["HalfRotation"]:
+        return None
+
+    def apply_to_query_key(self, q: torch.Tensor, k: torch.Tensor, ctx: "StepContext") -> None:
+        return None
+
+    def add_to_embedding(self, residual: torch.Tensor, ctx: "StepContext") -> None:
+        return None
 
 
 class Norm(Part):
@@ -184,7 +218,7 @@ class PendingNorm:
     """x = norm(residual + delta), not computed yet.
 
     A block hands this to a part that sets ``accepts_pending_norm``.  Such a part
-    either folds the add and the norm into its own first kernel (``fused_args``,
+    either folds the add and the norm into its own first kernel (``fused()``,
     possible when ``fusable``) or calls ``materialize`` and works on the tensor.
     Either way the sum residual + delta ends up in ``residual_after``: in place
     when materialised, in the spare buffer when fused (other CTAs of the fused
@@ -213,17 +247,34 @@ class PendingNorm:
         self.consumed = True
         return self.norm.forward(self.residual, self.delta, self.work, self.rows)
 
-    def fused_args(self) -> dict:
-        """Keyword arguments of ``kernels.gemm_skinny``'s norm prologue."""
+    def fused(self) -> "NormInFront":
+        """Hands the add and the norm over to the part, whose first kernel does both."""
         assert not self.consumed and self.fusable
         self.consumed = True
         gain, eps = self._rms
         if self.prenormed is not None:
-            return dict(prenormed=(self.prenormed.rows, self.prenormed.ss_parts), eps=eps)
+            return NormInFront(eps=eps, prepared_rows=self.prenormed.rows, prepared_sums=self.prenormed.ss_parts)
         if self.delta is not None:
             self.residual_after, self.spare_after = self.spare, self.residual
-        return dict(resid_in=self.residual, resid_out=self.spare if self.delta is not None else None,
-                    delta=self.delta, gain=gain, eps=eps)
+        return NormInFront(eps=eps, gain=gain, residual=self.residual, delta=self.delta,
+                           residual_out=self.spare if self.delta is not None else None)
+
+
+@dataclass
+class NormInFront:
+    """An add and an RMSNorm that a part's first kernel is to do itself, in one of two forms.
+    Either ``residual`` (float32 [T, hidden]), an optional ``delta`` to add to it first (the sum is
+    then also to be written to ``residual_out``, another buffer: other CTAs still read the old one),
+    ``gain`` and ``eps``.  Or ``prepared_rows`` (compute dtype [T, hidden], already gain * sum) and
+    ``prepared_sums`` (float32 [parts, padded T], partial sums of squares per token, to be added up in
+    their order) with ``eps``: only the scale 1/sqrt(mean + eps) is still missing."""
+    eps: float
+    gain: Optional[torch.Tensor] = None
+    residual: Optional[torch.Tensor] = None
+    delta: Optional[torch.Tensor] = None
+    residual_out: Optional[torch.Tensor] = None
+    prepared_rows: Optional[torch.Tensor] = None
+    prepared_sums: Optional[torch.Tensor] = None
 
 
 class Mixer(Part):

@@ -31,8 +31,9 @@ class TokenEmbedding(Part):
     def load(self, tensors, device, dtype):
         self.table = tensors[self.prefix + ".weight"].to(device=device, dtype=dtype).contiguous()
 
-    def forward(self, token_ids, residual, status):
-        kernels.embedding_gather(token_ids, self.table, residual, status)
+    def forward(self, ctx, residual):
+        """residual[t] = table[ctx.token_ids[t]] for the step's tokens (float32 [T, hidden])."""
+        kernels.embedding_gather(ctx.token_ids, self.table, residual, ctx.status)
 
 
 class LMHead(Part):
@@ -76,7 +77,7 @@ class LMHead(Part):
         if isinstance(x, PendingNorm):
             if x.fusable and self.fuse_norm:
                 out = torch.empty((x.residual.shape[0], self.vocab), device=x.residual.device, dtype=torch.float32)
-                kernels.gemm_skinny(self.linear.weight, None, out, kernels.EPI_F32, **x.fused_args())
+                kernels.gemm_skinny(self.linear.weight, None, out, kernels.EPI_F32, norm=x.fused())
                 return out
             x = x.materialize()
         return self.linear(x, out_dtype=torch.float32, status=status)

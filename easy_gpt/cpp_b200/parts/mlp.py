@@ -61,7 +61,7 @@ class SwiGLU(FeedForward):
         if isinstance(x, PendingNorm) and x.fusable:
             # decode: add + norm + gate/up product + SwiGLU in one kernel
             kernels.gemm_skinny(self.gate_up.weight, self.gate_up.bias_f32, act, kernels.EPI_SWIGLU, tokens=T,
-                                prefetch=self._hint(0), status=ctx.status, **x.fused_args())
+                                prefetch=self._hint(0), status=ctx.status, norm=x.fused())
         else:
             if isinstance(x, PendingNorm):
                 x = x.materialize()

@@ -10,7 +10,7 @@ import torch
 
 from .. import kernels
 from ..registry import register_part
-from .base import PositionEncoding
+from .base import HalfRotation, PositionEncoding
 
 
 class RotaryEncoding(PositionEncoding):
@@ -35,13 +35,8 @@ class RotaryEncoding(PositionEncoding):
     def load(self, tensors, device, dtype):
         self.inv_freq = self.inverse_frequencies(self.rotary_dim, self.theta).to(device)
 
-    def table(self, ctx) -> torch.Tensor:
-        """cos/sin [T, rotary_dim/2, 2] of this step's positions: computed by the first layer that
-        asks and shared by every layer with the same parameters."""
-        key = ("rope", self.theta, self.rotary_dim)
-        if key not in ctx.scratch:
-            ctx.scratch[key] = kernels.rope_table(ctx.positions, self.inv_freq)
-        return ctx.scratch[key]
+    def half_rotation(self) -> HalfRotation:
+        return HalfRotation(self.inv_freq, self.rotary_dim, key=("rope", self.theta, self.rotary_dim))
 
 
 register_part("position", "rope", RotaryEncoding)

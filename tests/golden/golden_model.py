@@ -24,6 +24,23 @@ CALLS = [
 ]
 
 
+# A second case for what the first cannot show: rotation angles of thousands of radians.  The same sizes with
+# RoPE base 1e6 (Qwen2.5's), one request of 2,100 tokens: 2,048 at once, a portion of 50 on that cache, two
+# single tokens.  Only the rows of KEPT_LONG are stored (the others are computed and dropped).
+CONFIG_LONG = dict(CONFIG, rope_theta=1000000.0, max_position_embeddings=4096)
+LONG_LENGTH = 2100
+CALLS_LONG = [[(0, 0, 2048)], [(0, 2048, 50)], [(0, 2098, 1)], [(0, 2099, 1)]]
+KEPT_LONG = [0, 1, 1000, 2046, 2047, 2048, 2049, 2050, 2051, 2052, 2095, 2096, 2097, 2098, 2099]
+
+
+def long_request() -> list:
+    z = (np.arange(LONG_LENGTH, dtype=np.uint64) + np.uint64(77)) * np.uint64(0x9E3779B97F4A7C15)
+    z ^= z >> np.uint64(29)
+    z *= np.uint64(0xBF58476D1CE4E5B9)
+    z ^= z >> np.uint64(32)
+    return [int(t) for t in (z % np.uint64(CONFIG["vocab_size"]))]
+
+
 def _hash_uniform(n: int, stream: int) -> np.ndarray:
     z = (np.arange(n, dtype=np.uint64) + np.uint64(stream) * np.uint64(0x100000001B3)) * np.uint64(0x9E3779B97F4A7C15)
     z ^= z >> np.uint64(30)
@@ -65,10 +82,11 @@ def weights() -> dict[str, np.ndarray]:
     return out
 
 
-def write_model_dir(folder) -> None:
+def write_model_dir(folder, config=None) -> None:
+    """The weights do not depend on the configuration's RoPE base: both cases share them."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    (folder / "config.json").write_text(json.dumps(CONFIG))
+    (folder / "config.json").write_text(json.dumps(config or CONFIG))
     header, blobs, off = {}, [], 0
     for k, v in weights().items():
         b = v.tobytes()
@@ -79,12 +97,13 @@ def write_model_dir(folder) -> None:
     (folder / "model.safetensors").write_bytes(struct.pack("<Q", len(hs)) + hs + b"".join(blobs))
 
 
-def script_text() -> str:
+def script_text(calls=None, requests=None) -> str:
+    calls, requests = calls or CALLS, requests or REQUESTS
     lines = []
-    for call in CALLS:
+    for call in calls:
         parts = [str(len(call))]
         for rid, start, n in call:
-            parts += [str(rid), str(start), str(n)] + [str(t) for t in REQUESTS[rid][start:start + n]]
+            parts += [str(rid), str(start), str(n)] + [str(t) for t in requests[rid][start:start + n]]
         lines.append(" ".join(parts))
     return "\n".join(lines) + "\n"
 

@@ -146,9 +146,13 @@ def test_rope_cache(dtype, NH, NKV, HD, rot, theta):
 
 # -- attention over the paged cache ----------------------------------------------------------
 
-def paged_case(seed, NH, NKV, HD, ps, contexts, queries, dtype, window=None, spike=None):
+def paged_case(seed, NH, NKV, HD, ps, contexts, queries, dtype, window=None, spike=None, point=None, point_strength=40.0,
+               keep_keys=False):
     """Builds a cache holding `contexts[i] + queries[i]` keys for each sequence in
-    shuffled pages, and the query tokens (the last queries[i] positions of each)."""
+    shuffled pages, and the query tokens (the last queries[i] positions of each).
+    ``point(sequence, position)`` names the key that the query at that position is aimed at (all of
+    its heads): the query becomes point_strength times that key's direction, so the key's score
+    stands out by far.  ``keep_keys``: the keys and values per sequence are returned too."""
     g = gen(seed)
     nseq = len(contexts)
     totals = [c + q for c, q in zip(contexts, queries)]
@@ -176,6 +180,17 @@ def paged_case(seed, NH, NKV, HD, ps, contexts, queries, dtype, window=None, spi
         V.append(v)
     T = sum(queries)
     q = torch.randn(T, NH, HD, generator=g)
+    if point is not None:
+        # every query head looks straight at one key of its KV head: that key's score beats all others by far
+        row = 0
+        for s in range(nseq):
+            for i in range(queries[s]):
+                j = point(s, contexts[s] + i)
+                if j is not None and 0 <= j < totals[s]:
+                    for h in range(NH):
+                        kj = K[s][j, h // (NH // NKV)]
+                        q[row + i, h] = point_strength * kj / kj.norm()
+            row += queries[s]
     token_seq = torch.tensor([s for s in range(nseq) for _ in range(queries[s])], dtype=torch.int32)
     positions = torch.tensor([contexts[s] + i for s in range(nseq) for i in range(queries[s])], dtype=torch.int32)
     if dtype == torch.bfloat16:
@@ -192,7 +207,10 @@ def paged_case(seed, NH, NKV, HD, ps, contexts, queries, dtype, window=None, spi
         full = plain_model.attention_core(qs, K[s], V[s], torch.arange(n), window)
         want[row:row + queries[s]] = full[contexts[s]:]
         row += queries[s]
-    return dict(q=q.reshape(T, NH * HD), kc=kc, vc=vc, table=table, token_seq=token_seq, positions=positions, want=want)
+    out = dict(q=q.reshape(T, NH * HD), kc=kc, vc=vc, table=table, token_seq=token_seq, positions=positions, want=want)
+    if keep_keys:
+        out.update(keys=K, values=V)
+    return out
 
 
 ATTENTION_CASES = [
@@ -298,31 +316,112 @@ def test_attention_kernels(case, dtype):
                 assert err <= tol and status.item() == 0, f"prefill tcgen05, {parts} parts of {part_tiles} tiles: {err}"
 
 
+def pointed_weight(c, NH, NKV, HD, s_keys, q_row, head, key, pos, window):
+    """Softmax weight that query row `q_row`, head `head` gives key `key` under the causal / window mask (float64)."""
+    k = s_keys[:pos + 1, head // (NH // NKV)].double()
+    scores = (k @ c["q"].float().reshape(-1, NH, HD)[q_row, head].double()) / math.sqrt(HD)
+    if window is not None:
+        scores[:max(0, pos - window + 1)] = -math.inf
+    w = torch.softmax(scores, 0)
+    return float(w[key]) if key <= pos else 0.0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_a_windows_edge(dtype):
-    """One key among hundreds carries nearly all the weight; it sits at a page's
-    edge, at a tile's edge, and right at / just outside a window's edge."""
+    """Every query head points at one key among hundreds, so that this key carries nearly all the weight
+    when it is visible: at position 0, at a page's edge, at a tile's edge, far away, and just inside /
+    just outside a window's edge.  A kernel that misses the key, or sees one it must not, is off by
+    the size of a value."""
     from easy_gpt.cpp_b200 import kernels
 
     NH, NKV, HD, ps = 4, 2, 64, 16
     scale = 1.0 / math.sqrt(HD)
     for far, window in ((0, None), (63, None), (64, None), (511, None), (600 - 100 + 1, 100), (600 - 100, 100)):
-        c = paged_case(far + 1, NH, NKV, HD, ps, [600], [1], dtype, window, spike=(far, 6.0))
-        # point the query at the spiked key: score of the far key dominates unless it is masked
-        args = {k: v.clone() for k, v in c.items()}
+        c = paged_case(far + 1, NH, NKV, HD, ps, [600], [1], dtype, window, point=lambda s, pos: far, keep_keys=True)
+        visible = window is None or far > 600 - window
+        weight = pointed_weight(c, NH, NKV, HD, c["keys"][0], 0, 1, far, 600, window)
+        v_far = c["values"][0][far].repeat_interleave(NH // NKV, dim=0).reshape(-1)
+        if visible:
+            assert weight > 0.9, (far, window, weight)
+            assert float((c["want"][0] - v_far).abs().max()) < 0.5
+        else:
+            assert weight == 0.0 and float((c["want"][0] - v_far).abs().max()) > 1.0
         status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        dev = [args[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
+        dev = [c[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
         tol = 3e-5 if dtype == torch.float32 else 3e-2
-        for name in ("generic", "paged"):
+        runs = [("generic", lambda out: kernels.attention_generic(*dev, out, NH, NKV, HD, window, scale, status))]
+        if dtype == torch.bfloat16:
+            runs += [(f"paged splits={n}", lambda out, n=n: kernels.attention_paged(*dev, out, NH, NKV, HD, window, scale, n, status))
+                     for n in (1, 3, 8)]
+        for name, run in runs:
             out = torch.zeros(1, NH * HD, dtype=dtype, device=DEV)
-            if name == "generic":
-                kernels.attention_generic(*dev, out, NH, NKV, HD, window, scale, status)
-            elif dtype == torch.bfloat16:
-                kernels.attention_paged(*dev, out, NH, NKV, HD, window, scale, 3, status)
-            else:
-                continue
+            run(out)
             err = float((out.float().cpu() - c["want"]).abs().max())
             assert err <= tol and status.item() == 0, (name, far, window, err)
+
+
+POINTED_PREFILL_CASES = [
+    # NH, NKV, HD, contexts, queries, window, which key the query at position p points at
+    (4, 2, 64, [300], [260], 100, lambda s, p: p - 99 if p % 2 == 0 else p - 100),       # just inside / just outside the window
+    (4, 2, 64, [129], [300], None, lambda s, p: (p, p + 1, p - 1)[p % 3]),                 # the diagonal, one beyond it, one before
+    (4, 2, 128, [200], [200], None, lambda s, p: (63, 64, 127, 128, 0, 191, 192)[p % 7]),  # edges of the tiles of 64 and 128 keys
+    (14, 2, 64, [0, 70], [333, 190], 150, lambda s, p: (p - 149, p - 150, p, p + 1)[p % 4] if p >= 150 else (0, p)[p % 2]),
+    (6, 2, 32, [40], [150], 33, lambda s, p: (p - 32, p - 33, p)[p % 3] if p >= 33 else p),
+]
+
+
+@pytest.mark.parametrize("case", POINTED_PREFILL_CASES)
+def test_prompt_attention_at_the_windows_edge_the_diagonal_and_tile_edges(case):
+    """The prompt-portion kernels (warp-level and tcgen05, keys cut into parts and not) on queries that each
+    point at one key: the first key inside the window or the last one outside it, the token itself or
+    the one after it, keys on both sides of a tile's edge."""
+    from easy_gpt.cpp_b200 import kernels
+
+    NH, NKV, HD, contexts, queries, window, point = case
+    ps = 16
+    c = paged_case(5, NH, NKV, HD, ps, contexts, queries, torch.bfloat16, window, point=point, keep_keys=True)
+    scale = 1.0 / math.sqrt(HD)
+    # the oracle's own sanity: the pointed key dominates where it is visible and has no weight where it is not
+    row, seen, hidden = 0, 0, 0
+    for s, (ctx, n) in enumerate(zip(contexts, queries)):
+        for i in range(0, n, 7):
+            pos = ctx + i
+            key = point(s, pos)
+            w = pointed_weight(c, NH, NKV, HD, c["keys"][s], row + i, NH - 1, key, pos, window) if 0 <= key < ctx + n else None
+            if w is None:
+                continue
+            visible = key <= pos and (window is None or key > pos - window)
+            assert (w > 0.9) if visible else (w == 0.0), (s, pos, key, w)
+            seen, hidden = seen + visible, hidden + (not visible)
+        row += n
+    assert seen > 5 and (hidden > 5 or case is POINTED_PREFILL_CASES[2])      # (the tile-edge case points at visible keys only)
+    T = c["q"].shape[0]
+    args = [c[k].to(DEV) for k in ("q", "kc", "vc", "table", "token_seq", "positions")]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tol = 3e-2
+    for tile in (64, 128):
+        tiles, t0 = [], 0
+        for s_idx, n in enumerate(queries):
+            tiles += [(s_idx, t0 + o, min(tile, n - o)) for o in range(0, n, tile)]
+            t0 += n
+        tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+        out = torch.zeros(T, NH * HD, dtype=torch.bfloat16, device=DEV)
+        kernels.attention_prefill(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window, scale, status)
+        err = float((out.float().cpu() - c["want"]).abs().max())
+        assert err <= tol and status.item() == 0, f"warp-level, tiles of {tile}: {err}"
+    if kernels.attention_prefill_tcgen05_takes(torch.bfloat16, HD, ps):
+        for parts, part_tiles in ((1, 0), (3, 1), (8, 1), (2, 2)):
+            out = torch.zeros(T, NH * HD, dtype=torch.bfloat16, device=DEV)
+            kernels.attention_prefill_tcgen05(args[0], args[1], args[2], args[3], args[5], tiles, out, NH, NKV, HD, window, scale,
+                                              status, parts=parts, part_tiles=part_tiles)
+            err = float((out.float().cpu() - c["want"]).abs().max())
+            assert err <= tol and status.item() == 0, f"tcgen05, {parts} parts of {part_tiles} tiles: {err}"
+    # the decode kernel takes the same tokens one by one
+    for splits in (1, 4):
+        out = torch.zeros(T, NH * HD, dtype=torch.bfloat16, device=DEV)
+        kernels.attention_paged(*args, out, NH, NKV, HD, window, scale, splits, status)
+        err = float((out.float().cpu() - c["want"]).abs().max())
+        assert err <= tol and status.item() == 0, f"paged, {splits} splits: {err}"
 
 
 def test_attention_flags_a_missing_page():

@@ -95,7 +95,8 @@ def test_norm_rope_feed_forward_and_head_alone(dtype, tmp_path):
     emb.load({"emb.weight": table}, DEV, dtype)
     ids = torch.randint(0, V_, (T,), generator=g, dtype=torch.int32)
     r = torch.empty(T, H_, device=DEV)
-    emb.forward(ids.to(DEV), r, ctx.status)
+    ctx.token_ids = ids.to(DEV)
+    emb.forward(ctx, r)
     assert torch.equal(r.cpu(), table[ids.long()])
     for tied in (True, False):
         head = LMHead(dict(vocab_size=V_, hidden_size=H_, tied_to="emb" if tied else None), "head")
@@ -278,7 +279,7 @@ def register_toys():
             return (y * prob[:, None]).to(x.dtype)
 
     class LearnedOffsets(PositionEncoding):
-        """Another position encoding: a learned vector per position, added by the mixer that asks for it."""
+        """Another position encoding: a learned vector per position, added to the residual stream at the embedding."""
 
         def tensor_requests(self):
             return [TensorRequest.matrix(self.prefix + ".table", self.params["max_positions"], self.params["hidden_size"])]
@@ -286,53 +287,70 @@ def register_toys():
         def load(self, tensors, device, dtype):
             self.table = tensors[self.prefix + ".table"].to(device=device, dtype=torch.float32)
 
-    class PositionedDecayingSum(DecayingSum):
-        def tensor_requests(self):
-            return super().tensor_requests() + self.position.tensor_requests()
+        def add_to_embedding(self, residual, ctx):
+            residual += self.table[ctx.positions.long()]
 
-        def load(self, tensors, device, dtype):
-            super().load(tensors, device, dtype)
-            self.position.load(tensors, device, dtype)
+    class SignFlip(PositionEncoding):
+        """A position encoding that is no half rotation: queries and keys at odd positions change sign
+        (so scores between positions of different parity are negated)."""
 
-        def forward(self, x, ctx, cache):
-            return super().forward((x.float() + self.position.table[ctx.positions.long()]).to(x.dtype), ctx, cache)
+        def apply_to_query_key(self, q, k, ctx):
+            sign = (1 - 2 * (ctx.positions % 2)).to(q.dtype)[:, None, None]
+            q.mul_(sign)
+            k.mul_(sign)
 
-    register_part("mixer", "toy_decaying_sum", PositionedDecayingSum)
+    register_part("mixer", "toy_decaying_sum", DecayingSum)
     register_part("feed_forward", "toy_top_one_experts", TopOneExperts)
     register_part("position", "toy_learned_offsets", LearnedOffsets)
+    register_part("position", "toy_sign_flip", SignFlip)
+
+
+def toy_attention(h, w, p, pos, flip=False, rotate=True):
+    """The framework's attention restated with the toy model's options: no rotation at all, or the
+    sign flip of the toy position encoding in place of it."""
+    T = h.shape[0]
+    q = (h @ w[p + ".att.q_proj.weight"].t()).reshape(T, 2, 16)
+    k = (h @ w[p + ".att.k_proj.weight"].t()).reshape(T, 1, 16)
+    v = (h @ w[p + ".att.v_proj.weight"].t()).reshape(T, 1, 16)
+    if rotate:
+        q, k = plain_model.rope(q, pos, 10000.0), plain_model.rope(k, pos, 10000.0)
+    if flip:
+        sign = (1 - 2 * (pos % 2)).float()[:, None, None]
+        q, k = q * sign, k * sign
+    return plain_model.attention_core(q, k, v, pos) @ w[p + ".att.o_proj.weight"].t()
 
 
 def toy_reference(w, ids, hidden, experts, decay, eps):
-    x = w["emb.weight"][torch.tensor(ids)]
     pos = torch.arange(len(ids))
-    for layer in range(2):
-        p = f"l{layer}"
-        if layer == 0:          # toy mixer with state + learned positions + routed experts
-            h = plain_model.rms_norm(x, w[p + ".n1.weight"], eps) + w[p + ".pos.table"][pos]
-            y = h @ w[p + ".mix.w"].t()
-            s, outs = torch.zeros(hidden), []
-            for t in range(len(ids)):
-                s = decay * s + y[t]
-                outs.append(s)
-            x = x + torch.stack(outs)
-            h = plain_model.rms_norm(x, w[p + ".n2.weight"], eps)
-            prob, choice = torch.softmax(h @ w[p + ".ff.router"].t(), -1).max(-1)
-            ex = torch.stack([w[f"{p}.ff.expert{i}"] for i in range(experts)])
-            x = x + torch.relu(torch.einsum("th,thk->tk", h, ex[choice].transpose(1, 2))) * prob[:, None]
-        else:                   # the framework's own attention and SwiGLU beside them
-            sz = dict(NH=2, NKV=1, HD=16, theta=10000.0)
-            h = plain_model.rms_norm(x, w[p + ".n1.weight"], eps)
-            x = x + plain_model.attention(h, {"L.self_attn." + k.split(".", 2)[2]: v for k, v in w.items() if k.startswith(p + ".att.")},
-                                          "L.", sz, pos, None)
-            h = plain_model.rms_norm(x, w[p + ".n2.weight"], eps)
-            x = x + plain_model.swiglu_mlp(h, {"L.mlp." + k.split(".", 2)[2]: v for k, v in w.items() if k.startswith(p + ".mlp.")}, "L.")
-    return plain_model.rms_norm(x, w["norm.weight"], eps) @ w["emb.weight"].t()
+    x = w["emb.weight"][torch.tensor(ids)] + w["pos.table"][pos]          # learned positions at the embedding
+    norm = lambda name, t: plain_model.rms_norm(t, w[name + ".weight"], eps)
+    # layer 0 (pre-norm): the toy mixer with state of its own, then routed experts
+    y = norm("l0.n1", x) @ w["l0.mix.w"].t()
+    s, outs = torch.zeros(hidden), []
+    for t in range(len(ids)):
+        s = decay * s + y[t]
+        outs.append(s)
+    x = x + torch.stack(outs)
+    h = norm("l0.n2", x)
+    prob, choice = torch.softmax(h @ w["l0.ff.router"].t(), -1).max(-1)
+    ex = torch.stack([w[f"l0.ff.expert{i}"] for i in range(experts)])
+    x = x + torch.relu(torch.einsum("th,thk->tk", h, ex[choice].transpose(1, 2))) * prob[:, None]
+    # layer 1 (post-norm): x = norm(x + attention(x)); x = norm(x + swiglu(x))
+    x = norm("l1.n1", x + toy_attention(x, w, "l1", pos))
+    x = norm("l1.n2", x + plain_model.swiglu_mlp(x, {"L.mlp." + k.split(".", 2)[2]: v for k, v in w.items() if k.startswith("l1.mlp.")}, "L."))
+    # layer 2: attention with the sign-flip encoding between two norms (a sandwich), and no feed-forward
+    x = x + norm("l2.n_out", toy_attention(norm("l2.n_in", x), w, "l2", pos, flip=True, rotate=False))
+    # layer 3: attention with no position encoding and no norm at all
+    x = x + toy_attention(x, w, "l3", pos, rotate=False)
+    return norm("norm", x) @ w["emb.weight"].t()
 
 
 def test_toy_parts_register_build_and_step(tmp_path):
-    """A model of one toy layer (mixer with state, learned positions, routed experts) and one
-    ordinary layer, built from a spec, loaded by name, stepped in portions and single tokens
-    with requests coming and going: the state slots are zeroed and kept per request."""
+    """A model of a toy layer (mixer with state, routed experts) behind learned positions at the
+    embedding, a post-norm layer, a layer with norms on both sides of its mixer, another position
+    encoding and no feed-forward, and a layer with no norm and no position encoding: built from a
+    spec alone, loaded by name, stepped in portions and single tokens with requests coming and
+    going; the state slots are zeroed and kept per request."""
     from easy_gpt.cpp_b200.config.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
     from easy_gpt.cpp_b200.engine import Model, StepRunner
     from easy_gpt.cpp_b200.weights.safetensors_io import write_safetensors
@@ -340,21 +358,31 @@ def test_toy_parts_register_build_and_step(tmp_path):
     register_toys()
     hidden, vocab, experts, decay, eps = 32, 50, 3, 0.9, 1e-5
     norm = lambda prefix: PartSpec("rmsnorm", dict(size=hidden, eps=eps), prefix)
+    from easy_gpt.cpp_b200.config.spec import SubLayerSpec
+
+    attention = lambda prefix: PartSpec("attention", dict(hidden_size=hidden, num_heads=2, num_kv_heads=1, head_dim=16,
+                                                            qkv_bias=False, out_bias=False, window=None), prefix)
     spec = ModelSpec(
         architecture="toy", vocab_size=vocab, hidden_size=hidden, max_positions=256,
         layers=(
+            # pre-norm, written with the four fields
             LayerSpec(mixer=PartSpec("toy_decaying_sum", dict(hidden_size=hidden, decay=decay), "l0.mix"),
                       feed_forward=PartSpec("toy_top_one_experts", dict(hidden_size=hidden, experts=experts), "l0.ff"),
-                      mixer_norm=norm("l0.n1"), feed_forward_norm=norm("l0.n2"),
-                      position=PartSpec("toy_learned_offsets", dict(hidden_size=hidden, max_positions=256), "l0.pos")),
-            LayerSpec(mixer=PartSpec("attention", dict(hidden_size=hidden, num_heads=2, num_kv_heads=1, head_dim=16,
-                                                       qkv_bias=False, out_bias=False, window=None), "l1.att"),
-                      feed_forward=PartSpec("swiglu", dict(hidden_size=hidden, intermediate_size=48, bias=False), "l1.mlp"),
-                      mixer_norm=norm("l1.n1"), feed_forward_norm=norm("l1.n2"),
+                      mixer_norm=norm("l0.n1"), feed_forward_norm=norm("l0.n2")),
+            # post-norm, by spec alone
+            LayerSpec(sublayers=(SubLayerSpec("mixer", attention("l1.att"), norm("l1.n1"), "post"),
+                                 SubLayerSpec("feed_forward", PartSpec("swiglu", dict(hidden_size=hidden, intermediate_size=48, bias=False), "l1.mlp"),
+                                              norm("l1.n2"), "post")),
                       position=PartSpec("rope", dict(head_dim=16, rotary_dim=16, theta=10000.0))),
+            # a norm before and a norm after the mixer, another position encoding, no feed-forward
+            LayerSpec(sublayers=(SubLayerSpec("mixer", attention("l2.att"), norm("l2.n_in"), "pre", output_norm=norm("l2.n_out")),),
+                      position=PartSpec("toy_sign_flip")),
+            # no norm and no position encoding at all
+            LayerSpec(sublayers=(SubLayerSpec("mixer", attention("l3.att")),)),
         ),
-        run_order=(RunEntry(0, 0), RunEntry(1, 1)),
+        run_order=(RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 2), RunEntry(3, 3)),
         embedding=PartSpec("embedding", dict(vocab_size=vocab, hidden_size=hidden), "emb"),
+        embedding_position=PartSpec("toy_learned_offsets", dict(hidden_size=hidden, max_positions=256), "pos"),
         final_norm=norm("norm"), lm_head=PartSpec("lm_head", dict(vocab_size=vocab, hidden_size=hidden, tied_to="emb"), "head"))
     model = Model(spec, DEV, torch.float32)
     g = torch.Generator().manual_seed(7)
@@ -365,7 +393,8 @@ def test_toy_parts_register_build_and_step(tmp_path):
     write_safetensors(tmp_path / "toy.safetensors", w.items())
     model.load_weights(tmp_path / "toy.safetensors")
     from easy_gpt.cpp_b200.parts.base import PagedKVNeed, StateNeed
-    assert model.cache_needs() == {0: StateNeed((hidden,)), 1: PagedKVNeed(1, 16, None)}
+    kv = PagedKVNeed(1, 16, None)
+    assert model.cache_needs() == {0: StateNeed((hidden,)), 1: kv, 2: kv, 3: kv}
 
     requests = {f"r{i}": np.random.default_rng(i).integers(0, vocab, n).tolist() for i, n in enumerate([40, 23, 64, 31, 12])}
     refs = {rid: toy_reference(w, ids, hidden, experts, decay, eps).numpy() for rid, ids in requests.items()}

@@ -27,6 +27,24 @@ def test_plain_matches_reference_logits():
         assert (mine.argmax(-1) == ref.argmax(-1)).all()
 
 
+def test_plain_matches_reference_logits_at_positions_in_the_thousands():
+    """RoPE base 1e6 over 2,100 positions (angles of thousands of radians), with a portion of 50 tokens
+    and two single tokens on top of a cache of 2,048: the reference's own 32-bit CPU logits at the rows
+    of golden_model.KEPT_LONG."""
+    ref = np.load(Path(__file__).parent / "golden" / "ref_logits_long.npy")
+    with tempfile.TemporaryDirectory() as tmp:
+        golden_model.write_model_dir(tmp, golden_model.CONFIG_LONG)
+        cfg, w = plain_model.read_model_dir(tmp)
+    assert cfg["rope_theta"] == 1e6
+    ids = golden_model.long_request()
+    with torch.no_grad():
+        mine = plain_model.forward_logits(cfg, w, ids, round_scores_like_reference=True).numpy()[golden_model.KEPT_LONG]
+    assert mine.shape == ref.shape
+    err = np.abs(mine - ref).max()
+    assert err < 2e-5, err
+    assert (mine.argmax(-1) == ref.argmax(-1)).all()
+
+
 def test_plain_float64_agrees_with_float32():
     with tempfile.TemporaryDirectory() as tmp:
         golden_model.write_model_dir(tmp)

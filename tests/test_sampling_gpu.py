@@ -100,3 +100,32 @@ def test_distribution_over_many_draws():
     freq = np.bincount(out.cpu().numpy(), minlength=vocab) / n
     p = plain_model.sampling_distribution(row, 0.7, 6, 0.9)
     assert np.abs(freq - p).max() < 0.03 and (freq[p == 0] == 0).all()
+
+
+@pytest.mark.parametrize("top_k,top_p", [(0, 1.0), (5, 1.0), (0, 0.8), (600, 0.9)])
+def test_a_nan_logit_is_never_drawn(top_k, top_p):
+    """A NaN in a row is left out at every temperature, as the greedy path leaves it out: the drawn
+    token follows the plain rule over the other logits."""
+    from easy_gpt.cpp_b200 import kernels
+
+    vocab, rows = 500, 16
+    rng = np.random.default_rng(top_k + 7)
+    logits = torch.from_numpy(rng.normal(0, 2.0, size=(rows, vocab)).astype(np.float32))
+    nan_at = [int(logits[r].argmax()) if r % 2 else 3 * r for r in range(rows)]       # the would-be winner, or any place
+    for r in range(rows):
+        logits[r, nan_at[r]] = float("nan")
+        logits[r, (nan_at[r] + 250) % vocab] = float("nan")
+    us = torch.tensor([uniform(5, r, 1) for r in range(rows)], dtype=torch.float32)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    kernels.sample(logits.cuda(), torch.full((rows,), 0.9).cuda(), torch.full((rows,), top_k, dtype=torch.int32).cuda(),
+                   torch.full((rows,), top_p).cuda(), us.cuda(), out)
+    exact = 0
+    for r, tok in enumerate(out.tolist()):
+        assert not np.isnan(float(logits[r, tok])), (r, tok)
+        clean = torch.nan_to_num(logits[r], nan=-1e30)
+        p = plain_model.sampling_distribution(clean, 0.9, top_k, top_p)
+        assert p[nan_at[r]] == 0.0
+        edge = plain_model.sampling_distribution(clean, 0.9, top_k, min(1.0, top_p + 1e-4))
+        assert edge[tok] > 0.0, (r, tok)
+        exact += tok == plain_model.sample_token(clean, 0.9, top_k, top_p, float(us[r]))
+    assert exact >= rows - 1

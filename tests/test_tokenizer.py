@@ -1,19 +1,25 @@
 """The command line's tokenizer against the reference's rules, on a handmade vocabulary (no GPU)."""
 import json
+from pathlib import Path
 
 from easy_gpt.cpp_b200.tokenizer import Tokenizer
+from golden import golden_tokenizer
 
 
 def make(tmp_path):
-    space = "Ġ"                                                  # the stand-in of the space byte
-    vocab = {t: i for i, t in enumerate(["h", "e", "l", "o", "w", "r", "d", space, "he", "ll", "hell", "hello",
-                                         space + "w", "or", space + "wor", "ld", "!", "Ã", "©"])}
-    merges = ["h e", "l l", "he ll", "hell o", space + " w", "o r", space + "w or", "l d"]
-    (tmp_path / "tokenizer.json").write_text(json.dumps({"model": {"vocab": vocab, "merges": merges}}))
-    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"added_tokens_decoder": {
-        "100": {"content": "<|im_start|>", "special": True}, "101": {"content": "<|im_end|>", "special": True},
-        "102": {"content": "<|im|>", "special": True}, "103": {"content": "<tool>", "special": False}}}))
-    return Tokenizer.from_dir(tmp_path), space
+    golden_tokenizer.write_files(tmp_path)
+    return Tokenizer.from_dir(tmp_path), golden_tokenizer.SPACE
+
+
+def test_same_tokens_and_ids_as_the_references_own_tokenizer(tmp_path):
+    """tests/golden/ref_tokens.json is what the reference's Tokenizer (src/tokenizer.cpp, src/bpe.cpp), compiled
+    on the CPU by tests/golden/make_golden.py, made of these texts with this vocabulary."""
+    tok, _ = make(tmp_path)
+    golden = json.loads((Path(__file__).parent / "golden" / "ref_tokens.json").read_text())
+    assert len(golden) == len(golden_tokenizer.TEXTS)
+    for text, want in zip(golden_tokenizer.TEXTS, golden):
+        assert tok.tokenize(text) == want["tokens"], repr(text)
+        assert tok.encode(text) == want["ids"], repr(text)
 
 
 def test_words_merges_and_spaces(tmp_path):
@@ -44,12 +50,17 @@ def test_bytes_round_trip(tmp_path):
     assert ids == [17, 18] and tok.decode(ids) == "é"
 
 
-def test_every_kind_of_white_space_splits_words(tmp_path):
+def test_only_ascii_white_space_splits_words(tmp_path):
+    """The reference splits on the classic locale's white space (src/bpe.cpp:32-62): space, tab, newline,
+    vertical tab, form feed, carriage return.  Other Unicode spaces are bytes of the word they stand in."""
     tok, sp = make(tmp_path)
-    for gap in ("\u00a0", "\u2003", "\u3000", "\x85", "\x1c", " \u2028\t"):
+    for gap in (" ", "\t", "\n", "\v", "\f", "\r", " \r\n\t "):
         assert tok.tokenize("hello" + gap + "world") == ["hello", sp + "wor", "ld"], repr(gap)
+    for gap in ("\u00a0", "\u2003", "\u3000", "\x85", "\x1c"):
+        tokens = tok.tokenize("hello" + gap + "world")
+        assert tokens[0] == "hello" and tokens[-3:] == ["w", "or", "ld"] and len(tokens) > 4, repr(gap)
     # white space beside a special token decides whether the next word gets its space
-    assert tok.tokenize("hello<|im|>\u00a0world") == ["hello", "<|im|>", sp + "wor", "ld"]
+    assert tok.tokenize("hello<|im|> world") == ["hello", "<|im|>", sp + "wor", "ld"]
     assert tok.tokenize("") == [] and tok.encode("   ") == [] and tok.decode([]) == ""
 
 

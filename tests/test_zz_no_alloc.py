@@ -9,6 +9,7 @@ so that a run that stops at the first failure has run every other test before it
 alone in a fresh process as well."""
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
@@ -25,6 +26,13 @@ def load():
     lib.eg_argmax_noalloc_message.argtypes = [ctypes.c_int]
     lib.eg_argmax_noalloc_message.restype = ctypes.c_char_p
     return lib
+
+
+def lowest_index_of_the_maximum(logits: torch.Tensor) -> np.ndarray:
+    """The rule on the CPU, by numpy: NaN never wins; a row without any number that can win gives 0."""
+    a = logits.detach().float().cpu().numpy()
+    a = np.where(np.isnan(a), -np.inf, a)
+    return np.argmax(a, axis=1).astype(np.int32)
 
 
 def call(lib, logits, out):
@@ -55,6 +63,45 @@ def test_matches_the_existing_entry_point_twice_in_a_row(rows, vocab):
         torch.cuda.synchronize()
         assert torch.equal(got, want), (attempt, got[:8].tolist(), want[:8].tolist())     # token ids: exact
         assert got[0].item() == 3
+        assert np.array_equal(got.cpu().numpy(), lowest_index_of_the_maximum(logits))     # and the rule itself, by numpy
+
+
+def test_rows_without_a_winner_a_row_stride_and_stale_scratch():
+    """Against numpy alone: a row of NaN only and a row of -inf only (both give token 0, like the CPU
+    rule over NaN-masked logits), rows that are a column slice of a wider tensor (row stride larger
+    than the vocabulary), and a small call right after the largest one, whose partial results are
+    still in the array."""
+    lib = load()
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(256, 151936, generator=g).cuda()
+    out = torch.full((256,), -7, dtype=torch.int32, device="cuda")
+    assert call(lib, big, out) == 0
+    small = torch.randn(3, 20000, generator=g).cuda()                        # fewer blocks a row, fewer rows: stale partials all around
+    small[1, 19999] = 9.0
+    got = torch.full((3,), -7, dtype=torch.int32, device="cuda")
+    assert call(lib, small, got) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), lowest_index_of_the_maximum(big))
+    assert np.array_equal(got.cpu().numpy(), lowest_index_of_the_maximum(small)) and got[1].item() == 19999
+    odd = torch.randn(6, 9000, generator=g)
+    odd[0] = float("nan")
+    odd[1] = float("-inf")
+    odd[2, :4500] = float("nan")
+    odd[3, 17] = float("inf")
+    odd[4, 8999] = odd[4].max() + 1
+    odd = odd.cuda()
+    got = torch.full((6,), -7, dtype=torch.int32, device="cuda")
+    assert call(lib, odd, got) == 0
+    want = lowest_index_of_the_maximum(odd)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want) and want[0] == 0 and want[1] == 0 and want[3] == 17
+    wide = torch.randn(5, 12000, generator=g).cuda()
+    part = wide[:, 1000:9001]                                                # 8001 columns, row stride 12000
+    assert part.stride(0) == 12000 and not part.is_contiguous()
+    got = torch.full((5,), -7, dtype=torch.int32, device="cuda")
+    assert call(lib, part, got) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), lowest_index_of_the_maximum(part))
 
 
 def test_refuses_more_rows_than_its_scratch_holds():

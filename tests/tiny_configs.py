@@ -58,7 +58,30 @@ CONFIG_E = {
 }
 RANDOM_E = dict(seed=9, std=0.08, bias_std=0.05, gain_std=0.1)
 
-CONFIGS = {"A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D),
+# The two tiny configurations of the benchmark description, word for word.
+# Tiny A: 2 layers, hidden 64, 4 query heads, 2 KV heads, head size 16, intermediate 160, vocabulary 256, RoPE base
+# 10000, eps 1e-6, QKV bias, tied, max positions 128, no window; weights and biases N(0, 0.02) from seed 0, gains 1.
+CONFIG_TINY_A = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "intermediate_size": 160, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 128, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_TINY_A = dict(seed=0, std=0.02, bias_std=0.02, gain_std=0.0)
+# Tiny B: 3 layers, hidden 128, 4 query heads on 1 KV head, head size 32, intermediate 352, vocabulary 384, RoPE base
+# 1e6, eps 1e-5, QKV bias, untied head, max positions 256, no window; weights N(0, 0.02), biases N(0, 0.05) from
+# seed 3, gains 1 + N(0, 0.1).
+CONFIG_TINY_B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 1,
+    "intermediate_size": 352, "vocab_size": 384, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 256, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_TINY_B = dict(seed=3, std=0.02, bias_std=0.05, gain_std=0.1)
+
+CONFIGS = {"TINY_A": (CONFIG_TINY_A, RANDOM_TINY_A), "TINY_B": (CONFIG_TINY_B, RANDOM_TINY_B), "A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D),
            "E": (CONFIG_E, RANDOM_E)}
 
 
