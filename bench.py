@@ -9,16 +9,18 @@ layers, hidden 896, 14 query heads, 2 KV heads, head size 64, intermediate
 requests and contexts that end at 4096 tokens.  A "step" is one decode step of
 the whole batch.  One JSON line is printed:
 
-  value      decoded tokens per second, timed on the device with CUDA events
-             around exactly K steps (token ids fed back on the device)
-  e2e        the same through GptEngine.step(), the call a user makes: every step
-             the packed batch metadata goes up from pinned host memory and the
-             sampled token ids come back to the host (read one step late: decode
+  value      decoded tokens per second: K calls of GptEngine.step(), the call a user
+             makes, timed on the device with CUDA events (median of three runs of K)
+  e2e        the same loop by the wall clock until the last tokens are on the host:
+             every step the packed batch metadata goes up from pinned host memory and
+             the sampled token ids come back to the host (read one step late: decode
              steps are pipelined and the device feeds itself the token ids)
   prefill    one prompt of 2,048 tokens in one step
   roofline   bytes the decode step has to read (every weight once, the cache of
              the live requests) / its time, against the measured copy bandwidth
-  points     decode at batch 1 and 64
+  points     decode at batch 1 and 64 (points_roofline: their fractions of the HBM
+             roofline), and the main batch with the engine's default options
+  fp32       the 32-bit path's decode step at the same batch, for information
 
 Inputs of a step (about 1.3 GB of weights and cache) are larger than the L2, so
 no flush is needed between steps.
@@ -155,100 +157,88 @@ def prepare_decode(engine, batch, start_context, new_tokens, vocab, seed):
     return reqs
 
 
-def time_decode_device(engine, reqs, steps, warmup):
-    """K decode steps with the sampled tokens fed back on the device: no host round
-    trip inside the timed region.  Returns (seconds, launches of our kernels, bytes read per step)."""
+def time_steps(engine, reqs, steps):
+    """K decode steps through GptEngine.step(), the product's own loop (scheduler, captured step, sampling
+    kernel, tokens read by the host one step late while the device feeds itself).  Returns (seconds on the
+    device by CUDA events around the K steps, wall-clock seconds until the last step's tokens are on the
+    host, launches of our kernels, bytes a step has to read on average)."""
     import torch
 
     from easy_gpt.cpp_b200 import kernels
 
-    runner, cache, sampler = engine.runner, engine.runner.cache, engine.sampler
-    rids = [r.id for r in reqs]
-    n = len(rids)
-    graph = runner.decode_graph(n)
-    tokens = [r.tokens[-1] for r in reqs]
-    bytes_per_step = []
-
-    def one_step(first):
-        for rid in rids:
-            cache.reserve(rid, 1)
-        logits = graph.replay(rids, tokens, tokens_on_device=not first)
-        kernels.argmax(logits[:n], sampler._out)
-        graph.set_tokens_from_device(sampler._out[:n])
-        for rid in rids:
-            cache.commit(rid, 1)
-
-    one_step(True)
-    for _ in range(warmup - 1):
-        one_step(False)
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cache = engine.runner.cache
     kv_per_token = cache.kv_bytes_per_token()
     weights = engine.model.weight_bytes_per_step()
-    before = kernels.launch_count
-    start.record()
-    for _ in range(steps):
-        bytes_per_step.append(weights + kv_per_token * sum(cache.length_of(r) + 1 for r in rids))
-        one_step(False)
-    stop.record()
-    torch.cuda.synchronize()
-    launches = (kernels.launch_count - before) + steps * graph.launches
-    # keep the scheduler's view in step with what was decoded here
-    final = sampler.to_host(sampler._out[:n])
-    for r, t in zip(reqs, final):
-        extra = cache.length_of(r.id) - r.computed
-        engine.scheduler.advance_decoded(r, [0] * (extra - 1) + [t])
-    return start.elapsed_time(stop) / 1e3, launches, sum(bytes_per_step) / len(bytes_per_step)
-
-
-def time_decode_e2e(engine, reqs, steps, warmup):
-    """K steps through GptEngine.step(): host token ids in (pinned staging, one copy
-    per step), sampled token ids read back to the host every step."""
-    import torch
-
-    for _ in range(warmup):
-        engine.step()
+    rids = [r.id for r in reqs]
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0, replays0 = kernels.launch_count, engine.runner.graph_replays
+    # step s (from 0) reads the weights once and the keys and values of every request: what it held before, plus s + 1
+    held = sum(cache.length_of(r) for r in rids)
+    step_bytes = steps * weights + kv_per_token * (steps * held + len(rids) * steps * (steps + 1) // 2)
     t0 = time.perf_counter()
     start.record()
     for _ in range(steps):
         engine.step()
-    engine.sync()                       # the last step's tokens have reached the host
     stop.record()
-    torch.cuda.synchronize()
+    engine.sync()                       # the last step's tokens have reached the host
     wall = time.perf_counter() - t0
-    return max(start.elapsed_time(stop) / 1e3, wall)
+    torch.cuda.synchronize()
+    replays = engine.runner.graph_replays - replays0
+    assert replays == steps, "the timed steps did not go through the captured decode step"
+    launches = (kernels.launch_count - launches0) + replays * engine.runner.last_graph.launches
+    return start.elapsed_time(stop) / 1e3, wall, launches, step_bytes / steps
 
 
-def measure_decode(folder, config, batch, steps, warmup, want_e2e):
+def median(values):
+    values = sorted(values)
+    return values[len(values) // 2]
+
+
+REPEATS = 3
+
+
+def measure_decode(folder, config, batch, steps, warmup, want_e2e, dtype="bfloat16", default_options=False):
+    """Decode steps that end at CONTEXT tokens: W warm-up steps, then REPEATS runs of K steps timed on the
+    device (the median is reported) and, with want_e2e, REPEATS more runs timed by the wall clock.
+    ``default_options``: the engine's own defaults for page size and request length instead of pages of
+    64 tokens and requests sized for this run."""
     import torch
 
     from easy_gpt.cpp_b200.engine import GptEngine
 
-    total_steps = warmup + steps + (warmup + steps if want_e2e else 0) + 4
-    start_context = CONTEXT - (2 * (warmup + steps) + 4 if want_e2e else warmup + steps + 4)
+    runs = REPEATS * (2 if want_e2e else 1)
+    total_steps = warmup + runs * steps + 4
+    start_context = CONTEXT - total_steps
     # the prompts are prefilled in large steps, so that the requests admitted first decode only a few tokens
     # while the others' prompts are still on their way (those tokens get room of their own)
     prefill_budget = 32768
     room = CONTEXT + 64 + -(-batch * start_context // prefill_budget) + 1
-    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (room + 63), max_active=batch,
-                       prefill_batch=batch, max_batch_tokens=prefill_budget, chunk_size=4096, max_tokens_per_request=room)
+    options = dict(cache_tokens=batch * (room + 63), max_active=batch, prefill_batch=batch, max_batch_tokens=prefill_budget,
+                   chunk_size=4096)
+    if not default_options:
+        options.update(page_size=64, max_tokens_per_request=room)
+    engine = GptEngine(folder, dtype=dtype, **options)
     reqs = prepare_decode(engine, batch, start_context, total_steps + 64, config["vocab_size"], seed=batch)
     out = {}
+    for _ in range(warmup):
+        engine.step()
     with ClockSampler() as clocks:
-        seconds, launches, step_bytes = time_decode_device(engine, reqs, steps, warmup)
+        timed = [time_steps(engine, reqs, steps) for _ in range(REPEATS)]
     out["clocks"] = clocks.summary()
-    out["seconds"], out["launches"], out["step_bytes"] = seconds, launches, step_bytes
+    seconds = median([t[0] for t in timed])
+    out["seconds"], out["launches"], out["step_bytes"] = seconds, timed[0][2], median([t[3] for t in timed])
     out["tok_s"] = batch * steps / seconds
-    out["context_end"] = max(engine.runner.cache.length_of(r.id) for r in reqs)
+    out["repeats_ms"] = [round(1e3 * t[0] / steps, 4) for t in timed]
     if want_e2e:
-        e2e_seconds = time_decode_e2e(engine, reqs, steps, warmup)
-        out["e2e_tok_s"] = batch * steps / e2e_seconds
+        walls = [max(t[0], t[1]) for t in (time_steps(engine, reqs, steps) for _ in range(REPEATS))]
+        out["e2e_tok_s"] = batch * steps / median(walls)
         # per step: the packed metadata of the batch goes up, the sampled tokens come back
-        graph = engine.runner.decode_graph(batch)
-        out["h2d"] = graph.size * 4
+        out["h2d"] = engine.runner.last_graph.size * 4
         out["d2h"] = batch * 4
+    out["context_end"] = max(engine.runner.cache.length_of(r.id) for r in reqs)
+    out["page_size"] = engine.runner.cache.page_size
+    engine.sync()
     engine.runner.check_status()
     del engine
     torch.cuda.empty_cache()
@@ -440,10 +430,14 @@ def run_ours(args):
     pk = peaks()
     folder = model_folder(config)
     if args.only == "decode":
-        r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False)
-        print(json.dumps({"only": "decode", "sizes": args.sizes, "batch": args.batch, "layers": config["num_hidden_layers"], "context": CONTEXT,
+        r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False, dtype=args.dtype,
+                           default_options=args.default_options)
+        gb_s = r["step_bytes"] / (r["seconds"] / args.steps) / 1e9
+        print(json.dumps({"only": "decode", "sizes": args.sizes, "dtype": args.dtype, "batch": args.batch,
+                          "layers": config["num_hidden_layers"], "context": CONTEXT, "page_size": r["page_size"],
                           "tok_s": round(r["tok_s"], 1), "ms_per_step": round(1e3 * r["seconds"] / args.steps, 4),
-                          "gb_s": round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9, 1)}))
+                          "repeats_ms_per_step": r["repeats_ms"], "gb_s": round(gb_s, 1),
+                          "roofline_frac": round(gb_s / pk["hbm_gbs"], 4), "peaks": pk["source"], "clocks": r["clocks"]}))
         return 0
     if args.only == "serve":
         print(json.dumps({"only": "serve", "sizes": args.sizes, "layers": config["num_hidden_layers"],
@@ -454,15 +448,24 @@ def run_ours(args):
     if args.only == "gemm":
         return print_gemm_comparison(config)
     if args.only == "prefill":
-        s = measure_prefill(folder, config)
+        sec = measure_prefill(folder, config)
+        flops = prefill_flops(config, PREFILL_TOKENS)
         print(json.dumps({"only": "prefill", "sizes": args.sizes, "tokens": PREFILL_TOKENS, "layers": config["num_hidden_layers"],
-                          "ms": round(s * 1e3, 3), "tflops": round(prefill_flops(config, PREFILL_TOKENS) / s / 1e12, 1)}))
+                          "ms": round(sec * 1e3, 3), "tok_s": round(PREFILL_TOKENS / sec, 1), "tflops": round(flops / sec / 1e12, 1),
+                          "frac": round(flops / sec / (pk["bf16_tflops"] * 1e12), 4), "peaks": pk["source"]}))
         return 0
     main = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=True)
-    points = {}
+    points, points_roofline = {}, {}
     for b in (1, 64):
         r = measure_decode(folder, config, b, args.steps, args.warmup, want_e2e=False)
         points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        points_roofline[f"decode_b{b}"] = round(r["step_bytes"] / (r["seconds"] / args.steps) / 1e9 / pk["hbm_gbs"], 4)
+    # the same batch with the engine's own defaults for page size and request length (what a user gets unasked)
+    r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False, default_options=True)
+    points[f"decode_b{args.batch}_default_options"] = round(r["tok_s"], 1)
+    # the 32-bit path, for information (its own FFMA products: no tensor cores)
+    fp32_steps = min(args.steps, 16)
+    r32 = measure_decode(folder, config, args.batch, fp32_steps, 3, want_e2e=False, dtype="float32")
     prefill_s = measure_prefill(folder, config)
     flops = prefill_flops(config, PREFILL_TOKENS)
     achieved = main["step_bytes"] / (main["seconds"] / args.steps) / 1e9
@@ -477,10 +480,11 @@ def run_ours(args):
             "hidden": config["hidden_size"], "heads": config["num_attention_heads"],
             "kv_heads": config["num_key_value_heads"], "head_dim": config["hidden_size"] // config["num_attention_heads"],
             "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "tied_head": True,
-            "context_end": main["context_end"], "page_size": 64, "prefill_tokens": PREFILL_TOKENS,
-            "l2": "inputs of a step exceed L2", "sampling": "greedy",
+            "context_end": main["context_end"], "page_size": main["page_size"], "prefill_tokens": PREFILL_TOKENS,
+            "l2": "inputs of a step exceed L2", "sampling": "greedy", "repeats": f"median of {REPEATS}",
         },
         "clocks": main["clocks"],
+        "repeats_ms_per_step": main["repeats_ms"],
         "e2e": {"value": round(main["e2e_tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
                 "d2h_bytes_per_step": main["d2h"]},
         "gpu_launches": main["launches"],
@@ -489,6 +493,9 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "points": points,
+        "points_roofline": points_roofline,
+        "fp32": {"ms_per_step": round(1e3 * r32["seconds"] / fp32_steps, 3), "value": round(r32["tok_s"], 1), "unit": "tokens/s",
+                 "steps": fp32_steps, "note": "the 32-bit path at the same batch and context, for information"},
     }
     print(json.dumps(line))
     return 0
@@ -537,6 +544,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
     ap.add_argument("--sizes", choices=list(SIZES), default="0.5b", help="layer sizes for --only runs")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="precision of --only decode")
+    ap.add_argument("--default-options", action="store_true",
+                    help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "serve"], default=None,

@@ -51,6 +51,15 @@ EGH_API long long egh_cache_query(void* c, long long rid, int what) {
     if (!r) return UNKNOWN_REQUEST;
     return what == 0 ? r->slot : what == 1 ? r->length : r->reserved;
 }
+// the most tokens committed to the cache among the given requests (one that is not live holds none)
+EGH_API long long egh_cache_max_length(void* c, int n, const long long* rids) {
+    long long most = 0;
+    for (int i = 0; i < n; ++i) {
+        const CachedRequest* r = static_cast<CacheCore*>(c)->find(rids[i]);
+        if (r && r->length > most) most = r->length;
+    }
+    return most;
+}
 EGH_API int egh_cache_pages_needed(void* c, long long rid, long long new_tokens, int* out) {
     return static_cast<CacheCore*>(c)->pages_needed(rid, new_tokens, out);
 }

@@ -198,6 +198,8 @@ inline int pack_replay(const CacheCore& cache, int n, const int64_t* rids, const
     for (int i = 0; i < n; ++i) {
         req[i] = cache.find(rids[i]);
         if (!req[i]) return UNKNOWN_REQUEST;
+        // the graph's block table is as wide as the context bucket it was captured for
+        if ((req[i]->length + counts[i] + ps - 1) / ps > table_width) return TOO_LONG;
         buf[off_context + i] = (int32_t)req[i]->length;
         buf[off_slots + i] = req[i]->slot;
         for (int k = 0; k < counts[i]; ++k, ++t) buf[off_positions + t] = (int32_t)(req[i]->length + k);

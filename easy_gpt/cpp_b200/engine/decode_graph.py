@@ -26,6 +26,18 @@ from .. import host, kernels
 from ..parts.base import GroupTables, StepContext
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+MIN_CONTEXT_BUCKET = 512           # tokens: shorter contexts share the smallest captured step
+
+
+def context_pages(tokens: int, page_size: int, most: int) -> int:
+    """Block-table width (pages) of the captured step that serves requests of up to ``tokens`` tokens:
+    the next power of two of tokens, at least MIN_CONTEXT_BUCKET, at most what a request may hold.
+    A request outgrows its bucket log2(length) times in its life, and each bucket's step is planned
+    for the contexts it really sees, not for the longest a request may ever get."""
+    bucket = MIN_CONTEXT_BUCKET
+    while bucket < tokens:
+        bucket *= 2
+    return max(1, min(most, -(-bucket // page_size)))
 
 
 def bucket_for(n: int) -> int:
@@ -40,7 +52,10 @@ class DecodeGraph:
     are wanted.  ``padded`` (decode buckets): fewer entries than the signature's may be replayed; the
     rest are padding rows."""
 
-    def __init__(self, runner, counts: Sequence[int], wants: Sequence[Sequence[int]], padded: bool):
+    def __init__(self, runner, counts: Sequence[int], wants: Sequence[Sequence[int]], padded: bool, table_width: int = 0):
+        """``table_width``: pages per block-table row that the captured step carries (0: as many as a request
+        may hold).  The step serves requests of up to table_width * page_size tokens; its launch plans
+        (how many CTAs share a request's keys) are made for that context length."""
         self.runner = runner
         self.counts = [int(c) for c in counts]
         self.padded = padded
@@ -49,7 +64,8 @@ class DecodeGraph:
         self.all_decode = all(c == 1 for c in self.counts)
         cache = runner.cache
         dev = runner.device
-        self.widths = {g.index: cache.max_pages_per_request for g in cache.groups}
+        self.table_width = W = min(table_width, cache.max_pages_per_request) if table_width else cache.max_pages_per_request
+        self.widths = {g.index: W for g in cache.groups}
         layout = [("token_ids", T), ("positions", T), ("seq_context", n), ("seq_slots", n)]
         for g in cache.groups:
             layout += [(f"slot_map{g.index}", T), (f"table{g.index}", n * self.widths[g.index])]
@@ -85,7 +101,7 @@ class DecodeGraph:
             groups={g.index: GroupTables(g.page_size, view(f"table{g.index}").view(n, self.widths[g.index]),
                                          view(f"slot_map{g.index}")) for g in cache.groups},
             host_seq_starts=starts.tolist(), host_seq_context=[0] * n, host_seq_slots=[0] * n,
-            max_query_len=max(self.counts), max_context_len=cache.max_pages_per_request * cache.page_size,
+            max_query_len=max(self.counts), max_context_len=W * cache.page_size,
             all_decode=self.all_decode,
             query_tiles=to_dev(np.asarray(tiles, dtype=np.int32).reshape(-1, 3)) if tiles else None,
             small_tokens=to_dev(np.asarray(small, dtype=np.int32)) if tiles and small else None)
@@ -139,7 +155,7 @@ class DecodeGraph:
             W = self.widths[g.index]
             hv[o + start_row * W:o + B * W] = g.scratch_page
 
-    def replay(self, requests: Sequence, tokens, tokens_on_device: bool = False) -> torch.Tensor:
+    def replay(self, requests: Sequence, tokens, tokens_on_device: bool = False, handles=None) -> torch.Tensor:
         """requests: ids of the live requests of this step, in the signature's order (fewer than the
         signature's only if it is padded); pages for their new tokens are already reserved.  tokens:
         their token ids, flat, in order (ignored with tokens_on_device: the device already holds them).
@@ -158,10 +174,11 @@ class DecodeGraph:
         # (with tokens_on_device the ids were put there by set_tokens_from_device; the rows that pad the
         # bucket keep whatever id they had: any valid id will do for them)
         # positions, cached lengths, slots, cache positions and block-table rows: packed by the host runtime
-        handles = np.fromiter((cache.handle(r) for r in requests), dtype=np.int64, count=n)
+        if handles is None:
+            handles = np.fromiter((cache.handle(r) for r in requests), dtype=np.int64, count=n)
         rc = cache._lib.egh_replay_pack(cache.core, n, handles.ctypes.data, self._counts32.ctypes.data, self.staging[i].data_ptr(),
                                         self.offsets["positions"][0], self.offsets["seq_context"][0], self.offsets["seq_slots"][0],
-                                        self._off_slot_map.ctypes.data, self._off_table.ctypes.data, cache.max_pages_per_request)
+                                        self._off_slot_map.ctypes.data, self._off_table.ctypes.data, self.table_width)
         if rc != 0:
             raise RuntimeError("a token of a captured step has no cache page" if rc == host.NO_PAGE
                                else f"packing a captured step failed with status {rc}")

@@ -77,7 +77,8 @@ class GptEngine:
         if on_device:
             # the device can feed itself only if every entry is a decode of a token of the step in flight
             all_decode = len(on_device) == len(batch) and all(s.count == 1 and s.samples for s in batch)
-            graph = self.runner.decode_graph(len(batch)) if (all_decode and self.runner.use_graphs) else None
+            graph, handles = self.runner.decode_graph_for([s.request.id for s in batch]) \
+                if (all_decode and self.runner.use_graphs) else (None, None)
             if graph is None:
                 # the general path needs every token id on the host: read what is in flight, drop what has ended
                 finished += self._resolve_inflight()
@@ -90,7 +91,7 @@ class GptEngine:
                         return finished
                 on_device = []
         if on_device:
-            logits = self._launch_on_device_tokens(batch, graph)
+            logits = self._launch_on_device_tokens(batch, graph, handles)
         else:
             entries = [StepEntry(s.request.id, s.request.token_slice(s.start, s.count),
                                  [s.count - 1] if s.samples else []) for s in batch]
@@ -107,7 +108,7 @@ class GptEngine:
             finished += self._resolve(previous)
         return finished
 
-    def _launch_on_device_tokens(self, batch, graph):
+    def _launch_on_device_tokens(self, batch, graph, handles):
         """A decode step whose input tokens are the previous step's samples, still on the device."""
         _, prev_dev, _, prev_rows = self._inflight
         rows = [prev_rows[s.request.id] for s in batch]
@@ -119,8 +120,9 @@ class GptEngine:
             index = torch.tensor(rows, dtype=torch.int64).pin_memory().to(self.model.device, non_blocking=True)
             tokens = prev_dev.index_select(0, index)
         graph.set_tokens_from_device(tokens)
-        logits = graph.replay([s.request.id for s in batch], None, tokens_on_device=True)
+        logits = graph.replay([s.request.id for s in batch], None, tokens_on_device=True, handles=handles)
         self.runner.graph_replays += 1
+        self.runner.last_graph = graph
         return logits[:len(batch)]
 
     def _resolve(self, inflight) -> List[Request]:

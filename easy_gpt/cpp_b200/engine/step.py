@@ -58,6 +58,7 @@ class StepRunner:
         self._graph_pool = None
         self._signature_seen: Dict[tuple, int] = {}
         self.graph_replays = 0
+        self.last_graph = None             # the captured step that ran last (for accounting)
 
     # -- request lifetime -------------------------------------------------------
     def end(self, request) -> None:
@@ -174,18 +175,34 @@ class StepRunner:
             self.check_status()
         return logits
 
-    def decode_graph(self, n: int):
-        """The captured step for n single-token entries (None if n is beyond the buckets)."""
-        from .decode_graph import DecodeGraph, bucket_for
+    def _handles(self, requests) -> np.ndarray:
+        return np.fromiter((self.cache.handle(r, create=True) for r in requests), dtype=np.int64, count=len(requests))
+
+    def _context_after(self, handles: np.ndarray, most_new_tokens: int) -> int:
+        """Tokens the longest of these requests holds once the step's tokens are in (requests not yet live hold none)."""
+        longest = int(self.cache._lib.egh_cache_max_length(self.cache.core, len(handles), handles.ctypes.data))
+        return max(longest, 0) + most_new_tokens
+
+    def decode_graph(self, n: int, context: int = 0):
+        """The captured step for n single-token entries whose requests hold up to ``context`` tokens after it
+        (0: as many as a request may hold); None if n is beyond the buckets."""
+        from .decode_graph import DecodeGraph, bucket_for, context_pages
 
         b = bucket_for(n)
         if b < 0 or b > self.cache.max_slots:
             b = self.cache.max_slots if n <= self.cache.max_slots else -1
         if b < 0:
             return None
-        if b not in self._graphs:
-            self._graphs[b] = DecodeGraph(self, [1] * b, [[0]] * b, padded=True)
-        return self._graphs[b]
+        most = self.cache.max_pages_per_request
+        width = context_pages(context, self.cache.page_size, most) if context else most
+        if (b, width) not in self._graphs:
+            self._graphs[(b, width)] = DecodeGraph(self, [1] * b, [[0]] * b, padded=True, table_width=width)
+        return self._graphs[(b, width)]
+
+    def decode_graph_for(self, requests):
+        """(graph, handles) for a decode step of these live requests."""
+        handles = self._handles(requests)
+        return self.decode_graph(len(requests), self._context_after(handles, 1)), handles
 
     MAX_SIGNATURE_GRAPHS = 48
     CAPTURE_MIXED_AFTER = 4            # times a shape of several entries is seen before it is captured
@@ -196,11 +213,14 @@ class StepRunner:
             self._graph_pool = torch.cuda.graph_pool_handle()
         return self._graph_pool
 
-    def _signature_graph(self, entries: Sequence[StepEntry]):
-        """The captured step for this exact batch shape, once the shape has come before (None the first time)."""
-        from .decode_graph import DecodeGraph
+    def _signature_graph(self, entries: Sequence[StepEntry], handles: np.ndarray):
+        """The captured step for this exact batch shape (and context bucket), once the shape has come before
+        (None the first time)."""
+        from .decode_graph import DecodeGraph, context_pages
 
-        sig = (tuple(len(e.tokens) for e in entries), tuple(tuple(e.want) for e in entries))
+        counts = tuple(len(e.tokens) for e in entries)
+        width = context_pages(self._context_after(handles, max(counts)), self.cache.page_size, self.cache.max_pages_per_request)
+        sig = (counts, tuple(tuple(e.want) for e in entries), width)
         graph = self._signature_graphs.get(sig)
         if graph is not None:
             self._signature_graphs[sig] = self._signature_graphs.pop(sig)         # most recently used last
@@ -216,7 +236,7 @@ class StepRunner:
             self._signature_graphs.pop(next(iter(self._signature_graphs)))        # the least recently used
             if len(self._signature_seen) > 4096:
                 self._signature_seen.clear()
-        graph = DecodeGraph(self, sig[0], sig[1], padded=False)
+        graph = DecodeGraph(self, sig[0], sig[1], padded=False, table_width=width)
         self._signature_graphs[sig] = graph
         return graph
 
@@ -264,21 +284,32 @@ class StepRunner:
         decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         if decode and not all(self.cache.has_request(e.request) for e in entries):
             return no
-        graph = self.decode_graph(len(entries)) if decode else None
+        if any(w < 0 or w >= len(e.tokens) for e in entries for w in e.want):
+            return no
+        handles = self._handles([e.request for e in entries])
+        graph = self.decode_graph(len(entries), self._context_after(handles, 1)) if decode else None
         if graph is None:
-            if any(w < 0 or w >= len(e.tokens) for e in entries for w in e.want):
-                return no
-            graph = self._signature_graph(entries)
+            graph = self._signature_graph(entries, handles)
         if graph is None:
+            self._forget_unborn(entries)
             return no
         if not self._reserve_for_step(entries):
             return no                        # the general path raises the proper error
         tokens = [t for e in entries for t in e.tokens]
-        logits = graph.replay([e.request for e in entries], tokens)
+        logits = graph.replay([e.request for e in entries], tokens, handles=handles)
         self.graph_replays += 1
+        self.last_graph = graph
         if logits is None:
             return True, None
         return True, (logits[:len(entries)] if graph.padded else logits)
+
+    def _forget_unborn(self, entries) -> None:
+        """Names that were made for requests which have not come to life (the general path makes them again)."""
+        for e in entries:
+            if not self.cache.has_request(e.request):
+                h = self.cache.handle(e.request)
+                if h is not None:
+                    self.cache._forget(e.request, h)
 
     def check_status(self) -> None:
         word = int(self.status.item())

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "egh_cache_end": (c_int, [c_void_p, c_longlong]),
     "egh_cache_take_fresh": (c_int, [c_void_p, c_void_p, c_int]),
     "egh_cache_query": (c_longlong, [c_void_p, c_longlong, c_int]),
+    "egh_cache_max_length": (c_longlong, [c_void_p, c_int, c_void_p]),
     "egh_cache_pages_needed": (c_int, [c_void_p, c_longlong, c_longlong, c_void_p]),
     "egh_cache_can_reserve": (c_int, [c_void_p, c_longlong, c_longlong, c_int]),
     "egh_cache_reserve": (c_int, [c_void_p, c_longlong, c_longlong, c_void_p]),

@@ -21,8 +21,8 @@ CONFIG = {
 }
 LENGTHS = {"long": 300, "short": 64, "middle": 150}
 F32_ATOL = 1e-4
-# bfloat16: largest error seen on B200 is 0.9% of the largest logit (whole, tail and mixed alike); the bound is
-# three times that
+# bfloat16: the largest error seen on B200 is 0.037 where the largest logit is 3.26, that is 1.1% (whole 1.0%, tail
+# 0.9%, mixed 1.1%); the bound is 2.7 times that
 BF16_REL = 3e-2
 
 

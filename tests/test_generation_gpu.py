@@ -35,7 +35,7 @@ def check_greedy(folder, prompts, outputs, dtype, tol):
             assert float(row.max() - row[tok]) <= tol, (dtype, i, tok, int(row.argmax()))
 
 
-@pytest.mark.parametrize("dtype, tol", [("float32", 1e-4), ("bfloat16", 0.25)])
+@pytest.mark.parametrize("dtype, tol", [("float32", 1e-4), ("bfloat16", 0.08)])
 def test_greedy_generation_matches_plain(model_a, dtype, tol):
     from easy_gpt.cpp_b200.engine import GptEngine
 

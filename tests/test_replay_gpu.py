@@ -12,9 +12,10 @@ import tiny_configs
 pytestmark = pytest.mark.gpu
 
 F32_ATOL = 1e-4
-# bfloat16: 8 bits of mantissa on every activation the kernels round; the bound is
-# relative to the largest logit of the model
-BF16_REL = 3e-2
+# bfloat16: 8 bits of mantissa on every activation the kernels round; the bound is relative to the largest
+# logit of the model (about 3 for these configurations).  Seen on B200, the same in every replay mode: 0.6% (A),
+# 1.2% (B), 0.9% (C), 0.9% (D), 1.2% (E) of it; the bound is twice the worst of these.
+BF16_REL = 2.5e-2
 
 
 @pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])

@@ -104,7 +104,7 @@ def test_a_step_shape_of_several_entries_is_captured_and_replayed(dtype, tmp_pat
     got = H.run_in_process(runner, steps)
     H.compare(got, refs, tolerance(refs, dtype), f"captured mixed step {dtype}")
     signature = ((1, 1, 6), ((0,), (0,), (0, 5)))
-    assert signature in runner._signature_graphs
+    assert any(key[:2] == signature for key in runner._signature_graphs)     # (the key's third part is the context bucket)
     assert runner.graph_replays >= 10 - runner.CAPTURE_MIXED_AFTER
 
 
