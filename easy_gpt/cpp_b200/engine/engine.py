@@ -10,8 +10,11 @@ import tempfile
 from pathlib import Path
 from typing import List, Optional, Sequence
 
+import time
+
 import torch
 
+from .. import log
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .model import Model
@@ -46,6 +49,9 @@ class GptEngine:
             eos_token_id=spec.eos_token_id, max_positions=spec.max_positions))
         self.sampler = Sampler(self.model.device, max_rows=max_active)
         self._inflight = None          # (batch, device tokens, host copy in progress, request id -> row) of the last step
+        self._added_at = {}            # request id -> time it was added (for the completion line)
+        log.info(f"engine on {self.model.device}: {spec.architecture}, {len(spec.run_order)} layers, {dtype}, pages of {page_size} "
+                 f"tokens, {num_pages} pages, up to {max_active} live requests")
 
     # -- requests -------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -57,9 +63,26 @@ class GptEngine:
         for t in prompt:
             if not 0 <= int(t) < vocab:
                 raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
-        return self.scheduler.add(prompt, params, max_new_tokens)
+        request = self.scheduler.add(prompt, params, max_new_tokens)
+        if log.enabled("info"):
+            self._added_at[request.id] = time.perf_counter()
+        return request
+
+    def _log_finished(self, finished: List[Request]) -> List[Request]:
+        """One line per finished request: tokens and rate (cf. src/continuous_batch_server.cpp:249-256)."""
+        for r in finished:
+            t0 = self._added_at.pop(r.id, None)
+            if t0 is not None and log.enabled("info"):
+                seconds = max(time.perf_counter() - t0, 1e-9)
+                log.info(f"request {r.id} finished ({r.finish_reason}): {len(r.prompt)} prompt tokens, {len(r.output)} new tokens "
+                         f"in {1e3 * seconds:.1f} ms ({len(r.output) / seconds:.1f} tok/s), {r.preemptions} preemptions")
+        return finished
 
     def step(self) -> List[Request]:
+        with log.nvtx_range("engine.step"):
+            return self._log_finished(self._step())
+
+    def _step(self) -> List[Request]:
         """One scheduler round and one model step.  Returns the requests that finished.
 
         Decode steps are pipelined: a step is put on the device before the previous step's sampled
@@ -90,6 +113,9 @@ class GptEngine:
                     if not batch:
                         return finished
                 on_device = []
+        if log.enabled("debug"):
+            log.debug(f"step {self.scheduler.stats.steps}: " + ", ".join(
+                f"{s.request.id}[{s.start}:{s.start + s.count}]" + ("*" if s.samples else "") for s in batch))
         if on_device:
             logits = self._launch_on_device_tokens(batch, graph, handles)
         else:
@@ -100,6 +126,11 @@ class GptEngine:
         sampling = [s for s in batch if s.samples]
         previous = self._inflight
         self._inflight = None
+        if sampling and log.enabled("trace"):
+            # the five best tokens of every sampled row (cf. src/models/gpt_model.cpp:76-110); costs a synchronisation
+            top = torch.topk(logits[:len(sampling)] if logits.shape[0] >= len(sampling) else logits, 5, dim=-1)
+            for s, ids, vals in zip(sampling, top.indices.tolist(), top.values.tolist()):
+                log.trace(f"request {s.request.id} top-5: " + ", ".join(f"{i}:{v:.3f}" for i, v in zip(ids, vals)))
         if sampling:
             dev = self.sampler.sample(logits, [s.request.params for s in sampling], [s.request.id for s in sampling],
                                       [len(s.request.output) + s.pending for s in sampling])
@@ -145,7 +176,7 @@ class GptEngine:
             done = self.step()
             if self.scheduler.stats.steps == before and not done and self._inflight is None and self.scheduler.has_work():
                 raise RuntimeError("the scheduler made no progress although requests are waiting")
-        self._resolve_inflight()
+        self._log_finished(self._resolve_inflight())
         self.runner.check_status()
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None,

@@ -14,7 +14,7 @@ import torch
 from .. import architectures, parts  # noqa: F401  (registers what the framework ships)
 from ..cache.manager import CacheManager
 from ..config.spec import LayerSpec, ModelSpec
-from .. import kernels
+from .. import kernels, log
 from ..parts.base import FollowingNorm, PendingNorm, StepContext
 from ..registry import model_spec_from_config, part_class
 from ..weights.loader import load_checked
@@ -91,27 +91,36 @@ class Block:
             following = subs[i + 1].norm if i + 1 < len(subs) and subs[i + 1].plain_pre_norm else \
                 (next_norm if i + 1 == len(subs) else None)
             args = (ctx, cache) if sub.role == "mixer" else (ctx,)
-            if sub.plain_pre_norm:
-                pending = PendingNorm(sub.norm, residual, delta, spare, work, max_fused_rows=fused_rows)
-                delta = sub.part.forward(pending if sub.part.accepts_pending_norm else pending.materialize(), *args,
-                                         **self._offer(sub.part, following, pending, ctx, fused_rows))
-                assert pending.consumed, "a part that accepts a pending norm must use it"
-                residual, spare = pending.residual_after, pending.spare_after
-                continue
-            # the general shapes: the stream is settled first, every norm is a kernel of its own
-            residual = self._settle(residual, delta)
-            if sub.norm is not None and sub.placement == "pre":
-                x = sub.norm.forward(residual, None, work)
-            else:
-                x = work.copy_(residual)
-            delta = sub.part.forward(x, *args)
-            if sub.output_norm is not None:
-                delta = self._normalised(sub.output_norm, delta, spare, like=work)
-            if sub.norm is not None and sub.placement == "post":
-                # x = norm(x + part(x)): the normalised sum is the new residual stream
-                sub.norm.forward(residual, delta, spare)
-                residual, spare = spare, residual
-                delta = None
+            if log.NVTX:
+                torch.cuda.nvtx.range_push(f"{sub.role}:{type(sub.part).__name__}")
+            try:
+                residual, spare, delta = self._run_sublayer(sub, following, args, residual, spare, delta, ctx, work, fused_rows)
+            finally:
+                if log.NVTX:
+                    torch.cuda.nvtx.range_pop()
+        return residual, spare, delta
+
+    def _run_sublayer(self, sub, following, args, residual, spare, delta, ctx, work, fused_rows):
+        if sub.plain_pre_norm:
+            pending = PendingNorm(sub.norm, residual, delta, spare, work, max_fused_rows=fused_rows)
+            delta = sub.part.forward(pending if sub.part.accepts_pending_norm else pending.materialize(), *args,
+                                     **self._offer(sub.part, following, pending, ctx, fused_rows))
+            assert pending.consumed, "a part that accepts a pending norm must use it"
+            return pending.residual_after, pending.spare_after, delta
+        # the general shapes: the stream is settled first, every norm is a kernel of its own
+        residual = self._settle(residual, delta)
+        if sub.norm is not None and sub.placement == "pre":
+            x = sub.norm.forward(residual, None, work)
+        else:
+            x = work.copy_(residual)
+        delta = sub.part.forward(x, *args)
+        if sub.output_norm is not None:
+            delta = self._normalised(sub.output_norm, delta, spare, like=work)
+        if sub.norm is not None and sub.placement == "post":
+            # x = norm(x + part(x)): the normalised sum is the new residual stream
+            sub.norm.forward(residual, delta, spare)
+            residual, spare = spare, residual
+            delta = None
         return residual, spare, delta
 
     @staticmethod

@@ -74,3 +74,28 @@ def test_sampling_params_are_checked():
     with pytest.raises(ValueError, match="Top-p"):
         SamplingParams(top_p=0.0)
     assert SamplingParams(temperature=0.0, greedy=True).is_greedy
+
+
+def test_log_levels(capsys, monkeypatch):
+    """EASYGPT_LOG picks the level; lines below it are dropped, an unknown name falls back to warn."""
+    import importlib
+
+    from easy_gpt.cpp_b200 import log
+
+    monkeypatch.setenv("EASYGPT_LOG", "debug")
+    importlib.reload(log)
+    log.debug("shown")
+    log.trace("hidden")
+    err = capsys.readouterr().err
+    assert "[debug] shown" in err and "hidden" not in err
+    monkeypatch.setenv("EASYGPT_LOG", "loud")
+    importlib.reload(log)
+    assert "is no level" in capsys.readouterr().err and log.level == log.LEVELS["warn"]
+    log.info("hidden")
+    log.warn("shown")
+    err = capsys.readouterr().err
+    assert "[warn] shown" in err and "hidden" not in err
+    with log.nvtx_range("nothing"):                      # a no-op unless EASY_GPT_NVTX is set
+        pass
+    monkeypatch.delenv("EASYGPT_LOG")
+    importlib.reload(log)
