@@ -154,6 +154,67 @@ def host_library_path(verbose: bool = True) -> Path:
     return out_dir / HOST_LIB_NAME
 
 
+ENGINE_LIB_NAME = "libeasygpt_engine.so"
+ENGINE_EXE_NAME = "easy_llm"
+ENGINE_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall"]
+
+
+def _cuda_home() -> Path:
+    for cand in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), str(Path(_nvcc()).resolve().parent.parent), "/usr/local/cuda"):
+        if cand and (Path(cand) / "include" / "cuda_runtime.h").is_file():
+            return Path(cand)
+    raise BuildError("the CUDA toolkit's headers were not found (set CUDA_HOME); the native engine cannot be built")
+
+
+def _engine_fingerprint(kernel_fp: str) -> str:
+    h = hashlib.sha256()
+    files = list((HERE / "engine").glob("*.cpp")) + list((HERE / "engine").glob("*.hpp")) + list((HERE / "engine").glob("*.h")) \
+        + list((HERE / "host").glob("*.hpp"))
+    for p in sorted(files):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(ENGINE_FLAGS).encode())
+    h.update(kernel_fp.encode())
+    return h.hexdigest()
+
+
+def engine_paths(verbose: bool = True):
+    """(library, program): the native engine (``engine/*.hpp`` behind the C interface of ``engine/engine_api.cpp``) as a
+    shared library, and the ``easy_llm`` program of ``engine/main.cpp`` linked against it.  Both are built by the C++
+    compiler against the CUDA runtime and cuBLAS and linked to the kernel library beside them."""
+    kernels = library_path(verbose)
+    out_dir = kernels.parent
+    build_dir = out_dir / "_build"
+    fp = _engine_fingerprint(_fingerprint())
+    lib, exe, stamp = out_dir / ENGINE_LIB_NAME, out_dir / ENGINE_EXE_NAME, build_dir / "engine_stamp.json"
+    if _current(lib, stamp, fp) and exe.is_file():
+        return lib, exe
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise BuildError("no C++ compiler was found (set CXX or put g++ on PATH); the native engine cannot be built")
+    cuda = _cuda_home()
+    lib_dirs = [d for d in (cuda / "lib64", cuda / "lib") if d.is_dir()]
+    if verbose:
+        print(f"[easy_gpt.cpp_b200] building the native engine into {out_dir} (first call only)", file=sys.stderr, flush=True)
+    common = [*ENGINE_FLAGS, "-I", str(cuda / "include"), "-I", str(HERE / "host")]
+    link = ["-L", str(out_dir), "-leasygpt_kernels", *[a for d in lib_dirs for a in ("-L", str(d))], "-lcudart", "-lcublas", "-lcublasLt",
+            "-Wl,-rpath,$ORIGIN", *[f"-Wl,-rpath,{d}" for d in lib_dirs]]
+    tmp_lib = out_dir / (ENGINE_LIB_NAME + f".{os.getpid()}.tmp")
+    r = subprocess.run([cxx, *common, "-shared", str(HERE / "engine" / "engine_api.cpp"), "-o", str(tmp_lib), *link], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"building {ENGINE_LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp_lib, lib)
+    tmp_exe = out_dir / (ENGINE_EXE_NAME + f".{os.getpid()}.tmp")
+    r = subprocess.run([cxx, *common, str(HERE / "engine" / "main.cpp"), "-o", str(tmp_exe), *link],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"building {ENGINE_EXE_NAME} failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp_exe, exe)
+    stamp.write_text(json.dumps({"fingerprint": fp}))
+    return lib, exe
+
+
 if __name__ == "__main__":
     print(library_path())
     print(host_library_path())
+    print(*engine_paths())

@@ -1,0 +1,202 @@
+// C interface of the native engine (libeasygpt_engine.so) for the Python face (native.py), bin/trace_run and any other
+// caller.  Handles are opaque pointers.  Functions return 0 or a non-negative result on success and -1 on failure, with the
+// error text in the caller's buffer.  Nothing here is specific to one architecture: the model class is chosen by config.json.
+#include <cstring>
+
+#include "engine.hpp"
+
+using namespace easygpt::engine;
+namespace host = easygpt::host;
+
+#define EGE_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+void put_error(char* buffer, int cap, const std::string& text) {
+    if (!buffer || cap <= 0) return;
+    std::strncpy(buffer, text.c_str(), (size_t)cap - 1);
+    buffer[cap - 1] = 0;
+}
+DType dtype_from(const char* name) {
+    const std::string s = name ? name : "";
+    if (s == "bfloat16" || s == "bf16") return DType::BF16;
+    if (s == "float32" || s == "fp32") return DType::F32;
+    throw std::invalid_argument("dtype must be bfloat16 or float32, not '" + s + "'");
+}
+template <class F> long long guarded(char* error, int cap, F f) {
+    try {
+        return f();
+    } catch (const std::exception& e) {
+        put_error(error, cap, e.what());
+        return -1;
+    }
+}
+struct Runner {
+    std::unique_ptr<Model> model;
+    std::unique_ptr<StepRunner> runner;
+    std::vector<float> host_logits;
+};
+}  // namespace
+
+// ---- the engine ---------------------------------------------------------------------------------------------------
+// options (8 long longs): page_size, cache_tokens (0: default), max_active, prefill_batch, max_batch_tokens, chunk_size,
+// max_tokens_per_request (0: default), use_graphs
+EGE_API void* ege_engine_create(const char* model_dir, const char* dtype, const long long* options, char* error, int cap) {
+    GptEngine* engine = nullptr;
+    guarded(error, cap, [&]() {
+        EngineOptions o;
+        o.page_size = (int)options[0];
+        o.cache_tokens = options[1];
+        o.max_active = (int)options[2];
+        o.prefill_batch = (int)options[3];
+        o.max_batch_tokens = options[4];
+        o.chunk_size = options[5];
+        o.max_tokens_per_request = options[6];
+        o.use_graphs = options[7] != 0;
+        engine = new GptEngine(model_dir, dtype_from(dtype), o);
+        return 0;
+    });
+    return engine;
+}
+EGE_API void ege_engine_destroy(void* e) { delete static_cast<GptEngine*>(e); }
+
+EGE_API long long ege_engine_add_request(void* e, const long long* prompt, long long n, float temperature, float top_p, int top_k, long long seed,
+                                         int greedy, long long max_new_tokens, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        SamplingParams p;
+        p.temperature = temperature;
+        p.top_p = top_p;
+        p.top_k = top_k;
+        p.seed = seed;
+        p.greedy = greedy != 0;
+        return (long long)static_cast<GptEngine*>(e)->add_request(std::vector<int64_t>(prompt, prompt + n), p, max_new_tokens);
+    });
+}
+// one scheduler round and one model step; the ids of the requests that finished go to `finished` (at most cap_finished)
+EGE_API long long ege_engine_step(void* e, long long* finished, int cap_finished, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        const std::vector<int64_t> done = static_cast<GptEngine*>(e)->step();
+        for (size_t i = 0; i < done.size() && (int)i < cap_finished; ++i) finished[i] = done[i];
+        return (long long)done.size();
+    });
+}
+EGE_API int ege_engine_has_work(void* e) { return static_cast<GptEngine*>(e)->scheduler->has_work() ? 1 : 0; }
+EGE_API long long ege_engine_run_to_completion(void* e, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        static_cast<GptEngine*>(e)->run_to_completion();
+        return 0;
+    });
+}
+// the tokens generated so far for a request; returns how many there are, writes what fits
+EGE_API long long ege_engine_output(void* e, long long id, long long* out, long long cap_out) {
+    GptEngine* g = static_cast<GptEngine*>(e);
+    auto it = g->requests.find(id);
+    if (it == g->requests.end()) return -1;
+    const auto& tokens = it->second.output;
+    for (size_t i = 0; i < tokens.size() && (long long)i < cap_out; ++i) out[i] = tokens[i];
+    return (long long)tokens.size();
+}
+// out (10 long longs): prompt length, output length, max new tokens, computed, state (0 waiting, 1 running, 2 finished),
+// finish reason (1 empty, 2 eos, 3 length, 4 max positions, 5 error), error code, pending, preemptions, admission counter
+EGE_API int ege_engine_request(void* e, long long id, long long* out, char* error_text, int cap) {
+    GptEngine* g = static_cast<GptEngine*>(e);
+    const host::SchedRequest* r = g->scheduler->find(id);
+    if (!r) return -1;
+    out[0] = r->prompt_len; out[1] = r->output_len; out[2] = r->max_new_tokens; out[3] = r->computed; out[4] = r->state;
+    out[5] = r->reason; out[6] = r->error; out[7] = r->pending; out[8] = r->preemptions; out[9] = r->admitted_at;
+    put_error(error_text, cap, g->error_text(id, r->error));
+    return 0;
+}
+EGE_API void ege_engine_forget(void* e, long long id) { static_cast<GptEngine*>(e)->forget(id); }
+// out (12 long longs): scheduler steps, prompt tokens, decode tokens, preemptions, finished, failed, captured-step replays,
+// steps run, live requests, free pages of group 0, vocabulary, bytes of weights a step reads
+EGE_API void ege_engine_stats(void* e, long long* out) {
+    GptEngine* g = static_cast<GptEngine*>(e);
+    const host::SchedulerStats& st = g->scheduler->stats();
+    out[0] = st.steps; out[1] = st.prompt_tokens; out[2] = st.decode_tokens; out[3] = st.preemptions; out[4] = st.finished; out[5] = st.failed;
+    out[6] = g->runner->graph_replays;
+    out[7] = g->runner->steps_run;
+    out[8] = (long long)g->runner->cache.core.live_count();
+    out[9] = g->runner->cache.groups.empty() ? 0 : g->runner->cache.core.group(0).pool.free_count();
+    out[10] = g->model->spec.vocab_size;
+    out[11] = (long long)g->model->weight_bytes_per_step();
+}
+// further figures for roofline arithmetic: what == 0: cache bytes per token, 1: bytes of metadata the last captured step
+// copied to the device, 2: tokens of request `id` in the cache (-1 if it is not live)
+EGE_API long long ege_engine_figure(void* e, int what, long long id) {
+    GptEngine* g = static_cast<GptEngine*>(e);
+    if (what == 0) return (long long)g->runner->cache.kv_bytes_per_token();
+    if (what == 1) return g->runner->last_graph ? (long long)g->runner->last_graph->meta_bytes() : 0;
+    if (what == 2) {
+        const host::CachedRequest* r = g->runner->cache.core.find(id);
+        return r ? r->length : -1;
+    }
+    return -1;
+}
+EGE_API void ege_engine_sync(void* e) { cudaStreamSynchronize(static_cast<GptEngine*>(e)->runner->stream); }
+
+// ---- the bare step function (trace replay, tests) ---------------------------------------------------------------------
+EGE_API void* ege_runner_create(const char* model_dir, const char* dtype, int page_size, int num_pages, int max_slots, long long max_tokens_per_request,
+                                int use_graphs, char* error, int cap) {
+    Runner* r = nullptr;
+    guarded(error, cap, [&]() {
+        std::unique_ptr<Runner> made(new Runner());
+        made->model = Model::from_dir(model_dir, dtype_from(dtype));
+        StepRunner::Options o;
+        o.page_size = page_size;
+        o.num_pages = num_pages;
+        o.max_slots = max_slots;
+        o.max_tokens_per_request = max_tokens_per_request;
+        o.use_graphs = use_graphs != 0;
+        made->runner.reset(new StepRunner(*made->model, o));
+        r = made.release();
+        return 0;
+    });
+    return r;
+}
+EGE_API void ege_runner_destroy(void* r) { delete static_cast<Runner*>(r); }
+// One step: n entries; entry i is request rids[i] with counts[i] tokens (flat in `tokens`) and wants[want_offsets[i] ..
+// want_offsets[i + 1]) as the places among its tokens whose logits are asked for.  The logits [rows, vocab] are copied to
+// `logits` (host, float32) if it holds them (cap_floats); returns the number of rows.
+EGE_API long long ege_runner_step(void* r, int n, const long long* rids, const long long* counts, const long long* tokens, const long long* want_offsets,
+                                  const long long* wants, float* logits, long long cap_floats, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        Runner* run = static_cast<Runner*>(r);
+        std::vector<StepEntry> entries((size_t)n);
+        long long at = 0;
+        for (int i = 0; i < n; ++i) {
+            entries[i].request = rids[i];
+            entries[i].tokens.assign(tokens + at, tokens + at + counts[i]);
+            entries[i].want.assign(wants + want_offsets[i], wants + want_offsets[i + 1]);
+            at += counts[i];
+        }
+        const StepRunner::Result res = run->runner->run(entries, /*check=*/false, /*commit=*/true);
+        const long long vocab = run->model->lm_head->vocab();
+        if (res.rows > 0) {
+            if ((long long)res.rows * vocab > cap_floats) throw std::invalid_argument("the caller's logits buffer is too small");
+            EG_CUDA(cudaMemcpyAsync(logits, res.logits, (size_t)res.rows * vocab * 4, cudaMemcpyDeviceToHost, run->runner->stream));
+        }
+        run->runner->check_status();           // synchronises the stream: the logits are on the host
+        return (long long)res.rows;
+    });
+}
+EGE_API void ege_runner_end(void* r, long long rid) { static_cast<Runner*>(r)->runner->end(rid); }
+// what: 0 vocabulary, 1 live requests, 2 captured-step replays, 3 free pages of group `arg`, 4 pages of group `arg`, 5 pages handed
+// out over the life of group `arg`'s pool, 6 number of groups, 7 books in order (1) or not (0)
+EGE_API long long ege_runner_info(void* r, int what, int arg) {
+    Runner* run = static_cast<Runner*>(r);
+    DeviceCache& cache = run->runner->cache;
+    switch (what) {
+        case 0: return run->model->lm_head->vocab();
+        case 1: return (long long)cache.core.live_count();
+        case 2: return run->runner->graph_replays;
+        case 3: return cache.core.group(arg).pool.free_count();
+        case 4: return cache.core.group(arg).pool.num_pages();
+        case 5: return cache.core.group(arg).pool.total_allocated();
+        case 6: return cache.core.num_groups();
+        case 7: {
+            std::string why;
+            return cache.core.check(&why) == host::OK ? 1 : 0;
+        }
+    }
+    return -1;
+}

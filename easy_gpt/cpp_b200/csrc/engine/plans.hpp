@@ -1,0 +1,107 @@
+// Launch plans and size rules of the kernel library, as the native engine uses them: which kernel takes
+// which sizes, how the CTAs of a launch share the work.  The numbers were measured on B200; they hang off
+// the device's SM count, never off a model's sizes.
+#pragma once
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+
+#include "device.hpp"
+
+namespace easygpt::engine::plans {
+
+constexpr int QUERY_TILE = 128;            // tokens per listed tile of a prompt portion
+constexpr int SMALL_ENTRY_TOKENS = 4;      // entries of up to this many tokens go through the decode attention kernel
+constexpr int SKINNY_MAX_TOKENS = 16;      // up to where the decode product beats the library product
+constexpr int FUSED_NORM_MAX_TOKENS = 16;  // every CTA repeats the norm prologue: worth it only for a few tokens
+constexpr int MAX_HEAD_DIM = 256;          // the generic attention kernel keeps up to eight dimensions of a head per lane
+constexpr int TCGEN05_ATTENTION_MIN_QUERY = 33;
+constexpr int USE_PDL = 2;                 // a decode kernel lets the next one start once it has passed its own wait
+enum Epilogue { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3, EPI_RESID_NORM = 4 };
+
+inline int sm_count() {
+    static int count = 0;
+    if (!count) {
+        if (const char* forced = std::getenv("EASY_GPT_SM_COUNT")) count = std::atoi(forced);
+        if (count <= 0) {
+            int device = 0;
+            cudaDeviceProp prop;
+            if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, device) == cudaSuccess) count = prop.multiProcessorCount;
+        }
+        if (count <= 0) count = 148;
+    }
+    return count;
+}
+
+inline bool attention_paged_takes(DType dtype, int head_dim, int page_size) {
+    return dtype == DType::BF16 && (head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256) && page_size % 16 == 0;
+}
+inline bool attention_prefill_takes(DType dtype, int head_dim, int page_size) {
+    return dtype == DType::BF16 && (head_dim == 32 || head_dim == 64 || head_dim == 128) && page_size % 16 == 0;
+}
+inline bool attention_prefill_tcgen05_takes(DType dtype, int head_dim, int page_size) {
+    return dtype == DType::BF16 && (head_dim == 64 || head_dim == 128) && page_size % 16 == 0;
+}
+
+// How many CTAs share one (token, KV head).  Up to 16 tokens the kernel is fastest with one wave of 128 to 256
+// CTAs that walk about eight key tiles of 64 each; with more tokens with about four CTAs per SM.  A power of two,
+// at least four tiles per CTA.
+inline int attention_paged_splits(int tokens, int num_heads, int num_kv_heads, long long max_context) {
+    const long long base = (long long)tokens * num_kv_heads * ((num_heads / num_kv_heads + 15) / 16);
+    const long long tiles = std::max<long long>(1, (max_context + 63) / 64);
+    const long long most = tokens <= SKINNY_MAX_TOKENS ? 256 : 4LL * sm_count();
+    int splits = 1;
+    while ((long long)splits * 2 * base <= most && tiles / (splits * 2) >= 4 && splits < 128) splits *= 2;
+    return splits;
+}
+
+// (parts, part_tiles): the most parts a query tile's keys are cut into and the fewest key tiles of a part.
+inline void attention_prefill_parts(int num_tiles, int num_heads, int* parts, int* part_tiles) {
+    const int wanted = std::min(2 * sm_count() / std::max(1, num_tiles * num_heads), 8);
+    if (wanted >= 2) { *parts = wanted; *part_tiles = 4; }
+    else { *parts = 1; *part_tiles = 1 << 20; }
+}
+
+// Up to how many tokens a step's add + RMSNorm over rows of `width` can ride in the decode product's prologue
+// (the rows of a token tile must fit the kernel's 200 KB of shared memory); 0: the norm runs on its own.
+inline int fused_norm_max_tokens(int width) {
+    if (width % 16) return 0;
+    for (int tile : {16, 8}) {
+        const long long row = (2LL * width + 127) / 128 * 128 + 64;
+        const long long need = tile * row + tile * 4 + width * 4LL + tile * 32 + (width + 15) / 16 * tile * 4LL;
+        if (need <= 200 * 1024) return std::min(tile, FUSED_NORM_MAX_TOKENS);
+    }
+    return 0;
+}
+
+struct SkinnyPlan {
+    int row_blocks, k_slices, k_split;
+};
+// How the warps of a CTA and the CTAs of the grid share a [n_rows, in_features] weight matrix.
+inline SkinnyPlan skinny_plan(int n_rows, int in_features, int head_dim = 0) {
+    const int chunks = (in_features + 63) / 64;
+    if (head_dim) {                                    // fused QKV: one CTA per head
+        const int rb = head_dim / 16;
+        int ks = 1;
+        while (ks * 2 * rb <= 16 && chunks > 4 * ks) ks *= 2;
+        return {rb, ks, 1};
+    }
+    if (n_rows >= 64 * sm_count()) return {4, 2, 1};   // wide matrices (gate/up, the head): 64 rows per CTA
+    const int rb = 1, ks = 8;
+    // (Python's round() sends halves to the even neighbour; so does nearbyint in the default rounding mode)
+    int split = (int)std::max(1.0, std::min(8.0, std::nearbyint(chunks / (ks * 2.5))));
+    if ((long long)((n_rows + 15) / 16) * split > 4LL * sm_count()) split = 1;
+    return {rb, ks, split};
+}
+inline bool gemm_skinny_takes(DType dtype, int tokens, int in_features) {
+    return dtype == DType::BF16 && tokens > 0 && tokens <= SKINNY_MAX_TOKENS && in_features % 16 == 0;
+}
+inline int skinny_padded_tokens(int tokens) { return tokens <= 8 ? 8 : tokens <= 16 ? 16 : tokens <= 32 ? 32 : 64; }
+
+// Products wide and tall enough for the persistent tcgen05 kernel on CTA pairs (one tile per SM at least).
+inline bool gemm_tcgen05_wide_takes(DType dtype, int tokens, int out_features, int in_features) {
+    return dtype == DType::BF16 && tokens > SKINNY_MAX_TOKENS && out_features % 256 == 0 && in_features % 64 == 0 &&
+           (long long)((tokens + 127) / 128) * (out_features / 256) >= sm_count();
+}
+
+}  // namespace easygpt::engine::plans

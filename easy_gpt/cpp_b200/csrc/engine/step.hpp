@@ -1,0 +1,553 @@
+// The cache manager's device side and the step function.
+//
+// DeviceCache: the bookkeeping of csrc/host/cache_core.hpp (pages, block tables, slots) with the device memory it
+// addresses: per group of caches with the same needs one tensor [caches, pages + 1, 2 (k, v), kv_heads, page_size,
+// head_dim] in the engine's dtype (the extra page is the scratch page that padding rows of a captured batch write
+// to), and per cache that asked for fixed-size state one tensor [slots, elements], zeroed when a request takes a slot.
+//
+// StepRunner: one batch of (request, its next tokens) through the model.  A batch is any mix of prompt portions and
+// single decoded tokens, cut anywhere.  run() reserves cache pages for the new tokens (all or nothing), packs the
+// batch's metadata into one pinned host buffer, copies it to the device once, runs the model over exactly the tokens
+// it was given (reading everything earlier from the cache) and returns float32 logits at the wanted places, in the
+// order of the entries and of each entry's `want`.  Decode steps are captured as CUDA graphs per bucket of batch size
+// and context length and replayed (one copy + one graph launch per step); nothing is allocated inside a step.
+// (The reference has two entry points that never mix, one for padded prompts and one for single tokens,
+// src/models/gpt_model.cpp:375-419, and computes logits at every position, :203-211.)
+#pragma once
+#include <array>
+#include <set>
+
+#include "../host/step_pack.hpp"
+#include "model.hpp"
+
+namespace easygpt::engine {
+
+struct StepError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct OutOfPages : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct OutOfSlots : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+inline std::string describe_status(int word) {
+    std::string out;
+    auto add = [&](int bit, const char* text) {
+        if (word & bit) out += (out.empty() ? "" : "; ") + std::string(text);
+    };
+    add(1, "a token id lies outside the vocabulary");
+    add(2, "a block table entry needed by attention is not a valid page");
+    add(4, "a cache write position lies outside the pool");
+    add(8, "a bounded wait inside a kernel gave up");
+    return out.empty() ? "ok" : out;
+}
+
+class DeviceCache {
+public:
+    struct Group {
+        int index;
+        CacheNeed need;
+        std::vector<int> cache_ids;
+        DeviceBuffer kv;
+        int num_pages;
+        int scratch_page;
+        size_t layer_elems;             // elements of one cache's [pages + 1, 2, kv_heads, page_size, head_dim]
+    };
+    struct State {
+        DeviceBuffer memory;
+        size_t bytes_per_slot;
+    };
+
+    DeviceCache(const std::map<int, CacheNeed>& needs, int page_size, int num_pages, int max_slots, long long max_tokens_per_request, DType dtype)
+        : core(page_size, max_slots, (int)((max_tokens_per_request + page_size - 1) / page_size)), page_size(page_size), max_slots(max_slots), dtype(dtype) {
+        if (page_size <= 0 || max_slots <= 0 || max_tokens_per_request <= 0) throw std::invalid_argument("page_size, max_slots and max_tokens_per_request must be positive");
+        if (num_pages <= 0) throw std::invalid_argument("a page pool needs at least one page");
+        for (auto& kv : needs) {
+            const CacheNeed& need = kv.second;
+            if (need.kind == CacheNeed::PagedKV) {
+                Group* g = nullptr;
+                for (auto& have : groups)
+                    if (have->need == need) g = have.get();
+                if (!g) {
+                    groups.emplace_back(new Group());
+                    g = groups.back().get();
+                    g->index = core.add_group(num_pages, need.window < 0 ? -1 : (int)need.window);
+                    g->need = need;
+                    g->num_pages = num_pages;
+                    g->scratch_page = num_pages;
+                    g->layer_elems = (size_t)(num_pages + 1) * 2 * need.num_kv_heads * page_size * need.head_dim;
+                }
+                g->cache_ids.push_back(kv.first);
+                group_of_cache[kv.first] = g->index;
+            } else if (need.kind == CacheNeed::State) {
+                size_t elems = 1;
+                for (long long s : need.state_shape) elems *= (size_t)s;
+                State st;
+                st.bytes_per_slot = elems * dtype_size(need.state_dtype);
+                st.memory.allocate(st.bytes_per_slot * max_slots, true);
+                states.emplace(kv.first, std::move(st));
+            }
+        }
+        for (auto& g : groups) g->kv.allocate(g->layer_elems * g->cache_ids.size() * dtype_size(dtype), true);
+        fresh_.resize(max_slots);
+    }
+
+    CacheView view(int cache_id, bool writes) const {
+        CacheView v;
+        v.writes = writes;
+        auto it = group_of_cache.find(cache_id);
+        if (it != group_of_cache.end()) {
+            const Group& g = *groups[it->second];
+            const size_t which = std::find(g.cache_ids.begin(), g.cache_ids.end(), cache_id) - g.cache_ids.begin();
+            const size_t es = dtype_size(dtype);
+            char* base = g.kv.as<char>() + which * g.layer_elems * es;
+            const long long plane = (long long)g.need.num_kv_heads * page_size * g.need.head_dim;
+            v.group = g.index;
+            v.k = base;
+            v.v = base + (size_t)plane * es;
+            v.page_stride = 2 * plane;
+            v.head_stride = (long long)page_size * g.need.head_dim;
+            v.num_pages = g.num_pages + 1;
+            v.page_size = page_size;
+            return v;
+        }
+        auto st = states.find(cache_id);
+        if (st != states.end()) {
+            v.state = st->second.memory.get();
+            v.state_bytes_per_slot = st->second.bytes_per_slot;
+        }
+        return v;
+    }
+    // Clears the state of every slot that a request has taken since the last call, whoever began the request.  The step
+    // function calls it before every forward pass, captured or not.
+    void zero_fresh_state(cudaStream_t stream) {
+        const int n = core.take_fresh_slots(fresh_.data(), max_slots);
+        if (states.empty()) return;
+        for (int i = 0; i < n; ++i)
+            for (auto& kv : states)
+                EG_CUDA(cudaMemsetAsync(kv.second.memory.as<char>() + (size_t)fresh_[i] * kv.second.bytes_per_slot, 0, kv.second.bytes_per_slot, stream));
+    }
+    size_t kv_bytes_per_token() const {
+        size_t total = 0;
+        for (auto& g : groups) total += g->cache_ids.size() * 2 * g->need.num_kv_heads * g->need.head_dim * dtype_size(dtype);
+        return total;
+    }
+
+    host::CacheCore core;
+    int page_size, max_slots;
+    DType dtype;
+    std::vector<std::unique_ptr<Group>> groups;
+    std::map<int, int> group_of_cache;
+    std::map<int, State> states;
+
+private:
+    std::vector<int> fresh_;
+};
+
+struct StepEntry {
+    int64_t request;
+    std::vector<int64_t> tokens;
+    std::vector<int64_t> want;          // indices into tokens whose logits are asked for
+};
+
+constexpr int kDecodeBuckets[] = {1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256};
+constexpr long long kMinContextBucket = 512;    // tokens: shorter contexts share the smallest captured step
+
+inline int decode_bucket_for(int n) {
+    for (int b : kDecodeBuckets)
+        if (n <= b) return b;
+    return -1;
+}
+// Block-table width (pages) of the captured step that serves requests of up to `tokens` tokens: the next power of two
+// of tokens, at least kMinContextBucket, at most what a request may hold.
+inline int context_pages(long long tokens, int page_size, int most) {
+    long long bucket = kMinContextBucket;
+    while (bucket < tokens) bucket *= 2;
+    return (int)std::max<long long>(1, std::min<long long>(most, (bucket + page_size - 1) / page_size));
+}
+
+class StepRunner {
+public:
+    struct Options {
+        int page_size = 16;
+        int num_pages = 0;
+        int max_slots = 16;
+        long long max_tokens_per_request = 0;   // 0: min(max positions, pool)
+        long long max_batch_tokens = 2048;      // the eager arena is made for steps of up to this many tokens
+        bool use_graphs = true;
+    };
+
+    StepRunner(Model& model, const Options& opt)
+        : model(model), options(opt),
+          cache(model.cache_needs(), opt.page_size, opt.num_pages, opt.max_slots,
+                opt.max_tokens_per_request > 0 ? opt.max_tokens_per_request
+                                               : std::min<long long>(model.spec.max_positions, (long long)opt.num_pages * opt.page_size),
+                model.dtype),
+          status_(sizeof(int), true) {
+        EG_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        EG_CUDA(cudaMallocHost((void**)&status_host_, sizeof(int)));
+        use_graphs = opt.use_graphs && model.capturable();
+        for (auto& e : ring_events_) EG_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    ~StepRunner() {
+        graphs_.clear();
+        for (auto& e : ring_events_) cudaEventDestroy(e);
+        if (status_host_) cudaFreeHost(status_host_);
+        if (stream) cudaStreamDestroy(stream);
+    }
+    StepRunner(const StepRunner&) = delete;
+    StepRunner& operator=(const StepRunner&) = delete;
+
+    void end(int64_t request) {
+        if (cache.core.find(request)) cache.core.end_request(request);
+    }
+
+    struct Result {
+        float* logits = nullptr;        // [rows, vocab] float32 on the device, valid until the next step; nullptr if nothing was wanted
+        int rows = 0;
+        bool captured = false;
+    };
+
+    // With `check` the device status word is read back (a synchronisation) and a complaint of a kernel becomes an
+    // exception.  With `commit` the requests' cached lengths advance here; a scheduler that keeps its own count passes
+    // false (its pages are reserved already: `reserved` true) and commits itself.
+    Result run(const std::vector<StepEntry>& entries, bool check = true, bool commit = true, bool reserved = false) {
+        validate(entries);
+        const int n = (int)entries.size();
+        std::vector<int64_t> rids(n), counts(n);
+        for (int i = 0; i < n; ++i) {
+            rids[i] = entries[i].request;
+            counts[i] = (int64_t)entries[i].tokens.size();
+        }
+        if (!reserved) reserve(entries, rids, counts);
+        Result r;
+        bool decode = use_graphs;
+        for (auto& e : entries)
+            if (e.tokens.size() != 1 || e.want.size() != 1 || e.want[0] != 0) decode = false;
+        DecodeGraph* graph = decode ? decode_graph(n, context_after(rids, 1)) : nullptr;
+        if (graph) {
+            std::vector<int32_t> tokens(n);
+            for (int i = 0; i < n; ++i) tokens[i] = (int32_t)entries[i].tokens[0];
+            r.logits = graph->replay(*this, rids, tokens.data());
+            r.rows = n;
+            r.captured = true;
+            ++graph_replays;
+        } else {
+            r = run_eager(entries, rids, counts);
+        }
+        if (commit)
+            for (int i = 0; i < n; ++i) cache.core.commit(rids[i], counts[i]);
+        ++steps_run;
+        if (check) check_status();
+        return r;
+    }
+
+    void check_status() {
+        EG_CUDA(cudaMemcpyAsync(status_host_, status_.get(), sizeof(int), cudaMemcpyDeviceToHost, stream));
+        EG_CUDA(cudaStreamSynchronize(stream));
+        const int word = *status_host_;
+        if (word) {
+            EG_CUDA(cudaMemsetAsync(status_.get(), 0, sizeof(int), stream));
+            throw StepError("a kernel reported: " + describe_status(word));
+        }
+    }
+    int* status() const { return status_.as<int>(); }
+
+    // ---- captured decode steps ------------------------------------------------------------------------------------
+    class DecodeGraph {
+    public:
+        DecodeGraph(StepRunner& r, int bucket, int table_width) : bucket(bucket), table_width(table_width) {
+            DeviceCache& cache = r.cache;
+            const int G = (int)cache.groups.size();
+            auto section = [&](long long size) {
+                const long long at = size_;
+                size_ += host::pad4(size);
+                return at;
+            };
+            off_tokens_ = section(bucket);
+            off_positions_ = section(bucket);
+            off_context_ = section(bucket);
+            off_slots_ = section(bucket);
+            off_token_seq_ = section(bucket);
+            off_starts_ = section(bucket + 1);
+            for (int g = 0; g < G; ++g) {
+                off_slot_map_.push_back(section(bucket));
+                off_table_.push_back(section((long long)bucket * table_width));
+            }
+            meta_.allocate((size_t)size_ * 4, true);
+            for (auto& s : staging_) s.ensure((size_t)size_ * 4);
+            for (auto& e : events_) EG_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            arena_.reset(new Arena(r.model.activation_bytes(bucket, bucket)));
+            counts_.assign(bucket, 1);
+            // what depends on the bucket alone, and rows of padding everywhere: written once
+            int32_t* hv = staging_[0].as<int32_t>();
+            std::fill(hv, hv + size_, 0);
+            for (int i = 0; i < bucket; ++i) hv[off_token_seq_ + i] = i;
+            for (int i = 0; i <= bucket; ++i) hv[off_starts_ + i] = i;
+            fill_padding(r, hv, 0);
+            EG_CUDA(cudaMemcpyAsync(meta_.get(), hv, (size_t)size_ * 4, cudaMemcpyHostToDevice, r.stream));
+            EG_CUDA(cudaStreamSynchronize(r.stream));
+            for (auto& s : staging_)
+                if (s.as<int32_t>() != hv) std::memcpy(s.as<int32_t>(), hv, (size_t)size_ * 4);
+            // run once eagerly (library plans come into being), then capture
+            forward(r);
+            EG_CUDA(cudaStreamSynchronize(r.stream));
+            arena_->reset();
+            EG_CUDA(cudaStreamBeginCapture(r.stream, cudaStreamCaptureModeThreadLocal));
+            try {
+                logits_ = forward(r);
+            } catch (...) {
+                cudaGraph_t broken = nullptr;
+                cudaStreamEndCapture(r.stream, &broken);
+                if (broken) cudaGraphDestroy(broken);
+                throw;
+            }
+            cudaGraph_t graph = nullptr;
+            EG_CUDA(cudaStreamEndCapture(r.stream, &graph));
+            const cudaError_t e = cudaGraphInstantiate(&exec_, graph, 0);
+            cudaGraphDestroy(graph);
+            cuda_check(e, "cudaGraphInstantiate");
+        }
+        ~DecodeGraph() {
+            if (exec_) cudaGraphExecDestroy(exec_);
+            for (auto& e : events_) cudaEventDestroy(e);
+        }
+        DecodeGraph(const DecodeGraph&) = delete;
+        DecodeGraph& operator=(const DecodeGraph&) = delete;
+
+        // requests: the live requests of this step (at most `bucket`; the rest are padding rows); pages for their new
+        // tokens are reserved.  tokens: their token ids, or nullptr if the device already holds them (see token_ids()).
+        float* replay(StepRunner& r, const std::vector<int64_t>& rids, const int32_t* tokens) {
+            const int n = (int)rids.size();
+            const int turn = next_++ % (int)staging_.size();
+            if (used_[turn]) EG_CUDA(cudaEventSynchronize(events_[turn]));
+            int32_t* hv = staging_[turn].as<int32_t>();
+            if (tokens) std::memcpy(hv + off_tokens_, tokens, (size_t)n * 4);
+            const int rc = host::pack_replay(r.cache.core, n, rids.data(), counts_.data(), hv, off_positions_, off_context_, off_slots_,
+                                             off_slot_map_.data(), off_table_.data(), table_width);
+            if (rc != host::OK)
+                throw StepError(rc == host::NO_PAGE ? "a token of a captured step has no cache page"
+                                                    : "packing a captured step failed with status " + std::to_string(rc));
+            if (n < bucket) fill_padding(r, hv, n);
+            if (tokens) {
+                EG_CUDA(cudaMemcpyAsync(meta_.get(), hv, (size_t)size_ * 4, cudaMemcpyHostToDevice, r.stream));
+            } else {
+                // token ids stay as the device left them (the sampler's output was copied in)
+                const long long first = off_positions_;
+                EG_CUDA(cudaMemcpyAsync(meta_.as<int32_t>() + first, hv + first, (size_t)(size_ - first) * 4, cudaMemcpyHostToDevice, r.stream));
+            }
+            EG_CUDA(cudaEventRecord(events_[turn], r.stream));
+            used_[turn] = true;
+            r.cache.zero_fresh_state(r.stream);
+            EG_CUDA(cudaGraphLaunch(exec_, r.stream));
+            return logits_;
+        }
+        int32_t* token_ids() const { return meta_.as<int32_t>() + off_tokens_; }
+        size_t meta_bytes() const { return (size_t)size_ * 4; }
+        const int bucket, table_width;
+
+    private:
+        void fill_padding(StepRunner& r, int32_t* hv, int first_row) {
+            for (int i = first_row; i < bucket; ++i) hv[off_tokens_ + i] = hv[off_positions_ + i] = hv[off_context_ + i] = hv[off_slots_ + i] = 0;
+            for (size_t g = 0; g < r.cache.groups.size(); ++g) {
+                const int scratch = r.cache.groups[g]->scratch_page;
+                for (int i = first_row; i < bucket; ++i) {
+                    hv[off_slot_map_[g] + i] = scratch * r.cache.page_size;
+                    std::fill(hv + off_table_[g] + (long long)i * table_width, hv + off_table_[g] + (long long)(i + 1) * table_width, scratch);
+                }
+            }
+        }
+        float* forward(StepRunner& r) {
+            StepContext ctx;
+            ctx.dtype = r.model.dtype;
+            ctx.stream = r.stream;
+            ctx.arena = arena_.get();
+            ctx.blas = &r.blas_;
+            ctx.scratch = &r.scratch_;
+            ctx.num_tokens = ctx.num_seqs = bucket;
+            const int32_t* m = meta_.as<int32_t>();
+            ctx.token_ids = m + off_tokens_;
+            ctx.positions = m + off_positions_;
+            ctx.token_seq = m + off_token_seq_;
+            ctx.seq_starts = m + off_starts_;
+            ctx.seq_context = m + off_context_;
+            ctx.seq_slots = m + off_slots_;
+            ctx.status = r.status();
+            for (size_t g = 0; g < r.cache.groups.size(); ++g)
+                ctx.groups.push_back(GroupTables{r.cache.page_size, m + off_table_[g], table_width, m + off_slot_map_[g]});
+            ctx.max_query_len = 1;
+            ctx.max_context_len = (long long)table_width * r.cache.page_size;
+            ctx.all_decode = true;
+            return r.model.forward(ctx, [&](int c, bool w) { return r.cache.view(c, w); }, nullptr, bucket, /*all_rows=*/true);
+        }
+
+        long long size_ = 0, off_tokens_ = 0, off_positions_ = 0, off_context_ = 0, off_slots_ = 0, off_token_seq_ = 0, off_starts_ = 0;
+        std::vector<long long> off_slot_map_, off_table_;
+        std::vector<int32_t> counts_;
+        DeviceBuffer meta_;
+        std::array<PinnedBuffer, 4> staging_;
+        std::array<cudaEvent_t, 4> events_{};
+        std::array<bool, 4> used_{};
+        int next_ = 0;
+        std::unique_ptr<Arena> arena_;
+        cudaGraphExec_t exec_ = nullptr;
+        float* logits_ = nullptr;
+    };
+
+    // tokens the longest of these requests holds once the step's tokens are in
+    long long context_after(const std::vector<int64_t>& rids, long long most_new_tokens) const {
+        long long longest = 0;
+        for (int64_t rid : rids)
+            if (const host::CachedRequest* c = cache.core.find(rid)) longest = std::max(longest, c->length);
+        return longest + most_new_tokens;
+    }
+    // the captured step for n single-token entries whose requests hold up to `context` tokens after it; nullptr if n is
+    // beyond the buckets
+    DecodeGraph* decode_graph(int n, long long context) {
+        if (!use_graphs) return nullptr;
+        int b = decode_bucket_for(n);
+        if (b < 0 || b > cache.max_slots) b = n <= cache.max_slots ? cache.max_slots : -1;
+        if (b < 0) return nullptr;
+        const int width = context_pages(context, cache.page_size, cache.core.max_pages_per_request());
+        auto key = std::make_pair(b, width);
+        auto it = graphs_.find(key);
+        if (it == graphs_.end()) it = graphs_.emplace(key, std::unique_ptr<DecodeGraph>(new DecodeGraph(*this, b, width))).first;
+        last_graph = it->second.get();
+        return last_graph;
+    }
+
+    Model& model;
+    Options options;
+    DeviceCache cache;
+    cudaStream_t stream = nullptr;
+    bool use_graphs = false;
+    long long steps_run = 0, graph_replays = 0;
+    DecodeGraph* last_graph = nullptr;
+
+private:
+    void validate(const std::vector<StepEntry>& entries) const {
+        if (entries.empty()) throw StepError("a step needs at least one entry");
+        std::set<int64_t> seen;
+        for (auto& e : entries) {
+            if (!seen.insert(e.request).second) throw StepError("request " + std::to_string(e.request) + " appears twice in one step");
+            if (e.tokens.empty()) throw StepError("request " + std::to_string(e.request) + " brings no tokens");
+            for (int64_t w : e.want)
+                if (w < 0 || w >= (int64_t)e.tokens.size())
+                    throw StepError("request " + std::to_string(e.request) + ": wanted place " + std::to_string(w) + " is outside its " +
+                                    std::to_string(e.tokens.size()) + " tokens");
+            for (int64_t t : e.tokens)
+                if (t < INT32_MIN || t > INT32_MAX) throw StepError("token ids do not fit 32 bits");
+        }
+    }
+    // begins the step's new requests and takes the pages for every entry's tokens: all of it, or an exception with nothing changed
+    void reserve(const std::vector<StepEntry>& entries, const std::vector<int64_t>& rids, const std::vector<int64_t>& counts) {
+        int info[3] = {0, 0, 0};
+        const int rc = host::reserve_step(cache.core, (int)rids.size(), rids.data(), counts.data(), info);
+        if (rc == host::OK) return;
+        if (rc == host::OUT_OF_PAGES)
+            throw OutOfPages("group " + std::to_string(info[0]) + ": the step needs " + std::to_string(info[1]) + " new pages, " + std::to_string(info[2]) + " are free");
+        if (rc == host::TOO_LONG)
+            throw OutOfPages("request " + std::to_string(entries[info[0]].request) + " would hold more tokens than a request may hold (" +
+                             std::to_string((long long)cache.core.max_pages_per_request() * cache.page_size) + ")");
+        if (rc == host::OUT_OF_SLOTS) throw OutOfSlots("all " + std::to_string(cache.max_slots) + " request slots are taken");
+        throw StepError("reserving the step's pages failed with status " + std::to_string(rc));
+    }
+
+    Result run_eager(const std::vector<StepEntry>& entries, const std::vector<int64_t>& rids, const std::vector<int64_t>& counts) {
+        const int n = (int)entries.size();
+        const int G = (int)cache.groups.size();
+        long long T = 0, R = 0;
+        std::vector<int64_t> token_ids, want_offsets(n + 1, 0), wants;
+        for (int i = 0; i < n; ++i) {
+            T += counts[i];
+            token_ids.insert(token_ids.end(), entries[i].tokens.begin(), entries[i].tokens.end());
+            wants.insert(wants.end(), entries[i].want.begin(), entries[i].want.end());
+            want_offsets[i + 1] = (int64_t)wants.size();
+        }
+        R = (long long)wants.size();
+        const long long bound = host::packed_step_bound(cache.core, n, T, R, plans::QUERY_TILE);
+        // pinned staging buffers in a ring: a buffer is rewritten only after the copy that read it has finished
+        const int turn = ring_next_++ % (int)ring_.size();
+        if (ring_used_[turn]) EG_CUDA(cudaEventSynchronize(ring_events_[turn]));
+        ring_[turn].ensure((size_t)bound * 4);
+        if (dev_meta_.bytes() < (size_t)bound * 4) {
+            EG_CUDA(cudaStreamSynchronize(stream));
+            size_t cap = 1u << 16;
+            while (cap < (size_t)bound * 4) cap *= 2;
+            dev_meta_.allocate(cap);
+        }
+        std::vector<long long> layout(2 * (host::FIXED_SECTIONS + 2 * G));
+        std::vector<int> widths(std::max(G, 1));
+        host::PackedStep packed;
+        if (wants.empty()) wants.push_back(0);
+        const int rc = host::pack_step(cache.core, n, rids.data(), counts.data(), token_ids.data(), want_offsets.data(), wants.data(), plans::QUERY_TILE,
+                                       plans::SMALL_ENTRY_TOKENS, ring_[turn].as<int32_t>(), bound, layout.data(), widths.data(), &packed);
+        if (rc != host::OK) throw StepError("packing the step failed with status " + std::to_string(rc));
+        EG_CUDA(cudaMemcpyAsync(dev_meta_.get(), ring_[turn].as<int32_t>(), (size_t)packed.total * 4, cudaMemcpyHostToDevice, stream));
+        EG_CUDA(cudaEventRecord(ring_events_[turn], stream));
+        ring_used_[turn] = true;
+
+        const size_t need = model.activation_bytes(T, R);
+        if (!arena_ || arena_->capacity() < need) {
+            EG_CUDA(cudaStreamSynchronize(stream));
+            arena_.reset();
+            arena_.reset(new Arena(std::max(need, model.activation_bytes(options.max_batch_tokens, options.max_slots))));
+        }
+        arena_->reset();
+        const int32_t* m = dev_meta_.as<int32_t>();
+        const int32_t* hv = ring_[turn].as<int32_t>();
+        auto at = [&](int section) { return m + layout[2 * section]; };
+        StepContext ctx;
+        ctx.dtype = model.dtype;
+        ctx.stream = stream;
+        ctx.arena = arena_.get();
+        ctx.blas = &blas_;
+        ctx.scratch = &scratch_;
+        ctx.num_tokens = (int)T;
+        ctx.num_seqs = n;
+        ctx.token_ids = at(host::TOKEN_IDS);
+        ctx.positions = at(host::POSITIONS);
+        ctx.token_seq = at(host::TOKEN_SEQ);
+        ctx.seq_starts = at(host::SEQ_STARTS);
+        ctx.seq_context = at(host::SEQ_CONTEXT);
+        ctx.seq_slots = at(host::SEQ_SLOTS);
+        ctx.host_seq_starts = hv + layout[2 * host::SEQ_STARTS];
+        ctx.host_seq_context = hv + layout[2 * host::SEQ_CONTEXT];
+        ctx.host_seq_slots = hv + layout[2 * host::SEQ_SLOTS];
+        ctx.status = status();
+        for (int g = 0; g < G; ++g)
+            ctx.groups.push_back(GroupTables{cache.page_size, at(host::FIXED_SECTIONS + 2 * g + 1), widths[g], at(host::FIXED_SECTIONS + 2 * g)});
+        ctx.max_query_len = (int)packed.max_query_len;
+        ctx.max_context_len = packed.max_context_len;
+        ctx.all_decode = packed.all_decode != 0;
+        if (packed.num_tiles) {
+            ctx.query_tiles = at(host::QUERY_TILES);
+            ctx.num_tiles = packed.num_tiles;
+            if (packed.num_small) {
+                ctx.small_tokens = at(host::SMALL_TOKENS);
+                ctx.num_small = packed.num_small;
+            }
+        }
+        cache.zero_fresh_state(stream);         // slots taken since the last step (by this step or by the scheduler)
+        Result r;
+        r.logits = model.forward(ctx, [&](int c, bool w) { return cache.view(c, w); }, R ? at(host::LOGIT_ROWS) : nullptr, (int)R, false);
+        r.rows = (int)R;
+        return r;
+    }
+
+    DeviceBuffer status_;
+    int* status_host_ = nullptr;
+    Blas blas_;
+    KernelScratch scratch_;
+    std::unique_ptr<Arena> arena_;
+    std::array<PinnedBuffer, 4> ring_;
+    std::array<cudaEvent_t, 4> ring_events_{};
+    std::array<bool, 4> ring_used_{};
+    int ring_next_ = 0;
+    DeviceBuffer dev_meta_;
+    std::map<std::pair<int, int>, std::unique_ptr<DecodeGraph>> graphs_;
+};
+
+}  // namespace easygpt::engine
