@@ -9,12 +9,12 @@ layers, hidden 896, 14 query heads, 2 KV heads, head size 64, intermediate
 requests and contexts that end at 4096 tokens.  A "step" is one decode step of
 the whole batch.  One JSON line is printed:
 
-  value      decoded tokens per second: K calls of GptEngine.step(), the call a user
-             makes, timed on the device with CUDA events (median of three runs of K)
-  e2e        the same loop by the wall clock until the last tokens are on the host:
+  value      decoded tokens per second: K calls of the engine's step(), the call a user
+             makes, timed on the device with CUDA events on the engine's stream
+             (median of three runs of K)
+  e2e        the same K calls by the wall clock until the last tokens are on the host:
              every step the packed batch metadata goes up from pinned host memory and
-             the sampled token ids come back to the host (read one step late: decode
-             steps are pipelined and the device feeds itself the token ids)
+             the sampled token ids come back to the host
   prefill    one prompt of 2,048 tokens in one step
   roofline   bytes the decode step has to read (every weight once, the cache of
              the live requests) / its time, against the measured copy bandwidth
@@ -30,7 +30,8 @@ For profiling and for further sizes (one short line each, never the JSON line ab
     python bench.py --only decode|prefill|timeline|gemm|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
 
 `serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
-decoding requests, 512 new tokens each) through GptEngine and reports wall-clock tokens a second.
+decoding requests, 512 new tokens each) through the engine and reports wall-clock tokens a second.
+The engine is the native one (csrc/engine); `timeline` and `gemm` use the kernels' Python face.
 """
 from __future__ import annotations
 
@@ -146,48 +147,22 @@ def prompts_for(batch, length, vocab, seed):
     return [rng.integers(0, vocab, size=length).tolist() for _ in range(batch)]
 
 
-def prepare_decode(engine, batch, start_context, new_tokens, vocab, seed):
-    """Adds `batch` requests and runs steps until every one of them is decoding."""
-    from easy_gpt.cpp_b200.sampling import GREEDY
-
-    reqs = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts_for(batch, start_context, vocab, seed)]
-    while any(r.known - r.computed != 1 or r.state != "running" for r in reqs):
-        engine.step()
-    engine.sync()                       # no token left in flight
-    return reqs
-
-
-def time_steps(engine, reqs, steps):
-    """K decode steps through GptEngine.step(), the product's own loop (scheduler, captured step, sampling
-    kernel, tokens read by the host one step late while the device feeds itself).  Returns (seconds on the
-    device by CUDA events around the K steps, wall-clock seconds until the last step's tokens are on the
-    host, launches of our kernels, bytes a step has to read on average)."""
-    import torch
-
-    from easy_gpt.cpp_b200 import kernels
-
-    cache = engine.runner.cache
-    kv_per_token = cache.kv_bytes_per_token()
-    weights = engine.model.weight_bytes_per_step()
-    rids = [r.id for r in reqs]
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0, replays0 = kernels.launch_count, engine.runner.graph_replays
+def time_steps(engine, ids, steps):
+    """K decode steps through the engine's step(), the product's own loop (scheduler, captured step, sampling kernel,
+    tokens back on the host every step).  Returns (seconds on the device by CUDA events on the engine's stream around
+    the K steps, wall-clock seconds until the last step's tokens are on the host, kernels launched, bytes a step has
+    to read on average)."""
+    kv_per_token = engine.kv_bytes_per_token()
+    weights = engine.stats()["weight_bytes_per_step"]
     # step s (from 0) reads the weights once and the keys and values of every request: what it held before, plus s + 1
-    held = sum(cache.length_of(r) for r in rids)
-    step_bytes = steps * weights + kv_per_token * (steps * held + len(rids) * steps * (steps + 1) // 2)
-    t0 = time.perf_counter()
-    start.record()
-    for _ in range(steps):
-        engine.step()
-    stop.record()
-    engine.sync()                       # the last step's tokens have reached the host
-    wall = time.perf_counter() - t0
-    torch.cuda.synchronize()
-    replays = engine.runner.graph_replays - replays0
+    held = sum(engine.cached_length(r) for r in ids)
+    step_bytes = steps * weights + kv_per_token * (steps * held + len(ids) * steps * (steps + 1) // 2)
+    replays0 = engine.stats()["graph_replays"]
+    device, wall = engine.time_steps(steps)
+    replays = engine.stats()["graph_replays"] - replays0
     assert replays == steps, "the timed steps did not go through the captured decode step"
-    launches = (kernels.launch_count - launches0) + replays * engine.runner.last_graph.launches
-    return start.elapsed_time(stop) / 1e3, wall, launches, step_bytes / steps
+    launches = replays * (engine.last_step_launches() + 1)             # the captured step's kernels and the sampling kernel
+    return device, wall, launches, step_bytes / steps
 
 
 def median(values):
@@ -199,16 +174,13 @@ REPEATS = 3
 
 
 def measure_decode(folder, config, batch, steps, warmup, want_e2e, dtype="bfloat16", default_options=False):
-    """Decode steps that end at CONTEXT tokens: W warm-up steps, then REPEATS runs of K steps timed on the
-    device (the median is reported) and, with want_e2e, REPEATS more runs timed by the wall clock.
-    ``default_options``: the engine's own defaults for page size and request length instead of pages of
-    64 tokens and requests sized for this run."""
-    import torch
+    """Decode steps that end at CONTEXT tokens: W warm-up steps, then REPEATS runs of K steps; the median of their device
+    times is `value`, the median of their wall-clock times `e2e`.  ``default_options``: the engine's own defaults for
+    page size and request length instead of pages of 64 tokens and requests sized for this run."""
+    from easy_gpt.cpp_b200.native import NativeEngine
+    from easy_gpt.cpp_b200.sampling import GREEDY
 
-    from easy_gpt.cpp_b200.engine import GptEngine
-
-    runs = REPEATS * (2 if want_e2e else 1)
-    total_steps = warmup + runs * steps + 4
+    total_steps = warmup + REPEATS * steps + 4
     start_context = CONTEXT - total_steps
     # the prompts are prefilled in large steps, so that the requests admitted first decode only a few tokens
     # while the others' prompts are still on their way (those tokens get room of their own)
@@ -218,30 +190,27 @@ def measure_decode(folder, config, batch, steps, warmup, want_e2e, dtype="bfloat
                    chunk_size=4096)
     if not default_options:
         options.update(page_size=64, max_tokens_per_request=room)
-    engine = GptEngine(folder, dtype=dtype, **options)
-    reqs = prepare_decode(engine, batch, start_context, total_steps + 64, config["vocab_size"], seed=batch)
-    out = {}
-    for _ in range(warmup):
+    engine = NativeEngine(folder, dtype=dtype, **options)
+    ids = [engine.add_request(p, GREEDY, max_new_tokens=total_steps + 64)
+           for p in prompts_for(batch, start_context, config["vocab_size"], seed=batch)]
+    while any(engine.request(r)["computed"] < start_context for r in ids):       # until every request is decoding
         engine.step()
+    engine.time_steps(warmup)
     with ClockSampler() as clocks:
-        timed = [time_steps(engine, reqs, steps) for _ in range(REPEATS)]
-    out["clocks"] = clocks.summary()
+        timed = [time_steps(engine, ids, steps) for _ in range(REPEATS)]
+    out = {"clocks": clocks.summary()}
     seconds = median([t[0] for t in timed])
     out["seconds"], out["launches"], out["step_bytes"] = seconds, timed[0][2], median([t[3] for t in timed])
     out["tok_s"] = batch * steps / seconds
     out["repeats_ms"] = [round(1e3 * t[0] / steps, 4) for t in timed]
     if want_e2e:
-        walls = [max(t[0], t[1]) for t in (time_steps(engine, reqs, steps) for _ in range(REPEATS))]
-        out["e2e_tok_s"] = batch * steps / median(walls)
+        out["e2e_tok_s"] = batch * steps / median([max(t[0], t[1]) for t in timed])
         # per step: the packed metadata of the batch goes up, the sampled tokens come back
-        out["h2d"] = engine.runner.last_graph.size * 4
+        out["h2d"] = engine.last_step_h2d_bytes()
         out["d2h"] = batch * 4
-    out["context_end"] = max(engine.runner.cache.length_of(r.id) for r in reqs)
-    out["page_size"] = engine.runner.cache.page_size
-    engine.sync()
-    engine.runner.check_status()
+    out["context_end"] = max(engine.cached_length(r) for r in ids)
+    out["page_size"] = options.get("page_size", 16)
     del engine
-    torch.cuda.empty_cache()
     return out
 
 
@@ -257,29 +226,20 @@ def prefill_flops(config, tokens):
 
 
 def measure_prefill(folder, config, repeats=5):
-    import torch
+    """One prompt of PREFILL_TOKENS tokens in one step through the step function (logits at its last token); the
+    median of the step's time on the device."""
+    from easy_gpt.cpp_b200.native import NativeStepRunner
 
-    from easy_gpt.cpp_b200.engine import Model, StepEntry, StepRunner
-
-    model = Model.from_dir(folder, device="cuda:0", dtype=torch.bfloat16)
-    runner = StepRunner(model, page_size=64, num_pages=2 * PREFILL_TOKENS // 64, max_slots=2)
+    runner = NativeStepRunner(folder, "bfloat16", page_size=64, num_pages=2 * PREFILL_TOKENS // 64, max_slots=2)
     prompt = prompts_for(1, PREFILL_TOKENS, config["vocab_size"], seed=99)[0]
     times = []
     for i in range(repeats + 2):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        runner.run([StepEntry("p", prompt, [PREFILL_TOKENS - 1])], check=False)
-        stop.record()
-        torch.cuda.synchronize()
+        runner.run([("p", prompt, [PREFILL_TOKENS - 1])])
         runner.end("p")
         if i >= 2:
-            times.append(start.elapsed_time(stop) / 1e3)
-    runner.check_status()
-    times.sort()
-    del runner, model
-    torch.cuda.empty_cache()
-    return times[len(times) // 2]
+            times.append(runner.last_step_device_seconds)
+    del runner
+    return median(times)
 
 
 def print_timeline(folder, config, batch):
@@ -376,50 +336,44 @@ def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
 
 
 def measure_serving(folder, config, requests=64, new_tokens=512, chunk=512, budget=2048, seed=0, repeats=2):
-    """Continuous batching through GptEngine: `requests` concurrent requests with prompt lengths uniform in
+    """Continuous batching through the engine: `requests` concurrent requests with prompt lengths uniform in
     [128, 4096] and `new_tokens` generated tokens each, prompts cut into portions of `chunk` tokens that share
     steps with the decoding requests.  Wall clock from the first add_request to the last token on the host;
-    the first repeat warms up (graphs of the step shapes are captured), the last one is reported."""
+    the first repeat warms up (the decode steps' graphs are captured), the last one is reported."""
     import numpy as np
-    import torch
 
-    from easy_gpt.cpp_b200.engine import GptEngine
+    from easy_gpt.cpp_b200.native import NativeEngine
     from easy_gpt.cpp_b200.sampling import GREEDY
 
     rng = np.random.default_rng(seed)
     lengths = rng.integers(128, 4097, size=requests)
     prompts = [rng.integers(0, config["vocab_size"], size=int(n)).tolist() for n in lengths]
-    engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=requests * (4096 + new_tokens + 64),
-                       max_active=requests, prefill_batch=4, max_batch_tokens=budget, chunk_size=chunk,
-                       max_tokens_per_request=4096 + new_tokens + 64)
+    engine = NativeEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=requests * (4096 + new_tokens + 64),
+                          max_active=requests, prefill_batch=4, max_batch_tokens=budget, chunk_size=chunk,
+                          max_tokens_per_request=4096 + new_tokens + 64)
     out = {}
     for _ in range(repeats):
-        steps0 = engine.scheduler.stats.steps
-        torch.cuda.synchronize()
+        before = engine.stats()
+        engine.sync()
         t0 = time.perf_counter()
-        reqs = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts]
+        ids = [engine.add_request(p, GREEDY, max_new_tokens=new_tokens) for p in prompts]
         engine.run_to_completion()
-        torch.cuda.synchronize()
+        engine.sync()
         seconds = time.perf_counter() - t0
-        assert all(len(r.output) == new_tokens and not r.error for r in reqs)
-        stats = engine.scheduler.stats
+        for r in ids:
+            assert len(engine.output(r)) == new_tokens and not engine.request(r)["error"]
+            engine.forget(r)
+        stats = engine.stats()
+        steps = stats["steps"] - before["steps"]
         out = {"requests": requests, "prompt_tokens": int(lengths.sum()), "generated_tokens": requests * new_tokens,
-               "seconds": round(seconds, 3), "steps": stats.steps - steps0, "preemptions": stats.preemptions,
+               "seconds": round(seconds, 3), "steps": steps, "preemptions": stats["preemptions"] - before["preemptions"],
                "generated_tok_s": round(requests * new_tokens / seconds, 1),
                "all_tok_s": round((int(lengths.sum()) + requests * new_tokens) / seconds, 1),
-               "ms_per_step": round(1e3 * seconds / max(1, stats.steps - steps0), 3), "graph_replays": engine.runner.graph_replays}
-        for r in reqs:
-            engine.scheduler.forget(r)
-    engine.runner.check_status()
+               "ms_per_step": round(1e3 * seconds / max(1, steps), 3), "graph_replays": stats["graph_replays"] - before["graph_replays"]}
     return out
 
 
 def run_ours(args):
-    import torch
-
-    if not torch.cuda.is_available():
-        print(json.dumps({"error": "no CUDA device; this engine has no CPU path"}))
-        return 1
     config = dict(CONFIG_05B, **SIZES[args.sizes])
     if args.sizes != "0.5b" and not args.only:
         print("bench.py: --sizes other than 0.5b goes with --only (the JSON line is defined for the 0.5B sizes)")

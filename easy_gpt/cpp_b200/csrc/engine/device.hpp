@@ -101,6 +101,7 @@ private:
 class Arena {
 public:
     explicit Arena(size_t bytes) : block_(bytes), used_(0) {}
+    Arena(Arena&&) = default;
     void* take(size_t bytes) {
         const size_t at = (used_ + 255) & ~size_t(255);
         if (at + bytes > block_.bytes())
@@ -117,6 +118,23 @@ public:
 private:
     DeviceBuffer block_;
     size_t used_;
+};
+
+// The activation memory of one step: what lives for the whole step, and two arenas that the sub-layers use in turn.
+struct ArenaSizes {
+    size_t step = 0, sub = 0;
+};
+struct StepArenas {
+    explicit StepArenas(const ArenaSizes& sizes) : sizes(sizes), step(sizes.step), sub{Arena(sizes.sub), Arena(sizes.sub)} {}
+    bool holds(const ArenaSizes& need) const { return sizes.step >= need.step && sizes.sub >= need.sub; }
+    void reset() {
+        step.reset();
+        sub[0].reset();
+        sub[1].reset();
+    }
+    ArenaSizes sizes;
+    Arena step;
+    Arena sub[2];
 };
 
 // out[M,N] = x[M,K] w[N,K]^T (+ bias) through the library.  Row-major operands are handed over as their

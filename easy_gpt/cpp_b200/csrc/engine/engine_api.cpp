@@ -121,7 +121,8 @@ EGE_API void ege_engine_stats(void* e, long long* out) {
     out[11] = (long long)g->model->weight_bytes_per_step();
 }
 // further figures for roofline arithmetic: what == 0: cache bytes per token, 1: bytes of metadata the last captured step
-// copied to the device, 2: tokens of request `id` in the cache (-1 if it is not live)
+// copied to the device, 2: tokens of request `id` in the cache (-1 if it is not live), 3: kernels one replay of the last
+// captured step launches (the nodes of its graph)
 EGE_API long long ege_engine_figure(void* e, int what, long long id) {
     GptEngine* g = static_cast<GptEngine*>(e);
     if (what == 0) return (long long)g->runner->cache.kv_bytes_per_token();
@@ -130,7 +131,33 @@ EGE_API long long ege_engine_figure(void* e, int what, long long id) {
         const host::CachedRequest* r = g->runner->cache.core.find(id);
         return r ? r->length : -1;
     }
+    if (what == 3) return g->runner->last_graph ? g->runner->last_graph->launches : 0;
     return -1;
+}
+// Runs `steps` calls of step() and times them: out[0] device milliseconds between CUDA events recorded on the engine's
+// stream before the first and after the last step, out[1] wall-clock milliseconds until the last step's tokens are on the
+// host.  Returns the number of requests that finished meanwhile.
+EGE_API long long ege_engine_time_steps(void* e, int steps, double* out, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        GptEngine* g = static_cast<GptEngine*>(e);
+        cudaEvent_t start, stop;
+        EG_CUDA(cudaEventCreate(&start));
+        EG_CUDA(cudaEventCreate(&stop));
+        EG_CUDA(cudaStreamSynchronize(g->runner->stream));
+        long long finished = 0;
+        const auto t0 = std::chrono::steady_clock::now();
+        EG_CUDA(cudaEventRecord(start, g->runner->stream));
+        for (int i = 0; i < steps; ++i) finished += (long long)g->step().size();
+        EG_CUDA(cudaEventRecord(stop, g->runner->stream));
+        EG_CUDA(cudaEventSynchronize(stop));
+        out[1] = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        float ms = 0.f;
+        EG_CUDA(cudaEventElapsedTime(&ms, start, stop));
+        out[0] = ms;
+        cudaEventDestroy(start);
+        cudaEventDestroy(stop);
+        return finished;
+    });
 }
 EGE_API void ege_engine_sync(void* e) { cudaStreamSynchronize(static_cast<GptEngine*>(e)->runner->stream); }
 
@@ -156,11 +183,19 @@ EGE_API void* ege_runner_create(const char* model_dir, const char* dtype, int pa
 EGE_API void ege_runner_destroy(void* r) { delete static_cast<Runner*>(r); }
 // One step: n entries; entry i is request rids[i] with counts[i] tokens (flat in `tokens`) and wants[want_offsets[i] ..
 // want_offsets[i + 1]) as the places among its tokens whose logits are asked for.  The logits [rows, vocab] are copied to
-// `logits` (host, float32) if it holds them (cap_floats); returns the number of rows.
+// `logits` (host, float32) if it holds them (cap_floats); returns the number of rows.  device_ms (optional): the step's time
+// on the device in milliseconds.
 EGE_API long long ege_runner_step(void* r, int n, const long long* rids, const long long* counts, const long long* tokens, const long long* want_offsets,
-                                  const long long* wants, float* logits, long long cap_floats, char* error, int cap) {
+                                  const long long* wants, float* logits, long long cap_floats, double* device_ms, char* error, int cap) {
     return guarded(error, cap, [&]() {
         Runner* run = static_cast<Runner*>(r);
+        cudaEvent_t start = nullptr, stop = nullptr;
+        if (device_ms) {                        // the step's time on the device, between events on the runner's stream
+            EG_CUDA(cudaEventCreate(&start));
+            EG_CUDA(cudaEventCreate(&stop));
+            EG_CUDA(cudaStreamSynchronize(run->runner->stream));
+            EG_CUDA(cudaEventRecord(start, run->runner->stream));
+        }
         std::vector<StepEntry> entries((size_t)n);
         long long at = 0;
         for (int i = 0; i < n; ++i) {
@@ -170,12 +205,20 @@ EGE_API long long ege_runner_step(void* r, int n, const long long* rids, const l
             at += counts[i];
         }
         const StepRunner::Result res = run->runner->run(entries, /*check=*/false, /*commit=*/true);
+        if (device_ms) EG_CUDA(cudaEventRecord(stop, run->runner->stream));
         const long long vocab = run->model->lm_head->vocab();
         if (res.rows > 0) {
             if ((long long)res.rows * vocab > cap_floats) throw std::invalid_argument("the caller's logits buffer is too small");
             EG_CUDA(cudaMemcpyAsync(logits, res.logits, (size_t)res.rows * vocab * 4, cudaMemcpyDeviceToHost, run->runner->stream));
         }
         run->runner->check_status();           // synchronises the stream: the logits are on the host
+        if (device_ms) {
+            float ms = 0.f;
+            EG_CUDA(cudaEventElapsedTime(&ms, start, stop));
+            *device_ms = ms;
+            cudaEventDestroy(start);
+            cudaEventDestroy(stop);
+        }
         return (long long)res.rows;
     });
 }

@@ -71,10 +71,13 @@ public:
 
     // Returns the buffer that now holds the residual stream, the other one, and what the last sub-layer left still to be
     // added (its output, or the PreNormed it prepared for next_norm, the norm that runs after this block).
-    Stream forward(const StepContext& ctx, Stream s, const CacheView& cache, void* work, const Norm* next_norm) const {
+    Stream forward(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, const Norm* next_norm) const {
         const int T = ctx.num_tokens;
         for (size_t i = 0; i < sublayers.size(); ++i) {
             const SubLayer& sub = sublayers[i];
+            // this sub-layer's arena: what the sub-layer before the last one left there is dead by now
+            ctx.arena = &arenas.sub[(*turn)++ & 1];
+            ctx.arena->reset();
             const Norm* following = (i + 1 < sublayers.size()) ? (sublayers[i + 1].plain_pre_norm ? sublayers[i + 1].norm.get() : nullptr) : next_norm;
             const int hidden = sub.norm ? sub.norm->size() : width_;
             if (sub.plain_pre_norm) {
@@ -229,25 +232,37 @@ public:
             for (Part* p : blocks[e.layer]->parts()) total += p->weight_bytes();
         return total + final_norm->weight_bytes() + lm_head->weight_bytes();
     }
-    // an upper bound of the activation memory a step of T tokens with R wanted rows takes from its arena
-    size_t activation_bytes(long long T, long long R) const {
-        long long widest = spec.hidden_size;
-        for (Part* p : all_parts())
-            for (const char* key : {"intermediate_size", "hidden_size"})
-                if (p->params.has(key)) widest = std::max(widest, 2 * p->params.integer(key));
-        for (Part* p : all_parts())
-            if (p->params.has("num_heads")) widest = std::max(widest, (p->params.integer("num_heads") + 2 * p->params.integer("num_kv_heads")) * p->params.integer("head_dim"));
-        // per token: the residual twice and a few rows of the widest activation in float32, with room for the attention's partial results
-        const size_t per_token = (size_t)(2 * spec.hidden_size + 8 * widest) * 4 + 64 * 1024;
-        return (size_t)T * per_token + (size_t)R * spec.vocab_size * 4 + (48u << 20);
+    // Upper bounds of the activation memory of a step of T tokens with R wanted rows: what lives for the whole step
+    // (residual stream, shared tables, normalised rows and logits of the wanted places) and what one sub-layer takes.
+    ArenaSizes activation_bytes(long long T, long long R) const {
+        long long widths = 4 * spec.hidden_size, head_dim = 0;
+        for (Part* p : all_parts()) {
+            if (p->params.has("intermediate_size")) widths = std::max(widths, 2 * spec.hidden_size + 3 * p->params.integer("intermediate_size"));
+            if (p->params.has("num_heads")) {
+                const long long hd = p->params.integer("head_dim"), q = p->params.integer("num_heads") * hd;
+                widths = std::max(widths, 2 * spec.hidden_size + 2 * q + 2 * p->params.integer("num_kv_heads") * hd);
+                head_dim = std::max(head_dim, hd);
+            }
+        }
+        ArenaSizes sizes;
+        // partial results of an attention whose keys are shared by several CTAs: bounded by the CTAs of a wave, not by T
+        const size_t partials = (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(head_dim + 2) * 4;
+        sizes.sub = (size_t)T * (size_t)widths * 4 + partials + (4u << 20);
+        sizes.step = (size_t)T * (size_t)(3 * spec.hidden_size + std::max<long long>(head_dim, 64)) * 4 + (size_t)R * (size_t)(spec.vocab_size + spec.hidden_size) * 4 +
+                     (4u << 20);
+        return sizes;
     }
 
     // Runs the batch through every run entry; returns float32 logits [R, vocab] at logit_rows (token indices into the
     // batch; nullptr with all_rows: rows 0..T-1 in order, a decode step), or nullptr when none is wanted.
-    float* forward(StepContext& ctx, const std::function<CacheView(int cache, bool writes)>& view, const int* logit_rows, int num_rows, bool all_rows) const {
+    float* forward(StepContext& ctx, StepArenas& arenas, const std::function<CacheView(int cache, bool writes)>& view, const int* logit_rows, int num_rows,
+                   bool all_rows) const {
         const int T = ctx.num_tokens;
         const int H = (int)spec.hidden_size;
         ctx.shared.clear();
+        arenas.reset();
+        ctx.step_arena = ctx.arena = &arenas.step;
+        int turn = 0;
         Block::Stream s;
         s.residual = ctx.take<float>((size_t)T * H);
         s.spare = ctx.take<float>((size_t)T * H);
@@ -257,8 +272,9 @@ public:
         const auto& order = spec.run_order;
         for (size_t i = 0; i < order.size(); ++i) {
             const Norm* next_norm = (i + 1 < order.size()) ? blocks[order[i + 1].layer]->first_norm() : final_norm.get();
-            s = blocks[order[i].layer]->forward(ctx, s, view(order[i].cache, order[i].writes_cache), work, next_norm);
+            s = blocks[order[i].layer]->forward(ctx, arenas, &turn, s, view(order[i].cache, order[i].writes_cache), work, next_norm);
         }
+        ctx.arena = &arenas.step;                // the head's rows and logits live for the step
         if (num_rows <= 0) return nullptr;
         PendingNorm pending(ctx, final_norm.get(), s.residual, s.delta, s.spare, work, T, all_rows ? nullptr : logit_rows, num_rows,
                             plans::fused_norm_max_tokens(H));

@@ -392,7 +392,7 @@ private:
         const std::string key = "rotation table " + rot.key;
         auto it = shared.find(key);
         if (it != shared.end()) return (const float*)it->second;
-        float* table = ctx.take<float>((size_t)ctx.num_tokens * rot.rotary_dim);
+        float* table = ctx.take_for_step<float>((size_t)ctx.num_tokens * rot.rotary_dim);
         launch_check(eg_rope_table(ctx.stream, ctx.positions, rot.inv_freq, table, ctx.num_tokens, rot.rotary_dim / 2), "rope_table");
         shared[key] = table;
         return table;

@@ -78,7 +78,11 @@ struct KernelScratch {
 struct StepContext {
     DType dtype = DType::BF16;
     cudaStream_t stream = nullptr;
+    // Activation memory.  `arena` is the current sub-layer's: a part takes what it needs from it, and what it hands back
+    // (its delta, prepared rows) stays valid until the sub-layer after the next one starts (two arenas take turns).
+    // `step_arena` holds what lives for the whole step (the residual stream, tables that layers share, the logits).
     Arena* arena = nullptr;
+    Arena* step_arena = nullptr;
     Blas* blas = nullptr;
     KernelScratch* scratch = nullptr;
     int num_tokens = 0, num_seqs = 0;
@@ -98,6 +102,7 @@ struct StepContext {
     std::map<std::string, void*> shared;    // per-step data that parts share between layers (cleared at every forward)
 
     template <class T> T* take(size_t n) const { return arena->take_n<T>(n); }
+    template <class T> T* take_for_step(size_t n) const { return step_arena->take_n<T>(n); }
     void* take_rows(size_t rows, size_t cols, DType t) const { return arena->take(rows * cols * dtype_size(t)); }
 };
 

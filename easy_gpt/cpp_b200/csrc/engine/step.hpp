@@ -279,7 +279,7 @@ public:
             meta_.allocate((size_t)size_ * 4, true);
             for (auto& s : staging_) s.ensure((size_t)size_ * 4);
             for (auto& e : events_) EG_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-            arena_.reset(new Arena(r.model.activation_bytes(bucket, bucket)));
+            arenas_.reset(new StepArenas(r.model.activation_bytes(bucket, bucket)));
             counts_.assign(bucket, 1);
             // what depends on the bucket alone, and rows of padding everywhere: written once
             int32_t* hv = staging_[0].as<int32_t>();
@@ -294,7 +294,6 @@ public:
             // run once eagerly (library plans come into being), then capture
             forward(r);
             EG_CUDA(cudaStreamSynchronize(r.stream));
-            arena_->reset();
             EG_CUDA(cudaStreamBeginCapture(r.stream, cudaStreamCaptureModeThreadLocal));
             try {
                 logits_ = forward(r);
@@ -306,6 +305,9 @@ public:
             }
             cudaGraph_t graph = nullptr;
             EG_CUDA(cudaStreamEndCapture(r.stream, &graph));
+            size_t nodes = 0;
+            cudaGraphGetNodes(graph, nullptr, &nodes);
+            launches = (int)nodes;
             const cudaError_t e = cudaGraphInstantiate(&exec_, graph, 0);
             cudaGraphDestroy(graph);
             cuda_check(e, "cudaGraphInstantiate");
@@ -347,6 +349,7 @@ public:
         int32_t* token_ids() const { return meta_.as<int32_t>() + off_tokens_; }
         size_t meta_bytes() const { return (size_t)size_ * 4; }
         const int bucket, table_width;
+        int launches = 0;               // nodes of the captured graph: the kernels one replay launches
 
     private:
         void fill_padding(StepRunner& r, int32_t* hv, int first_row) {
@@ -363,7 +366,6 @@ public:
             StepContext ctx;
             ctx.dtype = r.model.dtype;
             ctx.stream = r.stream;
-            ctx.arena = arena_.get();
             ctx.blas = &r.blas_;
             ctx.scratch = &r.scratch_;
             ctx.num_tokens = ctx.num_seqs = bucket;
@@ -380,7 +382,7 @@ public:
             ctx.max_query_len = 1;
             ctx.max_context_len = (long long)table_width * r.cache.page_size;
             ctx.all_decode = true;
-            return r.model.forward(ctx, [&](int c, bool w) { return r.cache.view(c, w); }, nullptr, bucket, /*all_rows=*/true);
+            return r.model.forward(ctx, *arenas_, [&](int c, bool w) { return r.cache.view(c, w); }, nullptr, bucket, /*all_rows=*/true);
         }
 
         long long size_ = 0, off_tokens_ = 0, off_positions_ = 0, off_context_ = 0, off_slots_ = 0, off_token_seq_ = 0, off_starts_ = 0;
@@ -391,7 +393,7 @@ public:
         std::array<cudaEvent_t, 4> events_{};
         std::array<bool, 4> used_{};
         int next_ = 0;
-        std::unique_ptr<Arena> arena_;
+        std::unique_ptr<StepArenas> arenas_;
         cudaGraphExec_t exec_ = nullptr;
         float* logits_ = nullptr;
     };
@@ -489,20 +491,19 @@ private:
         EG_CUDA(cudaEventRecord(ring_events_[turn], stream));
         ring_used_[turn] = true;
 
-        const size_t need = model.activation_bytes(T, R);
-        if (!arena_ || arena_->capacity() < need) {
+        const ArenaSizes need = model.activation_bytes(T, R);
+        if (!arenas_ || !arenas_->holds(need)) {
             EG_CUDA(cudaStreamSynchronize(stream));
-            arena_.reset();
-            arena_.reset(new Arena(std::max(need, model.activation_bytes(options.max_batch_tokens, options.max_slots))));
+            const ArenaSizes usual = model.activation_bytes(options.max_batch_tokens, options.max_slots);
+            arenas_.reset();
+            arenas_.reset(new StepArenas(ArenaSizes{std::max(need.step, usual.step), std::max(need.sub, usual.sub)}));
         }
-        arena_->reset();
         const int32_t* m = dev_meta_.as<int32_t>();
         const int32_t* hv = ring_[turn].as<int32_t>();
         auto at = [&](int section) { return m + layout[2 * section]; };
         StepContext ctx;
         ctx.dtype = model.dtype;
         ctx.stream = stream;
-        ctx.arena = arena_.get();
         ctx.blas = &blas_;
         ctx.scratch = &scratch_;
         ctx.num_tokens = (int)T;
@@ -532,7 +533,7 @@ private:
         }
         cache.zero_fresh_state(stream);         // slots taken since the last step (by this step or by the scheduler)
         Result r;
-        r.logits = model.forward(ctx, [&](int c, bool w) { return cache.view(c, w); }, R ? at(host::LOGIT_ROWS) : nullptr, (int)R, false);
+        r.logits = model.forward(ctx, *arenas_, [&](int c, bool w) { return cache.view(c, w); }, R ? at(host::LOGIT_ROWS) : nullptr, (int)R, false);
         r.rows = (int)R;
         return r;
     }
@@ -541,7 +542,7 @@ private:
     int* status_host_ = nullptr;
     Blas blas_;
     KernelScratch scratch_;
-    std::unique_ptr<Arena> arena_;
+    std::unique_ptr<StepArenas> arenas_;
     std::array<PinnedBuffer, 4> ring_;
     std::array<cudaEvent_t, 4> ring_events_{};
     std::array<bool, 4> ring_used_{};

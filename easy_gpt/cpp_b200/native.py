@@ -47,9 +47,10 @@ def library() -> ctypes.CDLL:
             "ege_engine_stats": (None, [c_void_p, c_void_p]),
             "ege_engine_figure": (c_longlong, [c_void_p, c_int, c_longlong]),
             "ege_engine_sync": (None, [c_void_p]),
+            "ege_engine_time_steps": (c_longlong, [c_void_p, c_int, c_void_p, c_char_p, c_int]),
             "ege_runner_create": (c_void_p, [c_char_p, c_char_p, c_int, c_int, c_int, c_longlong, c_int, c_char_p, c_int]),
             "ege_runner_destroy": (None, [c_void_p]),
-            "ege_runner_step": (c_longlong, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_char_p, c_int]),
+            "ege_runner_step": (c_longlong, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_char_p, c_int]),
             "ege_runner_end": (None, [c_void_p, c_longlong]),
             "ege_runner_info": (c_longlong, [c_void_p, c_int, c_int]),
         }
@@ -147,11 +148,23 @@ class NativeEngine:
     def last_step_h2d_bytes(self) -> int:
         return int(self._lib.ege_engine_figure(self._h, 1, 0))
 
+    def last_step_launches(self) -> int:
+        """Kernels that one replay of the last captured step launches."""
+        return int(self._lib.ege_engine_figure(self._h, 3, 0))
+
     def cached_length(self, rid: int) -> int:
         return int(self._lib.ege_engine_figure(self._h, 2, rid))
 
     def sync(self) -> None:
         self._lib.ege_engine_sync(self._h)
+
+    def time_steps(self, steps: int):
+        """Runs ``steps`` steps and returns (seconds on the device by CUDA events on the engine's stream around them,
+        wall-clock seconds until the last step's tokens are on the host)."""
+        out = np.zeros(2, dtype=np.float64)
+        if self._lib.ege_engine_time_steps(self._h, int(steps), out.ctypes.data, self._err, _ERR) < 0:
+            self._fail()
+        return float(out[0]) / 1e3, float(out[1]) / 1e3
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None, max_steps: Optional[int] = None,
                  temperature: float = 0.8, top_p: float = 0.95, top_k: int = 20, seed: int = 42, greedy: bool = False) -> List[List[int]]:
@@ -184,6 +197,7 @@ class NativeStepRunner:
         if not self._h:
             raise NativeError(self._err.value.decode(errors="replace"))
         self.vocab = int(self._lib.ege_runner_info(self._h, 0, 0))
+        self._device_ms = np.zeros(1, dtype=np.float64)
         self._handles: Dict[Hashable, int] = {}
         self._next = 1 << 40
 
@@ -213,10 +227,15 @@ class NativeStepRunner:
         rows = int(want_offsets[n])
         logits = np.empty((max(rows, 1), self.vocab), dtype=np.float32)
         got = self._lib.ege_runner_step(self._h, n, rids.ctypes.data, counts.ctypes.data, tokens.ctypes.data, want_offsets.ctypes.data,
-                                        wants.ctypes.data, logits.ctypes.data, logits.size, self._err, _ERR)
+                                        wants.ctypes.data, logits.ctypes.data, logits.size, self._device_ms.ctypes.data, self._err, _ERR)
         if got < 0:
             raise NativeError(self._err.value.decode(errors="replace"))
         return logits[:rows] if rows else None
+
+    @property
+    def last_step_device_seconds(self) -> float:
+        """The last step's time on the device (CUDA events on the runner's stream around its launches)."""
+        return float(self._device_ms[0]) / 1e3
 
     def end(self, rid) -> None:
         self._lib.ege_runner_end(self._h, self._handle(rid))
