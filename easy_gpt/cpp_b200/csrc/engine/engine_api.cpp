@@ -224,7 +224,8 @@ EGE_API long long ege_runner_step(void* r, int n, const long long* rids, const l
 }
 EGE_API void ege_runner_end(void* r, long long rid) { static_cast<Runner*>(r)->runner->end(rid); }
 // what: 0 vocabulary, 1 live requests, 2 captured-step replays, 3 free pages of group `arg`, 4 pages of group `arg`, 5 pages handed
-// out over the life of group `arg`'s pool, 6 number of groups, 7 books in order (1) or not (0)
+// out over the life of group `arg`'s pool, 6 number of groups, 7 books in order (1) or not (0), 8 captured steps of shapes other
+// than decode buckets
 EGE_API long long ege_runner_info(void* r, int what, int arg) {
     Runner* run = static_cast<Runner*>(r);
     DeviceCache& cache = run->runner->cache;
@@ -240,6 +241,7 @@ EGE_API long long ege_runner_info(void* r, int what, int arg) {
             std::string why;
             return cache.core.check(&why) == host::OK ? 1 : 0;
         }
+        case 8: return (long long)run->runner->signature_graph_count();
     }
     return -1;
 }

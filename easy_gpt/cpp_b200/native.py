@@ -243,5 +243,5 @@ class NativeStepRunner:
 
     def info(self, what: str, group: int = 0) -> int:
         index = {"vocab": 0, "live_requests": 1, "graph_replays": 2, "free_pages": 3, "pages": 4, "pages_handed_out": 5, "groups": 6,
-                 "books_in_order": 7}[what]
+                 "books_in_order": 7, "captured_shapes": 8}[what]
         return int(self._lib.ege_runner_info(self._h, index, group))

@@ -102,6 +102,32 @@ def test_native_many_live_requests(live, config, dtype, tmp_path):
     assert runner.info("graph_replays") >= 9
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_native_captures_a_step_shape_of_several_entries(dtype, tmp_path):
+    """Two decoding requests beside a portion of six tokens of a third, 24 steps in a row: the shape is captured when
+    it has come often enough and replayed afterwards; every step, eager or replayed, agrees with the plain implementation."""
+    from easy_gpt.cpp_b200.native import NativeStepRunner
+
+    folder = tiny_configs.write_tiny("TINY_B", tmp_path / "m")
+    requests = {"d0": tiny_configs.random_tokens(384, 54, 1), "d1": tiny_configs.random_tokens(384, 47, 2),
+                "p": tiny_configs.random_tokens(384, 144, 3)}
+    cfg, w = plain_model.read_model_dir(folder, round_to_bf16=(dtype == "bfloat16"))
+    refs = {rid: plain_model.forward_logits(cfg, w, toks).numpy() for rid, toks in requests.items()}
+    steps = [{"step": 0, "entries": [{"id": "d0", "tokens": requests["d0"][:30], "want": [29]},
+                                     {"id": "d1", "tokens": requests["d1"][:23], "want": [22]}], "end": []}]
+    for i in range(24):
+        steps.append({"step": len(steps), "end": [], "entries": [
+            {"id": "d0", "tokens": [requests["d0"][30 + i]], "want": [0]},
+            {"id": "d1", "tokens": [requests["d1"][23 + i]], "want": [0]},
+            {"id": "p", "tokens": requests["p"][6 * i:6 * i + 6], "want": [0, 5]}]})
+    steps[-1]["end"] = ["d0", "d1", "p"]
+    runner = NativeStepRunner(folder, dtype, 16, H.max_live_tokens(steps, 16) // 16, 4)
+    got = run_native(runner, steps)
+    tol = F32_ATOL if dtype == "float32" else 1.5e-2 * max(float(np.abs(r).max()) for r in refs.values())
+    H.compare(got, refs, tol, f"native captured mixed step {dtype}")
+    assert runner.info("captured_shapes") == 1 and runner.info("graph_replays") >= 8
+
+
 def check_greedy(folder, prompts, outputs, dtype, tol):
     cfg, w = plain_model.read_model_dir(folder, round_to_bf16=(dtype == "bfloat16"))
     for prompt, out in zip(prompts, outputs):
