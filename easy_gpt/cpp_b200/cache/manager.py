@@ -125,7 +125,8 @@ class CacheManager:
                 g.kv = torch.zeros((len(g.cache_ids), g.pool.num_pages + 1, 2, g.need.num_kv_heads, page_size, g.need.head_dim),
                                    device=device, dtype=dtype)
             for cache_id, need in self._state_needs.items():
-                self.state[cache_id] = torch.zeros((max_slots, *need.shape), device=device, dtype=getattr(torch, need.dtype))
+                # one slot more than requests can take: the scratch slot that padding rows of a captured batch use
+                self.state[cache_id] = torch.zeros((max_slots + 1, *need.shape), device=device, dtype=getattr(torch, need.dtype))
 
     def __del__(self):
         core = getattr(self, "core", None)

@@ -197,7 +197,7 @@ def engine_paths(verbose: bool = True):
     if verbose:
         print(f"[easy_gpt.cpp_b200] building the native engine into {out_dir} (first call only)", file=sys.stderr, flush=True)
     common = [*ENGINE_FLAGS, "-I", str(cuda / "include"), "-I", str(HERE / "host")]
-    link = ["-L", str(out_dir), "-leasygpt_kernels", *[a for d in lib_dirs for a in ("-L", str(d))], "-lcudart", "-lcublas", "-lcublasLt",
+    link = ["-L", str(out_dir), "-leasygpt_kernels", *[a for d in lib_dirs for a in ("-L", str(d))], "-lcudart", "-lcublas", "-lcublasLt", "-ldl",
             "-Wl,-rpath,$ORIGIN", *[f"-Wl,-rpath,{d}" for d in lib_dirs]]
     tmp_lib = out_dir / (ENGINE_LIB_NAME + f".{os.getpid()}.tmp")
     r = subprocess.run([cxx, *common, "-shared", str(HERE / "engine" / "engine_api.cpp"), "-o", str(tmp_lib), *link], capture_output=True, text=True)
@@ -212,6 +212,25 @@ def engine_paths(verbose: bool = True):
     os.replace(tmp_exe, exe)
     stamp.write_text(json.dumps({"fingerprint": fp}))
     return lib, exe
+
+
+def build_plugin(source, output, verbose: bool = True) -> Path:
+    """Builds a plugin of the native engine (a .cu or .cpp file that includes ``engine/plugin.hpp`` and exports
+    ``easygpt_register``) into a shared library at ``output``."""
+    library_path(verbose)
+    cuda = _cuda_home()
+    source, output = Path(source), Path(output)
+    flags = ["-std=c++17", "-O2", "-I", str(HERE / "engine"), "-I", str(HERE), "-I", str(HERE / "host"), "-I", str(cuda / "include")]
+    if source.suffix == ".cu":
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", *flags, str(source), "-o", str(output),
+               "-L", str(library_path(False).parent), "-leasygpt_kernels", "-lcublas", "-lcublasLt"]
+    else:
+        cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+        cmd = [cxx, "-shared", "-fPIC", *flags, str(source), "-o", str(output)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"building the plugin {source} failed:\n{r.stdout}\n{r.stderr}")
+    return output
 
 
 if __name__ == "__main__":

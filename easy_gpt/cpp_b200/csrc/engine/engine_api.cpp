@@ -1,6 +1,8 @@
 // C interface of the native engine (libeasygpt_engine.so) for the Python face (native.py), bin/trace_run and any other
 // caller.  Handles are opaque pointers.  Functions return 0 or a non-negative result on success and -1 on failure, with the
 // error text in the caller's buffer.  Nothing here is specific to one architecture: the model class is chosen by config.json.
+#include <dlfcn.h>
+
 #include <cstring>
 
 #include "engine.hpp"
@@ -36,6 +38,25 @@ struct Runner {
     std::vector<float> host_logits;
 };
 }  // namespace
+
+// ---- plugins: parts and architectures from outside the library ------------------------------------------------------------
+// A plugin is a shared library built against the engine's headers (csrc/engine/plugin.hpp) that exports
+//     extern "C" void easygpt_register(easygpt::engine::PartRegistry*, easygpt::engine::ArchitectureRegistry*);
+// It is loaded once, stays loaded, and adds its mixers, feed-forwards, norms, position encodings, embeddings, heads and
+// architectures to the registries that models are built from.  Nothing of the library's sources changes for it.
+EGE_API long long ege_load_plugin(const char* path, char* error, int cap) {
+    return guarded(error, cap, [&]() {
+        register_builtin_parts();
+        register_builtin_architectures();
+        void* handle = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+        if (!handle) throw std::runtime_error(std::string("cannot load the plugin ") + path + ": " + dlerror());
+        using RegisterFn = void (*)(PartRegistry*, ArchitectureRegistry*);
+        RegisterFn fn = reinterpret_cast<RegisterFn>(dlsym(handle, "easygpt_register"));
+        if (!fn) throw std::runtime_error(std::string(path) + " exports no easygpt_register");
+        fn(&PartRegistry::instance(), &ArchitectureRegistry::instance());
+        return 0;
+    });
+}
 
 // ---- the engine ---------------------------------------------------------------------------------------------------
 // options (8 long longs): page_size, cache_tokens (0: default), max_active, prefill_batch, max_batch_tokens, chunk_size,

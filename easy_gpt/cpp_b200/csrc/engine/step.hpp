@@ -3,7 +3,8 @@
 // DeviceCache: the bookkeeping of csrc/host/cache_core.hpp (pages, block tables, slots) with the device memory it
 // addresses: per group of caches with the same needs one tensor [caches, pages + 1, 2 (k, v), kv_heads, page_size,
 // head_dim] in the engine's dtype (the extra page is the scratch page that padding rows of a captured batch write
-// to), and per cache that asked for fixed-size state one tensor [slots, elements], zeroed when a request takes a slot.
+// to), and per cache that asked for fixed-size state one tensor [slots + 1, elements], zeroed when a request takes a slot
+// (the extra slot is the scratch slot that padding rows of a captured batch use).
 //
 // StepRunner: one batch of (request, its next tokens) through the model.  A batch is any mix of prompt portions and
 // single decoded tokens, cut anywhere.  run() reserves cache pages for the new tokens (all or nothing), packs the
@@ -87,7 +88,7 @@ public:
                 for (long long s : need.state_shape) elems *= (size_t)s;
                 State st;
                 st.bytes_per_slot = elems * dtype_size(need.state_dtype);
-                st.memory.allocate(st.bytes_per_slot * max_slots, true);
+                st.memory.allocate(st.bytes_per_slot * (size_t)(max_slots + 1), true);     // one slot more: the scratch slot of padding rows
                 states.emplace(kv.first, std::move(st));
             }
         }
@@ -401,7 +402,10 @@ public:
             int first_token = 0;
             for (int i = 0; i < first_row; ++i) first_token += counts_[i];
             for (int t = first_token; t < tokens; ++t) hv[off_tokens_ + t] = hv[off_positions_ + t] = 0;
-            for (int i = first_row; i < entries; ++i) hv[off_context_ + i] = hv[off_slots_ + i] = 0;
+            for (int i = first_row; i < entries; ++i) {
+                hv[off_context_ + i] = 0;
+                hv[off_slots_ + i] = r.cache.max_slots;           // the scratch slot: no request's state
+            }
             for (size_t g = 0; g < r.cache.groups.size(); ++g) {
                 const int scratch = r.cache.groups[g]->scratch_page;
                 for (int t = first_token; t < tokens; ++t) hv[off_slot_map_[g] + t] = scratch * r.cache.page_size;

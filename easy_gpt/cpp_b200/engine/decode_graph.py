@@ -145,9 +145,11 @@ class DecodeGraph:
         cache = self.runner.cache
         B = self.bucket
         first_token = int(self.starts[start_row])
-        for name, first in (("token_ids", first_token), ("positions", first_token), ("seq_context", start_row), ("seq_slots", start_row)):
+        for name, first in (("token_ids", first_token), ("positions", first_token), ("seq_context", start_row)):
             o, size = self.offsets[name]
             hv[o + first:o + size] = 0
+        o, size = self.offsets["seq_slots"]
+        hv[o + start_row:o + size] = cache.max_slots           # the scratch slot: no request's state
         for g in cache.groups:
             o, size = self.offsets[f"slot_map{g.index}"]
             hv[o + first_token:o + size] = g.scratch_page * g.page_size

@@ -48,6 +48,7 @@ def library() -> ctypes.CDLL:
             "ege_engine_figure": (c_longlong, [c_void_p, c_int, c_longlong]),
             "ege_engine_sync": (None, [c_void_p]),
             "ege_engine_time_steps": (c_longlong, [c_void_p, c_int, c_void_p, c_char_p, c_int]),
+            "ege_load_plugin": (c_longlong, [c_char_p, c_char_p, c_int]),
             "ege_runner_create": (c_void_p, [c_char_p, c_char_p, c_int, c_int, c_int, c_longlong, c_int, c_char_p, c_int]),
             "ege_runner_destroy": (None, [c_void_p]),
             "ege_runner_step": (c_longlong, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_char_p, c_int]),
@@ -62,6 +63,16 @@ def library() -> ctypes.CDLL:
 
 
 _ERR = 2048
+
+
+def load_plugin(path) -> None:
+    """Loads a shared library that registers further parts and architectures with the native engine (built with
+    ``csrc.build.build_plugin`` from a source that includes ``csrc/engine/plugin.hpp``)."""
+    err = ctypes.create_string_buffer(_ERR)
+    if library().ege_load_plugin(str(path).encode(), err, _ERR) < 0:
+        raise NativeError(err.value.decode(errors="replace"))
+
+
 _STATES = ("waiting", "running", "finished")
 _REASONS = (None, "empty", "eos", "length", "max_positions", "error")
 
