@@ -261,7 +261,12 @@ def print_timeline(folder, config, batch):
     engine = GptEngine(folder, dtype="bfloat16", page_size=64, cache_tokens=batch * (room + 63), max_active=batch,
                        prefill_batch=batch, max_batch_tokens=prefill_budget, chunk_size=4096, max_tokens_per_request=room)
     kernels.Timeline.names = []
-    prepare_decode(engine, batch, start_context, 100, config["vocab_size"], seed=1)
+    from easy_gpt.cpp_b200.sampling import GREEDY
+
+    reqs = [engine.add_request(p, GREEDY, max_new_tokens=100) for p in prompts_for(batch, start_context, config["vocab_size"], 1)]
+    while any(r.known - r.computed != 1 or r.state != "running" for r in reqs):
+        engine.step()
+    engine.sync()
     for _ in range(5):
         engine.step()
     torch.cuda.synchronize()
@@ -273,15 +278,23 @@ def print_timeline(folder, config, batch):
     print(f"decode step, batch {batch}, context {CONTEXT}: {len(rows)} traced kernels, {(t1 - t0) / 1e3:.1f} us from first start to last end")
     agg = collections.OrderedDict()
     prev_end = t0
-    for name, start, end, _ in rows:
-        a = agg.setdefault(name, [0, 0.0, 0.0])
+    for name, start, end, marks in rows:
+        a = agg.setdefault(name, [0, 0.0, 0.0, [0.0] * 6])
         a[0] += 1
         a[1] += (end - start) / 1e3
         a[2] += (prev_end - start) / 1e3
+        for i in range(6):                           # the kernel's phase stamps (latest over its CTAs), counted from the end of the kernel in front
+            a[3][i] += (marks[i] - prev_end) / 1e3 if marks[i] else 0.0
+        a.append(0.0) if len(a) == 4 else None
+        a[4] += (end - prev_end) / 1e3
         prev_end = end
     print(f"{'kernel':58s} {'n':>4s} {'first start..last end us':>25s} {'started before previous end us':>31s}")
-    for name, (n, dur, early) in agg.items():
+    for name, (n, dur, early, _, _) in agg.items():
         print(f"{name:58s} {n:4d} {dur / n:25.2f} {early / n:31.2f}")
+    print("\nphases, microseconds after the end of the kernel in front (mean): before the dependency wait, after it, input rows ready, "
+          "product done, summed inside the CTA, summed across CTAs, end of the kernel")
+    for name, (n, _, _, marks, total) in agg.items():
+        print(f"{name:58s} " + " ".join(f"{m / n:7.2f}" for m in marks) + f" {total / n:7.2f}")
     return 0
 
 

@@ -740,7 +740,9 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
     }
-    // persistent CTAs, two per SM, that deal the units out among themselves
+    // Persistent CTAs, two per SM, that deal the units out among themselves.  (Measured with one CTA per SM: a prompt of
+    // 2,048 tokens, which lasts as long as its longest unit, takes 38 us instead of 41; one of 8,192 tokens, where the SMs
+    // are full, 406 us instead of 251: the second CTA's MMAs run under the first one's softmax.)
     const long long units = (long long)num_tiles * num_heads * max_parts;
     const int ctas = (int)(units < 2ll * sm_count ? units : 2ll * sm_count);
     int code = head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, ctas) : launch<128>(stream, map_q, map_k, map_v, p, ctas);

@@ -245,8 +245,9 @@ public:
             }
         }
         ArenaSizes sizes;
-        // partial results of an attention whose keys are shared by several CTAs: bounded by the CTAs of a wave, not by T
-        const size_t partials = (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(head_dim + 2) * 4;
+        // partial results of an attention whose keys are shared by several CTAs: capped for prompt portions, and bounded by
+        // the CTAs of a few waves for single tokens
+        const size_t partials = plans::PREFILL_PARTS_SCRATCH_BYTES + (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(head_dim + 2) * 4;
         sizes.sub = (size_t)T * (size_t)widths * 4 + partials + (4u << 20);
         sizes.step = (size_t)T * (size_t)(3 * spec.hidden_size + std::max<long long>(head_dim, 64)) * 4 + (size_t)R * (size_t)(spec.vocab_size + spec.hidden_size) * 4 +
                      (4u << 20);

@@ -347,7 +347,7 @@ public:
                 int parts, part_tiles;
                 plans::attention_prefill_parts(ctx.num_tiles, heads_, &parts, &part_tiles);
                 const size_t slots = (size_t)ctx.num_tiles * heads_;
-                while (parts > 1 && slots * parts * 128 * (head_dim_ + 2) * 4 > (256u << 20)) --parts;
+                while (parts > 1 && slots * parts * 128 * (head_dim_ + 2) * 4 > plans::PREFILL_PARTS_SCRATCH_BYTES) --parts;
                 float *partial_o = nullptr, *partial_ml = nullptr;
                 if (parts > 1) {
                     partial_o = ctx.take<float>(slots * parts * 128 * head_dim_);

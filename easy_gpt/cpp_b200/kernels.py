@@ -462,7 +462,11 @@ def attention_prefill_parts(num_tiles: int, num_heads: int):
     (of 64) of a part; the kernel cuts a tile's keys into min(parts, key tiles / part_tiles) parts, so
     the cut follows the contexts of the step at hand (a captured step is replayed with others).
     A part costs its CTA a start-up of some microseconds and a pass of the merge kernel, which pays
-    only while there are fewer (tile, head) pairs than the two CTAs per SM."""
+    only while there are fewer (tile, head) pairs than the two CTAs per SM: the kernel is bound by
+    what an SM gets through (about 0.64 key tiles a microsecond with both its CTAs busy), not by its
+    longest unit.  Measured on B200 (14 heads of 64, pages of 64): a portion of 512 tokens on a context
+    of 3,584 takes 68 us uncut, 34 us in 4 parts and 43 us in 8; a prompt of 2,048 tokens (224 pairs for
+    296 CTAs) takes 41 us uncut and 40 to 62 us however it is cut."""
     wanted = min(2 * sm_count() // max(1, num_tiles * num_heads), 8)
     return (wanted, PREFILL_PART_TILES) if wanted >= 2 else (1, 1 << 20)
 
