@@ -279,22 +279,26 @@ def print_timeline(folder, config, batch):
     agg = collections.OrderedDict()
     prev_end = t0
     for name, start, end, marks in rows:
-        a = agg.setdefault(name, [0, 0.0, 0.0, [0.0] * 6])
+        a = agg.setdefault(name, [0, 0.0, 0.0, [0.0] * 6, 0.0, [0.0] * 6])
         a[0] += 1
         a[1] += (end - start) / 1e3
         a[2] += (prev_end - start) / 1e3
         for i in range(6):                           # the kernel's phase stamps (latest over its CTAs), counted from the end of the kernel in front
             a[3][i] += (marks[i] - prev_end) / 1e3 if marks[i] else 0.0
-        a.append(0.0) if len(a) == 4 else None
+            earliest = ~marks[7 + i] & ((1 << 64) - 1) if marks[7 + i] else 0      # stored as its complement
+            a[5][i] += (earliest - prev_end) / 1e3 if earliest else 0.0
         a[4] += (end - prev_end) / 1e3
         prev_end = end
     print(f"{'kernel':58s} {'n':>4s} {'first start..last end us':>25s} {'started before previous end us':>31s}")
-    for name, (n, dur, early, _, _) in agg.items():
+    for name, (n, dur, early, _, _, _) in agg.items():
         print(f"{name:58s} {n:4d} {dur / n:25.2f} {early / n:31.2f}")
     print("\nphases, microseconds after the end of the kernel in front (mean): before the dependency wait, after it, input rows ready, "
           "product done, summed inside the CTA, summed across CTAs, end of the kernel")
-    for name, (n, _, _, marks, total) in agg.items():
+    for name, (n, _, _, marks, total, _) in agg.items():
         print(f"{name:58s} " + " ".join(f"{m / n:7.2f}" for m in marks) + f" {total / n:7.2f}")
+    print("\nthe same for the CTA (at 'product done': the warp) that gets there first")
+    for name, (n, _, _, _, _, firsts) in agg.items():
+        print(f"{name:58s} " + " ".join(f"{m / n:7.2f}" for m in firsts))
     return 0
 
 

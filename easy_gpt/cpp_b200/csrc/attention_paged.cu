@@ -68,7 +68,7 @@ struct Params {
     int* status;
     const void* prefetch;         // weights of a kernel that runs soon: pulled into L2 meanwhile
     long long prefetch_bytes;
-    int* counters;                // [tokens * gridDim.y] tickets, zero before and after every launch
+    int* counters;                // [tokens of this launch * gridDim.y] tickets, zero before and after every launch
     int use_pdl;
     unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
     const int* token_list;        // optional: the tokens this launch works on (blockIdx.x indexes it); null: all, in order
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         }
     }
     cp_async_wait<0>();
-    trace_scope.mark(3);
+    trace_scope.mark(3, true);
     __syncthreads();                                                              // the pipeline's memory is free now
 
     // ---- merge the four warps: rows r = gid, gid + 8
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        int* counter = p.counters + (size_t)t * gridDim.y + blockIdx.y;
+        int* counter = p.counters + (size_t)blockIdx.x * gridDim.y + blockIdx.y;   // by the token's place in this launch
         const int ticket = atomicAdd(counter, 1);
         is_last = ticket == p.splits - 1;
         if (is_last) *counter = 0;                                                // all have arrived: ready for the next launch

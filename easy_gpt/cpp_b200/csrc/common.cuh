@@ -72,9 +72,14 @@ struct TraceScope {
     __device__ __forceinline__ ~TraceScope() {
         if (slot && threadIdx.x == 0) atomicMax(slot + 1, now());
     }
-    // Phase stamps, the latest over the launch's CTAs: slot[2 + i], i < 14.
-    __device__ __forceinline__ void mark(int i) const {
-        if (slot && threadIdx.x == 0) atomicMax(slot + 2 + i, now());
+    // Phase stamps, i < 7: slot[2 + i] the latest over the launch's CTAs, slot[9 + i] the complement of the earliest
+    // (so that zero means "none" for both).  every_warp: each warp's first lane stamps, not only the CTA's first thread.
+    __device__ __forceinline__ void mark(int i, bool every_warp = false) const {
+        if (slot && (every_warp ? (threadIdx.x & 31) == 0 : threadIdx.x == 0)) {
+            const unsigned long long t = now();
+            atomicMax(slot + 2 + i, t);
+            atomicMax(slot + 9 + i, ~t);
+        }
     }
 };
 

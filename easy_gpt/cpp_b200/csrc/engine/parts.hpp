@@ -123,7 +123,7 @@ public:
         }
         SkinnyRope none{};
         const SkinnyRope& r = rope ? *rope : none;
-        launch_check(eg_gemm_skinny(ctx.stream, epilogue, norm_mode, plans::USE_PDL, weight, in_features, bias_f32(), M, N, K,
+        launch_check(eg_gemm_skinny(ctx.stream, epilogue, norm_mode, plans::use_pdl(), weight, in_features, bias_f32(), M, N, K,
                                     x ? x->p : nullptr, x ? x->ld : 0, resid_in, resid_out, delta, gain, eps, out, ldo, plan.row_blocks,
                                     plan.k_slices, plan.k_split, partials, counters, r.num_heads, r.num_kv_heads, r.head_dim, r.positions,
                                     r.slot_map, r.k_cache, r.v_cache, r.inv_freq, r.page_size, r.page_stride, r.head_stride, r.pool_slots,
@@ -405,14 +405,14 @@ private:
             const size_t T = (size_t)ctx.num_tokens;
             acc = ctx.take<float>(T * heads_ * splits * head_dim_);
             ml = ctx.take<float>(T * heads_ * splits * 2);
-            if (T * kv_heads_ * ((heads_ / kv_heads_ + 15) / 16) > KernelScratch::ATTENTION_COUNTERS)
+            if ((size_t)tokens * kv_heads_ * ((heads_ / kv_heads_ + 15) / 16) > KernelScratch::ATTENTION_COUNTERS)
                 throw DeviceError("a step has more (token, KV head) pairs than the attention's ticket counters");
             counters = ctx.scratch->attention_counters.as<int>();
         }
         launch_check(eg_attention_paged(ctx.stream, qkv.p, (int)qkv.ld, cache.k, cache.v, tables.block_table, tables.table_width, ctx.token_seq,
                                         ctx.positions, seq_context, attn.p, (int)attn.ld, acc, ml, tokens, heads_, kv_heads_, head_dim_, cache.page_size,
                                         cache.page_stride, cache.head_stride, cache.num_pages, window, scale_, splits, ctx.status, nullptr, 0, counters,
-                                        plans::USE_PDL, nullptr, token_list), "attention_paged");
+                                        plans::use_pdl(), nullptr, token_list), "attention_paged");
     }
 
     int hidden_, heads_, kv_heads_, head_dim_;

@@ -17,7 +17,16 @@ constexpr int FUSED_NORM_MAX_TOKENS = 16;  // every CTA repeats the norm prologu
 constexpr int MAX_HEAD_DIM = 256;          // the generic attention kernel keeps up to eight dimensions of a head per lane
 constexpr int TCGEN05_ATTENTION_MIN_QUERY = 33;
 constexpr size_t PREFILL_PARTS_SCRATCH_BYTES = 64u << 20;   // most memory for the partial results of a prompt attention whose key ranges are cut
-constexpr int USE_PDL = 2;                 // a decode kernel lets the next one start once it has passed its own wait
+// When a decode kernel lets the next one start: 2 once it has passed its own wait (the fastest measured), 1 at once,
+// 0 never, i.e. no programmatic dependent launch (EASY_GPT_PDL, for measurements)
+inline int use_pdl() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* forced = std::getenv("EASY_GPT_PDL");
+        mode = forced ? std::atoi(forced) : 2;
+    }
+    return mode;
+}
 enum Epilogue { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3, EPI_RESID_NORM = 4 };
 
 inline int sm_count() {
@@ -92,7 +101,7 @@ inline SkinnyPlan skinny_plan(int n_rows, int in_features, int head_dim = 0) {
         while (ks * 2 * rb <= 16 && chunks > 4 * ks) ks *= 2;
         return {rb, ks, 1};
     }
-    if (n_rows >= 64 * sm_count()) return {4, 2, 1};   // wide matrices (gate/up, the head): 64 rows per CTA
+    if (n_rows >= 64 * sm_count()) return {4, 2, 1};   // wide matrices (gate/up, the head): 64 rows per CTA (sixteen warps measured slower)
     const int rb = 1, ks = 8;
     // (Python's round() sends halves to the even neighbour; so does nearbyint in the default rounding mode)
     int split = (int)std::max(1.0, std::min(8.0, std::nearbyint(chunks / (ks * 2.5))));

@@ -197,8 +197,22 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         for (int i = threadIdx.x; i < p.K / 4; i += blockDim.x) reinterpret_cast<float4*>(gain_s)[i] = g[i];
     }
 
+    // qkv_rope epilogue: positions, cache slots, frequencies and biases were there before the step began, so the
+    // rotation of this thread's first output pair is prepared here, off the critical path
+    float rope_cos = 1.f, rope_sin = 0.f;
+    if (EPI == EPI_QKV_ROPE) {
+        const int half = p.head_dim / 2, e = threadIdx.x;
+        if ((int)blockIdx.x < p.num_heads + p.num_kv_heads && e < half * p.M) {
+            const float a = (float)p.positions[e / half] * p.inv_freq[e % half];
+            rope_cos = cosf(a);
+            rope_sin = sinf(a);
+        }
+    }
+
     trace_scope.mark(0);
     if (p.use_pdl) grid_dependency_wait();                        // from here on the previous kernel's results are read
+    // (Measured on B200, decode at batch 8: letting the next kernel start here takes 0.855 ms a step; once this kernel's
+    // input rows are there 0.854, once its product is done 0.876, once its slices are summed 0.917.)
     if (p.use_pdl == 2) grid_dependents_launch();
     trace_scope.mark(1);
 
@@ -376,7 +390,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             fetch(c + UNROLL + u, wra[u], wrb[u]);                // this register set's next chunk, UNROLL chunks ahead
         }
     }
-    trace_scope.mark(3);
+    trace_scope.mark(3, true);
 
     // ---- sum the K slices of this CTA: red[warp][row][token] -> tile[row in CTA][token]
     float my_factor = 1.f;
@@ -486,8 +500,12 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             for (int e = threadIdx.x; e < half * p.M; e += blockDim.x) {
                 const int m = e / half, j = e % half;
                 const float x0 = value(j, m), x1 = value(j + half, m);
-                const float a = (float)p.positions[m] * p.inv_freq[j];
-                const float cs = cosf(a), sn = sinf(a);
+                float cs = rope_cos, sn = rope_sin;
+                if (e != (int)threadIdx.x) {
+                    const float a = (float)p.positions[m] * p.inv_freq[j];
+                    cs = cosf(a);
+                    sn = sinf(a);
+                }
                 const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
                 if (is_q) {
                     bf16* o = p.out + (size_t)m * p.ldo + (size_t)head * HD;

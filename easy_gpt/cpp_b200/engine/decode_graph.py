@@ -11,8 +11,9 @@ size, say) are captured when they come a second time (batches of several entries
 one layer at batch 1 and re-captures whenever a pointer changes,
 src/cuda/ops/self_attn.cu:750-828.)
 
-Rows that pad a batch up to its bucket are given position 0 and the group's
-scratch page, so they read and write nothing that belongs to a request.
+Rows that pad a batch up to its bucket are given position 0, the group's
+scratch page and the scratch state slot (one past the last slot a request can
+hold), so they read and write nothing that belongs to a request.
 """
 from __future__ import annotations
 

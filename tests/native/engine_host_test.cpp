@@ -52,15 +52,8 @@ static const char* kConfig = R"({"architectures": ["Qwen2ForCausalLM"], "model_t
   "rms_norm_eps": 1e-5, "tie_word_embeddings": false, "max_position_embeddings": 2048, "bos_token_id": null, "eos_token_id": [7, 9],
   "use_sliding_window": true, "sliding_window": 24, "max_window_layers": 1})";
 
+// The configuration text with `key` dropped (value empty) or set to `value`.
 static std::string with(const std::string& config, const std::string& key, const std::string& value) {
-    json::Value v = json::parse(config);
-    std::string out = "{";
-    bool seen = false;
-    for (auto& kv : v.object) {
-        if (kv.first == key) { seen = true; if (value.empty()) continue; }
-        (void)kv;
-    }
-    // rebuild textually: drop the key if present, append the new value
     std::string text = config;
     const std::string needle = "\"" + key + "\":";
     size_t at = text.find(needle);
@@ -75,8 +68,6 @@ static std::string with(const std::string& config, const std::string& key, const
         if (text[end] == ',') ++end;
         text.erase(at, end - at);
     }
-    (void)seen;
-    (void)out;
     if (!value.empty()) {
         const size_t brace = text.rfind('}');
         std::string head = text.substr(0, brace);
