@@ -302,6 +302,57 @@ def print_timeline(folder, config, batch):
     return 0
 
 
+def print_fused_timeline(folder, config, batch):
+    """The decode step as ONE persistent kernel (csrc/decode_fused.cu, an option of the step function): per kind of
+    operation the mean time from the last CTA's leaving the operation in front to the last CTA's entering this one (the
+    barrier across the grid), and inside the operation until the input rows are staged, until the products are done, and
+    in all.  From %globaltimer stamps that the kernel's CTAs leave; no profiler attached."""
+    import collections
+
+    os.environ["EASY_GPT_FUSED_DECODE"] = "1"
+    os.environ["EASY_GPT_FUSED_TRACE"] = "1"
+    from easy_gpt.cpp_b200.native import NativeEngine
+    from easy_gpt.cpp_b200.sampling.params import SamplingParams
+
+    start_context = CONTEXT - 40
+    room = CONTEXT + 64
+    engine = NativeEngine(str(folder), dtype="bfloat16", page_size=64, cache_tokens=batch * (room + 63), max_active=batch, prefill_batch=batch,
+                          max_batch_tokens=32768, chunk_size=4096, max_tokens_per_request=room)
+    for p in prompts_for(batch, start_context, config["vocab_size"], 1):
+        engine.add_request(p, SamplingParams(greedy=True), max_new_tokens=100)
+    for _ in range(12):
+        engine.step()
+    engine.sync()
+    engine.fused_trace()
+    engine.step()
+    engine.sync()
+    rows = [[int(v) for v in r] for r in engine.fused_trace()]
+    if not rows:
+        print("the step did not run as one fused kernel (sizes it does not take, or more than 8 tokens)")
+        return 1
+    names = {11: "norm -> head (float32 logits)", 12: "norm -> gate/up + SwiGLU", 13: "norm -> QKV + rotation + cache", 23: "embedding + norm -> QKV + ...",
+             100: "attention"}
+    agg = collections.OrderedDict()
+    previous_left, nth_rows = None, 0
+    for entered, staged, done, left, kind in rows:
+        label = names.get(kind)
+        if label is None:                               # rows -> residual: the output projection, then the down projection
+            label = "rows -> residual (O)" if nth_rows % 2 == 0 else "rows -> residual (down)"
+            nth_rows += 1
+        a = agg.setdefault(label, [0, 0.0, 0.0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += (entered - (previous_left if previous_left is not None else entered)) / 1e3
+        a[2] += ((staged or entered) - entered) / 1e3
+        a[3] += ((done or left) - (staged or entered)) / 1e3
+        a[4] += (left - entered) / 1e3
+        previous_left = left
+    print(f"fused decode step, batch {batch}, context {CONTEXT}: {len(rows)} operations, {(rows[-1][3] - rows[0][0]) / 1e3:.1f} us from the first entered to the last left")
+    print(f"{'operation':34s} {'n':>3s} {'barrier us':>11s} {'staging us':>11s} {'products us':>12s} {'whole us':>9s}")
+    for label, (n, barrier, staging, products, whole) in agg.items():
+        print(f"{label:34s} {n:3d} {barrier / n:11.2f} {staging / n:11.2f} {products / n:12.2f} {whole / n:9.2f}")
+    return 0
+
+
 def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
     """The package's tcgen05/TMA product against the library product at the prefill shapes: each
     timed as a CUDA graph of eight launches on distinct weights with the L2 flushed before."""
@@ -400,6 +451,8 @@ def run_ours(args):
         config["num_hidden_layers"] = args.layers
     pk = peaks()
     folder = model_folder(config)
+    if args.fused:
+        os.environ["EASY_GPT_FUSED_DECODE"] = "1"
     if args.only == "decode":
         r = measure_decode(folder, config, args.batch, args.steps, args.warmup, want_e2e=False, dtype=args.dtype,
                            default_options=args.default_options)
@@ -415,7 +468,7 @@ def run_ours(args):
                           **measure_serving(folder, config, requests=args.batch if args.batch != 8 else 64)}))
         return 0
     if args.only == "timeline":
-        return print_timeline(folder, config, args.batch)
+        return print_fused_timeline(folder, config, args.batch) if args.fused else print_timeline(folder, config, args.batch)
     if args.only == "gemm":
         return print_gemm_comparison(config)
     if args.only == "prefill":
@@ -520,6 +573,7 @@ def main():
                     help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
+    ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
     ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "serve"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()

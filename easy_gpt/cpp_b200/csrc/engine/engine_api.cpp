@@ -153,7 +153,22 @@ EGE_API long long ege_engine_figure(void* e, int what, long long id) {
         return r ? r->length : -1;
     }
     if (what == 3) return g->runner->last_graph ? g->runner->last_graph->launches : 0;
+    if (what == 4) return g->runner->fused_steps;
     return -1;
+}
+// The fused decode kernel's stamps of the last step (see CapturedStep::fused_trace): rows of five numbers into `out`;
+// returns the number of rows (0 if the last step was not a fused one or EASY_GPT_FUSED_TRACE is not set).
+EGE_API long long ege_engine_fused_trace(void* e, unsigned long long* out, long long cap_rows) {
+    GptEngine* g = static_cast<GptEngine*>(e);
+    if (!g->runner->last_graph) return 0;
+    const auto rows = g->runner->last_graph->fused_trace(g->runner->stream);
+    long long n = 0;
+    for (auto& r : rows) {
+        if (n >= cap_rows) break;
+        for (int k = 0; k < 5; ++k) out[n * 5 + k] = r[k];
+        ++n;
+    }
+    return n;
 }
 // Runs `steps` calls of step() and times them: out[0] device milliseconds between CUDA events recorded on the engine's
 // stream before the first and after the last step, out[1] wall-clock milliseconds until the last step's tokens are on the
@@ -246,7 +261,7 @@ EGE_API long long ege_runner_step(void* r, int n, const long long* rids, const l
 EGE_API void ege_runner_end(void* r, long long rid) { static_cast<Runner*>(r)->runner->end(rid); }
 // what: 0 vocabulary, 1 live requests, 2 captured-step replays, 3 free pages of group `arg`, 4 pages of group `arg`, 5 pages handed
 // out over the life of group `arg`'s pool, 6 number of groups, 7 books in order (1) or not (0), 8 captured steps of shapes other
-// than decode buckets
+// than decode buckets, 9 steps that ran as one fused kernel
 EGE_API long long ege_runner_info(void* r, int what, int arg) {
     Runner* run = static_cast<Runner*>(r);
     DeviceCache& cache = run->runner->cache;
@@ -263,6 +278,7 @@ EGE_API long long ege_runner_info(void* r, int what, int arg) {
             return cache.core.check(&why) == host::OK ? 1 : 0;
         }
         case 8: return (long long)run->runner->signature_graph_count();
+        case 9: return run->runner->fused_steps;
     }
     return -1;
 }

@@ -77,4 +77,9 @@ int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, 
 // sampling.cu
 int eg_sample(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, const float* temperature,
     const int* top_k, const float* top_p, const float* uniform, int* out);
+// decode_fused.cu
+int eg_decode_fused_smem(int stages, int xs_bytes, int num_ops, int num_tmpls);
+// decode_fused.cu
+int eg_decode_fused(cudaStream_t stream, const void* tmpls, int num_tmpls, const void* ops, int num_ops, int tokens, int stages, int xs_bytes, int ctas,
+    unsigned* sync, int* status, unsigned long long* trace);
 }  // extern "C"

@@ -254,6 +254,56 @@ public:
         return sizes;
     }
 
+    // The decode step of `ctx` (single tokens, logits for all of them) as a program for the fused decode kernel, if
+    // every part of the model can say what it does as operations of it; otherwise an empty program.  The activations
+    // come from the step arena, in the same order at every call, so the program stays valid while the arenas do.
+    struct FusedProgram {
+        std::vector<EgFusedTemplate> tmpls;
+        std::vector<EgFusedOp> ops;
+        int tokens = 0, stages = 0, xs_bytes = 0, grid = 0;
+        float* logits = nullptr;
+        bool ok() const { return !ops.empty(); }
+    };
+    FusedProgram fused_program(StepContext& ctx, StepArenas& arenas, const std::function<CacheView(int cache, bool writes)>& view) const {
+        FusedProgram none;
+        const int T = ctx.num_tokens;
+        if (dtype != DType::BF16 || !ctx.all_decode || T <= 0 || T > EGF_MAX_TOKENS || embedding_position || spec.hidden_size % 16) return none;
+        FusedBuilder b;
+        b.ctx = &ctx;
+        arenas.reset();
+        b.arena = &arenas.step;
+        b.tokens = T;
+        b.hidden = (int)spec.hidden_size;
+        b.grid = plans::sm_count();
+        if (!embedding->fused_gather(&b.embed_table, &b.vocab)) return none;
+        b.residual = b.arena->take_n<float>((size_t)T * b.hidden);
+        const float* gain = nullptr;
+        float eps = 0.f;
+        for (auto& e : spec.run_order) {
+            const Block& block = *blocks[e.layer];
+            for (auto& sub : block.sublayers) {
+                if (!sub.plain_pre_norm || !sub.norm->rms_parameters(&gain, &eps) || sub.norm->size() != b.hidden) return none;
+                const bool ok = sub.mixer ? sub.mixer->emit_fused(b, gain, eps, view(e.cache, e.writes_cache)) : sub.feed_forward->emit_fused(b, gain, eps);
+                if (!ok) return none;
+            }
+        }
+        if (b.embed_table) return none;                 // nothing took the embedding as its input
+        if (!final_norm->rms_parameters(&gain, &eps) || !lm_head->emit_fused(b, gain, eps) || !b.logits) return none;
+        // the ring of weight stages takes the shared memory that is left
+        int stages = 12;
+        while (stages >= 3 && eg_decode_fused_smem(stages, b.xs_bytes, (int)b.ops.size(), (int)b.tmpls.size()) > 227 * 1024) --stages;
+        if (stages < 3) return none;
+        FusedProgram prog;
+        prog.tmpls = std::move(b.tmpls);
+        prog.ops = std::move(b.ops);
+        prog.tokens = T;
+        prog.stages = stages;
+        prog.xs_bytes = b.xs_bytes;
+        prog.grid = b.grid;
+        prog.logits = b.logits;
+        return prog;
+    }
+
     // Runs the batch through every run entry; returns float32 logits [R, vocab] at logit_rows (token indices into the
     // batch; nullptr with all_rows: rows 0..T-1 in order, a decode step), or nullptr when none is wanted.
     float* forward(StepContext& ctx, StepArenas& arenas, const std::function<CacheView(int cache, bool writes)>& view, const int* logit_rows, int num_rows,

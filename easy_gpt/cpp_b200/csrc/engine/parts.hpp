@@ -298,6 +298,88 @@ public:
     bool accepts_pending_norm() const override { return true; }
     bool fuses_following_norm() const override { return true; }
 
+    // norm + QKV (+ bias, rotation, cache write); attention over the cache; output projection into the residual
+    bool emit_fused(FusedBuilder& b, const float* gain, float eps, const CacheView& cache) const override {
+        const StepContext& ctx = *b.ctx;
+        HalfRotation rot;
+        const bool rotates = position && position->half_rotation(&rot);
+        const int G = heads_ / kv_heads_;
+        if (ctx.dtype != DType::BF16 || head_dim_ != 64 || G > 16 || cache.group < 0 || !cache.writes || cache.page_size % 16 || hidden_ != b.hidden) return false;
+        if (position && (!rotates || rot.rotary_dim != head_dim_)) return false;
+        const GroupTables& tables = ctx.groups.at(cache.group);
+        const int q_width = heads_ * head_dim_, T = b.tokens;
+        void* q = b.arena->take((size_t)T * q_width * 2);
+        void* attn = b.arena->take((size_t)T * q_width * 2);
+        EgFusedTemplate t = FusedBuilder::blank();
+        t.input = EGF_IN_NORM;
+        t.output = EGF_OUT_QKV_ROPE;
+        t.N = (heads_ + 2 * kv_heads_) * head_dim_;
+        t.K = hidden_;
+        t.tiles_per_unit = 2;
+        t.group_rows = head_dim_;
+        t.units_per_group = head_dim_ / 16;
+        t.pair_offset = head_dim_ / 2;
+        t.eps = eps;
+        t.out = q;
+        t.ldo = q_width;
+        t.num_heads = heads_;
+        t.num_kv_heads = kv_heads_;
+        t.head_dim = head_dim_;
+        t.page_size = cache.page_size;
+        t.num_pages = cache.num_pages;
+        t.positions = ctx.positions;
+        t.slot_map = tables.slot_map;
+        t.inv_freq = rotates ? rot.inv_freq : nullptr;
+        t.page_stride = cache.page_stride;
+        t.head_stride = cache.head_stride;
+        t.pool_slots = (long long)cache.num_pages * cache.page_size;
+        if (!b.linear(t, qkv_.weight, hidden_, qkv_.bias_f32(), gain, cache.k, cache.v)) return false;
+
+        // as many CTAs per (token, KV head) as the grid has for them, a key tile each at least
+        const long long longest = window_ < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, window_ + 255);
+        const int tiles = (int)std::max<long long>(1, (longest + 63) / 64);
+        // (at most 16, and four tiles each where there are that many: the merge of the splits is one CTA's work)
+        const int splits = std::max(1, std::min({std::max(1, tiles / 4), 16, b.grid / std::max(1, T * kv_heads_)}));
+        EgFusedTemplate a = FusedBuilder::blank();
+        a.num_heads = heads_;
+        a.num_kv_heads = kv_heads_;
+        a.head_dim = head_dim_;
+        a.page_size = cache.page_size;
+        a.num_pages = cache.num_pages;
+        a.window = window_ < 0 ? 0 : (int)window_;
+        a.positions = ctx.positions;
+        a.page_stride = cache.page_stride;
+        a.head_stride = cache.head_stride;
+        a.q = q;
+        a.ldq = q_width;
+        a.block_table = tables.block_table;
+        a.table_stride = tables.table_width;
+        a.seq_context = ctx.seq_context;
+        a.scale = scale_;
+        a.splits = splits;
+        if (splits > 1) {
+            if ((size_t)T * kv_heads_ > KernelScratch::ATTENTION_COUNTERS) return false;
+            a.partial_acc = b.arena->take_n<float>((size_t)T * heads_ * splits * head_dim_);
+            a.partial_ml = b.arena->take_n<float>((size_t)T * heads_ * splits * 2);
+            a.tickets = ctx.scratch->attention_counters.as<int>();
+        }
+        a.attn_out = attn;
+        a.ld_attn = q_width;
+        b.attention(a, cache.k, cache.v);
+
+        EgFusedTemplate o = FusedBuilder::blank();
+        o.input = EGF_IN_ROWS;
+        o.output = EGF_OUT_RESIDUAL;
+        o.N = hidden_;
+        o.K = q_width;
+        o.tiles_per_unit = 1;
+        o.group_rows = 8;
+        o.units_per_group = 1;
+        o.x = attn;
+        o.ldx = q_width;
+        return b.linear(o, out_.weight, q_width, out_.bias_f32(), nullptr);
+    }
+
     Delta forward(const StepContext& ctx, PartInput in, const CacheView& cache, const FollowingNorm* follow) override {
         const int T = ctx.num_tokens;
         const GroupTables& tables = ctx.groups.at(cache.group);
@@ -461,6 +543,36 @@ public:
     bool accepts_pending_norm() const override { return true; }
     bool fuses_following_norm() const override { return true; }
 
+    // norm + gate/up + SwiGLU; down projection into the residual
+    bool emit_fused(FusedBuilder& b, const float* gain, float eps) const override {
+        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || inter_ % 8) return false;
+        void* act = b.arena->take((size_t)b.tokens * inter_ * 2);
+        EgFusedTemplate t = FusedBuilder::blank();
+        t.input = EGF_IN_NORM;
+        t.output = EGF_OUT_SWIGLU;
+        t.N = 2 * inter_;
+        t.K = hidden_;
+        t.tiles_per_unit = 1;
+        t.group_rows = 8;
+        t.units_per_group = 1;
+        t.warp_units = hidden_ <= EGF_STAGE_COLS;
+        t.eps = eps;
+        t.out = act;
+        t.ldo = inter_;
+        if (!b.linear(t, gate_up_.weight, hidden_, gate_up_.bias_f32(), gain)) return false;
+        EgFusedTemplate d = FusedBuilder::blank();
+        d.input = EGF_IN_ROWS;
+        d.output = EGF_OUT_RESIDUAL;
+        d.N = hidden_;
+        d.K = inter_;
+        d.tiles_per_unit = 1;
+        d.group_rows = 8;
+        d.units_per_group = 1;
+        d.x = act;
+        d.ldx = inter_;
+        return b.linear(d, down_.weight, inter_, down_.bias_f32(), nullptr);
+    }
+
     Delta forward(const StepContext& ctx, PartInput in, const FollowingNorm* follow) override {
         const int T = ctx.num_tokens;
         const DType dtype = ctx.dtype;
@@ -514,6 +626,12 @@ public:
                      "embedding_gather");
     }
     const void* table() const override { return table_.get(); }
+    bool fused_gather(const void** table, int* vocab) const override {
+        if (dtype_ != DType::BF16 || hidden_ % 4) return false;
+        *table = table_.get();
+        *vocab = vocab_;
+        return true;
+    }
 
 private:
     int vocab_, hidden_;
@@ -538,6 +656,23 @@ public:
     size_t weight_bytes() const override { return linear_.weight_bytes(); }
     bool capturable() const override { return true; }
     int vocab() const override { return vocab_; }
+    bool emit_fused(FusedBuilder& b, const float* gain, float eps) const override {
+        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || linear_.has_bias()) return false;
+        b.logits = b.arena->take_n<float>((size_t)b.tokens * vocab_);
+        EgFusedTemplate t = FusedBuilder::blank();
+        t.input = EGF_IN_NORM;
+        t.output = EGF_OUT_F32;
+        t.N = vocab_;
+        t.K = hidden_;
+        t.tiles_per_unit = 1;
+        t.group_rows = 8;
+        t.units_per_group = 1;
+        t.warp_units = hidden_ <= EGF_STAGE_COLS;
+        t.eps = eps;
+        t.out = b.logits;
+        t.ldo = vocab_;
+        return b.linear(t, linear_.weight, hidden_, nullptr, gain);
+    }
     float* forward(const StepContext& ctx, PartInput in, int rows) override {
         // Thousands of CTAs share the head's rows, and each would repeat the add + norm of the few tokens in front of its
         // product: the norm runs once, in a kernel of its own.

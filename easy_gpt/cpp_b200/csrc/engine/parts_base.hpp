@@ -15,6 +15,7 @@
 // To add a part: derive from the matching base, implement tensor_requests / load / forward (and
 // cache_need for a mixer that keeps something per request), and register a factory under a kind.
 #pragma once
+#include <cstring>
 #include <functional>
 #include <map>
 #include <memory>
@@ -22,6 +23,7 @@
 #include <vector>
 
 #include "device.hpp"
+#include "../decode_fused.h"
 #include "kernels_api.h"
 #include "plans.hpp"
 #include "spec.hpp"
@@ -281,6 +283,81 @@ struct PartInput {
     PendingNorm* pending = nullptr;
 };
 
+// ---- a decode step as one program (csrc/decode_fused.cu) ---------------------------------------------------------
+// A part that can say what it does in a decode step as operations of that program does so in emit_fused(); a model all
+// of whose parts can is stepped by ONE persistent kernel for small batches instead of a chain of kernels.  The builder
+// holds the step's buffers and collects the operations; what a part needs beyond them it takes from `arena`.
+struct FusedBuilder {
+    const StepContext* ctx = nullptr;
+    Arena* arena = nullptr;
+    int tokens = 0, hidden = 0, grid = 0;
+    float* residual = nullptr;                      // float32 [tokens, hidden]
+    const void* embed_table = nullptr;              // set until the first linear operation has taken the embedding as its input
+    int vocab = 0;
+    std::vector<EgFusedTemplate> tmpls;
+    std::vector<EgFusedOp> ops;
+    int xs_bytes = 0;                               // shared memory for the widest input rows (and the attention's key tiles)
+    int next_offset = 0;
+    float* logits = nullptr;
+
+    static EgFusedTemplate blank() {
+        EgFusedTemplate t;
+        std::memset(&t, 0, sizeof t);
+        return t;
+    }
+    int intern(const EgFusedTemplate& t) {
+        for (size_t i = 0; i < tmpls.size(); ++i)
+            if (std::memcmp(&tmpls[i], &t, sizeof t) == 0) return (int)i;
+        tmpls.push_back(t);
+        return (int)tmpls.size() - 1;
+    }
+    static int input_row_bytes(int K) { return ((K * 2 + 127) / 128) * 128 + 64; }
+    // a linear operation over weights [N, K]; gain/eps: the RMSNorm in front (input rows x otherwise)
+    bool linear(EgFusedTemplate t, const void* W, long long ldw, const float* bias, const float* gain, void* k_cache = nullptr, void* v_cache = nullptr) {
+        t.type = EGF_LINEAR;
+        if (t.K % 16 || t.N % t.group_rows || ldw % 8 || (uintptr_t)W % 16) return false;
+        if (t.input == EGF_IN_ROWS && (t.ldx % 8 || (uintptr_t)t.x % 16)) return false;
+        t.num_units = t.N / t.group_rows * t.units_per_group;
+        if (t.input != EGF_IN_ROWS) {
+            t.residual = residual;
+            if (embed_table) {
+                t.input = EGF_IN_EMBED_NORM;
+                t.embed_table = embed_table;
+                t.token_ids = ctx->token_ids;
+                t.vocab = vocab;
+                embed_table = nullptr;
+            }
+        }
+        if (t.output == EGF_OUT_RESIDUAL) t.residual = residual;
+        EgFusedOp op;
+        std::memset(&op, 0, sizeof op);
+        op.tmpl = intern(t);
+        op.unit_offset = next_offset;
+        op.W = W;
+        op.ldw = ldw;
+        op.bias = bias;
+        op.gain = gain;
+        op.k_cache = k_cache;
+        op.v_cache = v_cache;
+        ops.push_back(op);
+        next_offset = (next_offset + t.num_units) % grid;
+        xs_bytes = std::max(xs_bytes, EGF_MAX_TOKENS * input_row_bytes(t.K));
+        return true;
+    }
+    void attention(EgFusedTemplate t, void* k_cache, void* v_cache) {
+        t.type = EGF_ATTENTION;
+        EgFusedOp op;
+        std::memset(&op, 0, sizeof op);
+        op.tmpl = intern(t);
+        op.unit_offset = next_offset;
+        op.k_cache = k_cache;
+        op.v_cache = v_cache;
+        ops.push_back(op);
+        next_offset = (next_offset + tokens * t.num_kv_heads * t.splits) % grid;
+        xs_bytes = std::max(xs_bytes, (int)EGF_KV_BYTES);
+    }
+};
+
 class Mixer : public Part {
 public:
     Mixer(const Params& params, const std::string& prefix, std::shared_ptr<PositionEncoding> position) : Part(params, prefix), position(std::move(position)) {}
@@ -289,6 +366,8 @@ public:
     virtual CacheNeed cache_need() const { return CacheNeed(); }
     // x [T, hidden] normalised input -> delta [T, hidden], both in ctx.dtype
     virtual Delta forward(const StepContext& ctx, PartInput x, const CacheView& cache, const FollowingNorm* follow) = 0;
+    // x = x + this(rmsnorm(x; gain, eps)) as operations of a fused decode program; false: this part cannot say it so
+    virtual bool emit_fused(FusedBuilder&, const float* /*gain*/, float /*eps*/, const CacheView&) const { return false; }
     std::shared_ptr<PositionEncoding> position;
 };
 
@@ -298,6 +377,7 @@ public:
     virtual bool accepts_pending_norm() const { return false; }
     virtual bool fuses_following_norm() const { return false; }
     virtual Delta forward(const StepContext& ctx, PartInput x, const FollowingNorm* follow) = 0;
+    virtual bool emit_fused(FusedBuilder&, const float* /*gain*/, float /*eps*/) const { return false; }
 };
 
 class Embedding : public Part {
@@ -305,6 +385,8 @@ public:
     using Part::Part;
     virtual void forward(const StepContext& ctx, float* residual) = 0;      // residual[t] = table[token_ids[t]]
     virtual const void* table() const = 0;
+    // a plain gather from a bfloat16 table [vocab, hidden] that a fused decode program's first operation can do itself
+    virtual bool fused_gather(const void** /*table*/, int* /*vocab*/) const { return false; }
 };
 
 class Head : public Part {
@@ -314,6 +396,8 @@ public:
     // normalised rows or a pending norm -> float32 logits [R, vocab] (from the arena)
     virtual float* forward(const StepContext& ctx, PartInput x, int rows) = 0;
     virtual int vocab() const = 0;
+    // logits = this(rmsnorm(x; gain, eps)) as the last operation of a fused decode program (sets FusedBuilder::logits)
+    virtual bool emit_fused(FusedBuilder&, const float* /*gain*/, float /*eps*/) const { return false; }
 };
 
 // ---- registries ---------------------------------------------------------------------------------------------

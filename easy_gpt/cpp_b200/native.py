@@ -47,6 +47,7 @@ def library() -> ctypes.CDLL:
             "ege_engine_stats": (None, [c_void_p, c_void_p]),
             "ege_engine_figure": (c_longlong, [c_void_p, c_int, c_longlong]),
             "ege_engine_sync": (None, [c_void_p]),
+            "ege_engine_fused_trace": (c_longlong, [c_void_p, c_void_p, c_longlong]),
             "ege_engine_time_steps": (c_longlong, [c_void_p, c_int, c_void_p, c_char_p, c_int]),
             "ege_load_plugin": (c_longlong, [c_char_p, c_char_p, c_int]),
             "ege_runner_create": (c_void_p, [c_char_p, c_char_p, c_int, c_int, c_int, c_longlong, c_int, c_char_p, c_int]),
@@ -166,6 +167,19 @@ class NativeEngine:
     def cached_length(self, rid: int) -> int:
         return int(self._lib.ege_engine_figure(self._h, 2, rid))
 
+    def fused_trace(self):
+        """Rows (entered, input ready, products done, left, kind) of GPU nanosecond stamps, one per operation of the
+        fused decode kernel's last run; empty unless EASY_GPT_FUSED_TRACE=1 was set when the engine was made."""
+        import numpy as np
+
+        out = np.zeros((4096, 5), dtype=np.uint64)
+        n = int(self._lib.ege_engine_fused_trace(self._h, out.ctypes.data_as(ctypes.c_void_p), 4096))
+        return out[:n]
+
+    def fused_steps(self) -> int:
+        """Steps so far that ran as one persistent kernel (csrc/decode_fused.cu)."""
+        return int(self._lib.ege_engine_figure(self._h, 4, 0))
+
     def sync(self) -> None:
         self._lib.ege_engine_sync(self._h)
 
@@ -254,5 +268,5 @@ class NativeStepRunner:
 
     def info(self, what: str, group: int = 0) -> int:
         index = {"vocab": 0, "live_requests": 1, "graph_replays": 2, "free_pages": 3, "pages": 4, "pages_handed_out": 5, "groups": 6,
-                 "books_in_order": 7, "captured_shapes": 8}[what]
+                 "books_in_order": 7, "captured_shapes": 8, "fused_steps": 9}[what]
         return int(self._lib.ege_runner_info(self._h, index, group))

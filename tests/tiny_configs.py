@@ -81,7 +81,27 @@ CONFIG_TINY_B = {
 }
 RANDOM_TINY_B = dict(seed=3, std=0.02, bias_std=0.05, gain_std=0.1)
 
-CONFIGS = {"TINY_A": (CONFIG_TINY_A, RANDOM_TINY_A), "TINY_B": (CONFIG_TINY_B, RANDOM_TINY_B), "A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D),
+# F and G: sizes that the fused decode kernel takes (head size 64, widths and vocabularies that are multiples of 16), and
+# that differ from each other in everything else: F three layers, two KV heads of two query heads, biases, tied head, all
+# keys; G two layers, one KV head of six query heads, no biases, untied head, a window of 40 on every layer
+CONFIG_F = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "intermediate_size": 208, "vocab_size": 400, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 4096, "bos_token_id": -1, "eos_token_id": -1,
+    "use_sliding_window": False,
+}
+RANDOM_F = dict(seed=11, std=0.07, bias_std=0.08, gain_std=0.1)
+CONFIG_G = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 112, "num_attention_heads": 6, "num_key_value_heads": 1, "head_dim": 64,
+    "intermediate_size": 144, "vocab_size": 272, "rope_theta": 500000.0, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096, "attention_bias": False,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 0,
+}
+RANDOM_G = dict(seed=13, std=0.06, bias_std=0.0, gain_std=0.05)
+
+CONFIGS = {"F": (CONFIG_F, RANDOM_F), "G": (CONFIG_G, RANDOM_G), "TINY_A": (CONFIG_TINY_A, RANDOM_TINY_A), "TINY_B": (CONFIG_TINY_B, RANDOM_TINY_B), "A": (CONFIG_A, RANDOM_A), "B": (CONFIG_B, RANDOM_B), "C": (CONFIG_C, RANDOM_C), "D": (CONFIG_D, RANDOM_D),
            "E": (CONFIG_E, RANDOM_E)}
 
 
