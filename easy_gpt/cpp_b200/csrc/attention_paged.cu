@@ -17,6 +17,8 @@
 // score = (q . k) * scale in float32; the running softmax works in base 2 (scores times
 // log2 e, exp2f: one hardware instruction, 2 ulp); P is rounded to bfloat16 for the
 // P V product (as V is bfloat16 anyway); sums and the accumulator stay float32.
+#include <cstdlib>
+
 #include "mma_utils.cuh"
 
 namespace {
@@ -30,16 +32,18 @@ constexpr int QUARTER_TILES = 64;      // tiles whose cache addresses are kept i
 // many CTAs it is their number in flight that hides a tile's latency.
 constexpr int MAX_SPLITS = 128;
 
-template <int HD, bool DEEP = true>
+// TPI: key tiles that the CTA's warps work on at a time (four warps a tile)
+template <int HD, bool DEEP = true, int TPI = 1>
 struct Layout {
     static constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per key row
     static constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
     static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;          // K or V
-    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int GROUP_BYTES = 2 * TILE_BYTES;             // K and V of one tile
+    static constexpr int STAGE_BYTES = TPI * GROUP_BYTES;
     // up to five tiles in flight per CTA, within about 96 KB of shared memory (two stages at least)
-    static constexpr int DEEP_STAGES = (96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((96 * 1024 / STAGE_BYTES) >= 2 ? (96 * 1024 / STAGE_BYTES) : 2);
+    static constexpr int DEEP_STAGES = (TPI * 96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((TPI * 96 * 1024 / STAGE_BYTES) >= 2 ? (TPI * 96 * 1024 / STAGE_BYTES) : 2);
     static constexpr int STAGES = DEEP ? DEEP_STAGES : (DEEP_STAGES < 3 ? DEEP_STAGES : 3);
-    static constexpr int WARP_MERGE_BYTES = 4 * 16 * (HD + 2) * 4;            // the four warps' partial results
+    static constexpr int WARP_MERGE_BYTES = TPI * 4 * 16 * (HD + 2) * 4;      // the warps' partial results
     static constexpr int SPLIT_MERGE_BYTES = (2 * 16 * MAX_SPLITS + 16) * 4;  // (m, l) of every row and split, 1/l per row
     static constexpr int MERGE_BYTES = WARP_MERGE_BYTES > SPLIT_MERGE_BYTES ? WARP_MERGE_BYTES : SPLIT_MERGE_BYTES;
     static constexpr int SMEM = (STAGES * STAGE_BYTES > MERGE_BYTES) ? STAGES * STAGE_BYTES : MERGE_BYTES;
@@ -72,11 +76,14 @@ struct Params {
     int use_pdl;
     unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
     const int* token_list;        // optional: the tokens this launch works on (blockIdx.x indexes it); null: all, in order
+    int cluster_merge;            // the splits of a (token, KV head) are one cluster and are merged in its first CTA's shared memory
 };
 
-template <int HD, bool DEEP>
-__global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p) {
-    using L = Layout<HD, DEEP>;
+template <int HD, bool DEEP, int TPI>
+__global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Params p) {
+    using L = Layout<HD, DEEP, TPI>;
+    constexpr int NT = TPI * THREADS;                                // threads of the CTA
+    constexpr int WARPS = TPI * 4;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int is_last;
     TraceScope trace_scope(p.trace);
@@ -95,7 +102,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         const long long pieces = (p.prefetch_bytes + PIECE - 1) / PIECE;
         const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
-        for (long long i = cta * THREADS + threadIdx.x; i < pieces; i += ctas * THREADS) {
+        for (long long i = cta * NT + threadIdx.x; i < pieces; i += ctas * NT) {
             const long long off = i * PIECE;
             const long long n = p.prefetch_bytes - off < PIECE ? p.prefetch_bytes - off : PIECE;
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(static_cast<const char*>(p.prefetch) + off),
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     auto fill_quarters = [&](int tile0) {
         quarter_tile0 = tile0;
         const int count = min(QUARTER_TILES, my_hi - tile0 + 1);
-        for (int e = threadIdx.x; e < count * 4; e += THREADS) {
+        for (int e = threadIdx.x; e < count * 4; e += NT) {
             const int kpos0 = (tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
             long long base = -1;
             if (kpos0 <= pos && kpos0 + 15 >= first) {
@@ -137,11 +144,10 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     __syncthreads();
 
     // mode 0: every row; 1 (before the wait): all but the fresh keys; 2 (after it): the fresh keys only
-    auto load_tile = [&](int tile, int stage, int mode) {
-        unsigned char* ks = smem + stage * L::STAGE_BYTES;
+    auto load_one = [&](int tile, unsigned char* ks, int mode) {
         unsigned char* vs = ks + L::TILE_BYTES;
         const long long* qb = quarter_base + (tile - quarter_tile0) * 4;
-        for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
+        for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += NT) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = tile * TILE_KEYS + row;
             const long long base = qb[row >> 4];
@@ -153,6 +159,17 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
             cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
         }
     };
+    // the TPI tiles of iteration `it` into stage `stage` (those that exist); fresh_only: only tiles that hold fresh keys
+    auto load_tile = [&](int it_tile0, int stage, int mode) {
+#pragma unroll
+        for (int g = 0; g < TPI; ++g) {
+            const int tile = it_tile0 + g;
+            if (tile > my_hi) break;
+            if (mode == 2 && (tile + 1) * TILE_KEYS <= fresh_from) continue;
+            load_one(tile, smem + stage * L::STAGE_BYTES + g * L::GROUP_BYTES, mode);
+        }
+    };
+    const int niter = ntiles > 0 ? (ntiles + TPI - 1) / TPI : 0;
 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;                 // rows gid and gid + 8
     float acc[HD / 8][4];
@@ -161,7 +178,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
 
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s) {
-        if (s < ntiles) load_tile(my_lo + s, s, 1);
+        if (s < niter) load_tile(my_lo + s * TPI, s, 1);
         cp_async_commit();
     }
     trace_scope.mark(0);
@@ -170,7 +187,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     trace_scope.mark(1);
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s)
-        if (s < ntiles && (my_lo + s + 1) * TILE_KEYS > fresh_from) load_tile(my_lo + s, s, 2);
+        if (s < niter) load_tile(my_lo + s * TPI, s, 2);
     cp_async_commit();
 
     // ---- query rows as A fragments: row r <-> head kvh*G + g0 + r
@@ -190,23 +207,25 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
 
 
-    for (int it = 0; it < ntiles; ++it) {
+    const int group = warp >> 2, quarter = warp & 3;                             // which tile of the iteration, which 16 keys of it
+    for (int it = 0; it < niter; ++it) {
         if (it == 0) cp_async_wait<0>();                                          // the first tiles and their fresh rows
         else cp_async_wait<L::STAGES - 2>();
         __syncthreads();
         if (it == 0) trace_scope.mark(2);
         {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
             const int nxt = it + L::STAGES - 1;
-            if (nxt < ntiles && nxt % QUARTER_TILES == 0) {                       // the next stretch of the block table
-                fill_quarters(my_lo + nxt);
+            if (nxt < niter && (nxt * TPI) % QUARTER_TILES == 0) {                // the next stretch of the block table
+                fill_quarters(my_lo + nxt * TPI);
                 __syncthreads();
             }
-            if (nxt < ntiles) load_tile(my_lo + nxt, nxt % L::STAGES, 0);
+            if (nxt < niter) load_tile(my_lo + nxt * TPI, nxt % L::STAGES, 0);
             cp_async_commit();
         }
-        const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES;
+        const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES + group * L::GROUP_BYTES;
         const unsigned char* vs = ks + L::TILE_BYTES;
-        const int key_base = (my_lo + it) * TILE_KEYS + warp * 16;               // this warp's 16 keys
+        if (it * TPI + group >= ntiles) continue;                                 // the run has no tile for this group of warps any more
+        const int key_base = (my_lo + it * TPI + group) * TILE_KEYS + quarter * 16;   // this warp's 16 keys
         if (key_base > pos || key_base + 15 < first) continue;                    // nothing visible in this quarter
 
         // S = Q K^T for 16 rows x 16 keys
@@ -215,7 +234,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         for (int kk = 0; kk < HD / 16; ++kk) {
             uint32_t b[4];
             const int mi = lane >> 3, r = lane & 7;
-            ldmatrix_x4(b, ks + L::offset(warp * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+            ldmatrix_x4(b, ks + L::offset(quarter * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
             mma_bf16_16816(s[0], qf[kk], b[0], b[1]);
             mma_bf16_16816(s[1], qf[kk], b[2], b[3]);
         }
@@ -264,7 +283,7 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         for (int nt = 0; nt < HD / 8; nt += 2) {
             uint32_t b[4];
             const int mi = lane >> 3, r = lane & 7;
-            ldmatrix_x4_trans(b, vs + L::offset(warp * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
+            ldmatrix_x4_trans(b, vs + L::offset(quarter * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
             mma_bf16_16816(acc[nt], pf, b[0], b[1]);
             mma_bf16_16816(acc[nt + 1], pf, b[2], b[3]);
         }
@@ -278,9 +297,9 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float* wm = reinterpret_cast<float*>(smem);                                   // [4][16]
-    float* wl = wm + 64;                                                          // [4][16]
-    float* wacc = wl + 64;                                                        // [4][16][HD]
+    float* wm = reinterpret_cast<float*>(smem);                                   // [WARPS][16]
+    float* wl = wm + WARPS * 16;                                                  // [WARPS][16]
+    float* wacc = wl + WARPS * 16;                                                // [WARPS][16][HD]
     if (tig == 0) {
         wm[warp * 16 + gid] = m0;
         wm[warp * 16 + gid + 8] = m1;
@@ -297,17 +316,28 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         a1[0] = acc[i][2];
         a1[1] = acc[i][3];
     }
-    __syncthreads();
+    // Splits as a cluster: every CTA of it is past its key tiles here, so the first CTA's pipeline memory is free for
+    // the others' results (behind the part that its own warps' merge still uses).
+    unsigned cluster_rank = 0;
+    uint32_t incoming = 0;                                                         // [splits][rows][HD + 2] in the first CTA
+    if (p.cluster_merge) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(cluster_rank));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(incoming) : "r"(smem_u32(smem + L::WARP_MERGE_BYTES)), "r"(0));
+        asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    } else {
+        __syncthreads();
+    }
     const int rows = min(16, G - g0);
-    for (int e = threadIdx.x; e < rows * HD; e += THREADS) {
+    for (int e = threadIdx.x; e < rows * HD; e += NT) {
         const int r = e / HD, d = e % HD;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, wm[w * 16 + r]);
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, wm[w * 16 + r]);
         float l = 0.f, a = 0.f;
         if (m > -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < WARPS; ++w) {
                 const float f = exp2f(wm[w * 16 + r] - m);                          // -inf -> 0
                 l += wl[w * 16 + r] * f;
                 a += wacc[(w * 16 + r) * HD + d] * f;
@@ -316,6 +346,13 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
         const int h = kvh * G + g0 + r;
         if (p.splits == 1) {
             p.out[(size_t)t * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+        } else if (p.cluster_merge) {
+            const uint32_t at = incoming + (uint32_t)((cluster_rank * rows + r) * (HD + 2)) * 4u;
+            asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (uint32_t)d * 4u), "f"(a) : "memory");
+            if (d == 0) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (uint32_t)HD * 4u), "f"(m) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (uint32_t)(HD + 1) * 4u), "f"(l) : "memory");
+            }
         } else {
             const size_t slot = ((size_t)t * p.num_heads + h) * p.splits + split;
             p.partial_acc[slot * HD + d] = a;
@@ -327,6 +364,34 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
     trace_scope.mark(4);
     if (p.splits == 1) return;
+    if (p.cluster_merge) {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        trace_scope.mark(5);
+        if (cluster_rank != 0) return;
+        // out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}, the splits in order, from this CTA's own shared memory
+        const float* inc = reinterpret_cast<const float*>(smem + L::WARP_MERGE_BYTES);
+        constexpr int QUADS = HD / 4;
+        for (int q = threadIdx.x; q < rows * QUADS; q += NT) {
+            const int r = q / QUADS, dq = q % QUADS;
+            float m = -INFINITY;
+            for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, inc[(size_t)(s2 * rows + r) * (HD + 2) + HD]);
+            float l = 0.f;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+                const float* part = inc + (size_t)(s2 * rows + r) * (HD + 2);
+                const float w = m > -INFINITY ? exp2f(part[HD] - m) : 0.f;
+                l += part[HD + 1] * w;
+                const float2 lo = *reinterpret_cast<const float2*>(part + dq * 4), hi = *reinterpret_cast<const float2*>(part + dq * 4 + 2);
+                a.x += lo.x * w; a.y += lo.y * w; a.z += hi.x * w; a.w += hi.y * w;
+            }
+            const float il = l > 0.f ? 1.0f / l : 0.f;
+            const int h = kvh * G + g0 + r;
+            *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + (size_t)h * HD + dq * 4) =
+                make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
+        }
+        return;
+    }
 
     // ---- the last CTA of this (token, KV head) to get here merges the splits, in order:
     // out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}
@@ -350,12 +415,12 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     float* lpart = fac + 16 * p.splits;                                            // [rows][splits]: l_s
     float* inv_l = lpart + 16 * p.splits;                                          // [rows]
     const size_t head0 = (size_t)t * p.num_heads + kvh * G + g0;
-    for (int e = threadIdx.x; e < rows * p.splits; e += THREADS) {
+    for (int e = threadIdx.x; e < rows * p.splits; e += NT) {
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.partial_ml) + head0 * p.splits + e);   // rows are consecutive heads
         fac[e] = ml.x;
         lpart[e] = ml.y;
     }
-    for (int q0 = 0; q0 < rows * QUADS; q0 += THREADS) {
+    for (int q0 = 0; q0 < rows * QUADS; q0 += NT) {
         const int q = q0 + threadIdx.x;
         const bool mine = q < rows * QUADS;
         const int r = mine ? q / QUADS : 0, dq = mine ? q % QUADS : 0;
@@ -408,26 +473,67 @@ __global__ void __launch_bounds__(THREADS) attention_paged_kernel(const Params p
     }
 }
 
-template <int HD, bool DEEP>
-int launch_with(cudaStream_t stream, const Params& p, dim3 grid) {
-    using L = Layout<HD, DEEP>;
+template <int HD, bool DEEP, int TPI = 1>
+int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_cluster = false) {
+    using L = Layout<HD, DEEP, TPI>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(TPI * THREADS);
     cfg.dynamicSmemBytes = L::SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (p.use_pdl) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    // The splits of a (token, KV head) as one cluster (up to 16 CTAs, which needs the kernel's leave for a cluster of
+    // more than 8), merged through the first CTA's shared memory instead of scratch memory and a ticket: for the
+    // launches of fewer CTAs than SMs.
+    Params q = p;
+    static const bool cluster_allowed = !(getenv("EASY_GPT_CLUSTER_MERGE") && atoi(getenv("EASY_GPT_CLUSTER_MERGE")) == 0);
+    const int G = p.num_heads / p.num_kv_heads;
+    const size_t incoming_bytes = (size_t)p.splits * (G < 16 ? G : 16) * (HD + 2) * sizeof(float);
+    // (Measured on B200, 16 splits, context 4096: at batch 1 the step takes 0.708 ms with it against 0.749, at batch 4
+    // 0.753 against 0.777; at batch 8, 256 CTAs in 16 clusters, 0.966 against 0.826: so many clusters of 16 find room
+    // only when the kernel in front has left the SMs, and the early start is lost.)
+    int sms = 0, device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const long long ctas = (long long)grid.x * grid.y * grid.z;
+    if (DEEP && cluster_allowed && ctas <= sms && p.splits > 1 && p.splits <= 16 && L::WARP_MERGE_BYTES + incoming_bytes <= (size_t)L::SMEM) {
+        static int leave = 0;                                                      // 0 not asked yet, 1 given, -1 refused
+        if (!leave) leave = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : -1;
+        if (p.splits <= 8 || leave == 1) {
+            attr[nattr].id = cudaLaunchAttributeClusterDimension;
+            attr[nattr].val.clusterDim.x = 1;
+            attr[nattr].val.clusterDim.y = 1;
+            attr[nattr].val.clusterDim.z = (unsigned)p.splits;
+            cfg.attrs = attr;
+            cfg.numAttrs = nattr + 1;
+            int clusters = 0;
+            // all clusters have to be on the GPU together, or the last ones run as a second wave (measured: batch 8, 16
+            // clusters of 8 CTAs, of which 15 found room: the step took 0.92 ms instead of 0.80)
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_paged_kernel<HD, DEEP, TPI>, &cfg) == cudaSuccess &&
+                clusters >= (int)(grid.x * grid.y)) {
+                q.cluster_merge = 1;
+                ++nattr;
+            } else {
+                (void)cudaGetLastError();
+            }
+        }
+    }
+    if (must_cluster && !q.cluster_merge) return -1;                              // the caller has another way
     cfg.attrs = attr;
-    cfg.numAttrs = p.use_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP>, p);
+    cfg.numAttrs = nattr;
+    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP, TPI>, q);
 }
 
 template <int HD>
@@ -441,6 +547,20 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     const int G = p.num_heads / p.num_kv_heads;
     const dim3 grid(tokens, p.num_kv_heads * ((G + 15) / 16), p.splits);
     const long long ctas = (long long)grid.x * grid.y * grid.z;
+    // Up to twice as many CTAs as SMs: eight warps a CTA take two key tiles at a time and half as many splits (the same
+    // warps, tiles in flight and trips through the keys as with four warps), so that the splits of a (token, KV head)
+    // are at most 8 CTAs, one an SM, and can be merged as a cluster.  All clusters have to find room at once; if they
+    // do not, a split or two fewer may.  (Measured on B200, context 4096, ms a decode step with / without: batch 1
+    // 0.681 / 0.749, batch 4 0.702 / 0.777, batch 7 0.732; batch 8: 16 clusters of 8 do not find room.)
+    if constexpr (HD <= 128) if (ctas <= 2ll * sm_count && p.splits >= 4 && p.splits % 2 == 0) {
+        for (int fewer = 0; fewer <= 2; ++fewer) {
+            Params half = p;
+            half.splits = p.splits / 2 - fewer;
+            if (half.splits < 2) break;
+            const int rc = launch_with<HD, true, 2>(stream, half, dim3(grid.x, grid.y, half.splits), true);
+            if (rc != -1) return rc;
+        }
+    }
     return ctas <= 2ll * sm_count ? launch_with<HD, true>(stream, p, grid) : launch_with<HD, false>(stream, p, grid);
 }
 

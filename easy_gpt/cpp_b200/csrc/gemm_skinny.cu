@@ -44,6 +44,8 @@
 // of it (programmatic dependent launch), so the pipeline of small kernels overlaps.
 // A kernel can also be told which weights a later kernel will stream; when its own
 // stream has been issued it asks the L2 (126 MB) to fetch them.
+#include <cstdlib>
+
 #include "mma_utils.cuh"
 
 namespace {
@@ -93,6 +95,7 @@ struct Params {
     float* scratch;              // [gridDim.y][gridDim.x][RB*16][tokens] partial sums when K is cut across CTAs
     int* counters;               // [gridDim.x] tickets, zero before and after every launch
     unsigned long long* trace;   // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
+    int cluster_reduce;          // the gridDim.y CTAs of a row group are one cluster and sum their parts through the first one's shared memory
 };
 
 struct W32 {                      // 16 consecutive bfloat16 of one weight row
@@ -199,13 +202,23 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
 
     // qkv_rope epilogue: positions, cache slots, frequencies and biases were there before the step began, so the
     // rotation of this thread's first output pair is prepared here, off the critical path
-    float rope_cos = 1.f, rope_sin = 0.f;
+    float rope_cos = 1.f, rope_sin = 0.f, first_bias0 = 0.f, first_bias1 = 0.f;
+    long long first_slot = -1;
     if (EPI == EPI_QKV_ROPE) {
         const int half = p.head_dim / 2, e = threadIdx.x;
-        if ((int)blockIdx.x < p.num_heads + p.num_kv_heads && e < half * p.M) {
+        const bool rotated = (int)blockIdx.x < p.num_heads + p.num_kv_heads;
+        if (rotated && e < half * p.M) {
             const float a = (float)p.positions[e / half] * p.inv_freq[e % half];
             rope_cos = cosf(a);
             rope_sin = sinf(a);
+            if (p.bias) {
+                first_bias0 = p.bias[n0 + e % half];
+                first_bias1 = p.bias[n0 + e % half + half];
+            }
+            if ((int)blockIdx.x >= p.num_heads) first_slot = p.slot_map[e / half];
+        } else if (!rotated && e < p.head_dim * p.M) {
+            if (p.bias) first_bias0 = p.bias[n0 + e % p.head_dim];
+            first_slot = p.slot_map[e / p.head_dim];
         }
     }
 
@@ -234,6 +247,9 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         if (NORM == 2) {
             // rows bfloat16(gain * v) straight into xs, the partial sums of squares where the residual would be staged
             float* ss_s = const_cast<float*>(staged_resid);       // [ss_parts][MT]
+            // (Plain 16-byte loads by every thread instead of the bulk copies were measured slower: 0.853 against 0.821 ms a
+            // decode step at batch 8.)
+            {
             if (warp == 0) {
                 if (lane == 0) {
                     const unsigned bytes = (unsigned)p.M * (unsigned)p.K * 2u + (unsigned)p.ss_parts * MT * 4u;
@@ -249,6 +265,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             bool landed = false;
             for (unsigned i = 0; i < WAIT_LIMIT && !landed; ++i) landed = mbar_try_wait(&staged_bar, 0);
             if (!landed && p.status) atomicOr(p.status, EG_STATUS_WAIT_TIMEOUT);
+            }
             if (threadIdx.x < MT) {
                 float f = 0.f;
                 if ((int)threadIdx.x < p.M) {
@@ -419,6 +436,26 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     __syncthreads();
 
     trace_scope.mark(4);
+    // ---- K cut across CTAs that form a cluster: every CTA puts its part into the first one's shared memory (two
+    // trips to the L2 fewer than the ticket below), the first one sums them, in order
+    if (gridDim.y > 1 && p.cluster_reduce) {
+        float* parts = factor + MT;                                   // [gridDim.y][tile_elems], used in the cluster's first CTA only
+        unsigned rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_addr(parts + (size_t)rank * tile_elems)), "r"(0));
+        for (int e = threadIdx.x; e < tile_elems; e += blockDim.x)
+            asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote + (uint32_t)e * 4u), "f"(tile[e]) : "memory");
+        asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        if (rank != 0) return;
+        for (int e = threadIdx.x; e < tile_elems; e += blockDim.x) {
+            float v = 0.f;
+            for (int y = 0; y < (int)gridDim.y; ++y) v += parts[(size_t)y * tile_elems + e];
+            tile[e] = v;
+        }
+        __syncthreads();
+    } else
     // ---- K cut across CTAs: the last CTA of this row group to arrive sums all parts, in order
     if (gridDim.y > 1) {
         float* mine = p.scratch + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * tile_elems;
@@ -443,9 +480,13 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     }
 
     trace_scope.mark(5);
-    auto value = [&](int r, int m) -> float {                     // r: row inside the CTA
+    auto product = [&](int r, int m) -> float {                   // r: row inside the CTA; without the bias
         float v = tile[r * MT + m];
         if (NORM) v *= factor[m];
+        return v;
+    };
+    auto value = [&](int r, int m) -> float {
+        float v = product(r, m);
         const int n = n0 + r;
         if (p.bias && n < p.N) v += p.bias[n];
         return v;
@@ -499,9 +540,11 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         if (is_q || is_k) {
             for (int e = threadIdx.x; e < half * p.M; e += blockDim.x) {
                 const int m = e / half, j = e % half;
-                const float x0 = value(j, m), x1 = value(j + half, m);
+                const bool first = e == (int)threadIdx.x;               // what was fetched before the wait
+                const float x0 = first ? product(j, m) + first_bias0 : value(j, m);
+                const float x1 = first ? product(j + half, m) + first_bias1 : value(j + half, m);
                 float cs = rope_cos, sn = rope_sin;
-                if (e != (int)threadIdx.x) {
+                if (!first) {
                     const float a = (float)p.positions[m] * p.inv_freq[j];
                     cs = cosf(a);
                     sn = sinf(a);
@@ -512,7 +555,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
                     o[j] = __float2bfloat16_rn(y0);
                     o[j + half] = __float2bfloat16_rn(y1);
                 } else {
-                    const long long slot = p.slot_map[m];
+                    const long long slot = first ? first_slot : p.slot_map[m];
                     if (slot < 0 || slot >= p.pool_slots) {
                         if (slot >= p.pool_slots) atomicOr(p.status, EG_STATUS_BAD_SLOT);
                         continue;
@@ -526,14 +569,15 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
         } else {
             for (int e = threadIdx.x; e < HD * p.M; e += blockDim.x) {
                 const int m = e / HD, j = e % HD;
-                const long long slot = p.slot_map[m];
+                const bool first = e == (int)threadIdx.x;
+                const long long slot = first ? first_slot : p.slot_map[m];
                 if (slot < 0 || slot >= p.pool_slots) {
                     if (slot >= p.pool_slots) atomicOr(p.status, EG_STATUS_BAD_SLOT);
                     continue;
                 }
                 bf16* o = p.v_cache + (slot / p.page_size) * p.page_stride +
                           (long long)(head - p.num_heads - p.num_kv_heads) * p.head_stride + (slot % p.page_size) * HD;
-                o[j] = __float2bfloat16_rn(value(j, m));
+                o[j] = __float2bfloat16_rn(first ? product(j, m) + first_bias0 : value(j, m));
             }
         }
     }
@@ -544,7 +588,13 @@ int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
     constexpr int MT = NT * 8;
     Params p = p_in;
     const int nwarps = p.RB * p.KS;
-    const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
+    size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
+    // The CTAs that share a row group's K range as a cluster (up to 8, the portable size), where the input rows are
+    // not staged in the shared memory that the parts arrive in while the first CTA may still be multiplying.
+    static const bool cluster_allowed = !(getenv("EASY_GPT_CLUSTER_REDUCE") && atoi(getenv("EASY_GPT_CLUSTER_REDUCE")) == 0);
+    const size_t parts_bytes_cluster = (size_t)k_split * p.RB * 16 * MT * sizeof(float);
+    p.cluster_reduce = cluster_allowed && NORM == 0 && k_split > 1 && k_split <= 8 && parts_bytes_cluster <= 32 * 1024;
+    if (p.cluster_reduce) red_bytes += parts_bytes_cluster;
     size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) + (size_t)MT * 8 * sizeof(float) : 0;
     // the residual rows staged in shared memory, where they fit and the copies' alignment rule (16 bytes) holds
     const size_t staged_bytes = (size_t)p.M * p.K * sizeof(float);
@@ -571,11 +621,22 @@ int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
     cfg.blockDim = dim3(nwarps * 32);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (p.use_pdl) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    if (p.cluster_reduce) {
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = 1;
+        attr[nattr].val.clusterDim.y = (unsigned)k_split;
+        attr[nattr].val.clusterDim.z = 1;
+        ++nattr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = p.use_pdl ? 1 : 0;
+    cfg.numAttrs = nattr;
     return (int)cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
