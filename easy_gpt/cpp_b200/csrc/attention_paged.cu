@@ -552,11 +552,14 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     // are at most 8 CTAs, one an SM, and can be merged as a cluster.  All clusters have to find room at once; if they
     // do not, a split or two fewer may.  (Measured on B200, context 4096, ms a decode step with / without: batch 1
     // 0.681 / 0.749, batch 4 0.702 / 0.777, batch 7 0.732; batch 8: 16 clusters of 8 do not find room.)
+    // Only while a CTA's run of key tiles is short (up to 16 tiles here): a long run is a stream, and streams want all
+    // SMs and as many CTAs as the four-warp form has (context 32k, batch 8: 1.59 ms a step with it, 1.45 without).
+    const long long most_tiles = ((long long)p.table_stride * p.page_size + TILE_KEYS - 1) / TILE_KEYS;
     if constexpr (HD <= 128) if (ctas <= 2ll * sm_count && p.splits >= 4 && p.splits % 2 == 0) {
         for (int fewer = 0; fewer <= 2; ++fewer) {
             Params half = p;
             half.splits = p.splits / 2 - fewer;
-            if (half.splits < 2) break;
+            if (half.splits < 2 || most_tiles > 16ll * half.splits) break;
             const int rc = launch_with<HD, true, 2>(stream, half, dim3(grid.x, grid.y, half.splits), true);
             if (rc != -1) return rc;
         }
