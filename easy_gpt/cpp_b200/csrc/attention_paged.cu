@@ -32,14 +32,14 @@ constexpr int QUARTER_TILES = 64;      // tiles whose cache addresses are kept i
 // many CTAs it is their number in flight that hides a tile's latency.
 constexpr int MAX_SPLITS = 128;
 
-// TPI: key tiles that the CTA's warps work on at a time (four warps a tile)
-template <int HD, bool DEEP = true, int TPI = 1>
+// TPI: the CTA's warps in fours; TI: key tiles that they work on at a time (a warp takes 16 or 32 keys of a tile)
+template <int HD, bool DEEP = true, int TPI = 1, int TI = TPI>
 struct Layout {
     static constexpr int CHUNKS = HD / 8;                         // 16-byte chunks per key row
     static constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
     static constexpr int TILE_BYTES = TILE_KEYS * HD * 2;          // K or V
     static constexpr int GROUP_BYTES = 2 * TILE_BYTES;             // K and V of one tile
-    static constexpr int STAGE_BYTES = TPI * GROUP_BYTES;
+    static constexpr int STAGE_BYTES = TI * GROUP_BYTES;
     // up to five tiles in flight per CTA, within about 96 KB of shared memory (two stages at least)
     static constexpr int DEEP_STAGES = (TPI * 96 * 1024 / STAGE_BYTES) >= 5 ? 5 : ((TPI * 96 * 1024 / STAGE_BYTES) >= 2 ? (TPI * 96 * 1024 / STAGE_BYTES) : 2);
     static constexpr int STAGES = DEEP ? DEEP_STAGES : (DEEP_STAGES < 3 ? DEEP_STAGES : 3);
@@ -79,9 +79,11 @@ struct Params {
     int cluster_merge;            // the splits of a (token, KV head) are one cluster and are merged in its first CTA's shared memory
 };
 
-template <int HD, bool DEEP, int TPI>
+template <int HD, bool DEEP, int TPI, int KW>
 __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Params p) {
-    using L = Layout<HD, DEEP, TPI>;
+    constexpr int TI = TPI * KW / 16;                                // key tiles of an iteration
+    constexpr int KB = KW / 16;                                      // blocks of 16 keys a warp takes of its tile
+    using L = Layout<HD, DEEP, TPI, TI>;
     constexpr int NT = TPI * THREADS;                                // threads of the CTA
     constexpr int WARPS = TPI * 4;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -162,14 +164,14 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     // the TPI tiles of iteration `it` into stage `stage` (those that exist); fresh_only: only tiles that hold fresh keys
     auto load_tile = [&](int it_tile0, int stage, int mode) {
 #pragma unroll
-        for (int g = 0; g < TPI; ++g) {
+        for (int g = 0; g < TI; ++g) {
             const int tile = it_tile0 + g;
             if (tile > my_hi) break;
             if (mode == 2 && (tile + 1) * TILE_KEYS <= fresh_from) continue;
             load_one(tile, smem + stage * L::STAGE_BYTES + g * L::GROUP_BYTES, mode);
         }
     };
-    const int niter = ntiles > 0 ? (ntiles + TPI - 1) / TPI : 0;
+    const int niter = ntiles > 0 ? (ntiles + TI - 1) / TI : 0;
 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;                 // rows gid and gid + 8
     float acc[HD / 8][4];
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
 
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s) {
-        if (s < niter) load_tile(my_lo + s * TPI, s, 1);
+        if (s < niter) load_tile(my_lo + s * TI, s, 1);
         cp_async_commit();
     }
     trace_scope.mark(0);
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     trace_scope.mark(1);
 #pragma unroll
     for (int s = 0; s < L::STAGES - 1; ++s)
-        if (s < niter) load_tile(my_lo + s * TPI, s, 2);
+        if (s < niter) load_tile(my_lo + s * TI, s, 2);
     cp_async_commit();
 
     // ---- query rows as A fragments: row r <-> head kvh*G + g0 + r
@@ -207,7 +209,8 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     }
 
 
-    const int group = warp >> 2, quarter = warp & 3;                             // which tile of the iteration, which 16 keys of it
+    constexpr int WARPS_PER_TILE = TILE_KEYS / KW;
+    const int group = warp / WARPS_PER_TILE, key0 = (warp % WARPS_PER_TILE) * KW;   // which tile of the iteration, which keys of it
     for (int it = 0; it < niter; ++it) {
         if (it == 0) cp_async_wait<0>();                                          // the first tiles and their fresh rows
         else cp_async_wait<L::STAGES - 2>();
@@ -215,33 +218,38 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         if (it == 0) trace_scope.mark(2);
         {   // prefetch the tile STAGES-1 ahead into the stage freed by the previous iteration
             const int nxt = it + L::STAGES - 1;
-            if (nxt < niter && (nxt * TPI) % QUARTER_TILES == 0) {                // the next stretch of the block table
-                fill_quarters(my_lo + nxt * TPI);
+            if (nxt < niter && (nxt * TI) % QUARTER_TILES == 0) {                 // the next stretch of the block table
+                fill_quarters(my_lo + nxt * TI);
                 __syncthreads();
             }
-            if (nxt < niter) load_tile(my_lo + nxt * TPI, nxt % L::STAGES, 0);
+            if (nxt < niter) load_tile(my_lo + nxt * TI, nxt % L::STAGES, 0);
             cp_async_commit();
         }
         const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES + group * L::GROUP_BYTES;
         const unsigned char* vs = ks + L::TILE_BYTES;
-        if (it * TPI + group >= ntiles) continue;                                 // the run has no tile for this group of warps any more
-        const int key_base = (my_lo + it * TPI + group) * TILE_KEYS + quarter * 16;   // this warp's 16 keys
-        if (key_base > pos || key_base + 15 < first) continue;                    // nothing visible in this quarter
+        if (it * TI + group >= ntiles) continue;                                  // the run has no tile for this group of warps any more
+        const int key_base = (my_lo + it * TI + group) * TILE_KEYS + key0;        // this warp's KW keys
+        if (key_base > pos || key_base + KW - 1 < first) continue;                // nothing visible in them
 
-        // S = Q K^T for 16 rows x 16 keys
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // S = Q K^T for 16 rows x KW keys
+        float s[2 * KB][4];
+#pragma unroll
+        for (int j = 0; j < 2 * KB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-            uint32_t b[4];
-            const int mi = lane >> 3, r = lane & 7;
-            ldmatrix_x4(b, ks + L::offset(quarter * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
-            mma_bf16_16816(s[0], qf[kk], b[0], b[1]);
-            mma_bf16_16816(s[1], qf[kk], b[2], b[3]);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                uint32_t b[4];
+                const int mi = lane >> 3, r = lane & 7;
+                ldmatrix_x4(b, ks + L::offset(key0 + kb * 16 + (mi >> 1) * 8 + r, kk * 2 + (mi & 1)));
+                mma_bf16_16816(s[2 * kb], qf[kk], b[0], b[1]);
+                mma_bf16_16816(s[2 * kb + 1], qf[kk], b[2], b[3]);
+            }
         }
         // scale, mask, running softmax
         float tmax0 = -INFINITY, tmax1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 2 * KB; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
@@ -253,21 +261,24 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
-        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);               // finite: a key of this quarter is visible
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);               // finite: a key of these is visible
         const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
         m0 = mn0;
         m1 = mn1;
-        uint32_t pf[4];
+        uint32_t pf[KB][4];
         float ps0 = 0.f, ps1 = 0.f;
-        {
-            float e00 = exp2f(s[0][0] - mn0), e01 = exp2f(s[0][1] - mn0), e02 = exp2f(s[0][2] - mn1), e03 = exp2f(s[0][3] - mn1);
-            float e10 = exp2f(s[1][0] - mn0), e11 = exp2f(s[1][1] - mn0), e12 = exp2f(s[1][2] - mn1), e13 = exp2f(s[1][3] - mn1);
-            ps0 = e00 + e01 + e10 + e11;
-            ps1 = e02 + e03 + e12 + e13;
-            pf[0] = pack_bf16(e00, e01);
-            pf[1] = pack_bf16(e02, e03);
-            pf[2] = pack_bf16(e10, e11);
-            pf[3] = pack_bf16(e12, e13);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            const float (&sa)[4] = s[2 * kb];
+            const float (&sb)[4] = s[2 * kb + 1];
+            const float e00 = exp2f(sa[0] - mn0), e01 = exp2f(sa[1] - mn0), e02 = exp2f(sa[2] - mn1), e03 = exp2f(sa[3] - mn1);
+            const float e10 = exp2f(sb[0] - mn0), e11 = exp2f(sb[1] - mn0), e12 = exp2f(sb[2] - mn1), e13 = exp2f(sb[3] - mn1);
+            ps0 += (e00 + e01) + (e10 + e11);
+            ps1 += (e02 + e03) + (e12 + e13);
+            pf[kb][0] = pack_bf16(e00, e01);
+            pf[kb][1] = pack_bf16(e02, e03);
+            pf[kb][2] = pack_bf16(e10, e11);
+            pf[kb][3] = pack_bf16(e12, e13);
         }
         l0 = l0 * c0 + ps0;
         l1 = l1 * c1 + ps1;
@@ -280,13 +291,15 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         }
         // acc += P V
 #pragma unroll
-        for (int nt = 0; nt < HD / 8; nt += 2) {
-            uint32_t b[4];
-            const int mi = lane >> 3, r = lane & 7;
-            ldmatrix_x4_trans(b, vs + L::offset(quarter * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
-            mma_bf16_16816(acc[nt], pf, b[0], b[1]);
-            mma_bf16_16816(acc[nt + 1], pf, b[2], b[3]);
-        }
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                uint32_t b[4];
+                const int mi = lane >> 3, r = lane & 7;
+                ldmatrix_x4_trans(b, vs + L::offset(key0 + kb * 16 + (mi & 1) * 8 + r, nt + (mi >> 1)));
+                mma_bf16_16816(acc[nt], pf[kb], b[0], b[1]);
+                mma_bf16_16816(acc[nt + 1], pf[kb], b[2], b[3]);
+            }
     }
     cp_async_wait<0>();
     trace_scope.mark(3, true);
@@ -473,12 +486,12 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     }
 }
 
-template <int HD, bool DEEP, int TPI = 1>
+template <int HD, bool DEEP, int TPI = 1, int KW = 16>
 int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_cluster = false) {
-    using L = Layout<HD, DEEP, TPI>;
+    using L = Layout<HD, DEEP, TPI, TPI * KW / 16>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -510,7 +523,7 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
     const long long ctas = (long long)grid.x * grid.y * grid.z;
     if (DEEP && cluster_allowed && ctas <= sms && p.splits > 1 && p.splits <= 16 && L::WARP_MERGE_BYTES + incoming_bytes <= (size_t)L::SMEM) {
         static int leave = 0;                                                      // 0 not asked yet, 1 given, -1 refused
-        if (!leave) leave = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : -1;
+        if (!leave) leave = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : -1;
         if (p.splits <= 8 || leave == 1) {
             attr[nattr].id = cudaLaunchAttributeClusterDimension;
             attr[nattr].val.clusterDim.x = 1;
@@ -521,7 +534,7 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
             int clusters = 0;
             // all clusters have to be on the GPU together, or the last ones run as a second wave (measured: batch 8, 16
             // clusters of 8 CTAs, of which 15 found room: the step took 0.92 ms instead of 0.80)
-            if (cudaOccupancyMaxActiveClusters(&clusters, attention_paged_kernel<HD, DEEP, TPI>, &cfg) == cudaSuccess &&
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_paged_kernel<HD, DEEP, TPI, KW>, &cfg) == cudaSuccess &&
                 clusters >= (int)(grid.x * grid.y)) {
                 q.cluster_merge = 1;
                 ++nattr;
@@ -533,7 +546,7 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
     if (must_cluster && !q.cluster_merge) return -1;                              // the caller has another way
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
-    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP, TPI>, q);
+    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP, TPI, KW>, q);
 }
 
 template <int HD>
@@ -554,13 +567,14 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     // 0.681 / 0.749, batch 4 0.702 / 0.777, batch 7 0.732; batch 8: 16 clusters of 8 do not find room.)
     // Only while a CTA's run of key tiles is short (up to 16 tiles here): a long run is a stream, and streams want all
     // SMs and as many CTAs as the four-warp form has (context 32k, batch 8: 1.59 ms a step with it, 1.45 without).
+    constexpr int WIDE_KEYS = HD <= 64 ? 32 : 16;                                // keys a warp of the eight-warp form takes of a tile
     const long long most_tiles = ((long long)p.table_stride * p.page_size + TILE_KEYS - 1) / TILE_KEYS;
     if constexpr (HD <= 128) if (ctas <= 2ll * sm_count && p.splits >= 4 && p.splits % 2 == 0) {
         for (int fewer = 0; fewer <= 2; ++fewer) {
             Params half = p;
             half.splits = p.splits / 2 - fewer;
             if (half.splits < 2 || most_tiles > 16ll * half.splits) break;
-            const int rc = launch_with<HD, true, 2>(stream, half, dim3(grid.x, grid.y, half.splits), true);
+            const int rc = launch_with<HD, true, 2, WIDE_KEYS>(stream, half, dim3(grid.x, grid.y, half.splits), true);
             if (rc != -1) return rc;
         }
     }
