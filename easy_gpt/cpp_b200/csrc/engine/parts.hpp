@@ -403,7 +403,7 @@ public:
             const int* slot_map = cache.writes ? tables.slot_map : nullptr;
             void* kc = cache.writes ? cache.k : nullptr;
             void* vc = cache.writes ? cache.v : nullptr;
-            if (rotates && rot.rotary_dim == head_dim_ && head_dim_ % 8 == 0) {
+            if (rotates && rot.rotary_dim == head_dim_ && head_dim_ % (dtype == DType::BF16 ? 16 : 8) == 0) {      // halves of a head in 16-byte pieces
                 launch_check(eg_rope_cache_vec(ctx.stream, (int)dtype, qkv.p, (int)qkv.ld, rotation_table(ctx, rot), slot_map, kc, vc, T, heads_, kv_heads_,
                                                head_dim_, cache.page_size, cache.page_stride, cache.head_stride, slot_map ? pool_slots : 0, ctx.status),
                              "rope_cache_table");

@@ -252,10 +252,11 @@ def rope_cache_table(qkv: torch.Tensor, table: torch.Tensor, slot_map: Optional[
                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
                      head_dim: int, page_size: int, status: torch.Tensor) -> None:
     """``rope_cache`` for the whole head rotated, with cos/sin from ``rope_table`` (shared by the
-    layers of a step) and wide accesses.  head_dim % 8 == 0."""
+    layers of a step) and 16-byte accesses: half a head must be a multiple of 16 bytes (head_dim
+    % 16 == 0 in bfloat16, % 8 in float32)."""
     _cuda(qkv, table, slot_map, k_cache, v_cache, status)
     T = qkv.shape[0]
-    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim and head_dim % 8 == 0, "qkv row layout")
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim and head_dim % (32 // qkv.element_size()) == 0, "qkv row layout")
     _need(table.dtype == torch.float32 and table.is_contiguous() and tuple(table.shape) == (T, head_dim // 2, 2), "table [T, HD/2, 2]")
     page_stride = head_stride = pool_slots = 0
     if slot_map is not None:

@@ -118,7 +118,7 @@ class Attention(Mixer):
                 x = pending.materialize()
             qkv = self.qkv(x, status=ctx.status)
             store = (tables.slot_map, cache.k, cache.v) if cache.writes else (None, None, None)
-            if rot is not None and rot.rotary_dim == self.head_dim and self.head_dim % 8 == 0:
+            if rot is not None and rot.rotary_dim == self.head_dim and self.head_dim % (16 if qkv.dtype == torch.bfloat16 else 8) == 0:
                 kernels.rope_cache_table(qkv, self._rotation_table(rot, ctx), *store, self.num_heads, self.num_kv_heads,
                                          self.head_dim, tables.page_size, ctx.status)
             elif rot is not None:

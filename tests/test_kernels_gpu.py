@@ -603,12 +603,13 @@ def test_gemm_skinny_refuses_what_it_does_not_take():
                             x=bf(torch.randn(2, 40)).to(DEV))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_cache_with_table_equals_rope_cache(dtype):
+@pytest.mark.parametrize("dtype, T, NH, NKV, HD, ps, pages", [
+    (torch.float32, 37, 5, 1, 24, 8, 7), (torch.bfloat16, 37, 5, 1, 48, 8, 7),       # half a head: three 16-byte pieces
+    (torch.float32, 300, 6, 3, 32, 16, 20), (torch.bfloat16, 300, 6, 3, 64, 16, 20)])
+def test_rope_cache_with_table_equals_rope_cache(dtype, T, NH, NKV, HD, ps, pages):
     from easy_gpt.cpp_b200 import kernels
     from easy_gpt.cpp_b200.parts.rope import RotaryEncoding
 
-    T, NH, NKV, HD, ps, pages = 37, 5, 1, 24, 8, 7
     width = (NH + 2 * NKV) * HD
     qkv = torch.randn(T, width, generator=gen(40)).to(dtype).to(DEV)
     positions = torch.randint(0, 70000, (T,), generator=gen(41), dtype=torch.int32).to(DEV)
