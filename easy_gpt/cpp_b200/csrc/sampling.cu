@@ -7,6 +7,7 @@
 
 namespace {
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int ARGMAX_THREADS = 256;      // a thread keeps four 16-byte loads in flight
 }
 
 struct ArgMax {
@@ -50,25 +51,53 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
 // Several blocks share a row (one block cannot pull 600 KB of logits fast enough to
 // matter beside a decode step); each writes its best (value, index) to scratch and the
 // block that finishes last (a ticket counter; nobody waits) picks the row's winner.
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+__global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out,
               float* __restrict__ part_val, int* __restrict__ part_idx, int* __restrict__ counters) {
     __shared__ ArgMax scratch[32];
     __shared__ int is_last;
     const int r = blockIdx.x, nb = gridDim.y;
     const float* row = logits + (size_t)r * ld;
-    const int per = (vocab + nb - 1) / nb;
-    const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+    const int per = (((vocab + nb - 1) / nb) + 3) & ~3;              // a multiple of 4, so that every block's stretch starts on 16 bytes
+    const int lo = min(vocab, blockIdx.y * per), hi = min(vocab, lo + per);
     ArgMax best;
     best.v = -INFINITY;
     best.i = 0x7fffffff;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    auto take = [&](float v, int i) {
         ArgMax c;
-        c.v = row[i];
+        c.v = v;
         c.i = i;
         // NaN never wins; a row of NaNs yields index 0 below
-        if (c.v == c.v) best = argmax_better(best, c);
+        if (v == v) best = argmax_better(best, c);
+    };
+    int i0 = lo;
+    if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        // (measured on B200, 64 rows of 151,936: 35.7 us with 4-byte loads, one in flight a thread)
+        const float4* row4 = reinterpret_cast<const float4*>(row + lo);
+        const int n4 = (hi - lo) / 4;
+        constexpr int UNROLL = 4;
+        for (int q0 = threadIdx.x; q0 < n4; q0 += blockDim.x * UNROLL) {
+            float4 v[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int q = q0 + u * blockDim.x;
+                if (q < n4) v[u] = row4[q];
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int q = q0 + u * blockDim.x;
+                if (q < n4) {
+                    const int i = lo + 4 * q;
+                    take(v[u].x, i);
+                    take(v[u].y, i + 1);
+                    take(v[u].z, i + 2);
+                    take(v[u].w, i + 3);
+                }
+            }
+        }
+        i0 = lo + 4 * n4;
     }
+    for (int i = i0 + threadIdx.x; i < hi; i += blockDim.x) take(row[i], i);
     best = block_argmax(best, scratch);
     if (nb == 1) {
         if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
@@ -101,9 +130,9 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __
 EG_API int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, int* out,
                      int blocks_per_row, float* part_val, int* part_idx, int* counters) {
     if (rows <= 0) return 0;
-    if (blocks_per_row < 1 || blocks_per_row > SAMPLE_THREADS || (blocks_per_row > 1 && (!part_val || !part_idx || !counters)))
+    if (blocks_per_row < 1 || blocks_per_row > ARGMAX_THREADS || (blocks_per_row > 1 && (!part_val || !part_idx || !counters)))
         return (int)cudaErrorInvalidValue;
-    argmax_kernel<<<dim3(rows, blocks_per_row), SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out, part_val, part_idx, counters);
+    argmax_kernel<<<dim3(rows, blocks_per_row), ARGMAX_THREADS, 0, stream>>>(logits, ld, vocab, out, part_val, part_idx, counters);
     return eg_launch_status();
 }
 
