@@ -565,15 +565,18 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
     // are at most 8 CTAs, one an SM, and can be merged as a cluster.  All clusters have to find room at once; if they
     // do not, a split or two fewer may.  (Measured on B200, context 4096, ms a decode step with / without: batch 1
     // 0.681 / 0.749, batch 4 0.702 / 0.777, batch 7 0.732; batch 8: 16 clusters of 8 do not find room.)
-    // Only while a CTA's run of key tiles is short (up to 16 tiles here): a long run is a stream, and streams want all
-    // SMs and as many CTAs as the four-warp form has (context 32k, batch 8: 1.59 ms a step with it, 1.45 without).
+    // A long run of key tiles is a stream, and streams want all SMs: at the 0.5B sizes, batch 8, context 32k, 7 splits in
+    // 16 clusters are 112 CTAs and the step takes 1.59 ms with them, 1.45 with 256 four-warp CTAs.
     constexpr int WIDE_KEYS = HD <= 64 ? 32 : 16;                                // keys a warp of the eight-warp form takes of a tile
     const long long most_tiles = ((long long)p.table_stride * p.page_size + TILE_KEYS - 1) / TILE_KEYS;
     if constexpr (HD <= 128) if (ctas <= 2ll * sm_count && p.splits >= 4 && p.splits % 2 == 0) {
         for (int fewer = 0; fewer <= 2; ++fewer) {
             Params half = p;
             half.splits = p.splits / 2 - fewer;
-            if (half.splits < 2 || most_tiles > 16ll * half.splits) break;
+            if (half.splits < 2) break;
+            // long runs: only if the clusters still cover most of the SMs (7B sizes, batch 8, context 8k: 4.05 ms a step with
+            // 32 clusters of 4, 5.08 with 256 four-warp CTAs and tickets)
+            if (most_tiles > 16ll * half.splits && (long long)grid.x * grid.y * half.splits * 100 < 85ll * sm_count) break;
             const int rc = launch_with<HD, true, 2, WIDE_KEYS>(stream, half, dim3(grid.x, grid.y, half.splits), true);
             if (rc != -1) return rc;
         }
