@@ -630,3 +630,19 @@ def test_rope_cache_with_table_equals_rope_cache(dtype, T, NH, NKV, HD, ps, page
     for x, y in ((a, b), (ka, kb), (va, vb)):
         assert float((x.float() - y.float()).abs().max()) <= ulp
     assert status.item() == 0
+
+
+def test_kernels_are_right_without_clusters_too():
+    """Where CTAs share a result (the decode attention's splits, the K parts of a decode product) they meet in a
+    cluster's shared memory if the launch allows it, else through scratch memory and a ticket.  The tests above take
+    whichever path the launcher chooses; here the same tests run once more in a process that has the clusters
+    switched off, so that the ticket paths stay covered."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, EASY_GPT_CLUSTER_MERGE="0", EASY_GPT_CLUSTER_REDUCE="0")
+    out = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "(paged or skinny or attention) and not without_clusters"],
+                         env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout
