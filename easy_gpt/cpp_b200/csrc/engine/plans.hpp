@@ -119,6 +119,8 @@ inline int skinny_padded_tokens(int tokens) { return tokens <= 8 ? 8 : tokens <=
 
 // Products wide and tall enough for the persistent tcgen05 kernel on CTA pairs (one tile per SM at least).
 inline bool gemm_tcgen05_wide_takes(DType dtype, int tokens, int out_features, int in_features) {
+    // (with fewer tiles the library product and a SwiGLU kernel are faster: a decode step at batch 64 takes 1.74 ms with
+    // the pair kernel for gate/up, 38 tiles, against 1.67)
     return dtype == DType::BF16 && tokens > SKINNY_MAX_TOKENS && out_features % 256 == 0 && in_features % 64 == 0 &&
            (long long)((tokens + 127) / 128) * (out_features / 256) >= sm_count();
 }
