@@ -4,6 +4,7 @@
 #pragma once
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 
 #include "device.hpp"
@@ -73,10 +74,19 @@ inline int attention_paged_splits(int tokens, int num_heads, int num_kv_heads, l
 // CTAs per SM: the kernel is bound by what an SM gets through, not by its longest unit.  (Measured on B200, 14 heads of
 // 64: a portion of 512 tokens on a context of 3,584 takes 68 us uncut, 34 us in 4 parts and 43 us in 8; a prompt of
 // 2,048 tokens, 224 pairs for 296 CTAs, takes 41 us uncut and 40 to 62 us however it is cut.)
-inline void attention_prefill_parts(int num_tiles, int num_heads, int* parts, int* part_tiles) {
+inline void attention_prefill_parts(int num_tiles, int num_heads, long long longest_context, int* parts, int* part_tiles) {
     const int wanted = std::min(2 * sm_count() / std::max(1, num_tiles * num_heads), 8);
-    if (wanted >= 2) { *parts = wanted; *part_tiles = 4; }
-    else { *parts = 1; *part_tiles = 1 << 20; }
+    if (wanted >= 2) { *parts = wanted; *part_tiles = 4; return; }
+    *parts = 1;
+    *part_tiles = 1 << 20;
+    static int long_from = 48, long_part = 24, long_most = 4;
+    static bool read = false;
+    if (!read) {
+        if (const char* e = std::getenv("EASY_GPT_PARTS_LONG")) std::sscanf(e, "%d,%d,%d", &long_from, &long_part, &long_most);
+        read = true;
+    }
+    const long long key_tiles = (longest_context + 63) / 64;
+    if (long_most > 1 && key_tiles >= long_from) { *parts = (int)std::min<long long>(long_most, key_tiles / long_part); *part_tiles = long_part; }
 }
 
 // Up to how many tokens a step's add + RMSNorm over rows of `width` can ride in the decode product's prologue
