@@ -12,7 +12,9 @@ namespace easygpt::engine::plans {
 
 constexpr int QUERY_TILE = 128;            // tokens per listed tile of a prompt portion
 constexpr int SMALL_ENTRY_TOKENS = 4;      // entries of up to this many tokens go through the decode attention kernel
-constexpr int SKINNY_MAX_TOKENS = 16;      // up to where the decode product beats the library product
+// Up to where the decode product beats the library product.  (Measured again, ms a decode step with the limit at 16 / 32 /
+// 64 tokens: batch 24 1.29 / 1.38 / 1.40, batch 32 1.35 / 1.51 / 1.47, batch 64 1.60 / 1.61 / 2.87.)
+constexpr int SKINNY_MAX_TOKENS = 16;
 constexpr int FUSED_NORM_MAX_TOKENS = 16;  // every CTA repeats the norm prologue: worth it only for a few tokens
 constexpr int MAX_HEAD_DIM = 256;          // the generic attention kernel keeps up to eight dimensions of a head per lane
 constexpr int TCGEN05_ATTENTION_MIN_QUERY = 33;
