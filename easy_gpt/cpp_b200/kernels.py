@@ -558,8 +558,11 @@ def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
         return 4, 2, 1                             # (sixteen warps per CTA measured slower: one CTA per SM)
     rb, ks = 1, 8
     split = max(1, min(8, round(chunks / (ks * 2.5))))
-    if -(-n_rows // 16) * split > 4 * sm_count():
+    groups = -(-n_rows // 16)
+    if groups >= sm_count():                         # the row groups alone fill the SMs
         split = 1
+    while split > 1 and groups * split > 4 * sm_count():      # four CTAs an SM at most
+        split -= 1
     return rb, ks, split
 
 
