@@ -110,7 +110,16 @@ inline SkinnyPlan skinny_plan(int n_rows, int in_features, int head_dim = 0) {
         const int rb = head_dim / 16;
         int ks = 1;
         while (ks * 2 * rb <= 16 && chunks > 4 * ks) ks *= 2;
-        return {rb, ks, 1};
+        // A head of a larger model is more than one SM should stream alone (7B sizes: 917 KB): its K range is cut across
+        // up to 8 CTAs (a cluster) of about 128 KB each, at least four chunks a warp.  (1.5B sizes, three parts: 1.28 ms a
+        // decode step at batch 1 against 1.36; 7B sizes, seven parts, 252 CTAs: 3.80 against 3.58.)
+        const long long bytes = (long long)head_dim * in_features * 2;
+        const int heads = std::max(1, n_rows / head_dim);
+        int split = (int)std::max<long long>(1, std::min<long long>(8, (bytes + (64 << 10)) / (128 << 10)));
+        split = std::max(1, std::min(split, sm_count() / heads));      // no more CTAs than SMs: every CTA stages the input rows
+        if (heads * 8 > sm_count()) split = 1;                         // only where the heads leave most SMs idle (7B sizes, 36 heads in 4 parts: 4.11 ms against 4.04)
+        while (split > 1 && chunks < 4 * ks * split) --split;
+        return {rb, ks, split};
     }
     // wide matrices (gate/up, the head): 64 rows per CTA.  (Measured, ms a decode step at batch 8: 4 x 2 warps 0.737;
     // for the head alone 2 x 4 0.744, 4 x 1 0.733, 8 x 1 0.740, 2 x 2 0.735, 8 x 2 0.747; for both 2 x 4 0.803, 8 x 1 0.819.)

@@ -95,6 +95,7 @@ struct Params {
     float* scratch;              // [gridDim.y][gridDim.x][RB*16][tokens] partial sums when K is cut across CTAs
     int* counters;               // [gridDim.x] tickets, zero before and after every launch
     unsigned long long* trace;   // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
+    int parts_offset;            // where in shared memory the cluster's parts arrive (bytes)
     int cluster_reduce;          // the gridDim.y CTAs of a row group are one cluster and sum their parts through the first one's shared memory
 };
 
@@ -439,7 +440,7 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
     // ---- K cut across CTAs that form a cluster: every CTA puts its part into the first one's shared memory (two
     // trips to the L2 fewer than the ticket below), the first one sums them, in order
     if (gridDim.y > 1 && p.cluster_reduce) {
-        float* parts = factor + MT;                                   // [gridDim.y][tile_elems], used in the cluster's first CTA only
+        float* parts = reinterpret_cast<float*>(smem + p.parts_offset);   // [gridDim.y][tile_elems], used in the cluster's first CTA only; behind the input rows
         unsigned rank;
         asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
         uint32_t remote;
@@ -588,13 +589,12 @@ int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
     constexpr int MT = NT * 8;
     Params p = p_in;
     const int nwarps = p.RB * p.KS;
-    size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
-    // The CTAs that share a row group's K range as a cluster (up to 8, the portable size), where the input rows are
-    // not staged in the shared memory that the parts arrive in while the first CTA may still be multiplying.
+    const size_t red_bytes = ((size_t)nwarps * 16 * MT + (size_t)p.RB * 16 * MT + MT) * sizeof(float);
+    // The CTAs that share a row group's K range as a cluster (up to 8, the portable size): their parts arrive in the
+    // first CTA's shared memory behind everything else, since that CTA may still be multiplying from its input rows.
     static const bool cluster_allowed = !(getenv("EASY_GPT_CLUSTER_REDUCE") && atoi(getenv("EASY_GPT_CLUSTER_REDUCE")) == 0);
     const size_t parts_bytes_cluster = (size_t)k_split * p.RB * 16 * MT * sizeof(float);
-    p.cluster_reduce = cluster_allowed && NORM == 0 && k_split > 1 && k_split <= 8 && parts_bytes_cluster <= 32 * 1024;
-    if (p.cluster_reduce) red_bytes += parts_bytes_cluster;
+    p.cluster_reduce = cluster_allowed && k_split > 1 && k_split <= 8 && parts_bytes_cluster <= 32 * 1024;
     size_t xs_bytes = NORM ? (size_t)MT * (((p.K * 2 + 127) / 128) * 128 + 64) + MT * sizeof(float) + (size_t)p.K * sizeof(float) + (size_t)MT * 8 * sizeof(float) : 0;
     // the residual rows staged in shared memory, where they fit and the copies' alignment rule (16 bytes) holds
     const size_t staged_bytes = (size_t)p.M * p.K * sizeof(float);
@@ -604,10 +604,14 @@ int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
             return (int)cudaErrorInvalidValue;
         xs_bytes += parts_bytes;
     }
-    p.stage_norm = NORM == 1 && xs_bytes + staged_bytes <= 200 * 1024 && (uintptr_t)p.resid_in % 16 == 0 && (uintptr_t)p.delta % 16 == 0 &&
+    p.stage_norm = NORM == 1 && xs_bytes + staged_bytes + (p.cluster_reduce ? parts_bytes_cluster + 16 : 0) <= 200 * 1024 && (uintptr_t)p.resid_in % 16 == 0 && (uintptr_t)p.delta % 16 == 0 &&
                    (size_t)p.M * p.K * 6 < (1u << 20);
     if (p.stage_norm) xs_bytes += staged_bytes;
-    const size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
+    size_t smem_bytes = red_bytes > xs_bytes ? red_bytes : xs_bytes;
+    if (p.cluster_reduce) {
+        p.parts_offset = (int)((smem_bytes + 15) / 16 * 16);
+        smem_bytes = (size_t)p.parts_offset + parts_bytes_cluster;
+    }
     if (smem_bytes > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = skinny_kernel<NT, EPI, NORM>;
     static size_t configured = 0;

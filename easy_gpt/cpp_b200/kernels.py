@@ -553,7 +553,16 @@ def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
         ks = 1
         while ks * 2 * rb <= 16 and chunks > 4 * ks:
             ks *= 2
-        return rb, ks, 1
+        # a head of a larger model is more than one SM should stream alone: its K range is cut across up to
+        # 8 CTAs (a cluster) of about 128 KB each, at least four chunks a warp
+        split = max(1, min(8, (head_dim * in_features * 2 + (64 << 10)) // (128 << 10)))
+        heads = max(1, n_rows // head_dim)
+        split = max(1, min(split, sm_count() // heads))      # no more CTAs than SMs
+        if heads * 8 > sm_count():                            # only where the heads leave most SMs idle
+            split = 1
+        while split > 1 and chunks < 4 * ks * split:
+            split -= 1
+        return rb, ks, split
     if n_rows >= 64 * sm_count():                    # wide matrices (gate/up, the head): 64 rows per CTA
         return 4, 2, 1                             # (sixteen warps per CTA measured slower: one CTA per SM)
     rb, ks = 1, 8

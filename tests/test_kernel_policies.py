@@ -29,4 +29,6 @@ def test_decode_product_plans_cover_the_matrix():
         assert rb >= 1 and ks >= 1 and split >= 1
         assert rb * ks <= 32                                        # warps of a CTA
         if head:
-            assert rb * 16 == head and split == 1
+            assert rb * 16 == head and 1 <= split <= 8
+            # only heads that are much for one SM are cut, and only where the heads leave most SMs idle
+            assert (split == 1) == (head * width * 2 < (192 << 10) or (rows // head) * 8 > kernels.sm_count())
