@@ -446,10 +446,10 @@ public:
                                                   cache.page_stride, cache.head_stride, cache.num_pages, window, scale_, ctx.status), "attention_prefill");
             }
             if (ctx.small_tokens)      // the decoded tokens beside them: token by token, split over their keys
-                paged(ctx, qkv, cache, tables, attn, ctx.num_small, plans::attention_paged_splits(ctx.num_small, heads_, kv_heads_, longest), window,
+                paged(ctx, qkv, cache, tables, attn, ctx.num_small, plans::attention_paged_splits(ctx.num_small, heads_, kv_heads_, longest, head_dim_), window,
                       nullptr, ctx.small_tokens);
         } else if (plans::attention_paged_takes(dtype, head_dim_, cache.page_size)) {
-            paged(ctx, qkv, cache, tables, attn, T, plans::attention_paged_splits(T, heads_, kv_heads_, longest), window, ctx.seq_context, nullptr);
+            paged(ctx, qkv, cache, tables, attn, T, plans::attention_paged_splits(T, heads_, kv_heads_, longest, head_dim_), window, ctx.seq_context, nullptr);
         } else {
             launch_check(eg_attention_generic(ctx.stream, (int)dtype, qkv.p, (int)qkv.ld, cache.k, cache.v, tables.block_table, tables.table_width,
                                               ctx.token_seq, ctx.positions, attn.p, (int)attn.ld, T, heads_, kv_heads_, head_dim_, cache.page_size,

@@ -58,12 +58,14 @@ inline bool attention_prefill_tcgen05_takes(DType dtype, int head_dim, int page_
 // How many CTAs share one (token, KV head).  Up to 16 tokens the kernel is fastest with one wave of 128 to 256
 // CTAs that walk about eight key tiles of 64 each; with more tokens with about four CTAs per SM.  A power of two,
 // at least four tiles per CTA.
-inline int attention_paged_splits(int tokens, int num_heads, int num_kv_heads, long long max_context) {
+inline int attention_paged_splits(int tokens, int num_heads, int num_kv_heads, long long max_context, int head_dim = 64) {
     const long long base = (long long)tokens * num_kv_heads * ((num_heads / num_kv_heads + 15) / 16);
     const long long tiles = std::max<long long>(1, (max_context + 63) / 64);
     // (measured with 2 / 4 / 8 CTAs per SM as the most, ms a step at context 4096: batch 24 1.43 / 1.31 / -, batch 32
     // 1.35 / 1.40 / 1.54, batch 48 1.78 / 1.54 / -, batch 64 1.81 / 1.65 / 1.75)
-    const long long most = tokens <= SKINNY_MAX_TOKENS ? 256 : 4LL * sm_count();
+    // heads of more than 64: the kernel's three stages are 96 KB, two CTAs an SM (1.5B sizes, ms a step with 2 / 4 CTAs an
+    // SM as the most: batch 32 2.27 / 2.62, batch 64 3.20 / 3.35; 7B sizes, batch 64: 9.18 / 9.47)
+    const long long most = tokens <= SKINNY_MAX_TOKENS ? 256 : (head_dim > 64 ? 2LL : 4LL) * sm_count();
     int splits = 1;
     while ((long long)splits * 2 * base <= most && tiles / (splits * 2) >= 4 && splits < 128) splits *= 2;
     return splits;

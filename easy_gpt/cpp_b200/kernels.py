@@ -317,18 +317,19 @@ def attention_paged_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> 
     return dtype == torch.bfloat16 and head_dim in PAGED_ATTENTION_HEAD_DIMS and page_size % 16 == 0
 
 
-def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_context: int) -> int:
+def attention_paged_splits(tokens: int, num_heads: int, num_kv_heads: int, max_context: int, head_dim: int = 64) -> int:
     """How many CTAs share one (token, KV head).  Measured on B200 (context 4096): up to 16 tokens the kernel
     is fastest with one wave of 128 to 256 CTAs (two per SM, five key tiles of 64 in flight each) that walk
     about eight tiles; more, smaller CTAs pay in partial results and in the merge.  With more tokens it is
     fastest with about 400 to 600 CTAs, four per SM with three tiles in flight each (the kernel picks that
-    pipeline when there are more CTAs than two per SM).  A power of two, at least four tiles per CTA."""
+    pipeline when there are more CTAs than two per SM); heads of more than 64 leave room for two CTAs per SM
+    only, and are fastest with up to that many.  A power of two, at least four tiles per CTA."""
     forced = os.environ.get("EASY_GPT_ATTENTION_SPLITS")
     base = tokens * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
     tiles = max(1, -(-max_context // 64))
     if forced:
         return max(1, min(int(forced), tiles, 128))
-    most = 256 if tokens <= SKINNY_MAX_TOKENS else 4 * sm_count()
+    most = 256 if tokens <= SKINNY_MAX_TOKENS else (2 if head_dim > 64 else 4) * sm_count()
     splits = 1
     while splits * 2 * base <= most and tiles // (splits * 2) >= 4 and splits < 128:
         splits *= 2

@@ -152,10 +152,10 @@ class Attention(Mixer):
                 count = ctx.small_tokens.numel()
                 kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                         self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
-                                        kernels.attention_paged_splits(count, self.num_heads, self.num_kv_heads, longest),
+                                        kernels.attention_paged_splits(count, self.num_heads, self.num_kv_heads, longest, self.head_dim),
                                         ctx.status, token_list=ctx.small_tokens)
         elif kernels.attention_paged_takes(dtype, self.head_dim, tables.page_size):
-            splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest)
+            splits = kernels.attention_paged_splits(T, self.num_heads, self.num_kv_heads, longest, self.head_dim)
             kernels.attention_paged(qkv, cache.k, cache.v, tables.block_table, ctx.token_seq, ctx.positions, attn,
                                     self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale, splits,
                                     ctx.status, prefetch=self._hint(0) if T <= kernels.SKINNY_MAX_TOKENS else None,
