@@ -129,11 +129,13 @@ inline SkinnyPlan skinny_plan(int n_rows, int in_features, int head_dim = 0) {
     const int rb = 1, ks = 8;
     // (Python's round() sends halves to the even neighbour; so does nearbyint in the default rounding mode)
     int split = (int)std::max(1.0, std::min(8.0, std::nearbyint(chunks / (ks * 2.5))));
-    // four CTAs an SM at most; no split where the row groups alone fill the SMs (7B sizes, down product, 224 row groups:
-    // 4.04 ms a step at batch 8 unsplit, 4.24 in two parts)
+    // No more CTAs than are on the GPU at once, two an SM (their registers): a second wave starts when the first is done
+    // (1.5B sizes, down product, 96 row groups in 6 parts: the last CTAs started 15 us after the kernel in front had
+    // ended).  No split where the row groups alone fill the SMs (7B sizes, down product, 224 row groups: 4.04 ms a step
+    // at batch 8 unsplit, 4.24 in two parts).
     const long long groups = (n_rows + 15) / 16;
     if (groups >= sm_count()) split = 1;
-    while (split > 1 && groups * split > 4LL * sm_count()) --split;
+    while (split > 1 && groups * split > 2LL * sm_count()) --split;
     return {rb, ks, split};
 }
 inline bool gemm_skinny_takes(DType dtype, int tokens, int in_features) {

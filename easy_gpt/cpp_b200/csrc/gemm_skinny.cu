@@ -637,7 +637,19 @@ int launch_one(cudaStream_t stream, const Params& p_in, int ctas, int k_split) {
         attr[nattr].val.clusterDim.x = 1;
         attr[nattr].val.clusterDim.y = (unsigned)k_split;
         attr[nattr].val.clusterDim.z = 1;
-        ++nattr;
+        cfg.attrs = attr;
+        cfg.numAttrs = nattr + 1;
+        // All clusters have to find room on the GPU together, or the last ones run as a second wave, after the first
+        // (1.5B sizes, down product, 96 clusters of 3: their last CTAs started 9 us after the kernel in front had ended).
+        // Then the parts go through scratch memory and a ticket, which asks nothing of where the CTAs run.
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= ctas) {
+            ++nattr;
+        } else {
+            (void)cudaGetLastError();
+            if (!p.scratch || !p.counters) return (int)cudaErrorInvalidValue;
+            p.cluster_reduce = 0;
+        }
     }
     cfg.attrs = attr;
     cfg.numAttrs = nattr;

@@ -571,7 +571,7 @@ def skinny_plan(n_rows: int, in_features: int, head_dim: int = 0):
     groups = -(-n_rows // 16)
     if groups >= sm_count():                         # the row groups alone fill the SMs
         split = 1
-    while split > 1 and groups * split > 4 * sm_count():      # four CTAs an SM at most
+    while split > 1 and groups * split > 2 * sm_count():      # no more CTAs than are on the GPU at once, two an SM
         split -= 1
     return rb, ks, split
 
