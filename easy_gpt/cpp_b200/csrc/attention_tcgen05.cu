@@ -15,9 +15,9 @@
 //
 // Warp roles (256 threads; 128 registers each and at most 113 KB of shared memory, so that two CTAs share an SM
 // and one fills the other's waits; each allocates 256 of the 512 TMEM columns):
-//   warp 0     TMA loads: Q once; per key tile one box of 16 keys x 64 columns per page piece, K and V, 128-byte
-//              swizzled, into a ring of stages.  Issuing a copy costs the issuing thread a good hundred cycles, so
-//              every box of a tile has its own lane.  Block-table entries are fetched a ring ahead.
+//   warp 0     TMA loads: Q once; per key tile boxes of 64 keys x 64 columns (32 or 16 keys where the pages are no
+//              multiple of 64), K and V, 128-byte swizzled, into a ring of stages; every box of a tile has its own
+//              lane.  Block-table entries are fetched 32 pieces at a time, a batch ahead.
 //   warp 1     allocates TMEM; one thread issues the score products (descriptors ready before it waits: the
 //              arithmetic of a descriptor costs more than the issue of the MMA)
 //   warps 2-5  the softmax rows
@@ -46,25 +46,30 @@
 namespace {
 
 constexpr int BM = 128, BN = 64;
-constexpr int THREADS = 256;                                     // loader warp, two MMA warps (1 and 6), four softmax warps (2-5)
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 constexpr float REFERENCE_SLACK = 8.f;                            // the exponents' reference may lag the maximum by 2^8
 constexpr int SUB_ROW_BYTES = 128;                                // 64 bfloat16: one swizzle row
 
-template <int HD>
+template <int HD, int WGS>
 struct Shape {
     static constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of Q, K, V
-    static constexpr int STAGES = HD == 64 ? 5 : 2;
-    static constexpr int SCORE_BUFFERS = HD == 64 ? 3 : 2;        // TMEM buffers of S_j / P_j
+    static constexpr int STAGES = WGS == 1 ? (HD == 64 ? 5 : 2) : (HD == 64 ? 8 : 3);
+    static constexpr int SCORE_BUFFERS = HD == 64 ? 3 : 2;        // TMEM buffers of S_j / P_j of one softmax group
+    static constexpr int THREADS = WGS == 1 ? 256 : 384;          // loader warp, two MMA warps (1 and 6), four softmax warps a group (2-5, 8-11)
+    static constexpr int CTAS_PER_SM = WGS == 1 ? 2 : 1;
     static constexpr int Q_SUB_BYTES = BM * SUB_ROW_BYTES;        // 16 KB
     static constexpr int KV_SUB_BYTES = BN * SUB_ROW_BYTES;       // 8 KB
     static constexpr int Q_BYTES = SUBS * Q_SUB_BYTES;
     static constexpr int K_BYTES = SUBS * KV_SUB_BYTES;
     static constexpr int STAGE_BYTES = 2 * K_BYTES;               // K then V
-    static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024;
-    static constexpr int O_COL = SCORE_BUFFERS * BN;              // TMEM: S0/P0 [0,64) S1/P1 [64,128) S2/P2 [128,192) then O
-    static constexpr int TMEM_COLS = 256;                         // two CTAs share the SM's 512 columns
-    static_assert(O_COL + HD <= TMEM_COLS, "TMEM columns");
+    // where the second softmax group hands its rows to the first at the end of a unit: O as [column][row], then reference and sum
+    static constexpr int HANDOVER_BYTES = (WGS - 1) * (HD + 2) * BM * 4;
+    static constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + HANDOVER_BYTES + 1024;
+    // TMEM: the score buffers of group 0, of group 1, then O of either
+    static constexpr int O_COL = WGS * SCORE_BUFFERS * BN;
+    static constexpr int TMEM_COLS = WGS == 1 ? 256 : 512;        // two CTAs share the SM's 512 columns, or one has them all
+    static_assert(O_COL + WGS * HD <= TMEM_COLS, "TMEM columns");
+    static_assert(WGS == 1 || WGS == 2, "one or two softmax groups");
 };
 
 
@@ -194,6 +199,7 @@ struct Params {
     // work queue of the persistent CTAs: [0] next unit, [1] CTAs that have left; both zero before and after a launch
     int* queue;
     int num_tiles, max_parts, part_tiles;
+    int piece_rows;            // keys a TMA box of K or V holds: 64, 32 or 16, a divisor of the page size
 };
 
 // The 64-bit shared-memory descriptor from its constant high word and a low word (start address, leading offset).
@@ -202,21 +208,21 @@ __device__ __forceinline__ uint64_t desc_from(uint32_t lo, uint32_t hi) {
     asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 2)
+template <int HD, int WGS>
+__global__ void __launch_bounds__((Shape<HD, WGS>::THREADS), (Shape<HD, WGS>::CTAS_PER_SM))
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const Params p) {
-    using S = Shape<HD>;
-    constexpr int STAGES = S::STAGES, SCORE_BUFFERS = S::SCORE_BUFFERS;
+    using S = Shape<HD, WGS>;
+    constexpr int STAGES = S::STAGES, SCORE_BUFFERS = S::SCORE_BUFFERS, ALL_BUFFERS = WGS * S::SCORE_BUFFERS;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[SCORE_BUFFERS], p_full[SCORE_BUFFERS], o_done[SCORE_BUFFERS];
-    __shared__ int piece_page[STAGES][4];                         // the loader's block-table entries, per stage
+    __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[ALL_BUFFERS], p_full[ALL_BUFFERS], o_done[ALL_BUFFERS];
     __shared__ int unit_slot[2];                                  // the unit the CTA works on, by round parity
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_addr = base, ring_addr = base + S::Q_BYTES;
+    float* const handover = reinterpret_cast<float*>(smem_raw + (base - smem_addr(smem_raw)) + S::Q_BYTES + STAGES * S::STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -226,7 +232,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             mbar_init(&v_full[s], 1);
             mbar_init(&kv_empty[s], 1);
         }
-        for (int b = 0; b < SCORE_BUFFERS; ++b) {
+        for (int b = 0; b < ALL_BUFFERS; ++b) {
             mbar_init(&s_full[b], 1);
             mbar_init(&p_full[b], 4);                             // one arrival per softmax warp
             mbar_init(&o_done[b], 1);
@@ -246,10 +252,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // A unit of work: (query tile, head, part of its key range).  Units are numbered so that the query tiles listed
     // last (of a prompt: those that see most keys) come first, and dealt out through a counter: a CTA that is done
     // with a unit takes the next one, which evens out the SMs' loads.
-    // Every role counts alike: gt key tiles before this unit (stage and buffer indices and barrier phases run on),
-    // units before this one (phase of q_full).
+    // Every role counts alike: gt key tiles before this unit (stage indices and their barriers' phases run on), the
+    // key tiles that either softmax group had before this unit (its score buffers and their barriers), units before
+    // this one (phase of q_full).  Key tile j of a unit belongs to group j % WGS, as that group's tile j / WGS.
     const int total_units = p.num_tiles * p.num_heads * p.max_parts;
-    int gt = 0, units_done = 0;
+    int gt = 0, units_done = 0, group_tiles[WGS] = {};
     for (int round = 0;; ++round) {
         if (threadIdx.x == 0) {
             int u;
@@ -291,59 +298,57 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
 
         if (warp == 0) {                                         // ---- TMA loader: one lane per box of a key tile
-            // lane = sub * 8 + kv * 4 + g: 64-column sub-tile, K or V, 16-key piece.  Issuing a TMA copy costs the
-            // issuing thread a good hundred cycles; eight (sixteen) lanes issue their boxes with one instruction.
-            const int g = lane & 3, is_v = (lane >> 2) & 1, sub = lane >> 3;
-            const bool loads = lane < 8 * S::SUBS;
+            // A key tile comes as boxes of `piece_rows` keys (64 where the pages allow it, else 32 or 16) x 64 columns:
+            // lane = (sub * 2 + kv) * pieces + g for the 64-column sub-tile, K or V, and the piece.  Issuing a TMA copy
+            // costs the issuing thread about ninety cycles and the lanes of a warp take turns at it (measured: eight boxes
+            // 700 cycles of the 1,700 that the loader took per tile, more than the softmax rows), so the boxes are as tall
+            // as the pages allow.
+            const int pieces = BN / p.piece_rows;
+            const int g = lane % pieces, is_v = (lane / pieces) & 1, sub = lane / (2 * pieces);
+            const bool loads = lane < 2 * pieces * S::SUBS;
             if (lane == 0) {
                 mbar_expect_tx(&q_full, S::Q_BYTES);
 #pragma unroll
                 for (int qs = 0; qs < S::SUBS; ++qs) tma_load_2d(q_addr + qs * S::Q_SUB_BYTES, &map_q, &q_full, h * HD + qs * 64, t0);
             }
             const int* table = p.block_table + (size_t)seq * p.table_stride;
-            // the block-table entry of a 16-key piece of key tile j; a piece outside the visible keys reads the last page
-            auto entry_of = [&](int j, int piece) {
-                const int kpos0 = (tile_lo + j) * BN + piece * 16;
-                if (j >= ntiles || kpos0 > pos_hi || kpos0 + 15 < first) return p.num_pages - 1;
+            // The pieces of the unit, numbered through (piece f of the unit is piece f % pieces of key tile f / pieces), are
+            // looked up 32 at a time, one by each lane, a batch ahead: the block-table entry, and from it the piece's row in
+            // the cache maps.  A piece outside the visible keys reads the last page.
+            auto entry_of = [&](int f) {
+                const int kpos0 = (tile_lo + f / pieces) * BN + (f % pieces) * p.piece_rows;
+                if (f / pieces >= ntiles || kpos0 > pos_hi || kpos0 + p.piece_rows - 1 < first) return p.num_pages - 1;
                 return __ldg(table + kpos0 / p.page_size);
             };
-            // lanes 0..3 keep the entries: those of the first STAGES tiles go to shared memory at once, those of the
-            // tile after them wait in a register; every iteration moves one tile's entries on
-            int ahead = 0;
-            if (lane < 4) {
-#pragma unroll
-                for (int s = 0; s < STAGES; ++s) piece_page[(gt + s) % STAGES][lane] = entry_of(s, lane);
-                ahead = entry_of(STAGES, lane);
-            }
-            __syncwarp();
+            auto row_of = [&](int page, int f) {
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.status, EG_STATUS_BAD_PAGE);
+                    page = p.num_pages - 1;
+                }
+                const int kpos0 = (tile_lo + f / pieces) * BN + (f % pieces) * p.piece_rows;
+                return (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+            };
+            int rows = row_of(entry_of(lane), lane), ahead = entry_of(32 + lane);
             const CUtensorMap* map = is_v ? &map_v : &map_k;
             int issued = 0;
             for (int j = 0; j < ntiles; ++j, ++issued) {
-                const int s = (gt + j) % STAGES, use = (gt + j) / STAGES;
-                if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[s], (use - 1) & 1, &abort_flag, p.status))) break;
-                int page = piece_page[s][g];
-                if (page < 0 || page >= p.num_pages) {
-                    if (loads) atomicOr(p.status, EG_STATUS_BAD_PAGE);
-                    page = p.num_pages - 1;
+                const int s = (gt + j) % STAGES, use = (gt + j) / STAGES, f0 = j * pieces;
+                if (j > 0 && (f0 & 31) == 0) {                   // the next batch of pieces (a tile's pieces lie in one batch)
+                    rows = row_of(ahead, f0 + lane);
+                    ahead = entry_of(f0 + 32 + lane);
                 }
-                const int kpos0 = (tile_lo + j) * BN + g * 16;
-                const int row = (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
+                // one lane polls, the others wait for it at the vote
+                if (use > 0 && !__all_sync(0xffffffffu, lane != 0 || mbar_wait(&kv_empty[s], (use - 1) & 1, &abort_flag, p.status))) break;
                 if (lane == 0) {
                     mbar_expect_tx(&k_full[s], S::K_BYTES);
                     mbar_expect_tx(&v_full[s], S::K_BYTES);
                 }
+                const int row = __shfl_sync(0xffffffffu, rows, (f0 + g) & 31);
                 __syncwarp();
                 if (loads) {
-                    const uint32_t dst = ring_addr + s * S::STAGE_BYTES + is_v * S::K_BYTES + sub * S::KV_SUB_BYTES + g * 16 * SUB_ROW_BYTES;
+                    const uint32_t dst = ring_addr + s * S::STAGE_BYTES + is_v * S::K_BYTES + sub * S::KV_SUB_BYTES + g * p.piece_rows * SUB_ROW_BYTES;
                     tma_load_2d(dst, map, is_v ? &v_full[s] : &k_full[s], sub * 64, row);
                 }
-                __syncwarp();
-                // tile j + STAGES will use this stage: its entries were fetched an iteration ago; fetch the next ones
-                if (lane < 4) {
-                    piece_page[s][lane] = ahead;
-                    ahead = entry_of(j + STAGES + 1, lane);
-                }
-                __syncwarp();
             }
             // every copy has to land before the CTA gives up its shared memory, also when a role has given up
             if (lane == 0 && abort_flag) {
@@ -363,17 +368,19 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 bool ok = mbar_wait(&q_full, units_done & 1, &abort_flag, p.status);
                 for (int j = 0; j < ntiles && ok; ++j) {
                     const int n = gt + j;
+                    const int g = j % WGS, ng = (g ? group_tiles[WGS - 1] : group_tiles[0]) + j / WGS;    // the group's running tile
+                    const int sb = g * SCORE_BUFFERS + ng % SCORE_BUFFERS;
                     const uint32_t stage_lo = k_lo + (uint32_t)(((n % STAGES) * S::STAGE_BYTES) >> 4);
-                    const uint32_t d = tmem_base + (uint32_t)((n % SCORE_BUFFERS) * BN);
+                    const uint32_t d = tmem_base + (uint32_t)(sb * BN);
                     uint64_t a[HD / 16], b[HD / 16];
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         a[kk] = desc_from(q_lo + (uint32_t)(((kk / 4) * S::Q_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
                         b[kk] = desc_from(stage_lo + (uint32_t)(((kk / 4) * S::KV_SUB_BYTES + (kk % 4) * 32) >> 4), desc_hi);
                     }
-                    // S goes where the S and P of SCORE_BUFFERS tiles before were: the product that read that P must be done
-                    if (n >= SCORE_BUFFERS) {
-                        ok = mbar_wait(&o_done[n % SCORE_BUFFERS], (n / SCORE_BUFFERS - 1) & 1, &abort_flag, p.status);
+                    // S goes where the group's S and P of SCORE_BUFFERS tiles before were: the product that read that P must be done
+                    if (ng >= SCORE_BUFFERS) {
+                        ok = mbar_wait(&o_done[sb], (ng / SCORE_BUFFERS - 1) & 1, &abort_flag, p.status);
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -382,7 +389,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     tc_mma<false>(d, a[0], b[0], idesc_s);
 #pragma unroll
                     for (int kk = 1; kk < HD / 16; ++kk) tc_mma<true>(d, a[kk], b[kk], idesc_s);
-                    tc_commit(&s_full[n % SCORE_BUFFERS]);
+                    tc_commit(&s_full[sb]);
                 }
             }
         } else if (warp == 6) {
@@ -390,28 +397,34 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const uint32_t idesc_o = idesc(HD, true);
                 const uint32_t desc_hi = (uint32_t)(desc_k_major(0) >> 32);
                 const uint32_t v_lo = (uint32_t)desc_n_major(ring_addr + S::K_BYTES, S::KV_SUB_BYTES);
-                const uint32_t d = tmem_base + (uint32_t)S::O_COL;
                 bool ok = true;
                 for (int j = 0; j < ntiles && ok; ++j) {
                     const int n = gt + j;
+                    const int g = j % WGS, ng = (g ? group_tiles[WGS - 1] : group_tiles[0]) + j / WGS;
+                    const int sb = g * SCORE_BUFFERS + ng % SCORE_BUFFERS;
+                    const uint32_t d = tmem_base + (uint32_t)(S::O_COL + g * HD);                  // the group's own O
                     const uint32_t stage_lo = v_lo + (uint32_t)(((n % STAGES) * S::STAGE_BYTES) >> 4);
-                    const uint32_t pa = tmem_base + (uint32_t)((n % SCORE_BUFFERS) * BN);     // P_j: 32 columns of bfloat16 pairs
+                    const uint32_t pa = tmem_base + (uint32_t)(sb * BN);                             // P_j: 32 columns of bfloat16 pairs
                     uint64_t b[BN / 16];
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; ++kk) b[kk] = desc_from(stage_lo + (uint32_t)((kk * 2048) >> 4), desc_hi);
                     ok = mbar_wait(&v_full[n % STAGES], (n / STAGES) & 1, &abort_flag, p.status) &&
-                         mbar_wait(&p_full[n % SCORE_BUFFERS], (n / SCORE_BUFFERS) & 1, &abort_flag, p.status);
+                         mbar_wait(&p_full[sb], (ng / SCORE_BUFFERS) & 1, &abort_flag, p.status);
                     if (!ok) break;
                     tc_fence_after();
-                    if (j == 0) tc_mma_a_tmem<false>(d, pa, b[0], idesc_o);
+                    if (j < WGS) tc_mma_a_tmem<false>(d, pa, b[0], idesc_o);                         // the group's first tile of the unit
                     else tc_mma_a_tmem<true>(d, pa, b[0], idesc_o);
 #pragma unroll
                     for (int kk = 1; kk < BN / 16; ++kk) tc_mma_a_tmem<true>(d, pa + (uint32_t)(kk * 8), b[kk], idesc_o);
-                    tc_commit(&o_done[n % SCORE_BUFFERS]);
+                    tc_commit(&o_done[sb]);
                     tc_commit(&kv_empty[n % STAGES]);            // K and V of this stage have been read
                 }
             }
-        } else if (warp >= 2 && warp < 6) {                      // ---- softmax rows, warps 2..5
+        } else if ((warp >= 2 && warp < 6) || (WGS > 1 && warp >= 8)) {      // ---- softmax rows, warps 2..5 (and 8..11)
+            // With two groups the first takes the unit's even key tiles and the second the odd ones, each with a
+            // reference, a sum and an O of its own; at the end of the unit the second hands its rows to the first.
+            const int g = (WGS > 1 && warp >= 8) ? 1 : 0;
+            const int my_tiles = (ntiles + WGS - 1 - g) / WGS, my_before = g ? group_tiles[WGS - 1] : group_tiles[0];
             const int quad = warp & 3;                           // a warp may touch TMEM lanes 32 * (warp % 4) ..
             const int row = quad * 32 + lane;
             const bool valid = row < count;
@@ -421,15 +434,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const bool warp_has_rows = quad * 32 < count;
             const float scale_log2 = p.scale * 1.4426950408889634f;
             const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-            const uint32_t o_lane = lane_base + (uint32_t)S::O_COL;
+            const uint32_t o_lane = lane_base + (uint32_t)(S::O_COL + g * HD);
 
             // m: the reference of the exponents, a maximum the row has seen (in scaled base-2 units); l: the sum against it
             float m = -INFINITY, l = 0.f;
             bool ok = true;
             const bool tracing = p.trace && blockIdx.x == 0 && round == 0 && threadIdx.x == 64;
-#define STAMP(k) if (tracing && j < 32) p.trace[j * 8 + (k)] = clock64();
-            for (int j = 0; j < ntiles; ++j) {
-                const int n = gt + j, b = n % SCORE_BUFFERS;
+#define STAMP(k) if (tracing && i < 32) p.trace[i * 8 + (k)] = clock64();
+            for (int i = 0; i < my_tiles; ++i) {
+                const int j = g + i * WGS, n = my_before + i, b = g * SCORE_BUFFERS + n % SCORE_BUFFERS;
                 STAMP(0)
                 ok = __all_sync(0xffffffffu, mbar_wait(&s_full[b], (n / SCORE_BUFFERS) & 1, &abort_flag, p.status));   // the warp stays together
                 if (!ok) break;
@@ -483,8 +496,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 // Rows whose reference moved scale what they have accumulated so far: the product of the tile before
                 // must be done.  (The barriers take turns like the score buffers: a parity tells two phases apart, not
                 // more, and nobody who waits on one of them is ever further than one phase from it.)
-                if (j > 0 && __any_sync(0xffffffffu, c != 1.f)) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&o_done[(n - 1) % SCORE_BUFFERS], ((n - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+                if (i > 0 && __any_sync(0xffffffffu, c != 1.f)) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&o_done[g * SCORE_BUFFERS + (n - 1) % SCORE_BUFFERS], ((n - 1) / SCORE_BUFFERS) & 1, &abort_flag, p.status));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
@@ -528,23 +541,74 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 STAMP(7)
             }
 #undef STAMP
-            const int last = gt + ntiles - 1;
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[last % SCORE_BUFFERS], (last / SCORE_BUFFERS) & 1, &abort_flag, p.status));
-            if (ok && parts == 1) {
+            const int last = my_before + my_tiles - 1;
+            if (ok && my_tiles > 0)
+                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[g * SCORE_BUFFERS + last % SCORE_BUFFERS], (last / SCORE_BUFFERS) & 1, &abort_flag, p.status));
+            // what the groups hold together: the first group's rows take in the second group's
+            float o_scale = 1.f;                                 // of this group's O in TMEM
+            float other_scale = 0.f;                             // of the other group's O in shared memory (0: nothing there)
+            if constexpr (WGS > 1) {
+                float* const other_o = handover;                                  // [HD][BM]
+                float* const other_ml = handover + HD * BM;                       // [2][BM]
+                if (g == 1) {
+                    const bool have = ok && my_tiles > 0;
+                    other_ml[row] = have ? m : -INFINITY;
+                    other_ml[BM + row] = have ? l : 0.f;
+                    if (have) {
+                        tc_fence_after();
+#pragma unroll
+                        for (int c0 = 0; c0 < HD; c0 += 32) {
+                            uint32_t r[32];
+                            tmem_ld32(o_lane + (uint32_t)c0, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) other_o[(c0 + e) * BM + row] = __uint_as_float(r[e]);
+                        }
+                    }
+                }
+                // both groups, whatever happened before: a wait that gave up must not leave the others at this barrier
+                asm volatile("bar.sync 1, %0;\n" ::"n"(WGS * 128) : "memory");
+                if (g == 0) {
+                    const float m1 = other_ml[row], l1 = other_ml[BM + row];
+                    if (m1 != -INFINITY) {
+                        const float top = fmaxf(m, m1);
+                        o_scale = m == -INFINITY ? 0.f : exp2f(m - top);
+                        other_scale = exp2f(m1 - top);
+                        l = l * o_scale + l1 * other_scale;
+                        m = top;
+                    }
+                }
+            }
+            // this row's columns c0 .. c0 + 31 of O, unnormalised: the group's own and, where there is one, the other's
+            auto load_o = [&](int c0, float (&v)[32]) {
+                uint32_t r[32];
+                tmem_ld32(o_lane + (uint32_t)c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+                if constexpr (WGS > 1) {
+                    if (other_scale != 0.f) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = fmaf(handover[(c0 + e) * BM + row], other_scale, v[e] * o_scale);
+                    }
+                }
+            };
+            if (g != 0) {
+                // the second group's rows are with the first
+            } else if (ok && parts == 1) {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(o_lane + (uint32_t)c0, r);
-                    tmem_ld_wait();
+                    float o[32];
+                    load_o(c0, o);
                     if (valid) {
 #pragma unroll
                         for (int ch = 0; ch < 4; ++ch) {
                             float v[8];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * ch + e]) * inv;
+                            for (int e = 0; e < 8; ++e) v[e] = o[8 * ch + e] * inv;
                             dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
                         }
                     }
@@ -557,13 +621,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 float* my_o = p.partial_o + ((slot0 + part) * BM + row) * HD;
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(o_lane + (uint32_t)c0, r);
-                    tmem_ld_wait();
+                    float o[32];
+                    load_o(c0, o);
                     if (valid) {
 #pragma unroll
                         for (int e = 0; e < 32; e += 4)
-                            *reinterpret_cast<uint4*>(my_o + c0 + e) = make_uint4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+                            *reinterpret_cast<float4*>(my_o + c0 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
                     }
                 }
                 if (valid) *reinterpret_cast<float2*>(p.partial_ml + ((slot0 + part) * BM + row) * 2) = make_float2(m, l);
@@ -579,6 +642,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             p.trace[256 + unit * 4 + 1] = (long long)now;
         }
         gt += ntiles;
+#pragma unroll
+        for (int w = 0; w < WGS; ++w) group_tiles[w] += (ntiles + WGS - 1 - w) / WGS;
         ++units_done;
     }
     // the last CTA to leave puts the queue back to zero for the next launch
@@ -668,20 +733,26 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int HD>
-int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int ctas) {
-    using S = Shape<HD>;
+template <int HD, int WGS>
+int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int sm_count) {
+    using S = Shape<HD, WGS>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_prefill_tcgen05_kernel<HD><<<ctas, THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+    const long long units = (long long)p.num_tiles * p.num_heads * p.max_parts, places = (long long)S::CTAS_PER_SM * sm_count;
+    const int ctas = (int)(units < places ? units : places);
+    attention_prefill_tcgen05_kernel<HD, WGS><<<ctas, S::THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
     return eg_launch_status();
 }
 
 }  // namespace
+
+// How many softmax groups a CTA of the kernel has for this head size (with two the CTAs have an SM each, with one
+// they share it in pairs): what a caller needs to know to count the CTAs.
+EG_API int eg_attention_prefill_groups(int head_dim) { return head_dim == 64 ? 2 : 1; }
 
 // q: [total_tokens, >= num_heads * head_dim] bfloat16 with row stride ldq; k_cache / v_cache: [num_pages][num_kv_heads]
 // [page_size][head_dim] with the same strides (in elements); the last page must hold finite numbers (pieces of a
@@ -727,12 +798,13 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     p.num_tiles = num_tiles;
     p.max_parts = max_parts;
     p.part_tiles = part_tiles;
+    p.piece_rows = page_size % 64 == 0 ? 64 : page_size % 32 == 0 ? 32 : 16;
     // rows of head_dim elements that the cache maps cover: up to the last row of the last page
     const long long kv_rows = (long long)(num_pages - 1) * p.page_rows + (long long)(num_kv_heads - 1) * p.head_rows + page_size;
     if (kv_rows >= (1ll << 31)) return (int)cudaErrorInvalidValue;
     CUtensorMap map_q, map_k, map_v;
     if (make_map(&map_q, q, total_tokens, (long long)num_heads * head_dim, ldq, BM) ||
-        make_map(&map_k, k_cache, kv_rows, head_dim, head_dim, 16) || make_map(&map_v, v_cache, kv_rows, head_dim, head_dim, 16))
+        make_map(&map_k, k_cache, kv_rows, head_dim, head_dim, p.piece_rows) || make_map(&map_v, v_cache, kv_rows, head_dim, head_dim, p.piece_rows))
         return (int)cudaErrorInvalidValue;
     static int sm_count = 0;
     if (!sm_count) {
@@ -740,12 +812,15 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
     }
-    // Persistent CTAs, two per SM, that deal the units out among themselves.  (Measured with one CTA per SM: a prompt of
-    // 2,048 tokens, which lasts as long as its longest unit, takes 38 us instead of 41; one of 8,192 tokens, where the SMs
-    // are full, 406 us instead of 251: the second CTA's MMAs run under the first one's softmax.)
-    const long long units = (long long)num_tiles * num_heads * max_parts;
-    const int ctas = (int)(units < 2ll * sm_count ? units : 2ll * sm_count);
-    int code = head_dim == 64 ? launch<64>(stream, map_q, map_k, map_v, p, ctas) : launch<128>(stream, map_q, map_k, map_v, p, ctas);
+    // Persistent CTAs that deal the units out among themselves: one per SM with two softmax groups, which share a
+    // unit's key tiles between them, or two per SM with one group each.  Either way an SM runs the softmax of two key
+    // tiles at a time, and the tensor core works under it; with two groups the longest unit of a prompt takes half as
+    // long.  EASY_GPT_PREFILL_GROUPS=1 or 2 sets the form for a measurement.
+    static const int asked = getenv("EASY_GPT_PREFILL_GROUPS") ? atoi(getenv("EASY_GPT_PREFILL_GROUPS")) : 0;
+    const int groups = asked == 1 || asked == 2 ? asked : eg_attention_prefill_groups(head_dim);
+    int code;
+    if (groups == 1) code = head_dim == 64 ? launch<64, 1>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 1>(stream, map_q, map_k, map_v, p, sm_count);
+    else code = head_dim == 64 ? launch<64, 2>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 2>(stream, map_q, map_k, map_v, p, sm_count);
     if (code || max_parts == 1) return code;
     // the parts are added up behind the main kernel (launched early: it waits for it by itself)
     cudaLaunchConfig_t cfg = {};

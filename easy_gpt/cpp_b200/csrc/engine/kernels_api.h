@@ -31,6 +31,7 @@ int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long l
     const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim,
     int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status,
     long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue);
+int eg_attention_prefill_groups(int head_dim);
 // embedding.cu
 int eg_embedding_gather(cudaStream_t stream, int dtype, const int* ids, const void* table, float* residual, int tokens,
     int hidden, int vocab, int* status);

@@ -427,7 +427,7 @@ public:
             // long enough to fill their 128-row tiles
             if (ctx.max_query_len >= plans::TCGEN05_ATTENTION_MIN_QUERY && plans::attention_prefill_tcgen05_takes(dtype, head_dim_, cache.page_size)) {
                 int parts, part_tiles;
-                plans::attention_prefill_parts(ctx.num_tiles, heads_, longest, &parts, &part_tiles);
+                plans::attention_prefill_parts(ctx.num_tiles, heads_, head_dim_, longest, &parts, &part_tiles);
                 const size_t slots = (size_t)ctx.num_tiles * heads_;
                 while (parts > 1 && slots * parts * 128 * (head_dim_ + 2) * 4 > plans::PREFILL_PARTS_SCRATCH_BYTES) --parts;
                 float *partial_o = nullptr, *partial_ml = nullptr;

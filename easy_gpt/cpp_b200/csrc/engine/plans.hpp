@@ -7,6 +7,7 @@
 #include <cstdlib>
 
 #include "device.hpp"
+#include "kernels_api.h"
 
 namespace easygpt::engine::plans {
 
@@ -73,12 +74,14 @@ inline int attention_paged_splits(int tokens, int num_heads, int num_kv_heads, l
 
 // (parts, part_tiles): the most parts a query tile's keys are cut into and the fewest key tiles (of 64) of a part; the
 // kernel cuts a tile's keys into min(parts, key tiles / part_tiles) parts.  A part costs its CTA a start-up of some
-// microseconds and a pass of the merge kernel, which pays only while there are fewer (tile, head) pairs than the two
-// CTAs per SM: the kernel is bound by what an SM gets through, not by its longest unit.  (Measured on B200, 14 heads of
-// 64: a portion of 512 tokens on a context of 3,584 takes 68 us uncut, 34 us in 4 parts and 43 us in 8; a prompt of
-// 2,048 tokens, 224 pairs for 296 CTAs, takes 41 us uncut and 40 to 62 us however it is cut.)
-inline void attention_prefill_parts(int num_tiles, int num_heads, long long longest_context, int* parts, int* part_tiles) {
-    const int wanted = std::min(2 * sm_count() / std::max(1, num_tiles * num_heads), 8);
+// microseconds and a pass of the merge kernel, which pays only while there are fewer (tile, head) pairs than CTAs (one
+// per SM for heads of 64, whose CTAs share a unit's keys between two softmax groups already; two per SM else): the
+// kernel is bound by what an SM gets through, not by its longest unit.  (Measured on B200, 14 heads of 64: a portion of
+// 512 tokens on a context of 3,584, 56 pairs, takes 68 us uncut with one softmax group a CTA and 34 us in 4 parts; a
+// prompt of 2,048 tokens, 224 pairs, 41 us uncut and 40 to 62 us however it is cut, with two groups a CTA 30 us.)
+inline void attention_prefill_parts(int num_tiles, int num_heads, int head_dim, long long longest_context, int* parts, int* part_tiles) {
+    const int ctas = sm_count() * (eg_attention_prefill_groups(head_dim) == 2 ? 1 : 2);
+    const int wanted = std::min(ctas / std::max(1, num_tiles * num_heads), 8);
     if (wanted >= 2) { *parts = wanted; *part_tiles = 4; return; }
     *parts = 1;
     *part_tiles = 1 << 20;

@@ -77,6 +77,7 @@ class _Signatures:
     eg_attention_prefill_tcgen05 = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
                                     c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    eg_attention_prefill_groups = [c_int]
     eg_gemm_skinny = [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_longlong,
                       c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
                       c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong,
@@ -459,17 +460,19 @@ def _prefill_parts_scratch(device, slots: int, parts: int, head_dim: int):
     return have
 
 
-def attention_prefill_parts(num_tiles: int, num_heads: int):
+def attention_prefill_parts(num_tiles: int, num_heads: int, head_dim: int = 64):
     """(parts, part_tiles): the most parts a query tile's keys are cut into, and the fewest key tiles
     (of 64) of a part; the kernel cuts a tile's keys into min(parts, key tiles / part_tiles) parts, so
     the cut follows the contexts of the step at hand (a captured step is replayed with others).
     A part costs its CTA a start-up of some microseconds and a pass of the merge kernel, which pays
-    only while there are fewer (tile, head) pairs than the two CTAs per SM: the kernel is bound by
-    what an SM gets through (about 0.64 key tiles a microsecond with both its CTAs busy), not by its
-    longest unit.  Measured on B200 (14 heads of 64, pages of 64): a portion of 512 tokens on a context
-    of 3,584 takes 68 us uncut, 34 us in 4 parts and 43 us in 8; a prompt of 2,048 tokens (224 pairs for
-    296 CTAs) takes 41 us uncut and 40 to 62 us however it is cut."""
-    wanted = min(2 * sm_count() // max(1, num_tiles * num_heads), 8)
+    only while there are fewer (tile, head) pairs than CTAs (one per SM for heads of 64, whose CTAs
+    share a unit's keys between two softmax groups already; two per SM else): the kernel is bound by
+    what an SM gets through (about 0.64 key tiles a microsecond), not by its longest unit.  Measured on
+    B200 (14 heads of 64, pages of 64): a portion of 512 tokens on a context of 3,584 (56 pairs) takes
+    68 us uncut with one softmax group a CTA and 34 us in 4 parts; a prompt of 2,048 tokens (224 pairs)
+    41 us uncut and 40 to 62 us however it is cut, with two groups a CTA 30 us."""
+    ctas = sm_count() * (1 if library().eg_attention_prefill_groups(head_dim) == 2 else 2)
+    wanted = min(ctas // max(1, num_tiles * num_heads), 8)
     return (wanted, PREFILL_PART_TILES) if wanted >= 2 else (1, 1 << 20)
 
 

@@ -139,7 +139,7 @@ class Attention(Mixer):
             tensor_core = (kernels.TCGEN05_ATTENTION and ctx.max_query_len >= kernels.TCGEN05_ATTENTION_MIN_QUERY
                            and kernels.attention_prefill_tcgen05_takes(dtype, self.head_dim, tables.page_size))
             if tensor_core:
-                parts, part_tiles = kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads)
+                parts, part_tiles = kernels.attention_prefill_parts(ctx.query_tiles.shape[0], self.num_heads, self.head_dim)
                 kernels.attention_prefill_tcgen05(
                     qkv, cache.k, cache.v, tables.block_table, ctx.positions, ctx.query_tiles, attn, self.num_heads,
                     self.num_kv_heads, self.head_dim, self.window, self.scale, ctx.status, parts=parts, part_tiles=part_tiles)

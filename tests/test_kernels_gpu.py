@@ -642,7 +642,23 @@ def test_kernels_are_right_without_clusters_too():
     import sys
 
     env = dict(os.environ, EASY_GPT_CLUSTER_MERGE="0", EASY_GPT_CLUSTER_REDUCE="0")
-    out = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "(paged or skinny or attention) and not without_clusters"],
+    out = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "(paged or skinny or attention) and not without_clusters and not softmax_groups"],
+                         env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout
+
+
+@pytest.mark.parametrize("groups", [1, 2])
+def test_prompt_attention_with_either_number_of_softmax_groups(groups):
+    """The tcgen05 prompt attention has two forms: CTAs with one softmax group, two to an SM, and CTAs with two groups
+    that share a unit's key tiles, one to an SM; the launcher picks by head size.  Here the attention tests run once
+    more with either form forced for every head size."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, EASY_GPT_PREFILL_GROUPS=str(groups))
+    out = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "(attention or prefill) and not without_clusters and not softmax_groups"],
                          env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
     assert " passed" in out.stdout
