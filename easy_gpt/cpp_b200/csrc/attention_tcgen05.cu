@@ -175,6 +175,28 @@ __device__ __forceinline__ float exp2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two float32 in a 64-bit register, for the packed instructions
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void split_pair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -477,13 +499,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             if (!see) s[e] = -INFINITY;
                         }
                     }
-                    float t[16];
+                    // the row's maximum with the three-input instruction: 64 -> 22 -> 8 -> 3 -> 1
+                    float t[22];
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) t[e] = fmaxf(fmaxf(s[e], s[16 + e]), fmaxf(s[32 + e], s[48 + e]));
+                    for (int e = 0; e < 21; ++e) t[e] = max3(s[3 * e], s[3 * e + 1], s[3 * e + 2]);
+                    t[21] = s[63];
 #pragma unroll
-                    for (int w = 8; w >= 1; w >>= 1)
-#pragma unroll
-                        for (int e = 0; e < w; ++e) t[e] = fmaxf(t[e], t[e + w]);
+                    for (int e = 0; e < 7; ++e) t[e] = max3(t[3 * e], t[3 * e + 1], t[3 * e + 2]);
+                    t[7] = t[21];
+                    t[0] = max3(t[0], t[1], t[2]);
+                    t[1] = max3(t[3], t[4], t[5]);
+                    t[0] = max3(t[0], t[1], fmaxf(t[6], t[7]));
                     const float mn = t[0] * scale_log2;
                     if (mn > m + REFERENCE_SLACK) {               // also the first finite maximum (m = -inf)
                         c = exp2_approx(m - mn);                 // 0 for the first
@@ -512,7 +538,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 }
                 STAMP(4)
                 // P_j over the first 32 columns of S_j, element pairs (2e, 2e + 1) of this row, sixteen columns at a time
-                float sum0 = 0.f, sum1 = 0.f;
+                // (Multiply-adds and sums on pairs: the packed float32 instructions halve their count.  With two softmax warps
+                // on an SM sub-core this loop runs at the exponent unit's rate, 4 results a clock: 1,100 cycles for the two.
+                // Measured with every second or every fourth pair's exponent as a polynomial of degree 4 on the
+                // multiply-add pipe instead, eleven instructions a pair: 2,100 and 1,600 cycles.  Measured with the next
+                // tile's maximum taken inside this loop, from a second read of its scores: 1,780 cycles against 1,100 + 290.)
+                uint64_t sums = 0;
+                const uint64_t scale2 = pair_of(scale_log2, scale_log2), shift2 = pair_of(-ref, -ref);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t packed[16];
@@ -522,15 +554,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     } else {
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
-                            const float e0 = exp2_approx(fmaf(s[32 * half + 2 * e], scale_log2, -ref));
-                            const float e1 = exp2_approx(fmaf(s[32 * half + 2 * e + 1], scale_log2, -ref));
-                            sum0 += e0;
-                            sum1 += e1;
+                            float x0, x1;
+                            split_pair(fma_pair(pair_of(s[32 * half + 2 * e], s[32 * half + 2 * e + 1]), scale2, shift2), x0, x1);
+                            const float e0 = exp2_approx(x0), e1 = exp2_approx(x1);
+                            sums = add_pair(sums, pair_of(e0, e1));
                             packed[e] = pack2(e0, e1);
                         }
                     }
                     tmem_st16(lane_base + (uint32_t)(b * BN + 16 * half), packed);
                 }
+                float sum0, sum1;
+                split_pair(sums, sum0, sum1);
                 l = l * c + (sum0 + sum1);
                 STAMP(5)
                 tmem_st_wait();
