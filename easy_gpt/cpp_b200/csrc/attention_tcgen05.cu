@@ -13,14 +13,18 @@
 // grown by more than 2^8 since the reference was set does the row's thread move the reference, and then it scales
 // its row of O in TMEM (tcgen05.ld, multiply, tcgen05.st) and its sum; O / sum stays the same.
 //
-// Warp roles (256 threads; 128 registers each and at most 113 KB of shared memory, so that two CTAs share an SM
-// and one fills the other's waits; each allocates 256 of the 512 TMEM columns):
+// Warp roles, in two forms.  With ONE softmax group a CTA has 256 threads of 128 registers and at most 113 KB of shared
+// memory, so that two CTAs share an SM and one fills the other's waits; each allocates 256 of the 512 TMEM columns.
+// With TWO groups (heads of 64) a CTA has 384 threads and the SM to itself: the groups take the unit's even and odd
+// key tiles, each with a reference, a sum, score buffers and an O of its own, and the second hands its rows to the
+// first through shared memory when the unit ends.  An SM runs the softmax of two key tiles at a time either way; with
+// two groups the longest unit of a prompt, which is what a prompt of a few thousand tokens waits for, takes half as long.
 //   warp 0     TMA loads: Q once; per key tile boxes of 64 keys x 64 columns (32 or 16 keys where the pages are no
 //              multiple of 64), K and V, 128-byte swizzled, into a ring of stages; every box of a tile has its own
 //              lane.  Block-table entries are fetched 32 pieces at a time, a batch ahead.
 //   warp 1     allocates TMEM; one thread issues the score products (descriptors ready before it waits: the
 //              arithmetic of a descriptor costs more than the issue of the MMA)
-//   warps 2-5  the softmax rows
+//   warps 2-5  the softmax rows (warps 8-11: the second group's)
 //   warp 6     one thread issues the output products
 // S has three TMEM buffers (two for head size 128): the tensor core computes the scores of later key tiles while
 // the rows work on this one.  S_j goes where S and P of three tiles before were, once the output product of that
@@ -542,7 +546,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 // on an SM sub-core this loop runs at the exponent unit's rate, 4 results a clock: 1,100 cycles for the two.
                 // Measured with every second or every fourth pair's exponent as a polynomial of degree 4 on the
                 // multiply-add pipe instead, eleven instructions a pair: 2,100 and 1,600 cycles.  Measured with the next
-                // tile's maximum taken inside this loop, from a second read of its scores: 1,780 cycles against 1,100 + 290.)
+                // tile's maximum taken inside this loop, from a second read of its scores: 1,780 cycles against 1,100 + 290.  Measured
+                // with the two warps of a sub-core taking turns at this loop: 830 cycles each, one after the other, which is
+                // no better than 1,100 together; a warp alone does not fill the unit.)
                 uint64_t sums = 0;
                 const uint64_t scale2 = pair_of(scale_log2, scale_log2), shift2 = pair_of(-ref, -ref);
 #pragma unroll
