@@ -286,8 +286,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int round = 0;; ++round) {
         if (threadIdx.x == 0) {
             int u;
-            for (;;) {                                           // the next unit that has keys (at most total_units probes)
-                u = atomicAdd(&p.queue[0], 1);
+            for (bool own = round == 0;; own = false) {          // the next unit that has keys (at most total_units probes)
+                // a CTA's first unit is the one of its own number (no trip to the counter before the CTA's longest unit);
+                // the counter deals out the units behind the grid's
+                u = own ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(&p.queue[0], 1);
                 if (u >= total_units) break;
                 const int u_tile = p.num_tiles - 1 - u / (p.max_parts * p.num_heads);
                 const int u_t0 = p.tiles[u_tile * 3 + 1], u_count = p.tiles[u_tile * 3 + 2];
