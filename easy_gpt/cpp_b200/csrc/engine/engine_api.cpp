@@ -282,3 +282,30 @@ EGE_API long long ege_runner_info(void* r, int what, int arg) {
     }
     return -1;
 }
+
+// A launch plan as this library computes it, for the test that compares the rules with their twins in the PyTorch face.
+// what 0: the decode product's plan for (rows, width, head size or 0) -> (row blocks, K slices, K parts); 1: the decode
+// attention's splits for (tokens, heads, KV heads, longest context, head size); 2: the most tokens whose norm rides in
+// a decode product's prologue, for (width); 3: the prompt attention's (most parts, fewest key tiles of a part) for
+// (query tiles, heads, head size, longest context); 4: the SM count the plans hang off.
+EGE_API void ege_plan(int what, const long long* in, long long* out) {
+    switch (what) {
+        case 0: {
+            const plans::SkinnyPlan plan = plans::skinny_plan((int)in[0], (int)in[1], (int)in[2]);
+            out[0] = plan.row_blocks;
+            out[1] = plan.k_slices;
+            out[2] = plan.k_split;
+            break;
+        }
+        case 1: out[0] = plans::attention_paged_splits((int)in[0], (int)in[1], (int)in[2], in[3], (int)in[4]); break;
+        case 2: out[0] = plans::fused_norm_max_tokens((int)in[0]); break;
+        case 3: {
+            int parts = 0, part_tiles = 0;
+            plans::attention_prefill_parts((int)in[0], (int)in[1], (int)in[2], in[3], &parts, &part_tiles);
+            out[0] = parts;
+            out[1] = part_tiles;
+            break;
+        }
+        case 4: out[0] = plans::sm_count(); break;
+    }
+}

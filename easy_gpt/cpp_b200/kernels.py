@@ -470,7 +470,10 @@ def attention_prefill_parts(num_tiles: int, num_heads: int, head_dim: int = 64):
     what an SM gets through (about 0.64 key tiles a microsecond), not by its longest unit.  Measured on
     B200 (14 heads of 64, pages of 64): a portion of 512 tokens on a context of 3,584 (56 pairs) takes
     68 us uncut with one softmax group a CTA and 34 us in 4 parts; a prompt of 2,048 tokens (224 pairs)
-    41 us uncut and 40 to 62 us however it is cut, with two groups a CTA 30 us."""
+    41 us uncut and 40 to 62 us however it is cut, with two groups a CTA 30 us.  (The native engine's
+    rule, ``plans::attention_prefill_parts``, also cuts key ranges of 48 tiles and more into parts of 24
+    when the units are many, which pays in serving runs with portions deep in long contexts; this face
+    keeps the plain rule.)"""
     ctas = sm_count() * (1 if library().eg_attention_prefill_groups(head_dim) == 2 else 2)
     wanted = min(ctas // max(1, num_tiles * num_heads), 8)
     return (wanted, PREFILL_PART_TILES) if wanted >= 2 else (1, 1 << 20)

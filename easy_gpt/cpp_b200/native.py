@@ -55,6 +55,7 @@ def library() -> ctypes.CDLL:
             "ege_runner_step": (c_longlong, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_char_p, c_int]),
             "ege_runner_end": (None, [c_void_p, c_longlong]),
             "ege_runner_info": (c_longlong, [c_void_p, c_int, c_int]),
+            "ege_plan": (None, [c_int, c_void_p, c_void_p]),
         }
         for name, (restype, argtypes) in sig.items():
             fn = getattr(lib, name)
@@ -64,6 +65,15 @@ def library() -> ctypes.CDLL:
 
 
 _ERR = 2048
+
+
+def plan(what: int, *numbers: int):
+    """A launch plan as the native engine computes it (``ege_plan`` in ``csrc/engine/engine_api.cpp`` lists what
+    ``what`` may be): four numbers, of which the plan uses the first ones."""
+    args = (ctypes.c_longlong * 8)(*numbers)
+    out = (ctypes.c_longlong * 4)()
+    library().ege_plan(int(what), args, out)
+    return tuple(int(v) for v in out)
 
 
 def load_plugin(path) -> None:
