@@ -33,8 +33,9 @@
 // Scale, maximum, exponent and sums are 32-bit; the exponent is the hardware's base-2 approximation with the scale
 // folded into its multiply-add.
 //
-// A step with few query tiles cuts their key ranges over several CTAs (gridDim.z): each writes its unnormalised O,
-// reference and sum; the CTA that draws the last ticket of the query tile adds them up.
+// A step with fewer (query tile, head) pairs than CTAs cuts the tiles' key ranges into parts, which are units of
+// their own: each writes its unnormalised O, reference and sum, and a small kernel behind this one (launched early; it
+// waits for this one by itself) adds a tile's parts up in order.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread raises the CTA's abort flag and
 // EG_STATUS_WAIT_TIMEOUT; every role then leaves its loop, the loader waits (bounded again) for the copies it
