@@ -27,7 +27,7 @@ no flush is needed between steps.
 
 For profiling and for further sizes (one short line each, never the JSON line above):
 
-    python bench.py --only decode|prefill|timeline|gemm|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
+    python bench.py --only decode|prefill|timeline|gemm|attention|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
 
 `serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
 decoding requests, 512 new tokens each) through the engine and reports wall-clock tokens a second.
@@ -403,6 +403,60 @@ def print_gemm_comparison(config, tokens=PREFILL_TOKENS):
     return 0
 
 
+def print_attention_timings():
+    """The two prompt-attention kernels alone (warp-level `mma.sync` and tcgen05), one request, pages of 64: each timed
+    as a CUDA graph of eight launches, the tcgen05 kernel with the parts the engine's policy gives it."""
+    import math
+
+    import torch
+
+    from easy_gpt.cpp_b200 import kernels
+
+    dev = "cuda"
+    page = 64
+    print("tokens, context before them, heads x head size: microseconds and TFLOP/s, mma.sync | tcgen05 (parts)")
+    for T, ctx0, NH, NKV, HD in ((2048, 0, 14, 2, 64), (8192, 0, 14, 2, 64), (2048, 0, 28, 4, 128), (512, 3584, 14, 2, 64),
+                                 (512, 7680, 28, 4, 128), (64, 4000, 14, 2, 64), (256, 1024, 14, 2, 64)):
+        pages = (ctx0 + T + page - 1) // page
+        kv = torch.randn(pages + 1, 2, NKV, page, HD, device=dev).bfloat16()
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1)
+        q = torch.randn(T, (NH + 2 * NKV) * HD, device=dev).bfloat16()
+        positions = torch.arange(ctx0, ctx0 + T, dtype=torch.int32, device=dev)
+        tiles = torch.tensor([(0, o, min(128, T - o)) for o in range(0, T, 128)], dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        parts, part_tiles = kernels.attention_prefill_parts(len(tiles), NH, HD)
+        flops = 4 * HD * NH * (T * (T + 1) / 2 + T * ctx0)
+        line, outs = f"  T={T:5d} ctx {ctx0:5d}  {NH:2d} x {HD:3d}", []
+        for fn, extra in ((kernels.attention_prefill, {}), (kernels.attention_prefill_tcgen05, {"parts": parts, "part_tiles": part_tiles})):
+            out = torch.zeros(T, NH * HD, device=dev, dtype=torch.bfloat16)
+
+            def launch():
+                fn(q, kv[:, 0], kv[:, 1], table, positions, tiles, out, NH, NKV, HD, None, 1 / math.sqrt(HD), status, **extra)
+
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                launch()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(8):
+                    launch()
+            times = []
+            for _ in range(10):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) * 1e3 / 8)
+            us = sorted(times)[len(times) // 2]
+            line += f"   {us:8.2f} us {flops / us / 1e6:6.1f}"
+            outs.append(out.float())
+        print(f"{line}  ({parts} parts)   largest difference between the kernels {float((outs[0] - outs[1]).abs().max()):.4f}")
+        assert status.item() == 0
+    return 0
+
+
 def measure_serving(folder, config, requests=64, new_tokens=512, chunk=512, budget=2048, seed=0, repeats=2):
     """Continuous batching through the engine: `requests` concurrent requests with prompt lengths uniform in
     [128, 4096] and `new_tokens` generated tokens each, prompts cut into portions of `chunk` tokens that share
@@ -446,6 +500,8 @@ def run_ours(args):
     if args.sizes != "0.5b" and not args.only:
         print("bench.py: --sizes other than 0.5b goes with --only (the JSON line is defined for the 0.5B sizes)")
         return 2
+    if args.only == "attention":                                   # kernels alone: no model folder
+        return print_attention_timings()
     layers_full = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
@@ -574,7 +630,7 @@ def main():
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "serve"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:
